@@ -1,0 +1,213 @@
+/*
+ * litenn_b200 -- C ABI of the sm_100a device backend for the LiteNN op layer.
+ *
+ * Every entry point is plain C: device pointers cross the boundary as uint64_t,
+ * sizes as int64_t/int, all tensors are contiguous row-major fp32 (images NCHW).
+ * Every call returns 0 on success or a negative LNN_E_* code; the text of the
+ * last failure on the calling thread is returned by lnn_last_error().
+ * All op entry points only enqueue work on the device's single in-order stream
+ * (the counterpart of LiteNN's in-order command queue, litenn/core/minicl/
+ * api/OpenCL/OpenCL.py:349-351); lnn_d2h and lnn_sync are the blocking points.
+ * The library is not re-entrant per device: one host thread drives a device.
+ *
+ * Citations "ref:" name the file:line of iperov/litenn that an entry replaces.
+ */
+#ifndef LITENN_B200_H
+#define LITENN_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LNN_OK              0
+#define LNN_E_INVALID      -1   /* bad argument (shape, null pointer, unknown op id)   */
+#define LNN_E_CUDA         -2   /* a CUDA runtime/driver call failed                    */
+#define LNN_E_NOMEM        -3   /* device allocation failed even after pool eviction    */
+#define LNN_E_NOTINIT      -4   /* device not initialised with lnn_init                 */
+#define LNN_E_UNSUPPORTED  -5   /* configuration outside what the kernels implement     */
+#define LNN_E_NCCL         -6   /* NCCL missing or a collective failed                  */
+#define LNN_E_TIMEOUT      -7   /* a bounded device-side wait expired (status word set) */
+
+#define LNN_MAX_DEVICES 16
+#define LNN_MAX_DIMS 6
+
+/* ---- runtime: replaces litenn/core/minicl/{devices,CLDevice,CLBuffer}.py ------------ */
+
+int lnn_version(void);
+const char* lnn_last_error(void);
+
+/* ref: minicl/devices.py:88-105 (get_all) */
+int lnn_device_count(int* count);
+/* ref: minicl/devices.py:107-143 (device name / global_mem_size) */
+int lnn_device_info(int dev, char* name, int name_len, uint64_t* total_mem,
+                    int* sm_count, int* cc_major, int* cc_minor);
+/* ref: minicl/CLDevice.py:180-190 (context + in-order queue created on demand) */
+int lnn_init(int dev);
+/* ref: minicl/CLDevice.py:105-118 (_cleanup) */
+int lnn_shutdown(int dev);
+/* ref: minicl/CLDevice.py:120-165 (_mem_alloc: size-keyed pool, evict largest pooled and retry) */
+int lnn_alloc(int dev, uint64_t bytes, uint64_t* ptr);
+/* ref: minicl/CLDevice.py:167-178 (_mem_free: return buffer to the pool) */
+int lnn_free(int dev, uint64_t ptr, uint64_t bytes);
+/* ref: minicl/CLDevice.py:39-49 (memory counters) */
+int lnn_mem_stats(int dev, uint64_t* allocated_bytes, uint64_t* pooled_bytes);
+/* release every pooled (unused) buffer back to the driver */
+int lnn_pool_trim(int dev);
+/* ref: minicl/CLBuffer.py:78-80 (blocking write from host memory) */
+int lnn_h2d(int dev, uint64_t dst, const void* src, uint64_t bytes);
+/* ref: minicl/CLBuffer.py:99-115 (blocking read into host memory) */
+int lnn_d2h(int dev, void* dst, uint64_t src, uint64_t bytes);
+/* ref: minicl/CLBuffer.py:66-67 (same-device copy) */
+int lnn_d2d(int dev, uint64_t dst, uint64_t src, uint64_t bytes);
+/* ref: minicl/CLBuffer.py:83-96 (fill), initializer/Scalar.py */
+int lnn_fill_f32(int dev, uint64_t dst, int64_t count, float value);
+/* ref: minicl/CLDevice.py:51-55 (wait = clFinish) */
+int lnn_sync(int dev);
+/* asynchronous copies on the device stream; host memory should come from lnn_host_alloc */
+int lnn_h2d_async(int dev, uint64_t dst, const void* src, uint64_t bytes);
+int lnn_d2h_async(int dev, void* dst, uint64_t src, uint64_t bytes);
+int lnn_host_alloc(uint64_t bytes, void** ptr);   /* pinned host memory */
+int lnn_host_free(void* ptr);
+/* number of kernels this library has launched on the device since lnn_init */
+int lnn_launch_count(int dev, uint64_t* count);
+/* read-and-clear the device status word that bounded waits set when they give up */
+int lnn_device_status(int dev, int* status);
+/* CUDA events on the device stream (for timing on the stream the kernels run on) */
+int lnn_event_create(int dev, uint64_t* ev);
+int lnn_event_record(int dev, uint64_t ev);
+int lnn_event_elapsed_ms(int dev, uint64_t ev_start, uint64_t ev_stop, float* ms);
+int lnn_event_destroy(int dev, uint64_t ev);
+
+/* ---- element-wise: replaces litenn/core/op/element_wise_op.py ------------------------ */
+
+enum {
+  LNN_EW_ABS = 0, LNN_EW_ADD_CONST, LNN_EW_CLIP, LNN_EW_COS, LNN_EW_EXP, LNN_EW_LEAKY_RELU,
+  LNN_EW_LOG, LNN_EW_MUL_CONST, LNN_EW_RDIV_CONST, LNN_EW_RSUB_CONST, LNN_EW_RELU,
+  LNN_EW_SIGMOID, LNN_EW_SIN, LNN_EW_SQRT, LNN_EW_SQUARE, LNN_EW_TANH, LNN_EW_COUNT
+};
+/* O (+)= f(I).  p0,p1: op constants (value / min,max / alpha); flag: clip preserve_gradient.
+ * ref: op/element_wise_op.py:83-96 (forward template), :112-364 (bodies) */
+int lnn_eltwise_fwd(int dev, int op, uint64_t O, uint64_t I, int64_t n,
+                    float p0, float p1, int flag, int accumulate);
+/* dI += g(I, O, dO).  ref: op/element_wise_op.py:98-110 */
+int lnn_eltwise_bwd(int dev, int op, uint64_t dI, uint64_t I, uint64_t O, uint64_t dO,
+                    int64_t n, float p0, float p1, int flag);
+
+/* ---- broadcast binary: replaces litenn/core/op/dual_wise_op.py ----------------------- */
+
+enum {
+  LNN_BIN_ADD = 0, LNN_BIN_SUB, LNN_BIN_MUL, LNN_BIN_DIV, LNN_BIN_MAX, LNN_BIN_MIN,
+  LNN_BIN_BCE, LNN_BIN_COUNT
+};
+/* O (+)= f(A,B) with numpy broadcasting.  rank <= LNN_MAX_DIMS; a_shape/b_shape are the
+ * operands' shapes left-padded with 1 to `rank`; o_shape the broadcast result.
+ * ref: op/dual_wise_op.py:132-151, info/InfoBroadcast.py:40-86 */
+int lnn_binary_fwd(int dev, int op, uint64_t O, uint64_t A, uint64_t B, int rank,
+                   const int64_t* o_shape, const int64_t* a_shape, const int64_t* b_shape,
+                   int accumulate);
+/* which = 0: dX += dA(A,B,O,dO) ; which = 1: dX += dB(A,B,O,dO).  dX has the OUTPUT shape
+ * (the caller reduces it over the broadcast axes).  ref: op/dual_wise_op.py:153-191 */
+int lnn_binary_bwd(int dev, int op, int which, uint64_t dX, uint64_t A, uint64_t B,
+                   uint64_t O, uint64_t dO, int rank, const int64_t* o_shape,
+                   const int64_t* a_shape, const int64_t* b_shape);
+/* y (+)= leaky_relu(x*g + b, alpha) for x[N,C,HW], g,b[C]: the three reference kernels
+ * mul, add, leaky_relu (separately rounded) in one pass.
+ * ref: op/dual_wise_op.py:194-204,283-295 + op/element_wise_op.py:207-221 */
+int lnn_scale_bias_lrelu(int dev, uint64_t y, uint64_t x, uint64_t g, uint64_t b,
+                         int64_t n, int64_t c, int64_t hw, float alpha, int accumulate);
+
+/* ---- pooling: replaces litenn/core/op/pool2D.py -------------------------------------- */
+
+enum { LNN_POOL_AVG = 0, LNN_POOL_MAX = 1, LNN_POOL_MIN = 2 };
+/* ref: op/pool2D.py:111-146 */
+int lnn_pool2d_fwd(int dev, int mode, uint64_t O, uint64_t I, int64_t n, int64_t c,
+                   int ih, int iw, int oh, int ow, int pool, int stride, int padl, int padt);
+/* dI += ... ; ref: op/pool2D.py:147-230 (I and O are only read for max/min) */
+int lnn_pool2d_bwd(int dev, int mode, uint64_t dI, uint64_t I, uint64_t dO, uint64_t O,
+                   int64_t n, int64_t c, int ih, int iw, int oh, int ow,
+                   int pool, int stride, int padl, int padt);
+
+/* ---- reductions: replaces litenn/core/op/reduce.py ----------------------------------- */
+
+enum { LNN_RED_SUM = 0, LNN_RED_MEAN = 1, LNN_RED_MAX = 2, LNN_RED_MIN = 3 };
+/* Input viewed as [outer][r0][mid][r1][inner]; axes r0 and r1 are reduced (COLS = r0*r1,
+ * column index r0_i*r1 + r1_i), output [outer][mid][inner].  The summation tree is the
+ * reference's ceil-halving tree (column c pairs with c + ceil(n/2)), so results are
+ * bit-identical to it.  O (+)= result.  Uses pooled scratch when one row is split.
+ * ref: op/reduce.py:166-205,279-301, info/InfoReduction.py:25-50 */
+int lnn_reduce(int dev, int op, uint64_t O, uint64_t I, int64_t outer, int64_t r0,
+               int64_t mid, int64_t r1, int64_t inner, int accumulate);
+/* dI += broadcast(dO) [/COLS] (sum, mean) or dO at the first column equal to O (max, min).
+ * ref: op/reduce.py:207-216,250-276 (ties: lowest column index wins) */
+int lnn_reduce_bwd(int dev, int op, uint64_t dI, uint64_t I, uint64_t dO, uint64_t O,
+                   int64_t outer, int64_t r0, int64_t mid, int64_t r1, int64_t inner);
+
+/* ---- data movement: replaces op/transpose.py, op/slice.py ---------------------------- */
+
+/* O[perm(i)] (+)= I[i]; in_shape has `rank` extents, axes the permutation (out axis k =
+ * in axis axes[k]).  ref: op/transpose.py:60-103 */
+int lnn_transpose(int dev, uint64_t O, uint64_t I, int rank, const int64_t* in_shape,
+                  const int* axes, int accumulate);
+/* O[o] (+)= I[begin + o*step] per axis (fwd) ; ref: op/slice.py:168-178 */
+int lnn_slice_fwd(int dev, uint64_t O, uint64_t I, int rank, const int64_t* in_shape,
+                  const int64_t* out_shape, const int64_t* begin, const int64_t* step,
+                  int accumulate);
+/* dI[begin + o*step] += dO[o] ; ref: op/slice.py:180-190 */
+int lnn_slice_bwd(int dev, uint64_t dI, uint64_t dO, int rank, const int64_t* in_shape,
+                  const int64_t* out_shape, const int64_t* begin, const int64_t* step);
+
+/* ---- contractions (tcgen05 tile engine) ----------------------------------------------- */
+
+/* C[b] (+)= op(A[b]) * op(B[b]) (+ bias[n]) for b < batch, row-major fp32.
+ * trans_a = 0: A is [M,K]; 1: A is stored [K,M].  trans_b = 0: B is [K,N]; 1: stored [N,K].
+ * bias may be 0.  tf32_passes: 3 = split-TF32 (fp32-level accuracy), 1 = plain TF32.
+ * ref: op/matmul.py:8-164 (forward), :64-72 (gradients = the transposed variants),
+ *      module/Dense.py:44-48 (bias) */
+int lnn_gemm_f32(int dev, uint64_t C, uint64_t A, uint64_t B, uint64_t bias,
+                 int64_t batch, int64_t m, int64_t n, int64_t k,
+                 int trans_a, int trans_b, int accumulate, int tf32_passes);
+
+/* geometry shared by the three convolution entry points (NCHW / OIHW) */
+typedef struct lnn_conv_geom {
+  int n, ic, ih, iw;        /* input  [n, ic, ih, iw]   */
+  int oc, kh, kw;           /* kernel [oc, ic, kh, kw]  */
+  int oh, ow;               /* output [n, oc, oh, ow]   */
+  int stride, dilation;
+  int padl, padt;           /* left / top zero padding (right / bottom follow from oh, ow) */
+} lnn_conv_geom;
+
+/* act: 0 none, 1 leaky_relu(alpha) applied after the optional bias[oc].
+ * Y (+)= conv2D(X, W) (+ bias).  ref: op/conv2D.py:9-44, op/unfold2D.py:84-111,
+ * module/Conv2D.py:58-62 */
+int lnn_conv2d_fwd(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint64_t W,
+                   uint64_t bias, int act, float alpha, int accumulate, int tf32_passes);
+/* dX += conv2D_transpose-like gradient.  ref: op/conv2D.py:46-50, op/unfold2D.py:112-138 */
+int lnn_conv2d_dx(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY, uint64_t W,
+                  int tf32_passes);
+/* dW += gradient of the kernel.  ref: op/conv2D.py:52-54 */
+int lnn_conv2d_dw(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY, uint64_t X,
+                  int tf32_passes);
+
+/* ---- optimiser + data-parallel sync --------------------------------------------------- */
+
+/* V += -lr * (G * gscale)   (momentum 0 form of the reference's two kernels, with the
+ * 1/ndev of gradient averaging folded into gscale).  ref: optimizer/SGD.py:42-83 */
+int lnn_sgd_step(int dev, uint64_t V, uint64_t G, int64_t n, float lr, float gscale);
+
+/* NCCL (loaded with dlopen on first use).  One communicator per device slot.
+ * ref: optimizer/Optimizer.py:149-153 (host-staged replica averaging, replaced by a
+ * gradient all-reduce) */
+int lnn_nccl_unique_id(void* id128);                       /* writes 128 bytes */
+int lnn_nccl_init_rank(int dev, int nranks, int rank, const void* id128);
+int lnn_nccl_init_all(const int* devs, int ndev);          /* single-process, all devices */
+int lnn_nccl_allreduce_sum(int dev, uint64_t buf, int64_t count);
+int lnn_nccl_group_start(void);
+int lnn_nccl_group_end(void);
+int lnn_nccl_destroy(int dev);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LITENN_B200_H */

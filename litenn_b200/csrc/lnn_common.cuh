@@ -1,0 +1,70 @@
+// Internal declarations shared by the translation units of liblitenn_b200.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+#include <map>
+#include <vector>
+#include "../../include/litenn_b200.h"
+
+namespace lnn {
+
+// Per-device state: one non-blocking stream, a size-keyed buffer pool, counters.
+struct Device {
+  bool inited = false;
+  int ordinal = -1;
+  int sm_count = 0;
+  cudaStream_t stream = nullptr;
+  std::map<uint64_t, std::vector<void*>> pool;   // free buffers by exact byte size
+  uint64_t allocated_bytes = 0;                  // live + pooled
+  uint64_t pooled_bytes = 0;
+  uint64_t launches = 0;
+  int* status_dev = nullptr;                     // device status word (bounded waits)
+  int* status_host = nullptr;                    // pinned mirror
+  void* nccl_comm = nullptr;
+};
+
+Device* get_device(int dev);          // nullptr + error set when not initialised
+int set_error(int code, const char* fmt, ...);
+int alloc_bytes(Device* d, uint64_t bytes, void** out);
+int free_bytes(Device* d, void* p, uint64_t bytes);
+
+// RAII scratch buffer taken from the device pool; returned to the pool on scope exit.
+// Stream order makes reuse safe: every consumer runs on the same in-order stream.
+struct Scratch {
+  Device* d; void* p = nullptr; uint64_t bytes = 0;
+  explicit Scratch(Device* dev) : d(dev) {}
+  int get(uint64_t nbytes) { bytes = nbytes; return alloc_bytes(d, nbytes, &p); }
+  ~Scratch() { if (p) free_bytes(d, p, bytes); }
+  template <class T> T* as() { return reinterpret_cast<T*>(p); }
+};
+
+}  // namespace lnn
+
+#define LNN_CUDA(call)                                                                   \
+  do {                                                                                   \
+    cudaError_t _e = (call);                                                             \
+    if (_e != cudaSuccess)                                                               \
+      return lnn::set_error(LNN_E_CUDA, "%s failed: %s (%s:%d)", #call,                  \
+                            cudaGetErrorString(_e), __FILE__, __LINE__);                 \
+  } while (0)
+
+#define LNN_DEV(d, dev)                                                                  \
+  lnn::Device* d = lnn::get_device(dev);                                                 \
+  if (!d) return LNN_E_NOTINIT;                                                          \
+  LNN_CUDA(cudaSetDevice(d->ordinal))
+
+#define LNN_CHECK_LAUNCH(d)                                                              \
+  do {                                                                                   \
+    (d)->launches++;                                                                     \
+    cudaError_t _e = cudaGetLastError();                                                 \
+    if (_e != cudaSuccess)                                                               \
+      return lnn::set_error(LNN_E_CUDA, "kernel launch failed: %s (%s:%d)",              \
+                            cudaGetErrorString(_e), __FILE__, __LINE__);                 \
+  } while (0)
+
+#define LNN_REQUIRE(cond, ...)                                                           \
+  do { if (!(cond)) return lnn::set_error(LNN_E_INVALID, __VA_ARGS__); } while (0)
+
+static inline int64_t lnn_ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }

@@ -1,0 +1,464 @@
+// HBM-bound element-wise, broadcast-binary, fused scale+bias+leaky_relu, fill and SGD
+// kernels.  Arithmetic follows the OpenCL C text the reference generates, with every
+// literal single precision (the reference builds with -cl-single-precision-constant,
+// litenn/core/minicl/CLDevice.py:93), comparisons converted int->float and multiplied
+// in, and no fused multiply-add: each reference operator is its own rounding step, so
+// the intrinsics __fmul_rn/__fadd_rn/__fsub_rn/__fdiv_rn are used throughout.
+#include "lnn_common.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ float fmul(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ float fadd(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ float fsub(float a, float b) { return __fsub_rn(a, b); }
+__device__ __forceinline__ float fdiv(float a, float b) { return __fdiv_rn(a, b); }
+__device__ __forceinline__ float b2f(bool c) { return c ? 1.0f : 0.0f; }
+
+// ---- element-wise bodies (litenn/core/op/element_wise_op.py:112-364) -------------------
+
+template <int OP>
+__device__ __forceinline__ float ew_fwd(float I, float p0, float p1) {
+  if (OP == LNN_EW_ABS) return fabsf(I);
+  if (OP == LNN_EW_ADD_CONST) return fadd(I, p0);
+  if (OP == LNN_EW_CLIP)
+    return fadd(fadd(fmul(I, b2f((I >= p0) & (I <= p1))), fmul(p0, b2f(I < p0))),
+                fmul(p1, b2f(I > p1)));
+  if (OP == LNN_EW_COS) return cosf(I);
+  if (OP == LNN_EW_EXP) return expf(I);
+  if (OP == LNN_EW_LEAKY_RELU)
+    return fadd(fmul(I, b2f(I >= 0.0f)), fmul(fmul(p0, I), b2f(I < 0.0f)));
+  if (OP == LNN_EW_LOG) return logf(I);
+  if (OP == LNN_EW_MUL_CONST) return fmul(I, p0);
+  if (OP == LNN_EW_RDIV_CONST) return fdiv(p0, I);
+  if (OP == LNN_EW_RSUB_CONST) return fsub(p0, I);
+  if (OP == LNN_EW_RELU) return fmul(I, b2f(I >= 0.0f));
+  if (OP == LNN_EW_SIGMOID) return fdiv(1.0f, fadd(1.0f, expf(-I)));
+  if (OP == LNN_EW_SIN) return sinf(I);
+  if (OP == LNN_EW_SQRT) return __fsqrt_rn(I);
+  if (OP == LNN_EW_SQUARE) return fmul(I, I);
+  if (OP == LNN_EW_TANH)
+    return fsub(fdiv(2.0f, fadd(1.0f, expf(fmul(-2.0f, I)))), 1.0f);
+  return 0.0f;
+}
+
+template <int OP>
+__device__ __forceinline__ float ew_bwd(float I, float O, float dO, float p0, float p1, int flag) {
+  if (OP == LNN_EW_ABS) return fmul(dO, fdiv(I, fabsf(I)));
+  if (OP == LNN_EW_ADD_CONST) return dO;
+  if (OP == LNN_EW_CLIP) return flag ? dO : fmul(dO, b2f((I >= p0) & (I <= p1)));
+  if (OP == LNN_EW_COS) return fmul(dO, -sinf(I));
+  if (OP == LNN_EW_EXP) return fmul(dO, expf(I));
+  if (OP == LNN_EW_LEAKY_RELU)
+    return fmul(dO, fadd(b2f(I >= 0.0f), fmul(p0, b2f(I < 0.0f))));
+  if (OP == LNN_EW_LOG) return fmul(dO, fdiv(1.0f, I));
+  if (OP == LNN_EW_MUL_CONST) return fmul(dO, p0);
+  if (OP == LNN_EW_RDIV_CONST) return fmul(dO, -fdiv(p0, fmul(I, I)));
+  if (OP == LNN_EW_RSUB_CONST) return -dO;
+  if (OP == LNN_EW_RELU) return fmul(dO, b2f(I >= 0.0f));
+  if (OP == LNN_EW_SIGMOID) return fmul(dO, fmul(O, fsub(1.0f, O)));
+  if (OP == LNN_EW_SIN) return fmul(dO, cosf(I));
+  if (OP == LNN_EW_SQRT) return fmul(dO, fdiv(1.0f, fmul(2.0f, __fsqrt_rn(I))));
+  if (OP == LNN_EW_SQUARE) return fmul(fmul(dO, 2.0f), I);
+  if (OP == LNN_EW_TANH) return fmul(dO, fsub(1.0f, fmul(O, O)));
+  return 0.0f;
+}
+
+template <int OP>
+__global__ void __launch_bounds__(kThreads)
+ew_fwd_kernel(float* __restrict__ O, const float* __restrict__ I, int64_t n, float p0, float p1,
+              int acc, int vec) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  if (vec) {
+    const int64_t n4 = n >> 2;
+    const float4* I4 = reinterpret_cast<const float4*>(I);
+    float4* O4 = reinterpret_cast<float4*>(O);
+    for (int64_t i = tid; i < n4; i += nthreads) {
+      float4 v = __ldcs(I4 + i);
+      float4 r;
+      r.x = ew_fwd<OP>(v.x, p0, p1); r.y = ew_fwd<OP>(v.y, p0, p1);
+      r.z = ew_fwd<OP>(v.z, p0, p1); r.w = ew_fwd<OP>(v.w, p0, p1);
+      if (acc) {
+        float4 o = O4[i];
+        r.x = fadd(o.x, r.x); r.y = fadd(o.y, r.y); r.z = fadd(o.z, r.z); r.w = fadd(o.w, r.w);
+      }
+      O4[i] = r;
+    }
+    for (int64_t i = (n4 << 2) + tid; i < n; i += nthreads) {
+      float r = ew_fwd<OP>(I[i], p0, p1);
+      O[i] = acc ? fadd(O[i], r) : r;
+    }
+  } else {
+    for (int64_t i = tid; i < n; i += nthreads) {
+      float r = ew_fwd<OP>(I[i], p0, p1);
+      O[i] = acc ? fadd(O[i], r) : r;
+    }
+  }
+}
+
+template <int OP>
+__global__ void __launch_bounds__(kThreads)
+ew_bwd_kernel(float* __restrict__ dI, const float* __restrict__ I, const float* __restrict__ O,
+              const float* __restrict__ dO, int64_t n, float p0, float p1, int flag, int vec) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  if (vec) {
+    const int64_t n4 = n >> 2;
+    for (int64_t i = tid; i < n4; i += nthreads) {
+      float4 vi = reinterpret_cast<const float4*>(I)[i];
+      float4 vo = reinterpret_cast<const float4*>(O)[i];
+      float4 vd = reinterpret_cast<const float4*>(dO)[i];
+      float4 g = reinterpret_cast<float4*>(dI)[i];
+      g.x = fadd(g.x, ew_bwd<OP>(vi.x, vo.x, vd.x, p0, p1, flag));
+      g.y = fadd(g.y, ew_bwd<OP>(vi.y, vo.y, vd.y, p0, p1, flag));
+      g.z = fadd(g.z, ew_bwd<OP>(vi.z, vo.z, vd.z, p0, p1, flag));
+      g.w = fadd(g.w, ew_bwd<OP>(vi.w, vo.w, vd.w, p0, p1, flag));
+      reinterpret_cast<float4*>(dI)[i] = g;
+    }
+    for (int64_t i = (n4 << 2) + tid; i < n; i += nthreads)
+      dI[i] = fadd(dI[i], ew_bwd<OP>(I[i], O[i], dO[i], p0, p1, flag));
+  } else {
+    for (int64_t i = tid; i < n; i += nthreads)
+      dI[i] = fadd(dI[i], ew_bwd<OP>(I[i], O[i], dO[i], p0, p1, flag));
+  }
+}
+
+// ---- broadcast binary bodies (litenn/core/op/dual_wise_op.py:194-312) ------------------
+
+template <int OP>
+__device__ __forceinline__ float bin_fwd(float A, float B) {
+  if (OP == LNN_BIN_ADD) return fadd(A, B);
+  if (OP == LNN_BIN_SUB) return fsub(A, B);
+  if (OP == LNN_BIN_MUL) return fmul(A, B);
+  if (OP == LNN_BIN_DIV) return fdiv(A, B);
+  if (OP == LNN_BIN_MAX) return fmaxf(A, B);
+  if (OP == LNN_BIN_MIN) return fminf(A, B);
+  if (OP == LNN_BIN_BCE)
+    return fsub(fmul(-B, logf(A)), fmul(fsub(1.0f, B), logf(fsub(1.0f, A))));
+  return 0.0f;
+}
+
+template <int OP, int WHICH>
+__device__ __forceinline__ float bin_bwd(float A, float B, float O, float dO) {
+  if (WHICH == 0) {
+    if (OP == LNN_BIN_ADD || OP == LNN_BIN_SUB) return dO;
+    if (OP == LNN_BIN_MUL) return fmul(dO, B);
+    if (OP == LNN_BIN_DIV) return fdiv(dO, B);
+    if (OP == LNN_BIN_MAX) return fmul(dO, b2f(A >= B));
+    if (OP == LNN_BIN_MIN) return fmul(dO, b2f(A <= B));
+    if (OP == LNN_BIN_BCE) return fdiv(fmul(dO, fsub(A, B)), fmul(A, fsub(1.0f, A)));
+  } else {
+    if (OP == LNN_BIN_ADD) return dO;
+    if (OP == LNN_BIN_SUB) return -dO;
+    if (OP == LNN_BIN_MUL) return fmul(dO, A);
+    if (OP == LNN_BIN_DIV) return fmul(dO, -fdiv(A, fmul(B, B)));
+    if (OP == LNN_BIN_MAX) return fmul(dO, b2f(A < B));
+    if (OP == LNN_BIN_MIN) return fmul(dO, b2f(A > B));
+    if (OP == LNN_BIN_BCE) return dO;
+  }
+  return 0.0f;
+}
+
+struct BcastDims {
+  int rank;
+  int64_t o[LNN_MAX_DIMS];     // output extents
+  int64_t as[LNN_MAX_DIMS];    // element strides of A (0 where broadcast)
+  int64_t bs[LNN_MAX_DIMS];
+};
+
+__device__ __forceinline__ void bcast_offsets(const BcastDims& d, int64_t gid, int64_t& ao,
+                                              int64_t& bo) {
+  ao = 0; bo = 0;
+#pragma unroll
+  for (int k = LNN_MAX_DIMS - 1; k >= 0; --k) {
+    if (k < d.rank) {
+      int64_t q = gid / d.o[k];
+      int64_t r = gid - q * d.o[k];
+      ao += r * d.as[k];
+      bo += r * d.bs[k];
+      gid = q;
+    }
+  }
+}
+
+// mode 0: forward; 1: dA; 2: dB.  same=1: no broadcasting at all (flat indexing).
+template <int OP, int MODE>
+__global__ void __launch_bounds__(kThreads)
+bin_kernel(float* __restrict__ X, const float* __restrict__ A, const float* __restrict__ B,
+           const float* __restrict__ O, const float* __restrict__ dO, int64_t n, BcastDims d,
+           int acc, int same) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = tid; i < n; i += nthreads) {
+    int64_t ao = i, bo = i;
+    if (!same) bcast_offsets(d, i, ao, bo);
+    float a = A[ao], b = B[bo];
+    float r;
+    if (MODE == 0) {
+      r = bin_fwd<OP>(a, b);
+      X[i] = acc ? fadd(X[i], r) : r;
+    } else {
+      r = bin_bwd<OP, MODE - 1>(a, b, O[i], dO[i]);
+      X[i] = fadd(X[i], r);
+    }
+  }
+}
+
+// y (+)= leaky_relu(x*g + b): x[N,C,HW]; each (n,c) plane is contiguous.  One float4 per
+// thread per step; the channel index is recovered per vector (HW % 4 == 0 on this path).
+__global__ void __launch_bounds__(kThreads)
+scale_bias_lrelu_vec_kernel(float4* __restrict__ Y, const float4* __restrict__ X,
+                            const float* __restrict__ G, const float* __restrict__ Bv,
+                            int64_t n4, int64_t hw4, int64_t c, float alpha, int acc) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = tid; i < n4; i += nthreads) {
+    const int64_t ch = (i / hw4) % c;
+    const float g = __ldg(G + ch), b = __ldg(Bv + ch);
+    float4 v = __ldcs(X + i);
+    float4 r;
+    float t;
+    t = fadd(fmul(v.x, g), b); r.x = fadd(fmul(t, b2f(t >= 0.0f)), fmul(fmul(alpha, t), b2f(t < 0.0f)));
+    t = fadd(fmul(v.y, g), b); r.y = fadd(fmul(t, b2f(t >= 0.0f)), fmul(fmul(alpha, t), b2f(t < 0.0f)));
+    t = fadd(fmul(v.z, g), b); r.z = fadd(fmul(t, b2f(t >= 0.0f)), fmul(fmul(alpha, t), b2f(t < 0.0f)));
+    t = fadd(fmul(v.w, g), b); r.w = fadd(fmul(t, b2f(t >= 0.0f)), fmul(fmul(alpha, t), b2f(t < 0.0f)));
+    if (acc) {
+      float4 o = Y[i];
+      r.x = fadd(o.x, r.x); r.y = fadd(o.y, r.y); r.z = fadd(o.z, r.z); r.w = fadd(o.w, r.w);
+      Y[i] = r;
+    } else {
+      __stcs(Y + i, r);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+scale_bias_lrelu_kernel(float* __restrict__ Y, const float* __restrict__ X,
+                        const float* __restrict__ G, const float* __restrict__ Bv, int64_t n,
+                        int64_t hw, int64_t c, float alpha, int acc) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = tid; i < n; i += nthreads) {
+    const int64_t ch = (i / hw) % c;
+    float t = fadd(fmul(X[i], G[ch]), Bv[ch]);
+    float r = fadd(fmul(t, b2f(t >= 0.0f)), fmul(fmul(alpha, t), b2f(t < 0.0f)));
+    Y[i] = acc ? fadd(Y[i], r) : r;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+fill_kernel(float* __restrict__ p, int64_t n, float v, int vec) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  if (vec) {
+    const int64_t n4 = n >> 2;
+    float4 v4 = make_float4(v, v, v, v);
+    for (int64_t i = tid; i < n4; i += nthreads) reinterpret_cast<float4*>(p)[i] = v4;
+    for (int64_t i = (n4 << 2) + tid; i < n; i += nthreads) p[i] = v;
+  } else {
+    for (int64_t i = tid; i < n; i += nthreads) p[i] = v;
+  }
+}
+
+// A = -lr*G ; V += A  (litenn/core/optimizer/SGD.py:42-74 with momentum 0: the product
+// is rounded, then added -- two kernels in the reference, two roundings here).
+__global__ void __launch_bounds__(kThreads)
+sgd_kernel(float* __restrict__ V, const float* __restrict__ G, int64_t n, float lr, float gscale,
+           int use_scale) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = tid; i < n; i += nthreads) {
+    float g = G[i];
+    if (use_scale) g = fmul(g, gscale);
+    V[i] = fadd(V[i], fmul(-lr, g));
+  }
+}
+
+inline int grid_for(const lnn::Device* d, int64_t work_items) {
+  int64_t blocks = lnn_ceil_div(work_items, kThreads);
+  int64_t cap = (int64_t)d->sm_count * 8;   // 8 resident blocks of 256 threads per SM
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (int)blocks;
+}
+
+inline bool aligned16(uint64_t p) { return (p & 15) == 0; }
+
+}  // namespace
+
+#define EW_DISPATCH(OPV, CALL)                                                            \
+  switch (OPV) {                                                                          \
+    case LNN_EW_ABS: { CALL(LNN_EW_ABS); break; }                                         \
+    case LNN_EW_ADD_CONST: { CALL(LNN_EW_ADD_CONST); break; }                             \
+    case LNN_EW_CLIP: { CALL(LNN_EW_CLIP); break; }                                       \
+    case LNN_EW_COS: { CALL(LNN_EW_COS); break; }                                         \
+    case LNN_EW_EXP: { CALL(LNN_EW_EXP); break; }                                         \
+    case LNN_EW_LEAKY_RELU: { CALL(LNN_EW_LEAKY_RELU); break; }                           \
+    case LNN_EW_LOG: { CALL(LNN_EW_LOG); break; }                                         \
+    case LNN_EW_MUL_CONST: { CALL(LNN_EW_MUL_CONST); break; }                             \
+    case LNN_EW_RDIV_CONST: { CALL(LNN_EW_RDIV_CONST); break; }                           \
+    case LNN_EW_RSUB_CONST: { CALL(LNN_EW_RSUB_CONST); break; }                           \
+    case LNN_EW_RELU: { CALL(LNN_EW_RELU); break; }                                       \
+    case LNN_EW_SIGMOID: { CALL(LNN_EW_SIGMOID); break; }                                 \
+    case LNN_EW_SIN: { CALL(LNN_EW_SIN); break; }                                         \
+    case LNN_EW_SQRT: { CALL(LNN_EW_SQRT); break; }                                       \
+    case LNN_EW_SQUARE: { CALL(LNN_EW_SQUARE); break; }                                   \
+    case LNN_EW_TANH: { CALL(LNN_EW_TANH); break; }                                       \
+    default: return lnn::set_error(LNN_E_INVALID, "unknown element-wise op %d", OPV);     \
+  }
+
+#define BIN_DISPATCH(OPV, CALL)                                                           \
+  switch (OPV) {                                                                          \
+    case LNN_BIN_ADD: { CALL(LNN_BIN_ADD); break; }                                       \
+    case LNN_BIN_SUB: { CALL(LNN_BIN_SUB); break; }                                       \
+    case LNN_BIN_MUL: { CALL(LNN_BIN_MUL); break; }                                       \
+    case LNN_BIN_DIV: { CALL(LNN_BIN_DIV); break; }                                       \
+    case LNN_BIN_MAX: { CALL(LNN_BIN_MAX); break; }                                       \
+    case LNN_BIN_MIN: { CALL(LNN_BIN_MIN); break; }                                       \
+    case LNN_BIN_BCE: { CALL(LNN_BIN_BCE); break; }                                       \
+    default: return lnn::set_error(LNN_E_INVALID, "unknown binary op %d", OPV);           \
+  }
+
+static int make_bcast(BcastDims& bd, int rank, const int64_t* o_shape, const int64_t* a_shape,
+                      const int64_t* b_shape, int64_t* n_out, int* same) {
+  LNN_REQUIRE(rank >= 1 && rank <= LNN_MAX_DIMS, "rank %d out of range", rank);
+  LNN_REQUIRE(o_shape && a_shape && b_shape, "null shape");
+  bd.rank = rank;
+  int64_t n = 1, astr = 1, bstr = 1;
+  *same = 1;
+  for (int k = rank - 1; k >= 0; --k) {
+    LNN_REQUIRE(o_shape[k] >= 1, "bad extent");
+    LNN_REQUIRE(a_shape[k] == o_shape[k] || a_shape[k] == 1, "A axis %d not broadcastable", k);
+    LNN_REQUIRE(b_shape[k] == o_shape[k] || b_shape[k] == 1, "B axis %d not broadcastable", k);
+    bd.o[k] = o_shape[k];
+    bd.as[k] = (a_shape[k] == 1) ? 0 : astr;
+    bd.bs[k] = (b_shape[k] == 1) ? 0 : bstr;
+    if (a_shape[k] != o_shape[k] || b_shape[k] != o_shape[k]) *same = 0;
+    astr *= a_shape[k];
+    bstr *= b_shape[k];
+    n *= o_shape[k];
+  }
+  for (int k = rank; k < LNN_MAX_DIMS; ++k) { bd.o[k] = 1; bd.as[k] = 0; bd.bs[k] = 0; }
+  *n_out = n;
+  return LNN_OK;
+}
+
+extern "C" {
+
+int lnn_fill_f32(int dev, uint64_t dst, int64_t count, float value) {
+  LNN_DEV(d, dev);
+  LNN_REQUIRE(dst && count > 0, "bad arguments");
+  int vec = aligned16(dst);
+  fill_kernel<<<grid_for(d, vec ? count / 4 + 1 : count), kThreads, 0, d->stream>>>(
+      (float*)(uintptr_t)dst, count, value, vec);
+  LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
+}
+
+int lnn_eltwise_fwd(int dev, int op, uint64_t O, uint64_t I, int64_t n, float p0, float p1,
+                    int flag, int accumulate) {
+  LNN_DEV(d, dev);
+  (void)flag;
+  LNN_REQUIRE(O && I && n > 0, "bad arguments");
+  int vec = aligned16(O) && aligned16(I);
+  int grid = grid_for(d, vec ? n / 4 + 1 : n);
+#define CALL(OPC)                                                                         \
+  ew_fwd_kernel<OPC><<<grid, kThreads, 0, d->stream>>>((float*)(uintptr_t)O,              \
+      (const float*)(uintptr_t)I, n, p0, p1, accumulate, vec)
+  EW_DISPATCH(op, CALL)
+#undef CALL
+  LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
+}
+
+int lnn_eltwise_bwd(int dev, int op, uint64_t dI, uint64_t I, uint64_t O, uint64_t dO, int64_t n,
+                    float p0, float p1, int flag) {
+  LNN_DEV(d, dev);
+  LNN_REQUIRE(dI && I && O && dO && n > 0, "bad arguments");
+  int vec = aligned16(dI) && aligned16(I) && aligned16(O) && aligned16(dO);
+  int grid = grid_for(d, vec ? n / 4 + 1 : n);
+#define CALL(OPC)                                                                         \
+  ew_bwd_kernel<OPC><<<grid, kThreads, 0, d->stream>>>((float*)(uintptr_t)dI,             \
+      (const float*)(uintptr_t)I, (const float*)(uintptr_t)O, (const float*)(uintptr_t)dO, \
+      n, p0, p1, flag, vec)
+  EW_DISPATCH(op, CALL)
+#undef CALL
+  LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
+}
+
+int lnn_binary_fwd(int dev, int op, uint64_t O, uint64_t A, uint64_t B, int rank,
+                   const int64_t* o_shape, const int64_t* a_shape, const int64_t* b_shape,
+                   int accumulate) {
+  LNN_DEV(d, dev);
+  LNN_REQUIRE(O && A && B, "null buffer");
+  BcastDims bd; int64_t n; int same;
+  int rc = make_bcast(bd, rank, o_shape, a_shape, b_shape, &n, &same);
+  if (rc) return rc;
+  int grid = grid_for(d, n);
+#define CALL(OPC)                                                                         \
+  bin_kernel<OPC, 0><<<grid, kThreads, 0, d->stream>>>((float*)(uintptr_t)O,              \
+      (const float*)(uintptr_t)A, (const float*)(uintptr_t)B, nullptr, nullptr, n, bd,    \
+      accumulate, same)
+  BIN_DISPATCH(op, CALL)
+#undef CALL
+  LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
+}
+
+int lnn_binary_bwd(int dev, int op, int which, uint64_t dX, uint64_t A, uint64_t B, uint64_t O,
+                   uint64_t dO, int rank, const int64_t* o_shape, const int64_t* a_shape,
+                   const int64_t* b_shape) {
+  LNN_DEV(d, dev);
+  LNN_REQUIRE(dX && A && B && O && dO, "null buffer");
+  LNN_REQUIRE(which == 0 || which == 1, "which must be 0 or 1");
+  BcastDims bd; int64_t n; int same;
+  int rc = make_bcast(bd, rank, o_shape, a_shape, b_shape, &n, &same);
+  if (rc) return rc;
+  int grid = grid_for(d, n);
+#define CALL(OPC)                                                                         \
+  if (which == 0)                                                                         \
+    bin_kernel<OPC, 1><<<grid, kThreads, 0, d->stream>>>((float*)(uintptr_t)dX,           \
+        (const float*)(uintptr_t)A, (const float*)(uintptr_t)B, (const float*)(uintptr_t)O, \
+        (const float*)(uintptr_t)dO, n, bd, 1, same);                                     \
+  else                                                                                    \
+    bin_kernel<OPC, 2><<<grid, kThreads, 0, d->stream>>>((float*)(uintptr_t)dX,           \
+        (const float*)(uintptr_t)A, (const float*)(uintptr_t)B, (const float*)(uintptr_t)O, \
+        (const float*)(uintptr_t)dO, n, bd, 1, same)
+  BIN_DISPATCH(op, CALL)
+#undef CALL
+  LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
+}
+
+int lnn_scale_bias_lrelu(int dev, uint64_t y, uint64_t x, uint64_t g, uint64_t b, int64_t n,
+                         int64_t c, int64_t hw, float alpha, int accumulate) {
+  LNN_DEV(d, dev);
+  LNN_REQUIRE(y && x && g && b && n > 0 && c > 0 && hw > 0, "bad arguments");
+  int64_t total = n * c * hw;
+  if ((hw & 3) == 0 && aligned16(y) && aligned16(x)) {
+    int64_t n4 = total >> 2;
+    scale_bias_lrelu_vec_kernel<<<grid_for(d, n4), kThreads, 0, d->stream>>>(
+        (float4*)(uintptr_t)y, (const float4*)(uintptr_t)x, (const float*)(uintptr_t)g,
+        (const float*)(uintptr_t)b, n4, hw >> 2, c, alpha, accumulate);
+  } else {
+    scale_bias_lrelu_kernel<<<grid_for(d, total), kThreads, 0, d->stream>>>(
+        (float*)(uintptr_t)y, (const float*)(uintptr_t)x, (const float*)(uintptr_t)g,
+        (const float*)(uintptr_t)b, total, hw, c, alpha, accumulate);
+  }
+  LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
+}
+
+int lnn_sgd_step(int dev, uint64_t V, uint64_t G, int64_t n, float lr, float gscale) {
+  LNN_DEV(d, dev);
+  LNN_REQUIRE(V && G && n > 0, "bad arguments");
+  sgd_kernel<<<grid_for(d, n), kThreads, 0, d->stream>>>(
+      (float*)(uintptr_t)V, (const float*)(uintptr_t)G, n, lr, gscale, gscale != 1.0f);
+  LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,217 @@
+// 2-D pooling forward/backward (avg, max, min) on NCHW fp32.
+// Semantics follow litenn/core/op/pool2D.py:111-230: taps are visited in row-major
+// window order; avg divides the ordered sum by the number of in-bounds taps; max/min of
+// an empty window is 0; the max/min gradient goes to the FIRST tap (row-major) equal to
+// the pooled value.  HBM-bound: the 2x2/stride-2 even-width case reads two float4 rows
+// per two outputs and writes float2; everything else uses the generic scalar kernel.
+#include "lnn_common.cuh"
+#include <math_constants.h>
+
+namespace {
+
+constexpr int kThreads = 256;
+
+struct PoolGeom {
+  int ih, iw, oh, ow, pool, stride, padl, padt;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreads)
+pool_fwd_kernel(float* __restrict__ O, const float* __restrict__ I, int64_t total, PoolGeom g) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t gid = tid; gid < total; gid += nthreads) {
+    const int ow = (int)(gid % g.ow);
+    const int64_t t = gid / g.ow;
+    const int oh = (int)(t % g.oh);
+    const int64_t plane = t / g.oh;               // n*C + c
+    const float* ip = I + plane * g.ih * g.iw;
+    float v = MODE == LNN_POOL_AVG ? 0.0f : (MODE == LNN_POOL_MAX ? -CUDART_INF_F : CUDART_INF_F);
+    int cnt = 0;
+    for (int ph = 0; ph < g.pool; ++ph)
+      for (int pw = 0; pw < g.pool; ++pw) {
+        const int ih = -g.padt + ph + oh * g.stride;
+        const int iw = -g.padl + pw + ow * g.stride;
+        if (iw >= 0 && ih >= 0 && iw < g.iw && ih < g.ih) {
+          const float x = ip[(int64_t)ih * g.iw + iw];
+          if (MODE == LNN_POOL_AVG) { v = __fadd_rn(v, x); ++cnt; }
+          else if (MODE == LNN_POOL_MAX) v = fmaxf(v, x);
+          else v = fminf(v, x);
+        }
+      }
+    if (MODE == LNN_POOL_AVG) { if (cnt != 0) v = __fdiv_rn(v, (float)cnt); }
+    else if (MODE == LNN_POOL_MAX) { if (v == -CUDART_INF_F) v = 0.0f; }
+    else { if (v == CUDART_INF_F) v = 0.0f; }
+    O[gid] = v;
+  }
+}
+
+// 2x2 / stride 2 / no left-top padding / even IW, OW == IW/2, IW % 4 == 0: every thread
+// produces two horizontally adjacent outputs from two float4 loads.  All taps in bounds
+// except possibly the bottom row when IH is odd (padded bottom).
+template <int MODE>
+__global__ void __launch_bounds__(kThreads)
+pool2x2_fwd_kernel(float2* __restrict__ O, const float* __restrict__ I, int64_t total2, int ih,
+                   int iw, int oh, int ow2) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t gid = tid; gid < total2; gid += nthreads) {
+    const int x2 = (int)(gid % ow2);
+    const int64_t t = gid / ow2;
+    const int y = (int)(t % oh);
+    const int64_t plane = t / oh;
+    const float* row0 = I + (plane * ih + 2 * y) * (int64_t)iw + 4 * x2;
+    const float4 a = __ldcs(reinterpret_cast<const float4*>(row0));
+    const bool has1 = (2 * y + 1) < ih;
+    float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (has1) b = __ldcs(reinterpret_cast<const float4*>(row0 + iw));
+    float2 r;
+    if (MODE == LNN_POOL_AVG) {
+      // ordered sum ((0 + t00) + t01) + t10) + t11 ; 0 + t00 == t00 except for -0
+      float s0 = __fadd_rn(__fadd_rn(0.0f, a.x), a.y);
+      float s1 = __fadd_rn(__fadd_rn(0.0f, a.z), a.w);
+      if (has1) {
+        s0 = __fadd_rn(__fadd_rn(s0, b.x), b.y);
+        s1 = __fadd_rn(__fadd_rn(s1, b.z), b.w);
+      }
+      const float cnt = has1 ? 4.0f : 2.0f;
+      r.x = __fdiv_rn(s0, cnt);
+      r.y = __fdiv_rn(s1, cnt);
+    } else if (MODE == LNN_POOL_MAX) {
+      float m0 = fmaxf(fmaxf(-CUDART_INF_F, a.x), a.y), m1 = fmaxf(fmaxf(-CUDART_INF_F, a.z), a.w);
+      if (has1) { m0 = fmaxf(fmaxf(m0, b.x), b.y); m1 = fmaxf(fmaxf(m1, b.z), b.w); }
+      r.x = (m0 == -CUDART_INF_F) ? 0.0f : m0;
+      r.y = (m1 == -CUDART_INF_F) ? 0.0f : m1;
+    } else {
+      float m0 = fminf(fminf(CUDART_INF_F, a.x), a.y), m1 = fminf(fminf(CUDART_INF_F, a.z), a.w);
+      if (has1) { m0 = fminf(fminf(m0, b.x), b.y); m1 = fminf(fminf(m1, b.z), b.w); }
+      r.x = (m0 == CUDART_INF_F) ? 0.0f : m0;
+      r.y = (m1 == CUDART_INF_F) ? 0.0f : m1;
+    }
+    __stcs(O + gid, r);
+  }
+}
+
+// Backward, one thread per INPUT element, exactly the reference's gather formulation.
+template <int MODE>
+__global__ void __launch_bounds__(kThreads)
+pool_bwd_kernel(float* __restrict__ dI, const float* __restrict__ I, const float* __restrict__ dO,
+                const float* __restrict__ O, int64_t total, PoolGeom g) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t gid = tid; gid < total; gid += nthreads) {
+    const int iw = (int)(gid % g.iw);
+    const int64_t t = gid / g.iw;
+    const int ih = (int)(t % g.ih);
+    const int64_t plane = t / g.ih;
+    const float* ip = I ? I + plane * g.ih * g.iw : nullptr;
+    const float* op = O ? O + plane * g.oh * g.ow : nullptr;
+    const float* dop = dO + plane * g.oh * g.ow;
+    float v = 0.0f;
+    for (int ph = 0; ph < g.pool; ++ph)
+      for (int pw = 0; pw < g.pool; ++pw) {
+        const int oh = (g.padt + ih - ph) / g.stride;   // C division truncates toward zero
+        const int ow = (g.padl + iw - pw) / g.stride;
+        if (ow >= 0 && oh >= 0 && ow < g.ow && oh < g.oh &&
+            iw == (-g.padl + pw + ow * g.stride) && ih == (-g.padt + ph + oh * g.stride)) {
+          if (MODE == LNN_POOL_AVG) {
+            int dcount = 0;
+            for (int dph = 0; dph < g.pool; ++dph)
+              for (int dpw = 0; dpw < g.pool; ++dpw) {
+                const int dih = -g.padt + dph + oh * g.stride;
+                const int diw = -g.padl + dpw + ow * g.stride;
+                dcount += (diw >= 0 && dih >= 0 && diw < g.iw && dih < g.ih);
+              }
+            v = __fadd_rn(v, __fdiv_rn(dop[(int64_t)oh * g.ow + ow], (float)dcount));
+          } else {
+            const float ov = op[(int64_t)oh * g.ow + ow];
+            for (int k = 0; k < g.pool * g.pool; ++k) {
+              const int dih = -g.padt + (k / g.pool) + oh * g.stride;
+              const int diw = -g.padl + (k % g.pool) + ow * g.stride;
+              if (diw >= 0 && dih >= 0 && diw < g.iw && dih < g.ih &&
+                  ip[(int64_t)dih * g.iw + diw] == ov) {
+                if (dih == ih && diw == iw) v = __fadd_rn(v, dop[(int64_t)oh * g.ow + ow]);
+                break;
+              }
+            }
+          }
+        }
+      }
+    dI[gid] = __fadd_rn(dI[gid], v);
+  }
+}
+
+inline int grid_for(const lnn::Device* d, int64_t work_items) {
+  int64_t blocks = lnn_ceil_div(work_items, kThreads);
+  int64_t cap = (int64_t)d->sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (int)blocks;
+}
+
+}  // namespace
+
+extern "C" {
+
+int lnn_pool2d_fwd(int dev, int mode, uint64_t O, uint64_t I, int64_t n, int64_t c, int ih, int iw,
+                   int oh, int ow, int pool, int stride, int padl, int padt) {
+  LNN_DEV(d, dev);
+  LNN_REQUIRE(O && I, "null buffer");
+  LNN_REQUIRE(n > 0 && c > 0 && ih > 0 && iw > 0 && oh > 0 && ow > 0, "bad extents");
+  LNN_REQUIRE(pool >= 2 && stride >= 1, "pool_size must be >= 2 and stride >= 1");
+  LNN_REQUIRE(mode >= 0 && mode <= 2, "unknown pool mode %d", mode);
+  const int64_t total = n * c * oh * ow;
+  float* o = (float*)(uintptr_t)O;
+  const float* i = (const float*)(uintptr_t)I;
+  const bool fast = pool == 2 && stride == 2 && padl == 0 && padt == 0 && (iw % 4) == 0 &&
+                    ow == iw / 2 && oh == (ih + 1) / 2 && (O & 7) == 0 && (I & 15) == 0;
+  if (fast) {
+    const int64_t total2 = total / 2;
+    const int grid = grid_for(d, total2);
+    if (mode == LNN_POOL_AVG)
+      pool2x2_fwd_kernel<LNN_POOL_AVG><<<grid, kThreads, 0, d->stream>>>((float2*)o, i, total2, ih, iw, oh, ow / 2);
+    else if (mode == LNN_POOL_MAX)
+      pool2x2_fwd_kernel<LNN_POOL_MAX><<<grid, kThreads, 0, d->stream>>>((float2*)o, i, total2, ih, iw, oh, ow / 2);
+    else
+      pool2x2_fwd_kernel<LNN_POOL_MIN><<<grid, kThreads, 0, d->stream>>>((float2*)o, i, total2, ih, iw, oh, ow / 2);
+  } else {
+    PoolGeom g{ih, iw, oh, ow, pool, stride, padl, padt};
+    const int grid = grid_for(d, total);
+    if (mode == LNN_POOL_AVG)
+      pool_fwd_kernel<LNN_POOL_AVG><<<grid, kThreads, 0, d->stream>>>(o, i, total, g);
+    else if (mode == LNN_POOL_MAX)
+      pool_fwd_kernel<LNN_POOL_MAX><<<grid, kThreads, 0, d->stream>>>(o, i, total, g);
+    else
+      pool_fwd_kernel<LNN_POOL_MIN><<<grid, kThreads, 0, d->stream>>>(o, i, total, g);
+  }
+  LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
+}
+
+int lnn_pool2d_bwd(int dev, int mode, uint64_t dI, uint64_t I, uint64_t dO, uint64_t O, int64_t n,
+                   int64_t c, int ih, int iw, int oh, int ow, int pool, int stride, int padl,
+                   int padt) {
+  LNN_DEV(d, dev);
+  LNN_REQUIRE(dI && dO, "null buffer");
+  LNN_REQUIRE(mode >= 0 && mode <= 2, "unknown pool mode %d", mode);
+  LNN_REQUIRE(mode == LNN_POOL_AVG || (I && O), "max/min backward needs I and O");
+  LNN_REQUIRE(n > 0 && c > 0 && ih > 0 && iw > 0 && oh > 0 && ow > 0, "bad extents");
+  LNN_REQUIRE(pool >= 2 && stride >= 1, "pool_size must be >= 2 and stride >= 1");
+  const int64_t total = n * c * ih * iw;
+  PoolGeom g{ih, iw, oh, ow, pool, stride, padl, padt};
+  const int grid = grid_for(d, total);
+  float* di = (float*)(uintptr_t)dI;
+  const float* i = (const float*)(uintptr_t)I;
+  const float* dout = (const float*)(uintptr_t)dO;
+  const float* o = (const float*)(uintptr_t)O;
+  if (mode == LNN_POOL_AVG)
+    pool_bwd_kernel<LNN_POOL_AVG><<<grid, kThreads, 0, d->stream>>>(di, i, dout, o, total, g);
+  else if (mode == LNN_POOL_MAX)
+    pool_bwd_kernel<LNN_POOL_MAX><<<grid, kThreads, 0, d->stream>>>(di, i, dout, o, total, g);
+  else
+    pool_bwd_kernel<LNN_POOL_MIN><<<grid, kThreads, 0, d->stream>>>(di, i, dout, o, total, g);
+  LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
+}
+
+}  // extern "C"

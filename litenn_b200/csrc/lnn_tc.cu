@@ -1,0 +1,1064 @@
+// tcgen05 tile engine: device kernel, operand pre-split passes, tensor-map construction
+// and the planners behind lnn_gemm_f32 / lnn_conv2d_fwd / lnn_conv2d_dx / lnn_conv2d_dw.
+#include "lnn_tc.cuh"
+#include <stdlib.h>
+#include <string.h>
+#include <algorithm>
+
+using namespace lnn_tc;
+
+// =========================================================================================
+// device helpers (inline PTX)
+// =========================================================================================
+namespace {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Bounded wait.  Returns false when the budget ran out or another role aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int role, int step) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitBudget) {
+      *abort_flag = 1;
+      if (atomicCAS(status, 0, LNN_E_TIMEOUT) == 0) {
+        status[1] = role;
+        status[2] = (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
+        status[3] = step;
+      }
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* tm, uint32_t bar,
+                                            int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"((uint64_t)tm), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* tm, uint32_t bar,
+                                            int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"((uint64_t)tm), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+        "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+        "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+        "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of tcgen05.mma: start address, leading / stride byte
+// offsets (all in 16-byte units), descriptor version 1, swizzle mode in bits 61-63.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes,
+                                                   uint32_t sbo_bytes, uint32_t layout_type) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= 1ull << 46;
+  d |= (uint64_t)layout_type << 61;
+  return d;
+}
+__device__ __forceinline__ uint32_t layout_of_swizzle(int swz_bytes) {
+  return swz_bytes == 128 ? 2u : (swz_bytes == 64 ? 4u : 6u);
+}
+
+__device__ __forceinline__ float apply_act(float v, int act, float alpha) {
+  if (act == 1) {
+    // leaky_relu as the reference writes it: I*(I>=0) + alpha*I*(I<0)
+    const float pos = __fmul_rn(v, v >= 0.0f ? 1.0f : 0.0f);
+    const float neg = __fmul_rn(__fmul_rn(alpha, v), v < 0.0f ? 1.0f : 0.0f);
+    return __fadd_rn(pos, neg);
+  }
+  return v;
+}
+
+// =========================================================================================
+// the tile kernel
+// =========================================================================================
+template <int MODE>
+__global__ void __launch_bounds__(kThreadsTc)
+tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
+          const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
+          const __grid_constant__ TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t full_bar[8];
+  __shared__ uint64_t empty_bar[8];
+  __shared__ uint64_t accum_bar;
+  __shared__ uint32_t tmem_base_smem;
+  __shared__ int abort_flag_smem;
+
+  // an earlier CTA already gave up: leave as a whole CTA (the decision must be uniform)
+  if (threadIdx.x == 0) abort_flag_smem = (*(volatile int*)p.status != 0) ? 2 : 0;
+  __syncthreads();
+  if (abort_flag_smem == 2) return;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  volatile int* abort_flag = &abort_flag_smem;
+
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles = (raw + 1023u) & ~1023u;      // operand ring, 1024-byte aligned
+  const int nbuf = p.passes == 3 ? 2 : 1;
+  const uint32_t a_sz = (uint32_t)((p.a_tile_bytes + 1023) & ~1023);
+  const uint32_t b_sz = (uint32_t)((p.b_tile_bytes + 1023) & ~1023);
+  const uint32_t stage_sz = nbuf * (a_sz + b_sz);
+
+  // ---- tile coordinates -----------------------------------------------------------------
+  int m0 = 0, n0 = 0, bz = 0;              // GEMM
+  int pb0 = 0, pa0 = 0, pn0 = 0;           // CONV pixel-tile origin (logical output coords)
+  int split = 0, oc_t = 0, ic_t = 0, tap = 0, patch0 = 0;   // DW
+  int num_kb = p.num_kb;
+  if (MODE == MODE_GEMM) {
+    m0 = blockIdx.x * 128; n0 = blockIdx.y * p.bn; bz = blockIdx.z;
+  } else if (MODE == MODE_CONV) {
+    const int pt = blockIdx.x;
+    const int bt = pt % p.tiles_b;
+    const int at = (pt / p.tiles_b) % p.tiles_a;
+    const int nt = pt / (p.tiles_b * p.tiles_a);
+    pb0 = bt * p.tw; pa0 = at * p.th; pn0 = nt * p.tn;
+    n0 = blockIdx.y * p.bn;
+  } else {
+    split = blockIdx.x;
+    oc_t = blockIdx.y / p.ic_tiles;
+    ic_t = blockIdx.y % p.ic_tiles;
+    tap = blockIdx.z;
+    patch0 = split * p.patches_per_split;
+    num_kb = min(p.patches_per_split, p.patches_total - patch0);
+    if (num_kb < 0) num_kb = 0;
+  }
+
+  // ---- set-up ---------------------------------------------------------------------------
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    mbar_init(smem_u32(&accum_bar), 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_smem), p.tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_smem;
+
+  // ---- roles ----------------------------------------------------------------------------
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint32_t tx_bytes =
+          (uint32_t)nbuf * (uint32_t)(p.a_loads * p.a_load_bytes + p.b_loads * p.b_load_bytes);
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % p.stages;
+        const uint32_t ph = (uint32_t)(kb / p.stages) & 1u;
+        if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, abort_flag, p.status, 0, kb)) break;
+        const uint32_t fb = smem_u32(&full_bar[s]);
+        mbar_expect_tx(fb, tx_bytes);
+        const uint32_t sa = tiles + s * stage_sz;
+        const uint32_t sb = sa + nbuf * a_sz;
+        for (int half = 0; half < nbuf; ++half) {
+          const CUtensorMap* ta = half ? &tmAl : &tmAh;
+          const CUtensorMap* tb = half ? &tmBl : &tmBh;
+          const uint32_t da = sa + half * a_sz;
+          const uint32_t db = sb + half * b_sz;
+          if (MODE == MODE_GEMM) {
+            const int k0 = kb * 32;
+            if (p.a_major == 0) {
+              tma_load_3d(da, ta, fb, k0, m0, bz);
+            } else {
+              for (int i = 0; i < p.a_loads; ++i)
+                tma_load_3d(da + i * p.a_load_bytes, ta, fb, m0 + i * 32, k0, bz);
+            }
+            if (p.b_major == 0) {
+              tma_load_3d(db, tb, fb, k0, n0, bz);
+            } else {
+              for (int i = 0; i < p.b_loads; ++i)
+                tma_load_3d(db + i * p.b_load_bytes, tb, fb, n0 + i * 32, k0, bz);
+            }
+          } else if (MODE == MODE_CONV) {
+            const int t = kb / p.ncb;
+            const int cbi = kb - t * p.ncb;
+            tma_load_4d(da, ta, fb, cbi * p.cb, pb0 * p.es + p.tap_dx[t], pa0 * p.es + p.tap_dy[t], pn0);
+            tma_load_3d(db, tb, fb, cbi * p.cb, n0, p.tap_w[t]);
+          } else {
+            const int pidx = patch0 + kb;
+            const int bt = pidx % p.tiles_b;
+            const int at = (pidx / p.tiles_b) % p.tiles_a;
+            const int nt = pidx / (p.tiles_b * p.tiles_a);
+            const int ea = p.swz_a >> 2, eb = p.swz_b >> 2;
+            for (int i = 0; i < p.a_loads; ++i)
+              tma_load_4d(da + i * p.a_load_bytes, ta, fb, oc_t * 128 + i * ea, bt * p.tw,
+                          at * p.th, nt * p.tn);
+            for (int i = 0; i < p.b_loads; ++i)
+              tma_load_4d(db + i * p.b_load_bytes, tb, fb, ic_t * p.bn + i * eb,
+                          bt * p.tw * p.es + p.tap_dx[tap], at * p.th * p.es + p.tap_dy[tap],
+                          nt * p.tn);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t la = layout_of_swizzle(p.swz_a), lb = layout_of_swizzle(p.swz_b);
+      const uint32_t a_lbo = p.a_major ? (uint32_t)(p.a_krows * p.swz_a) : 16u;
+      const uint32_t b_lbo = p.b_major ? (uint32_t)(p.b_krows * p.swz_b) : 16u;
+      const uint32_t a_sbo = 8u * p.swz_a, b_sbo = 8u * p.swz_b;
+      const uint32_t a_step = p.a_major ? 8u * p.swz_a : 32u;
+      const uint32_t b_step = p.b_major ? 8u * p.swz_b : 32u;
+      bool ok = true;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % p.stages;
+        const uint32_t ph = (uint32_t)(kb / p.stages) & 1u;
+        if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag, p.status, 1, kb)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sa = tiles + s * stage_sz;
+        const uint32_t sb = sa + nbuf * a_sz;
+        for (int ks = 0; ks < p.ksteps; ++ks) {
+          const uint64_t ah = make_smem_desc(sa + ks * a_step, a_lbo, a_sbo, la);
+          const uint64_t bh = make_smem_desc(sb + ks * b_step, b_lbo, b_sbo, lb);
+          umma_tf32(tmem_base, ah, bh, p.idesc, (kb | ks) ? 1u : 0u);
+          if (nbuf == 2) {
+            const uint64_t al = make_smem_desc(sa + a_sz + ks * a_step, a_lbo, a_sbo, la);
+            const uint64_t bl = make_smem_desc(sb + b_sz + ks * b_step, b_lbo, b_sbo, lb);
+            umma_tf32(tmem_base, ah, bl, p.idesc, 1u);
+            umma_tf32(tmem_base, al, bh, p.idesc, 1u);
+          }
+        }
+        umma_commit(smem_u32(&empty_bar[s]));
+      }
+      if (ok) umma_commit(smem_u32(&accum_bar));
+    }
+  } else {
+    // ---- epilogue warps: TMEM lane quarter = warp % 4 --------------------------------------
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    bool have_acc = true;
+    if (num_kb > 0) {
+      have_acc = mbar_wait(smem_u32(&accum_bar), 0u, abort_flag, p.status, 2, 0);
+      have_acc = __all_sync(0xffffffffu, have_acc);   // tcgen05.ld below is warp-collective
+      tc_fence_after();
+    }
+    if (have_acc) {
+      bool row_ok;
+      int64_t row_off;
+      int64_t col_stride = 1;
+      int col0 = 0, col_limit = 0;
+      if (MODE == MODE_GEMM) {
+        const int64_t m = (int64_t)m0 + r;
+        row_ok = m < p.M;
+        row_off = (int64_t)bz * p.batch_stride_c + m * p.ldc;
+        col0 = n0; col_limit = (int)min((int64_t)p.bn, p.N - n0);
+      } else if (MODE == MODE_CONV) {
+        const int hw = p.th * p.tw;
+        const int tn_i = r / hw;
+        const int rem = r - tn_i * hw;
+        const int th_i = rem / p.tw;
+        const int tw_i = rem - th_i * p.tw;
+        const int n = pn0 + tn_i, a = pa0 + th_i, b = pb0 + tw_i;
+        row_ok = r < p.rows_valid && n < p.NL && a < p.AH && b < p.AW;
+        row_off = p.out_base + (int64_t)n * p.out_sn + (int64_t)a * p.out_sa + (int64_t)b * p.out_sb;
+        col_stride = p.out_sc;
+        col0 = n0; col_limit = min(p.bn, p.OC - n0);
+      } else {
+        row_ok = true;
+        row_off = (int64_t)split * p.part_stride_split + (int64_t)tap * p.part_stride_tap +
+                  ((int64_t)oc_t * 128 + r) * p.part_ld + (int64_t)ic_t * p.bn;
+        col0 = 0; col_limit = p.bn;
+      }
+      float* outp = p.out + row_off;
+      const bool vec_ok = (MODE != MODE_CONV) && ((((uintptr_t)outp) & 15) == 0);
+      for (int c0 = 0; c0 < p.bn; c0 += 32) {
+        uint32_t v[32];
+        if (num_kb > 0) {
+          tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0u;
+        }
+        if (!row_ok) {
+          // nothing to store for this lane
+        } else if (MODE == MODE_DW) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            if (c0 + j < col_limit) {
+              float4 q = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]),
+                                     __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+              *reinterpret_cast<float4*>(outp + c0 + j) = q;
+            }
+          }
+        } else if (MODE == MODE_GEMM && vec_ok && (c0 + 32) <= col_limit) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            float x[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float t = __uint_as_float(v[j + e]);
+              if (p.bias) t = __fadd_rn(t, __ldg(p.bias + col0 + c0 + j + e));
+              x[e] = apply_act(t, p.act, p.alpha);
+            }
+            float4* dst = reinterpret_cast<float4*>(outp + col0 + c0 + j);
+            if (p.accumulate) {
+              const float4 o = *dst;
+              x[0] = __fadd_rn(o.x, x[0]); x[1] = __fadd_rn(o.y, x[1]);
+              x[2] = __fadd_rn(o.z, x[2]); x[3] = __fadd_rn(o.w, x[3]);
+            }
+            *dst = make_float4(x[0], x[1], x[2], x[3]);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (c0 + j < col_limit) {
+              float t = __uint_as_float(v[j]);
+              if (p.bias) t = __fadd_rn(t, __ldg(p.bias + col0 + c0 + j));
+              t = apply_act(t, p.act, p.alpha);
+              float* dst = outp + (int64_t)(col0 + c0 + j) * col_stride;
+              if (p.accumulate) t = __fadd_rn(*dst, t);
+              *dst = t;
+            }
+          }
+        }
+        __syncwarp();   // reconverge before the next warp-collective TMEM load
+      }
+    }
+  }
+
+  // ---- tear-down ------------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // copies issued before the abort may still be landing in this CTA's shared memory
+    const long long t0 = clock64();
+    while (clock64() - t0 < kAbortDelay) { }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, p.tmem_cols);
+  }
+}
+
+// =========================================================================================
+// operand preparation (HBM-bound)
+// =========================================================================================
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ float to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+__device__ __forceinline__ void split1(float x, float& hi, float& lo) {
+  hi = to_tf32(x);
+  lo = to_tf32(__fsub_rn(x, hi));
+}
+
+// hi/lo split of a dense [rows][cols] matrix into buffers of row pitch `pitch`
+__global__ void __launch_bounds__(kThreads)
+split_rows_kernel(float* __restrict__ hi, float* __restrict__ lo, const float* __restrict__ src,
+                  int64_t rows, int64_t cols, int64_t pitch, int want_lo) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  if (pitch == cols && (cols & 3) == 0) {
+    const int64_t n4 = rows * cols / 4;
+    for (int64_t i = tid; i < n4; i += nthreads) {
+      const float4 v = __ldcs(reinterpret_cast<const float4*>(src) + i);
+      float4 h, l;
+      split1(v.x, h.x, l.x); split1(v.y, h.y, l.y); split1(v.z, h.z, l.z); split1(v.w, h.w, l.w);
+      reinterpret_cast<float4*>(hi)[i] = h;
+      if (want_lo) reinterpret_cast<float4*>(lo)[i] = l;
+    }
+  } else {
+    const int64_t n = rows * pitch;
+    for (int64_t i = tid; i < n; i += nthreads) {
+      const int64_t r = i / pitch, c = i - r * pitch;
+      float h = 0.0f, l = 0.0f;
+      if (c < cols) split1(src[r * cols + c], h, l);
+      hi[i] = h;
+      if (want_lo) lo[i] = l;
+    }
+  }
+}
+
+// NCHW -> NHWC with channel padding to cp, split into hi/lo.  One block transposes a
+// [32 channels] x [32 pixels] tile of one image through shared memory.
+__global__ void __launch_bounds__(256)
+nchw_to_nhwc_split_kernel(float* __restrict__ hi, float* __restrict__ lo,
+                          const float* __restrict__ src, int64_t n, int c, int64_t hw, int cp,
+                          int want_lo) {
+  __shared__ float tile[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int64_t tiles_p = (hw + 31) / 32;
+  const int tiles_c = (cp + 31) / 32;
+  const int64_t total = n * tiles_p * tiles_c;
+  for (int64_t t = blockIdx.x; t < total; t += gridDim.x) {
+    const int tc = (int)(t % tiles_c);
+    const int64_t t2 = t / tiles_c;
+    const int64_t tp = t2 % tiles_p;
+    const int64_t img = t2 / tiles_p;
+    const float* sp = src + img * (int64_t)c * hw;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int ch = tc * 32 + ty + k * 8;
+      const int64_t px = tp * 32 + tx;
+      tile[ty + k * 8][tx] = (ch < c && px < hw) ? sp[(int64_t)ch * hw + px] : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int64_t px = tp * 32 + ty + k * 8;
+      const int ch = tc * 32 + tx;
+      if (px < hw && ch < cp) {
+        float h, l;
+        split1(tile[tx][ty + k * 8], h, l);
+        const int64_t o = (img * hw + px) * cp + ch;
+        hi[o] = h;
+        if (want_lo) lo[o] = l;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// Kernel OIHW -> [tap][rows][kp] hi/lo.  transpose_io = 0: rows = oc, k = ic (forward);
+// 1: rows = ic, k = oc (input gradient).  k is zero-padded to kp.
+__global__ void __launch_bounds__(kThreads)
+weight_split_kernel(float* __restrict__ hi, float* __restrict__ lo, const float* __restrict__ w,
+                    int oc, int ic, int taps, int kp, int transpose_io, int want_lo) {
+  const int rows = transpose_io ? ic : oc;
+  const int64_t total = (int64_t)taps * rows * kp;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  const int kvalid = transpose_io ? oc : ic;
+  for (int64_t i = tid; i < total; i += nthreads) {
+    const int k = (int)(i % kp);
+    const int64_t t2 = i / kp;
+    const int row = (int)(t2 % rows);
+    const int t = (int)(t2 / rows);
+    float h = 0.0f, l = 0.0f;
+    if (k < kvalid) {
+      const int o = transpose_io ? k : row;
+      const int c = transpose_io ? row : k;
+      split1(w[((int64_t)o * ic + c) * taps + t], h, l);
+    }
+    hi[i] = h;
+    if (want_lo) lo[i] = l;
+  }
+}
+
+// dW[oc][ic][tap] += sum over splits of P[split][tap][ocp][icp], splits added in order
+__global__ void __launch_bounds__(kThreads)
+dw_finalize_kernel(float* __restrict__ dW, const float* __restrict__ P, int oc, int ic, int taps,
+                   int splits, int64_t stride_split, int64_t stride_tap, int64_t ld) {
+  const int64_t total = (int64_t)oc * ic * taps;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = tid; i < total; i += nthreads) {
+    const int t = (int)(i % taps);
+    const int64_t t2 = i / taps;
+    const int c = (int)(t2 % ic);
+    const int o = (int)(t2 / ic);
+    const float* pp = P + (int64_t)t * stride_tap + (int64_t)o * ld + c;
+    float s = 0.0f;
+    for (int k = 0; k < splits; ++k) s = __fadd_rn(s, pp[(int64_t)k * stride_split]);
+    dW[i] = __fadd_rn(dW[i], s);
+  }
+}
+
+// =========================================================================================
+// host side
+// =========================================================================================
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+int get_encode() {
+  if (g_encode) return LNN_OK;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  LNN_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+  if (!fn || qres != cudaDriverEntryPointSuccess)
+    return lnn::set_error(LNN_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  g_encode = (EncodeTiledFn)fn;
+  return LNN_OK;
+}
+
+// dims/box/estr have `rank` entries, innermost first; strides_bytes has rank-1 entries.
+int encode_map(CUtensorMap* tm, const void* base, int rank, const uint64_t* dims,
+               const uint64_t* strides_bytes, const uint32_t* box, const uint32_t* estr,
+               int swz_bytes) {
+  int rc = get_encode();
+  if (rc) return rc;
+  cuuint64_t gd[5], gs[4];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < rank; ++i) { gd[i] = dims[i]; bx[i] = box[i]; es[i] = estr[i]; }
+  for (int i = 0; i + 1 < rank; ++i) gs[i] = strides_bytes[i];
+  for (int i = 0; i < rank; ++i)
+    if (bx[i] < 1 || bx[i] > 256)
+      return lnn::set_error(LNN_E_UNSUPPORTED, "TMA box extent %u (dim %d) outside 1..256", bx[i], i);
+  const CUtensorMapSwizzle sw = swz_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                              : swz_bytes == 64  ? CU_TENSOR_MAP_SWIZZLE_64B
+                                                 : CU_TENSOR_MAP_SWIZZLE_32B;
+  CUresult r = g_encode(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, (void*)base, gd, gs,
+                        bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return lnn::set_error(LNN_E_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return LNN_OK;
+}
+
+inline int grid_for(const lnn::Device* d, int64_t work_items) {
+  int64_t blocks = lnn_ceil_div(work_items, kThreads);
+  int64_t cap = (int64_t)d->sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (int)blocks;
+}
+
+inline int env_int(const char* name, int dflt) {
+  const char* e = getenv(name);
+  return (e && *e) ? atoi(e) : dflt;
+}
+
+inline uint32_t make_idesc(int bn, int a_major, int b_major) {
+  // c_format F32 (bits 4-5 = 1), a/b format TF32 (= 2) at bits 7-9 / 10-12, majors at 15 / 16,
+  // N >> 3 at bits 17-22, M >> 4 at bits 24-28.
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)a_major << 15) |
+         ((uint32_t)b_major << 16) | ((uint32_t)(bn >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+inline uint32_t tmem_cols_for(int bn) {
+  uint32_t c = 32;
+  while ((int)c < bn) c <<= 1;
+  return c;
+}
+
+constexpr int kSmemLimit = 227 * 1024;
+constexpr int kSmemSlack = 2048;   // alignment slack + static barriers
+
+template <int MODE>
+int launch_tc(lnn::Device* d, dim3 grid, const CUtensorMap& ah, const CUtensorMap& al,
+              const CUtensorMap& bh, const CUtensorMap& bl, TcParams& p) {
+  const int nbuf = p.passes == 3 ? 2 : 1;
+  const int a_sz = (p.a_tile_bytes + 1023) & ~1023;
+  const int b_sz = (p.b_tile_bytes + 1023) & ~1023;
+  const int stage = nbuf * (a_sz + b_sz);
+  int stages = env_int("LNN_TC_STAGES", 0);
+  if (stages <= 0) {
+    stages = (kSmemLimit - kSmemSlack) / stage;
+    if (stages > 4) stages = 4;
+  }
+  if (stages > 8) stages = 8;
+  if (stages < 1 || stages * stage + kSmemSlack > kSmemLimit)
+    return lnn::set_error(LNN_E_UNSUPPORTED, "operand stage of %d bytes does not fit shared memory", stage);
+  p.stages = stages;
+  p.status = d->status_dev;
+  const int smem = stages * stage + 1024;
+  static bool attr_set[3] = {false, false, false};
+  if (!attr_set[MODE]) {
+    LNN_CUDA(cudaFuncSetAttribute(tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  kSmemLimit - 1024));
+    attr_set[MODE] = true;
+  }
+  tc_kernel<MODE><<<grid, kThreadsTc, smem, d->stream>>>(ah, al, bh, bl, p);
+  LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
+}
+
+int check_passes(int tf32_passes) {
+  LNN_REQUIRE(tf32_passes == 1 || tf32_passes == 3, "tf32_passes must be 1 or 3");
+  return LNN_OK;
+}
+
+// Split a dense [rows][cols] matrix (per batch entry) into hi/lo scratch with padded pitch.
+int split_matrix(lnn::Device* d, lnn::Scratch& hi, lnn::Scratch& lo, const float* src,
+                 int64_t rows, int64_t cols, int64_t* pitch_out, int want_lo) {
+  const int64_t pitch = (cols + 3) & ~3ll;
+  int rc = hi.get((uint64_t)rows * pitch * 4);
+  if (rc) return rc;
+  if (want_lo) { rc = lo.get((uint64_t)rows * pitch * 4); if (rc) return rc; }
+  split_rows_kernel<<<grid_for(d, rows * pitch / 4 + 1), kThreads, 0, d->stream>>>(
+      hi.as<float>(), want_lo ? lo.as<float>() : nullptr, src, rows, cols, pitch, want_lo);
+  LNN_CHECK_LAUNCH(d);
+  *pitch_out = pitch;
+  return LNN_OK;
+}
+
+// Geometry of the pixel tiling used by the convolution passes.
+struct PixTile { int tw, th, tn, tiles_b, tiles_a, tiles_n; };
+
+// rows of a CONV tile: up to 128 logical output pixels as tn x th x tw
+PixTile plan_conv_tile(int NL, int AH, int AW, int es) {
+  PixTile t;
+  const int wcap = std::min(128, 256 / es);
+  if (AW >= wcap) { t.tw = wcap; t.th = 1; t.tn = 1; }
+  else {
+    t.tw = AW;
+    int hmax = std::min(std::min(AH, 128 / t.tw), 256 / es);
+    if (hmax < 1) hmax = 1;
+    // pick th <= hmax minimising padded rows over the image height
+    int best = 1; double best_eff = 0;
+    for (int th = 1; th <= hmax; ++th) {
+      const int tiles = (AH + th - 1) / th;
+      const double eff = (double)AH / (tiles * th) * (double)(th * t.tw) / 128.0;
+      if (eff > best_eff + 1e-9) { best_eff = eff; best = th; }
+    }
+    t.th = best;
+    t.tn = 1;
+    if (t.th == AH) t.tn = std::max(1, std::min(NL, 128 / (t.tw * t.th)));
+  }
+  t.tiles_b = (AW + t.tw - 1) / t.tw;
+  t.tiles_a = (AH + t.th - 1) / t.th;
+  t.tiles_n = (NL + t.tn - 1) / t.tn;
+  return t;
+}
+
+int gcd_int(int a, int b) { while (b) { int t = a % b; a = b; b = t; } return a; }
+int chan_pad(int c) { return (c + 7) & ~7; }
+int chan_block(int cp) { return (cp % 32 == 0) ? 32 : ((cp % 16 == 0) ? 16 : 8); }
+
+// 4-D map over an NHWC activation copy [N][H][W][cp]
+int encode_nhwc(CUtensorMap* tm, const float* base, int n, int h, int w, int cp, int box_c,
+                int box_w, int box_h, int box_n, int estride) {
+  uint64_t dims[4] = {(uint64_t)cp, (uint64_t)w, (uint64_t)h, (uint64_t)n};
+  uint64_t str[3] = {(uint64_t)cp * 4, (uint64_t)w * cp * 4, (uint64_t)h * w * cp * 4};
+  uint32_t box[4] = {(uint32_t)box_c, (uint32_t)(box_w * estride), (uint32_t)(box_h * estride),
+                     (uint32_t)box_n};
+  uint32_t es[4] = {1, (uint32_t)estride, (uint32_t)estride, 1};
+  return encode_map(tm, base, 4, dims, str, box, es, box_c * 4);
+}
+
+int nhwc_split(lnn::Device* d, lnn::Scratch& hi, lnn::Scratch& lo, const float* src, int n, int c,
+               int h, int w, int cp, int want_lo) {
+  const uint64_t bytes = (uint64_t)n * h * w * cp * 4;
+  int rc = hi.get(bytes);
+  if (rc) return rc;
+  if (want_lo) { rc = lo.get(bytes); if (rc) return rc; }
+  const int64_t hw = (int64_t)h * w;
+  const int64_t tiles = (int64_t)n * ((hw + 31) / 32) * ((cp + 31) / 32);
+  int64_t grid = std::min<int64_t>(tiles, (int64_t)d->sm_count * 16);
+  nchw_to_nhwc_split_kernel<<<(unsigned)grid, 256, 0, d->stream>>>(
+      hi.as<float>(), want_lo ? lo.as<float>() : nullptr, src, n, c, hw, cp, want_lo);
+  LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
+}
+
+int weights_split(lnn::Device* d, lnn::Scratch& hi, lnn::Scratch& lo, const float* w, int oc, int ic,
+                  int taps, int kp, int transpose_io, int want_lo) {
+  const int rows = transpose_io ? ic : oc;
+  const uint64_t bytes = (uint64_t)taps * rows * kp * 4;
+  int rc = hi.get(bytes);
+  if (rc) return rc;
+  if (want_lo) { rc = lo.get(bytes); if (rc) return rc; }
+  weight_split_kernel<<<grid_for(d, (int64_t)taps * rows * kp), kThreads, 0, d->stream>>>(
+      hi.as<float>(), want_lo ? lo.as<float>() : nullptr, w, oc, ic, taps, kp, transpose_io, want_lo);
+  LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
+}
+
+int check_geom(const lnn_conv_geom* g) {
+  LNN_REQUIRE(g, "geometry is null");
+  LNN_REQUIRE(g->n > 0 && g->ic > 0 && g->ih > 0 && g->iw > 0 && g->oc > 0 && g->kh > 0 &&
+              g->kw > 0 && g->oh > 0 && g->ow > 0, "bad convolution extents");
+  LNN_REQUIRE(g->stride >= 1 && g->stride <= 8 && g->dilation >= 1, "stride must be 1..8, dilation >= 1");
+  LNN_REQUIRE(g->kh * g->kw <= kMaxTaps, "kernels larger than %d taps are not supported", kMaxTaps);
+  return LNN_OK;
+}
+
+// Shared launcher of the "pixels on M" implicit GEMM (forward and input gradient).
+// act_hi/lo: NHWC copy [NL][H][W][kp]; w_hi/lo: [taps][rows][kp]; the logical output grid is
+// AH x AW per image; tap t reads the activation at (a*es + dy[t], b*es + dx[t]).
+int launch_conv_like(lnn::Device* d, const float* act_hi, const float* act_lo, int NL, int H, int W,
+                     int kp, const float* w_hi, const float* w_lo, int wrows, int wtaps, int AH,
+                     int AW, int es, int ntaps, const int* dy, const int* dx, const int* widx,
+                     int OCv, float* out, int64_t out_base, int64_t out_sn, int64_t out_sa,
+                     int64_t out_sb, int64_t out_sc, const float* bias, int act, float alpha,
+                     int accumulate, int passes) {
+  const int cb = chan_block(kp);
+  const int swz = cb * 4;
+  PixTile t = plan_conv_tile(NL, AH, AW, es);
+  int bn = std::min(256, (OCv + 15) & ~15);
+  const int bn_env = env_int("LNN_TC_BN", 0);
+  if (bn_env >= 16 && bn_env <= 256 && bn_env % 16 == 0) bn = std::min(bn, bn_env);
+  TcParams p;
+  memset(&p, 0, sizeof(p));
+  p.mode = MODE_CONV; p.passes = passes; p.bn = bn;
+  p.a_major = 0; p.b_major = 0; p.swz_a = swz; p.swz_b = swz;
+  p.ksteps = cb / 8;
+  p.a_tile_bytes = 128 * swz; p.b_tile_bytes = bn * swz;
+  p.a_loads = 1; p.b_loads = 1;
+  p.a_load_bytes = t.tn * t.th * t.tw * swz;
+  p.b_load_bytes = bn * swz;
+  p.idesc = make_idesc(bn, 0, 0);
+  p.tmem_cols = tmem_cols_for(bn);
+  p.ncb = kp / cb; p.cb = cb; p.ntaps = ntaps;
+  p.num_kb = ntaps * p.ncb;
+  p.tw = t.tw; p.th = t.th; p.tn = t.tn;
+  p.tiles_b = t.tiles_b; p.tiles_a = t.tiles_a; p.tiles_n = t.tiles_n;
+  p.AW = AW; p.AH = AH; p.NL = NL; p.es = es;
+  p.rows_valid = t.tn * t.th * t.tw;
+  p.out_sn = out_sn; p.out_sa = out_sa; p.out_sb = out_sb; p.out_sc = out_sc; p.out_base = out_base;
+  p.OC = OCv;
+  p.accumulate = accumulate; p.act = act; p.alpha = alpha; p.bias = bias; p.out = out;
+  for (int i = 0; i < ntaps; ++i) { p.tap_dy[i] = dy[i]; p.tap_dx[i] = dx[i]; p.tap_w[i] = widx[i]; }
+  CUtensorMap mah, mal, mbh, mbl;
+  int rc = encode_nhwc(&mah, act_hi, NL, H, W, kp, cb, t.tw, t.th, t.tn, es);
+  if (rc) return rc;
+  rc = encode_nhwc(&mal, passes == 3 ? act_lo : act_hi, NL, H, W, kp, cb, t.tw, t.th, t.tn, es);
+  if (rc) return rc;
+  {
+    uint64_t dims[3] = {(uint64_t)kp, (uint64_t)wrows, (uint64_t)wtaps};
+    uint64_t str[2] = {(uint64_t)kp * 4, (uint64_t)wrows * kp * 4};
+    uint32_t box[3] = {(uint32_t)cb, (uint32_t)bn, 1};
+    uint32_t es1[3] = {1, 1, 1};
+    rc = encode_map(&mbh, w_hi, 3, dims, str, box, es1, swz);
+    if (rc) return rc;
+    rc = encode_map(&mbl, passes == 3 ? w_lo : w_hi, 3, dims, str, box, es1, swz);
+    if (rc) return rc;
+  }
+  const int64_t ptiles = (int64_t)t.tiles_b * t.tiles_a * t.tiles_n;
+  LNN_REQUIRE(ptiles < (1ll << 31), "too many pixel tiles");
+  dim3 grid((unsigned)ptiles, (unsigned)((OCv + bn - 1) / bn), 1);
+  return launch_tc<MODE_CONV>(d, grid, mah, mal, mbh, mbl, p);
+}
+
+}  // namespace
+
+extern "C" {
+
+int lnn_gemm_f32(int dev, uint64_t C, uint64_t A, uint64_t B, uint64_t bias, int64_t batch,
+                 int64_t m, int64_t n, int64_t k, int trans_a, int trans_b, int accumulate,
+                 int tf32_passes) {
+  LNN_DEV(d, dev);
+  LNN_REQUIRE(C && A && B, "null buffer");
+  LNN_REQUIRE(batch >= 1 && m >= 1 && n >= 1 && k >= 1, "bad GEMM extents");
+  LNN_REQUIRE(batch < 65536, "batch too large");
+  int rc = check_passes(tf32_passes);
+  if (rc) return rc;
+  const int want_lo = tf32_passes == 3;
+  // A is stored [m][k] (K-major) or [k][m] (MN-major); same for B with n.
+  const int64_t a_rows = trans_a ? k : m, a_cols = trans_a ? m : k;
+  const int64_t b_rows = trans_b ? n : k, b_cols = trans_b ? k : n;
+  lnn::Scratch ah(d), al(d), bh(d), bl(d);
+  int64_t a_pitch, b_pitch;
+  rc = split_matrix(d, ah, al, (const float*)(uintptr_t)A, batch * a_rows, a_cols, &a_pitch, want_lo);
+  if (rc) return rc;
+  rc = split_matrix(d, bh, bl, (const float*)(uintptr_t)B, batch * b_rows, b_cols, &b_pitch, want_lo);
+  if (rc) return rc;
+
+  int bn = (int)std::min<int64_t>(256, (n + 31) & ~31ll);
+  const int bn_env = env_int("LNN_TC_BN", 0);
+  if (bn_env >= 32 && bn_env <= 256 && bn_env % 32 == 0) bn = std::min(bn, bn_env);
+  TcParams p;
+  memset(&p, 0, sizeof(p));
+  p.mode = MODE_GEMM; p.passes = tf32_passes; p.bn = bn;
+  p.a_major = trans_a ? 1 : 0;
+  p.b_major = trans_b ? 0 : 1;
+  p.swz_a = 128; p.swz_b = 128; p.ksteps = 4;
+  p.a_tile_bytes = 128 * 128; p.b_tile_bytes = bn * 128;
+  if (p.a_major == 0) { p.a_loads = 1; p.a_load_bytes = 128 * 128; }
+  else { p.a_loads = 4; p.a_load_bytes = 32 * 128; p.a_krows = 32; }
+  if (p.b_major == 0) { p.b_loads = 1; p.b_load_bytes = bn * 128; }
+  else { p.b_loads = bn / 32; p.b_load_bytes = 32 * 128; p.b_krows = 32; }
+  p.idesc = make_idesc(bn, p.a_major, p.b_major);
+  p.tmem_cols = tmem_cols_for(bn);
+  p.num_kb = (int)((k + 31) / 32);
+  p.M = m; p.N = n; p.ldc = n; p.batch_stride_c = m * n;
+  p.accumulate = accumulate; p.act = 0; p.alpha = 0.0f;
+  p.bias = (const float*)(uintptr_t)bias;
+  p.out = (float*)(uintptr_t)C;
+
+  CUtensorMap mah, mal, mbh, mbl;
+  {
+    // innermost-first dims: (cols, rows, batch)
+    uint64_t dims[3] = {(uint64_t)a_cols, (uint64_t)a_rows, (uint64_t)batch};
+    uint64_t str[2] = {(uint64_t)a_pitch * 4, (uint64_t)a_rows * a_pitch * 4};
+    uint32_t box[3] = {32, (uint32_t)(p.a_major ? 32 : 128), 1};
+    uint32_t es[3] = {1, 1, 1};
+    rc = encode_map(&mah, ah.p, 3, dims, str, box, es, 128);
+    if (rc) return rc;
+    rc = encode_map(&mal, want_lo ? al.p : ah.p, 3, dims, str, box, es, 128);
+    if (rc) return rc;
+  }
+  {
+    uint64_t dims[3] = {(uint64_t)b_cols, (uint64_t)b_rows, (uint64_t)batch};
+    uint64_t str[2] = {(uint64_t)b_pitch * 4, (uint64_t)b_rows * b_pitch * 4};
+    uint32_t box[3] = {32, (uint32_t)(p.b_major ? 32 : bn), 1};
+    uint32_t es[3] = {1, 1, 1};
+    rc = encode_map(&mbh, bh.p, 3, dims, str, box, es, 128);
+    if (rc) return rc;
+    rc = encode_map(&mbl, want_lo ? bl.p : bh.p, 3, dims, str, box, es, 128);
+    if (rc) return rc;
+  }
+  dim3 grid((unsigned)((m + 127) / 128), (unsigned)((n + bn - 1) / bn), (unsigned)batch);
+  return launch_tc<MODE_GEMM>(d, grid, mah, mal, mbh, mbl, p);
+}
+
+int lnn_conv2d_fwd(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint64_t W,
+                   uint64_t bias, int act, float alpha, int accumulate, int tf32_passes) {
+  LNN_DEV(d, dev);
+  int rc = check_geom(g);
+  if (rc) return rc;
+  rc = check_passes(tf32_passes);
+  if (rc) return rc;
+  LNN_REQUIRE(Y && X && W, "null buffer");
+  LNN_REQUIRE(act == 0 || act == 1, "unknown activation %d", act);
+  const int want_lo = tf32_passes == 3;
+  const int cp = chan_pad(g->ic);
+  const int taps = g->kh * g->kw;
+  lnn::Scratch xh(d), xl(d), wh(d), wl(d);
+  rc = nhwc_split(d, xh, xl, (const float*)(uintptr_t)X, g->n, g->ic, g->ih, g->iw, cp, want_lo);
+  if (rc) return rc;
+  rc = weights_split(d, wh, wl, (const float*)(uintptr_t)W, g->oc, g->ic, taps, cp, 0, want_lo);
+  if (rc) return rc;
+  int dy[kMaxTaps], dx[kMaxTaps], wi[kMaxTaps];
+  for (int kh = 0; kh < g->kh; ++kh)
+    for (int kw = 0; kw < g->kw; ++kw) {
+      const int t = kh * g->kw + kw;
+      dy[t] = kh * g->dilation - g->padt;
+      dx[t] = kw * g->dilation - g->padl;
+      wi[t] = t;
+    }
+  const int64_t plane = (int64_t)g->oh * g->ow;
+  return launch_conv_like(d, xh.as<float>(), xl.as<float>(), g->n, g->ih, g->iw, cp, wh.as<float>(),
+                          wl.as<float>(), g->oc, taps, g->oh, g->ow, g->stride, taps, dy, dx, wi,
+                          g->oc, (float*)(uintptr_t)Y, 0, (int64_t)g->oc * plane, g->ow, 1, plane,
+                          (const float*)(uintptr_t)bias, act, alpha, accumulate, tf32_passes);
+}
+
+int lnn_conv2d_dx(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY, uint64_t W,
+                  int tf32_passes) {
+  LNN_DEV(d, dev);
+  int rc = check_geom(g);
+  if (rc) return rc;
+  rc = check_passes(tf32_passes);
+  if (rc) return rc;
+  LNN_REQUIRE(dX && dY && W, "null buffer");
+  const int want_lo = tf32_passes == 3;
+  const int ocp = chan_pad(g->oc);
+  const int taps = g->kh * g->kw;
+  const int s = g->stride;
+  lnn::Scratch yh(d), yl(d), wh(d), wl(d);
+  rc = nhwc_split(d, yh, yl, (const float*)(uintptr_t)dY, g->n, g->oc, g->oh, g->ow, ocp, want_lo);
+  if (rc) return rc;
+  rc = weights_split(d, wh, wl, (const float*)(uintptr_t)W, g->oc, g->ic, taps, ocp, 1, want_lo);
+  if (rc) return rc;
+  const int64_t plane = (int64_t)g->ih * g->iw;
+  // One launch per residue class (ih % s, iw % s): within a class every tap that reaches an
+  // input pixel does so from output row oh = a + dy with a = (ih - ph) / s.
+  for (int ph = 0; ph < s; ++ph)
+    for (int pw = 0; pw < s; ++pw) {
+      const int AH = (g->ih - ph + s - 1) / s, AW = (g->iw - pw + s - 1) / s;
+      if (AH <= 0 || AW <= 0) continue;
+      int dy[kMaxTaps], dx[kMaxTaps], wi[kMaxTaps];
+      int nt = 0;
+      for (int kh = 0; kh < g->kh; ++kh) {
+        const int ny = ph + g->padt - kh * g->dilation;
+        if (((ny % s) + s) % s != 0) continue;
+        for (int kw = 0; kw < g->kw; ++kw) {
+          const int nx = pw + g->padl - kw * g->dilation;
+          if (((nx % s) + s) % s != 0) continue;
+          // exact division (ny, nx are multiples of s, possibly negative)
+          dy[nt] = ny / s; dx[nt] = nx / s; wi[nt] = kh * g->kw + kw;
+          ++nt;
+        }
+      }
+      if (nt == 0) continue;
+      rc = launch_conv_like(d, yh.as<float>(), yl.as<float>(), g->n, g->oh, g->ow, ocp,
+                            wh.as<float>(), wl.as<float>(), g->ic, taps, AH, AW, 1, nt, dy, dx, wi,
+                            g->ic, (float*)(uintptr_t)dX, (int64_t)ph * g->iw + pw,
+                            (int64_t)g->ic * plane, (int64_t)s * g->iw, s, plane, nullptr, 0, 0.0f,
+                            1, tf32_passes);
+      if (rc) return rc;
+    }
+  return LNN_OK;
+}
+
+int lnn_conv2d_dw(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY, uint64_t X,
+                  int tf32_passes) {
+  LNN_DEV(d, dev);
+  int rc = check_geom(g);
+  if (rc) return rc;
+  rc = check_passes(tf32_passes);
+  if (rc) return rc;
+  LNN_REQUIRE(dW && dY && X, "null buffer");
+  const int want_lo = tf32_passes == 3;
+  const int s = g->stride;
+  const int cp = chan_pad(g->ic), ocp = chan_pad(g->oc);
+  const int taps = g->kh * g->kw;
+  lnn::Scratch xh(d), xl(d), yh(d), yl(d), part(d);
+  rc = nhwc_split(d, xh, xl, (const float*)(uintptr_t)X, g->n, g->ic, g->ih, g->iw, cp, want_lo);
+  if (rc) return rc;
+  rc = nhwc_split(d, yh, yl, (const float*)(uintptr_t)dY, g->n, g->oc, g->oh, g->ow, ocp, want_lo);
+  if (rc) return rc;
+
+  const int ea = chan_block(ocp), eb = chan_block(cp);     // elements per smem row
+  const int swa = ea * 4, swb = eb * 4;
+  int bn = std::min(256, (cp + 15) & ~15);
+  if (bn % eb != 0) bn = ((bn + eb - 1) / eb) * eb;
+  const int oc_tiles = (g->oc + 127) / 128, ic_tiles = (cp + bn - 1) / bn;
+  // pixel patch = one k-block: tw x th output pixels of one image, a multiple of 8 pixels,
+  // sized so that two stages of (128 + bn) x pix floats (x2 for hi/lo) fit shared memory
+  const int nbuf = want_lo ? 2 : 1;
+  int pix_cap = ((kSmemLimit - kSmemSlack) / 2) / (nbuf * (128 + bn) * 4);
+  pix_cap = std::min(pix_cap & ~7, 128);
+  const int wcap = std::min(pix_cap, 256 / s);
+  LNN_REQUIRE(wcap >= 8, "stride too large for the weight-gradient kernel");
+  int tw, th;
+  if (g->ow >= wcap) { tw = wcap & ~7; th = 1; }
+  else {
+    // box width may exceed ow (zero filled); choose (th, tw_box) with tw_box*th % 8 == 0
+    int best_tw = (g->ow + 7) & ~7, best_th = 1;
+    double best_eff = (double)g->ow / best_tw;
+    for (int h = 2; h <= 8 && h <= g->oh && h * s <= 256; ++h) {
+      const int mult = 8 / gcd_int(8, h);
+      const int w = ((g->ow + mult - 1) / mult) * mult;
+      if (w * h > pix_cap || w * s > 256) continue;
+      const int tiles = (g->oh + h - 1) / h;
+      const double eff = (double)g->ow / w * (double)g->oh / (tiles * h);
+      if (eff > best_eff + 1e-9 || (eff > best_eff - 1e-9 && w * h > best_tw * best_th)) {
+        best_eff = eff; best_tw = w; best_th = h;
+      }
+    }
+    tw = best_tw; th = best_th;
+  }
+  const int pix = tw * th;
+  const int tiles_b = (g->ow + tw - 1) / tw, tiles_a = (g->oh + th - 1) / th, tiles_n = g->n;
+  const int64_t patches = (int64_t)tiles_b * tiles_a * tiles_n;
+  LNN_REQUIRE(patches < (1ll << 30), "too many pixel patches");
+  int64_t want_ctas = (int64_t)d->sm_count * 4;
+  int64_t splits = want_ctas / ((int64_t)taps * oc_tiles * ic_tiles);
+  splits = std::max<int64_t>(1, std::min<int64_t>(splits, patches));
+  const int pps = (int)((patches + splits - 1) / splits);
+  splits = (patches + pps - 1) / pps;    // every split owns at least one patch
+
+  const int64_t part_ld = (int64_t)ic_tiles * bn;
+  const int64_t stride_tap = (int64_t)oc_tiles * 128 * part_ld;
+  const int64_t stride_split = stride_tap * taps;
+  rc = part.get((uint64_t)splits * stride_split * 4);
+  if (rc) return rc;
+
+  TcParams p;
+  memset(&p, 0, sizeof(p));
+  p.mode = MODE_DW; p.passes = tf32_passes; p.bn = bn;
+  p.a_major = 1; p.b_major = 1; p.swz_a = swa; p.swz_b = swb;
+  p.ksteps = pix / 8;
+  p.a_loads = 128 / ea; p.b_loads = bn / eb;
+  p.a_load_bytes = pix * swa; p.b_load_bytes = pix * swb;
+  p.a_tile_bytes = p.a_loads * p.a_load_bytes; p.b_tile_bytes = p.b_loads * p.b_load_bytes;
+  p.a_krows = pix; p.b_krows = pix;
+  p.idesc = make_idesc(bn, 1, 1);
+  p.tmem_cols = tmem_cols_for(bn);
+  p.tw = tw; p.th = th; p.tn = 1;
+  p.tiles_b = tiles_b; p.tiles_a = tiles_a; p.tiles_n = tiles_n;
+  p.es = s;
+  p.patches_total = (int)patches; p.patches_per_split = pps; p.num_kb = pps;
+  p.part_stride_split = stride_split; p.part_stride_tap = stride_tap; p.part_ld = part_ld;
+  p.oc_tiles = oc_tiles; p.ic_tiles = ic_tiles;
+  p.OC = g->oc; p.ICv = g->ic;
+  p.out = part.as<float>();
+  for (int kh = 0; kh < g->kh; ++kh)
+    for (int kw = 0; kw < g->kw; ++kw) {
+      const int t = kh * g->kw + kw;
+      p.tap_dy[t] = kh * g->dilation - g->padt;
+      p.tap_dx[t] = kw * g->dilation - g->padl;
+      p.tap_w[t] = t;
+    }
+  p.ntaps = taps;
+  CUtensorMap mah, mal, mbh, mbl;
+  rc = encode_nhwc(&mah, yh.as<float>(), g->n, g->oh, g->ow, ocp, ea, tw, th, 1, 1);
+  if (rc) return rc;
+  rc = encode_nhwc(&mal, want_lo ? yl.as<float>() : yh.as<float>(), g->n, g->oh, g->ow, ocp, ea, tw, th, 1, 1);
+  if (rc) return rc;
+  rc = encode_nhwc(&mbh, xh.as<float>(), g->n, g->ih, g->iw, cp, eb, tw, th, 1, s);
+  if (rc) return rc;
+  rc = encode_nhwc(&mbl, want_lo ? xl.as<float>() : xh.as<float>(), g->n, g->ih, g->iw, cp, eb, tw, th, 1, s);
+  if (rc) return rc;
+  dim3 grid((unsigned)splits, (unsigned)(oc_tiles * ic_tiles), (unsigned)taps);
+  rc = launch_tc<MODE_DW>(d, grid, mah, mal, mbh, mbl, p);
+  if (rc) return rc;
+  dw_finalize_kernel<<<grid_for(d, (int64_t)g->oc * g->ic * taps), kThreads, 0, d->stream>>>(
+      (float*)(uintptr_t)dW, part.as<float>(), g->oc, g->ic, taps, (int)splits, stride_split,
+      stride_tap, part_ld);
+  LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
+}
+
+}  // extern "C"

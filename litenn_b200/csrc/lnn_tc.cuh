@@ -1,0 +1,71 @@
+// tcgen05 / TMEM / TMA tile engine shared by matmul and the three convolution passes.
+//
+// One CTA (192 threads) produces one 128 x BN fp32 accumulator tile in tensor memory:
+//   warp 0    : TMA producer  -- cp.async.bulk.tensor loads into a ring of smem stages
+//   warp 1    : MMA issuer    -- one elected thread issues tcgen05.mma.kind::tf32, owns TMEM
+//   warps 2-5 : epilogue      -- tcgen05.ld the accumulator, bias / activation / "+=", store
+// fp32 accuracy comes from split-TF32: every operand is pre-split (by an HBM-bound pass)
+// into hi = rna_tf32(x) and lo = rna_tf32(x - hi); the MMA warp issues hi*hi + hi*lo +
+// lo*hi into the same accumulator.  Operands may be K-major or MN-major in shared memory
+// (both are native to tcgen05 for tf32), so no transposes are materialised for the
+// backward GEMMs, and the convolution A-tiles are gathered straight from an NHWC copy of
+// the activations by 4-D tiled TMA (zero fill outside the image = padding).
+//
+// Every wait on an mbarrier is bounded: when the budget runs out the role records a
+// status word, raises a CTA-wide abort flag and falls through to the common tear-down
+// (bounded delay for TMA copies still in flight, TMEM dealloc), so a wrong descriptor
+// shows up as LNN_E_TIMEOUT on the host instead of a hung GPU.
+#pragma once
+#include <cuda.h>
+#include "lnn_common.cuh"
+
+namespace lnn_tc {
+
+constexpr int kThreadsTc = 192;
+constexpr int kMaxTaps = 64;
+constexpr long long kWaitBudget = 1500000000ll;   // ~0.8 s of SM clocks
+constexpr int kAbortDelay = 400000;               // cycles granted to in-flight TMA copies
+
+enum { MODE_GEMM = 0, MODE_CONV = 1, MODE_DW = 2 };
+
+struct TcParams {
+  int mode, passes, stages, bn;
+  int a_major, b_major;          // 0 = K-major, 1 = MN-major
+  int swz_a, swz_b;              // bytes per smem row of the operand tiles (32/64/128)
+  int ksteps;                    // MMA steps (K = 8) per k-block
+  int a_tile_bytes, b_tile_bytes;// bytes of one (hi or lo) operand tile
+  int a_loads, b_loads;          // TMA boxes per operand tile
+  int a_load_bytes, b_load_bytes;// bytes per box
+  int a_krows, b_krows;          // MN-major: k rows per box (LBO = krows * swz)
+  uint32_t idesc;
+  uint32_t tmem_cols;
+  int num_kb;                    // k-blocks per output tile (GEMM/CONV); patches per split (DW)
+  // GEMM
+  int64_t M, N;                  // logical output extents
+  int64_t ldc, batch_stride_c;
+  // CONV / DW tile geometry
+  int tw, th, tn;                // logical pixels per tile along W, H, N
+  int tiles_b, tiles_a, tiles_n;
+  int AW, AH, NL;                // logical output grid (valid extents)
+  int es;                        // coordinate multiplier of the activation tensor map
+  int ncb, cb;                   // channel blocks per tap, channels per block
+  int ntaps;
+  int rows_valid;                // tn*th*tw
+  int64_t out_sn, out_sa, out_sb, out_sc, out_base;   // output element strides (CONV)
+  int OC;                        // valid output columns (CONV) / rows (DW)
+  int ICv;                       // valid columns (DW)
+  // DW
+  int patches_total, patches_per_split;
+  int dw_tap_dy, dw_tap_dx;      // unused placeholders (taps come from the arrays below)
+  int64_t part_stride_split, part_stride_tap, part_ld;   // partial buffer [split][tap][ocp][icp]
+  int oc_tiles, ic_tiles;
+  // epilogue
+  int accumulate, act;
+  float alpha;
+  const float* bias;
+  float* out;
+  int* status;
+  int tap_dy[kMaxTaps], tap_dx[kMaxTaps], tap_w[kMaxTaps];
+};
+
+}  // namespace lnn_tc
