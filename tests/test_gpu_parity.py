@@ -1,0 +1,153 @@
+"""GPU: litenn_b200 (CUDA kernels through the C ABI) against the reference's golden vectors
+and the CPU oracle on the same seeded inputs.  Bit-exact for element-wise algebra, broadcast
+binary, pooling, reductions (same summation tree), transpose/slice and integer-valued
+contractions; a few ulp for the transcendental functions (the reference leaves them to the
+device math library); the stated contraction tolerance (rel 1e-4 per element or 1e-3 max-abs
+after dividing by sqrt(K)) for real-valued conv/matmul."""
+import numpy as np
+import pytest
+
+import cases
+from conftest import assert_bit_exact, assert_contraction_close, load_golden, ulp_diff
+
+pytestmark = pytest.mark.gpu
+
+TRANSCENDENTAL_ULP = 4   # OpenCL 1.2 allows exp/log <= 3 ulp, sin/cos <= 4 ulp
+
+
+def _cases(*families):
+    return [pytest.param(n, f, p, id=n) for n, f, p in cases.all_cases() if f in families]
+
+
+def _check_ulp(got, want, max_ulp, what, atol=0.0):
+    d = ulp_diff(got, want)
+    bad = (d > max_ulp) & (np.abs(np.asarray(got, np.float64) - np.asarray(want, np.float64)) > atol)
+    assert not bad.any(), f"{what}: max ulp distance {int(d.max())} > {max_ulp}"
+
+
+@pytest.mark.parametrize("name,family,p", _cases("eltwise"))
+def test_eltwise(nn_gpu, name, family, p):
+    ins, outs = load_golden(family)[name]
+    got = cases.run_case(nn_gpu, family, p, ins)
+    if p["op"] in cases.EW_TRANSCENDENTAL:
+        _check_ulp(got["y"], outs["y"], TRANSCENDENTAL_ULP, name + " y", atol=1e-7)
+        # gradients combine the function value with dO and the pre-filled 1.0
+        np.testing.assert_allclose(got["dx"], outs["dx"], rtol=2e-6, atol=2e-6, err_msg=name + " dx")
+    else:
+        assert_bit_exact(got["y"], outs["y"], name + " y")
+        assert_bit_exact(got["dx"], outs["dx"], name + " dx")
+
+
+@pytest.mark.parametrize("name,family,p", _cases("binary"))
+def test_binary(nn_gpu, name, family, p):
+    ins, outs = load_golden(family)[name]
+    got = cases.run_case(nn_gpu, family, p, ins)
+    if p["op"] == "binary_crossentropy":      # contains log()
+        for k in ("y", "da", "db"):
+            np.testing.assert_allclose(got[k], outs[k], rtol=3e-6, atol=3e-6, err_msg=f"{name} {k}")
+    else:
+        for k in ("y", "da", "db"):
+            assert_bit_exact(got[k], outs[k], f"{name} {k}")
+
+
+@pytest.mark.parametrize("name,family,p", _cases("pool", "reduce", "transpose", "slice", "chain"))
+def test_exact_families(nn_gpu, name, family, p):
+    ins, outs = load_golden(family)[name]
+    got = cases.run_case(nn_gpu, family, p, ins)
+    for k in outs:
+        assert_bit_exact(got[k], outs[k], f"{name} {k}")
+
+
+@pytest.mark.parametrize("name,family,p", _cases("matmul"))
+def test_matmul(nn_gpu, name, family, p):
+    ins, outs = load_golden(family)[name]
+    got = cases.run_case(nn_gpu, family, p, ins)
+    a_shape, b_shape = p["a_shape"], p["b_shape"]
+    ks = {"y": a_shape[-1], "da": b_shape[-1], "db": a_shape[-2]}
+    for k in outs:
+        if p["integer"]:
+            assert_bit_exact(got[k], outs[k], f"{name} {k}")
+        else:
+            assert_contraction_close(got[k], outs[k], ks[k], f"{name} {k}")
+
+
+@pytest.mark.parametrize("name,family,p", _cases("conv"))
+def test_conv(nn_gpu, name, family, p):
+    ins, outs = load_golden(family)[name]
+    got = cases.run_case(nn_gpu, family, p, ins)
+    (N, IC, IH, IW), (OC, _, KH, KW) = p["x_shape"], p["w_shape"]
+    OH, OW = outs["y"].shape[2:]
+    ks = {"y": IC * KH * KW, "dx": OC * KH * KW, "dw": N * OH * OW}
+    for k in outs:
+        if p["integer"]:
+            assert_bit_exact(got[k], outs[k], f"{name} {k}")
+        else:
+            assert_contraction_close(got[k], outs[k], ks[k], f"{name} {k}")
+
+
+def test_conv_config1(nn_gpu):
+    """The single-conv configuration: x[8,16,32,32], w[32,16,3,3] He-normal, bias, 'same'."""
+    import oracle as o
+    ins, outs = load_golden("conv_config1")["conv_config1"]
+    got = cases.run_case(nn_gpu, "conv_config1", {}, ins)
+    assert_contraction_close(got["y"], outs["y"], 144, "config 1 vs reference")
+    y64 = o.conv2d_fwd(ins["x"], ins["w"], 1, 1, "same", bias=ins["b"], accum64=True)
+    assert_contraction_close(got["y"], y64, 144, "config 1 vs fp64 oracle")
+    # split-TF32 should be at least as close to the fp64 result as fp32 sequential accumulation
+    err_gpu = np.abs(got["y"].astype(np.float64) - y64).max()
+    err_ref = np.abs(outs["y"].astype(np.float64) - y64).max()
+    assert err_gpu <= 4 * err_ref + 1e-6, (err_gpu, err_ref)
+
+
+def test_fused_conv_bias_lrelu_equals_unfused(nn_gpu):
+    nn = nn_gpu
+    ins, _ = load_golden("conv_config1")["conv_config1"]
+    x, w, b = (nn.Tensor_from_value(ins[k]) for k in ("x", "w", "b"))
+    unfused = nn.leaky_relu(nn.conv2D(x, w) + b.reshape((1, -1, 1, 1)), 0.1).np()
+    fused = nn.conv2D(x, w, bias_t=b, activation="leaky_relu", alpha=0.1).np()
+    assert_bit_exact(fused, unfused, "conv epilogue fusion")
+
+
+def test_softmax_ce(nn_gpu):
+    ins, outs = load_golden("softmax_ce")["softmax_ce"]
+    got = cases.run_case(nn_gpu, "softmax_ce", {}, ins)
+    for k in outs:
+        np.testing.assert_allclose(got[k], outs[k], rtol=1e-5, atol=1e-6, err_msg=k)
+
+
+def test_cnn_training_step(nn_gpu):
+    """Forward, loss, backward and one SGD step of the small CNN against the reference."""
+    ins, outs = load_golden("cnn_step")["cnn_step"]
+    got = cases.run_case(nn_gpu, "cnn_step", {}, ins)
+    np.testing.assert_allclose(got["logits"], outs["logits"], rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(got["loss"], outs["loss"], rtol=1e-5)
+    for k in outs:
+        if k.startswith("grad_"):
+            scale = np.abs(outs[k]).max()
+            np.testing.assert_allclose(got[k], outs[k], rtol=1e-3, atol=1e-4 * scale, err_msg=k)
+        if k.startswith("new_"):
+            np.testing.assert_allclose(got[k], outs[k], rtol=1e-6, atol=1e-7, err_msg=k)
+
+
+def test_output_t_and_accumulate(nn_gpu):
+    """The `output_t=` / `is_add_to_output=` convention (e.g. element_wise_op.py:48-76)."""
+    nn = nn_gpu
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((4, 6)).astype(np.float32)
+    base = rng.standard_normal((24,)).astype(np.float32)
+    xt, out = nn.Tensor_from_value(x), nn.Tensor_from_value(base)
+    nn.op.square_op(xt, output_t=out, is_add_to_output=True)
+    assert_bit_exact(out.np(), base + (x * x).reshape(-1), "square += into other shape")
+    with pytest.raises(ValueError):
+        nn.op.square_op(xt, output_t=nn.Tensor((5,)))
+    a = nn.Tensor_from_value(rng.integers(0, 8, (6, 5)).astype(np.float32))
+    b = nn.Tensor_from_value(rng.integers(0, 8, (5, 7)).astype(np.float32))
+    c0 = rng.integers(0, 8, (6, 7)).astype(np.float32)
+    c = nn.Tensor_from_value(c0)
+    nn.op.matmul_op(a, b, output_t=c, is_add_to_output=True)
+    assert_bit_exact(c.np(), c0 + a.np() @ b.np(), "matmul +=")
+
+
+def test_device_status_clean(nn_gpu):
+    """No bounded device-side wait may have expired during the parity run."""
+    nn_gpu.devices.check_status()
