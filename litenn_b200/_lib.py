@@ -66,6 +66,8 @@ _SIGNATURES = {
     "lnn_event_record": (c_int, [c_int, c_uint64]),
     "lnn_event_elapsed_ms": (c_int, [c_int, c_uint64, c_uint64, POINTER(c_float)]),
     "lnn_event_destroy": (c_int, [c_int, c_uint64]),
+    "lnn_profile_enable": (c_int, [c_int, c_int]),
+    "lnn_profile_read": (c_int, [c_int, c_int, POINTER(c_uint64), POINTER(c_float)]),
     "lnn_eltwise_fwd": (c_int, [c_int, c_int, c_uint64, c_uint64, c_int64, c_float, c_float, c_int, c_int]),
     "lnn_eltwise_bwd": (c_int, [c_int, c_int, c_uint64, c_uint64, c_uint64, c_uint64, c_int64, c_float, c_float, c_int]),
     "lnn_binary_fwd": (c_int, [c_int, c_int, c_uint64, c_uint64, c_uint64, c_int, _I64P, _I64P, _I64P, c_int]),

@@ -23,6 +23,24 @@ struct Device {
   int* status_dev = nullptr;                     // device status word (bounded waits)
   int* status_host = nullptr;                    // pinned mirror
   void* nccl_comm = nullptr;
+  bool profiling = false;
+  struct ProfSpan { int slot; cudaEvent_t start, stop; };
+  std::vector<ProfSpan> prof_spans;
+};
+
+// Brackets the launches made while it is alive with a pair of events (profiling only).
+struct ProfScope {
+  Device* d; int slot; cudaEvent_t start = nullptr;
+  ProfScope(Device* dev, int s) : d(dev), slot(s) {
+    if (d->profiling && cudaEventCreate(&start) == cudaSuccess) cudaEventRecord(start, d->stream);
+  }
+  ~ProfScope() {
+    if (!start) return;
+    cudaEvent_t stop;
+    if (cudaEventCreate(&stop) != cudaSuccess) { cudaEventDestroy(start); return; }
+    cudaEventRecord(stop, d->stream);
+    d->prof_spans.push_back({slot, start, stop});
+  }
 };
 
 Device* get_device(int dev);          // nullptr + error set when not initialised

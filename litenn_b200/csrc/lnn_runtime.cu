@@ -305,6 +305,32 @@ int lnn_event_elapsed_ms(int dev, uint64_t ev_start, uint64_t ev_stop, float* ms
   return LNN_OK;
 }
 
+int lnn_profile_enable(int dev, int on) {
+  LNN_DEV(d, dev);
+  d->profiling = on != 0;
+  return LNN_OK;
+}
+
+int lnn_profile_read(int dev, int slot, uint64_t* launches, float* total_ms) {
+  LNN_DEV(d, dev);
+  LNN_REQUIRE(slot >= 0 && slot < LNN_PROF_SLOTS && launches && total_ms, "bad arguments");
+  LNN_CUDA(cudaStreamSynchronize(d->stream));
+  uint64_t n = 0;
+  float total = 0.0f;
+  std::vector<Device::ProfSpan> keep;
+  for (auto& sp : d->prof_spans) {
+    if (sp.slot != slot) { keep.push_back(sp); continue; }
+    float ms = 0.0f;
+    if (cudaEventElapsedTime(&ms, sp.start, sp.stop) == cudaSuccess) { total += ms; ++n; }
+    cudaEventDestroy(sp.start);
+    cudaEventDestroy(sp.stop);
+  }
+  d->prof_spans.swap(keep);
+  *launches = n;
+  *total_ms = total;
+  return LNN_OK;
+}
+
 int lnn_event_destroy(int dev, uint64_t ev) {
   LNN_DEV(d, dev);
   LNN_CUDA(cudaEventDestroy((cudaEvent_t)(uintptr_t)ev));

@@ -274,10 +274,14 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t la = layout_of_swizzle(p.swz_a), lb = layout_of_swizzle(p.swz_b);
+      // K-major: 8-row swizzle atoms, SBO = 8 rows.  MN-major tf32 only exists as the
+      // "128-byte swizzle with 32-byte atoms" layout: 4 k-rows per atom (SBO = 4 rows), the
+      // 32-element MN blocks LBO apart.
+      const uint32_t la = p.a_major ? 1u : layout_of_swizzle(p.swz_a);
+      const uint32_t lb = p.b_major ? 1u : layout_of_swizzle(p.swz_b);
       const uint32_t a_lbo = p.a_major ? (uint32_t)(p.a_krows * p.swz_a) : 16u;
       const uint32_t b_lbo = p.b_major ? (uint32_t)(p.b_krows * p.swz_b) : 16u;
-      const uint32_t a_sbo = 8u * p.swz_a, b_sbo = 8u * p.swz_b;
+      const uint32_t a_sbo = (p.a_major ? 4u : 8u) * p.swz_a, b_sbo = (p.b_major ? 4u : 8u) * p.swz_b;
       const uint32_t a_step = p.a_major ? 8u * p.swz_a : 32u;
       const uint32_t b_step = p.b_major ? 8u * p.swz_b : 32u;
       bool ok = true;
@@ -563,7 +567,7 @@ int get_encode() {
 // dims/box/estr have `rank` entries, innermost first; strides_bytes has rank-1 entries.
 int encode_map(CUtensorMap* tm, const void* base, int rank, const uint64_t* dims,
                const uint64_t* strides_bytes, const uint32_t* box, const uint32_t* estr,
-               int swz_bytes) {
+               int swz_bytes, bool mn_major = false) {
   int rc = get_encode();
   if (rc) return rc;
   cuuint64_t gd[5], gs[4];
@@ -573,7 +577,9 @@ int encode_map(CUtensorMap* tm, const void* base, int rank, const uint64_t* dims
   for (int i = 0; i < rank; ++i)
     if (bx[i] < 1 || bx[i] > 256)
       return lnn::set_error(LNN_E_UNSUPPORTED, "TMA box extent %u (dim %d) outside 1..256", bx[i], i);
-  const CUtensorMapSwizzle sw = swz_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+  // MN-major tf32 operands use the 128-byte swizzle whose atom is 32 bytes
+  const CUtensorMapSwizzle sw = mn_major         ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                              : swz_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
                               : swz_bytes == 64  ? CU_TENSOR_MAP_SWIZZLE_64B
                                                  : CU_TENSOR_MAP_SWIZZLE_32B;
   CUresult r = g_encode(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, (void*)base, gd, gs,
@@ -637,7 +643,10 @@ int launch_tc(lnn::Device* d, dim3 grid, const CUtensorMap& ah, const CUtensorMa
                                   kSmemLimit - 1024));
     attr_set[MODE] = true;
   }
-  tc_kernel<MODE><<<grid, kThreadsTc, smem, d->stream>>>(ah, al, bh, bl, p);
+  {
+    lnn::ProfScope prof(d, MODE);   // LNN_PROF_TC_GEMM / _CONV / _DW equal the mode numbers
+    tc_kernel<MODE><<<grid, kThreadsTc, smem, d->stream>>>(ah, al, bh, bl, p);
+  }
   LNN_CHECK_LAUNCH(d);
   return LNN_OK;
 }
@@ -654,6 +663,7 @@ int split_matrix(lnn::Device* d, lnn::Scratch& hi, lnn::Scratch& lo, const float
   int rc = hi.get((uint64_t)rows * pitch * 4);
   if (rc) return rc;
   if (want_lo) { rc = lo.get((uint64_t)rows * pitch * 4); if (rc) return rc; }
+  lnn::ProfScope prof(d, LNN_PROF_PREP);
   split_rows_kernel<<<grid_for(d, rows * pitch / 4 + 1), kThreads, 0, d->stream>>>(
       hi.as<float>(), want_lo ? lo.as<float>() : nullptr, src, rows, cols, pitch, want_lo);
   LNN_CHECK_LAUNCH(d);
@@ -696,13 +706,13 @@ int chan_block(int cp) { return (cp % 32 == 0) ? 32 : ((cp % 16 == 0) ? 16 : 8);
 
 // 4-D map over an NHWC activation copy [N][H][W][cp]
 int encode_nhwc(CUtensorMap* tm, const float* base, int n, int h, int w, int cp, int box_c,
-                int box_w, int box_h, int box_n, int estride) {
+                int box_w, int box_h, int box_n, int estride, bool mn_major = false) {
   uint64_t dims[4] = {(uint64_t)cp, (uint64_t)w, (uint64_t)h, (uint64_t)n};
   uint64_t str[3] = {(uint64_t)cp * 4, (uint64_t)w * cp * 4, (uint64_t)h * w * cp * 4};
   uint32_t box[4] = {(uint32_t)box_c, (uint32_t)(box_w * estride), (uint32_t)(box_h * estride),
                      (uint32_t)box_n};
   uint32_t es[4] = {1, (uint32_t)estride, (uint32_t)estride, 1};
-  return encode_map(tm, base, 4, dims, str, box, es, box_c * 4);
+  return encode_map(tm, base, 4, dims, str, box, es, box_c * 4, mn_major);
 }
 
 int nhwc_split(lnn::Device* d, lnn::Scratch& hi, lnn::Scratch& lo, const float* src, int n, int c,
@@ -714,6 +724,7 @@ int nhwc_split(lnn::Device* d, lnn::Scratch& hi, lnn::Scratch& lo, const float* 
   const int64_t hw = (int64_t)h * w;
   const int64_t tiles = (int64_t)n * ((hw + 31) / 32) * ((cp + 31) / 32);
   int64_t grid = std::min<int64_t>(tiles, (int64_t)d->sm_count * 16);
+  lnn::ProfScope prof(d, LNN_PROF_PREP);
   nchw_to_nhwc_split_kernel<<<(unsigned)grid, 256, 0, d->stream>>>(
       hi.as<float>(), want_lo ? lo.as<float>() : nullptr, src, n, c, hw, cp, want_lo);
   LNN_CHECK_LAUNCH(d);
@@ -727,6 +738,7 @@ int weights_split(lnn::Device* d, lnn::Scratch& hi, lnn::Scratch& lo, const floa
   int rc = hi.get(bytes);
   if (rc) return rc;
   if (want_lo) { rc = lo.get(bytes); if (rc) return rc; }
+  lnn::ProfScope prof(d, LNN_PROF_PREP);
   weight_split_kernel<<<grid_for(d, (int64_t)taps * rows * kp), kThreads, 0, d->stream>>>(
       hi.as<float>(), want_lo ? lo.as<float>() : nullptr, w, oc, ic, taps, kp, transpose_io, want_lo);
   LNN_CHECK_LAUNCH(d);
@@ -852,9 +864,9 @@ int lnn_gemm_f32(int dev, uint64_t C, uint64_t A, uint64_t B, uint64_t bias, int
     uint64_t str[2] = {(uint64_t)a_pitch * 4, (uint64_t)a_rows * a_pitch * 4};
     uint32_t box[3] = {32, (uint32_t)(p.a_major ? 32 : 128), 1};
     uint32_t es[3] = {1, 1, 1};
-    rc = encode_map(&mah, ah.p, 3, dims, str, box, es, 128);
+    rc = encode_map(&mah, ah.p, 3, dims, str, box, es, 128, p.a_major != 0);
     if (rc) return rc;
-    rc = encode_map(&mal, want_lo ? al.p : ah.p, 3, dims, str, box, es, 128);
+    rc = encode_map(&mal, want_lo ? al.p : ah.p, 3, dims, str, box, es, 128, p.a_major != 0);
     if (rc) return rc;
   }
   {
@@ -862,9 +874,9 @@ int lnn_gemm_f32(int dev, uint64_t C, uint64_t A, uint64_t B, uint64_t bias, int
     uint64_t str[2] = {(uint64_t)b_pitch * 4, (uint64_t)b_rows * b_pitch * 4};
     uint32_t box[3] = {32, (uint32_t)(p.b_major ? 32 : bn), 1};
     uint32_t es[3] = {1, 1, 1};
-    rc = encode_map(&mbh, bh.p, 3, dims, str, box, es, 128);
+    rc = encode_map(&mbh, bh.p, 3, dims, str, box, es, 128, p.b_major != 0);
     if (rc) return rc;
-    rc = encode_map(&mbl, want_lo ? bl.p : bh.p, 3, dims, str, box, es, 128);
+    rc = encode_map(&mbl, want_lo ? bl.p : bh.p, 3, dims, str, box, es, 128, p.b_major != 0);
     if (rc) return rc;
   }
   dim3 grid((unsigned)((m + 127) / 128), (unsigned)((n + bn - 1) / bn), (unsigned)batch);
@@ -969,10 +981,11 @@ int lnn_conv2d_dw(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY, uin
   rc = nhwc_split(d, yh, yl, (const float*)(uintptr_t)dY, g->n, g->oc, g->oh, g->ow, ocp, want_lo);
   if (rc) return rc;
 
-  const int ea = chan_block(ocp), eb = chan_block(cp);     // elements per smem row
-  const int swa = ea * 4, swb = eb * 4;
-  int bn = std::min(256, (cp + 15) & ~15);
-  if (bn % eb != 0) bn = ((bn + eb - 1) / eb) * eb;
+  // MN-major tf32 tiles are always 32 channels (128 bytes) wide; channels beyond the padded
+  // extent of the NHWC copy are zero-filled by the TMA unit
+  const int ea = 32, eb = 32;
+  const int swa = 128, swb = 128;
+  int bn = std::min(256, (cp + 31) & ~31);
   const int oc_tiles = (g->oc + 127) / 128, ic_tiles = (cp + bn - 1) / bn;
   // pixel patch = one k-block: tw x th output pixels of one image, a multiple of 8 pixels,
   // sized so that two stages of (128 + bn) x pix floats (x2 for hi/lo) fit shared memory
@@ -1043,13 +1056,13 @@ int lnn_conv2d_dw(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY, uin
     }
   p.ntaps = taps;
   CUtensorMap mah, mal, mbh, mbl;
-  rc = encode_nhwc(&mah, yh.as<float>(), g->n, g->oh, g->ow, ocp, ea, tw, th, 1, 1);
+  rc = encode_nhwc(&mah, yh.as<float>(), g->n, g->oh, g->ow, ocp, ea, tw, th, 1, 1, true);
   if (rc) return rc;
-  rc = encode_nhwc(&mal, want_lo ? yl.as<float>() : yh.as<float>(), g->n, g->oh, g->ow, ocp, ea, tw, th, 1, 1);
+  rc = encode_nhwc(&mal, want_lo ? yl.as<float>() : yh.as<float>(), g->n, g->oh, g->ow, ocp, ea, tw, th, 1, 1, true);
   if (rc) return rc;
-  rc = encode_nhwc(&mbh, xh.as<float>(), g->n, g->ih, g->iw, cp, eb, tw, th, 1, s);
+  rc = encode_nhwc(&mbh, xh.as<float>(), g->n, g->ih, g->iw, cp, eb, tw, th, 1, s, true);
   if (rc) return rc;
-  rc = encode_nhwc(&mbl, want_lo ? xl.as<float>() : xh.as<float>(), g->n, g->ih, g->iw, cp, eb, tw, th, 1, s);
+  rc = encode_nhwc(&mbl, want_lo ? xl.as<float>() : xh.as<float>(), g->n, g->ih, g->iw, cp, eb, tw, th, 1, s, true);
   if (rc) return rc;
   dim3 grid((unsigned)splits, (unsigned)(oc_tiles * ic_tiles), (unsigned)taps);
   rc = launch_tc<MODE_DW>(d, grid, mah, mal, mbh, mbl, p);
