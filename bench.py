@@ -1,0 +1,616 @@
+"""Benchmark of the LiteNN op-layer hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--no-ops] [--no-train]
+
+Headline workload (the one quoted at 1/2/4/8 GPUs): inference of the small CNN classifier
+(conv3x3 3->32 +leaky_relu, maxpool2; 32->64; 64->128; 128->256 +leaky_relu, global average;
+Dense 256->1000), random He-init fp32 weights, input [4096,3,128,128] ~U(0,1) sharded over the
+GPUs by batch index (no collective on the data path).  One step = one pass of a rank over its
+whole shard, in micro-batches of 512 images.  `value` times the pass with inputs resident in
+HBM; `e2e` times the same pass through the public API from pinned HOST buffers, host->device
+copy of the images and device->host copy of the logits inside the timed region.  Timing is
+by CUDA events on the stream the kernels run on, max over ranks.
+
+With N = 1 the line also carries `ops`: the single-op configurations (matmul / Dense / conv
+stages in TFLOP/s, the memory-bound sweep in GB/s) and `train`: one training step (softmax-CE,
+SGD lr 1e-3, NCCL gradient all-reduce when N > 1) in images/s.
+
+`--impl reference` times the CPU path on the host cores: the C oracle (oracle/lnn_oracle.c,
+a restatement of the reference's kernels, OpenMP over all host threads) on a bounded sample
+of the same workload.
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+TOTAL_BATCH = 4096
+MICRO_BATCH = 512
+IMG = (3, 128, 128)
+CHANS = [3, 32, 64, 128, 256]
+NCLASS = 1000
+FWD_FLOP_PER_IMAGE = (2 * 32 * 27 * 128 * 128 + 2 * 64 * 288 * 64 * 64 + 2 * 128 * 576 * 32 * 32 +
+                      2 * 256 * 1152 * 16 * 16 + 2 * 256 * 1000)
+
+
+# ---------------------------------------------------------------------------------------------
+# helpers
+# ---------------------------------------------------------------------------------------------
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index, self.proc, self.lines, self.thread = gpu_index, None, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu_index)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def mark(self):
+        return len(self.lines)
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()        # the exact process started above
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, begin=0, end=None):
+        sm, mx, reasons = [], [], set()
+        for line in self.lines[begin:end]:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+class Dist:
+    """Rendezvous, barrier and max-over-ranks for one-process-per-GPU runs (gloo, CPU
+    tensors): plumbing only -- the data path never goes through it."""
+
+    def __init__(self):
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        self.td = None
+        if self.world > 1:
+            import torch.distributed as td
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            td.init_process_group("gloo", rank=self.rank, world_size=self.world)
+            self.td = td
+
+    def barrier(self):
+        if self.td is not None:
+            self.td.barrier()
+
+    def max(self, value):
+        if self.td is None:
+            return float(value)
+        import torch
+        t = torch.tensor([float(value)], dtype=torch.float64)
+        self.td.all_reduce(t, op=self.td.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum(self, value):
+        if self.td is None:
+            return float(value)
+        import torch
+        t = torch.tensor([float(value)], dtype=torch.float64)
+        self.td.all_reduce(t, op=self.td.ReduceOp.SUM)
+        return float(t.item())
+
+    def bcast_bytes(self, data, n):
+        if self.td is None:
+            return data
+        import torch
+        t = torch.zeros(n, dtype=torch.uint8)
+        if self.rank == 0:
+            t = torch.frombuffer(bytearray(data), dtype=torch.uint8).clone()
+        self.td.broadcast(t, src=0)
+        return bytes(t.numpy().tobytes())
+
+    def close(self):
+        if self.td is not None:
+            self.td.destroy_process_group()
+
+
+class DevTimer:
+    """CUDA events on the library's stream."""
+
+    def __init__(self, nn, dev):
+        from litenn_b200 import _lib
+        self.lib, self.dev = _lib.get_lib(), dev.index
+        self.e0, self.e1 = ctypes.c_uint64(), ctypes.c_uint64()
+        self.lib.lnn_event_create(self.dev, ctypes.byref(self.e0))
+        self.lib.lnn_event_create(self.dev, ctypes.byref(self.e1))
+
+    def start(self):
+        self.lib.lnn_event_record(self.dev, self.e0.value)
+
+    def stop_ms(self):
+        self.lib.lnn_event_record(self.dev, self.e1.value)
+        ms = ctypes.c_float()
+        self.lib.lnn_event_elapsed_ms(self.dev, self.e0.value, self.e1.value, ctypes.byref(ms))
+        return float(ms.value)
+
+
+# ---------------------------------------------------------------------------------------------
+# the CNN
+# ---------------------------------------------------------------------------------------------
+def cnn_weights(seed=0):
+    """He-normal convolution kernels and Dense weight, U(-0.1, 0.1) biases (host arrays)."""
+    rng = np.random.default_rng(seed)
+    w = {}
+    for i in range(4):
+        fan = CHANS[i] * 9
+        w[f"k{i}"] = (rng.standard_normal((CHANS[i + 1], CHANS[i], 3, 3)) * np.sqrt(2.0 / fan)).astype(np.float32)
+        w[f"b{i}"] = rng.uniform(-0.1, 0.1, (CHANS[i + 1],)).astype(np.float32)
+    w["dw"] = (rng.standard_normal((256, NCLASS)) * np.sqrt(2.0 / 256)).astype(np.float32)
+    w["db"] = rng.uniform(-0.1, 0.1, (NCLASS,)).astype(np.float32)
+    return w
+
+
+class CNN:
+    """The classifier on the product namespace; conv bias + leaky_relu ride in the conv epilogue."""
+
+    def __init__(self, nn, weights):
+        self.nn = nn
+        self.convs = []
+        for i in range(4):
+            c = nn.Conv2D(CHANS[i], CHANS[i + 1], 3, padding="same",
+                          kernel_initializer=nn.initializer.NumpyArray(weights[f"k{i}"]),
+                          bias_initializer=nn.initializer.NumpyArray(weights[f"b{i}"]))
+            self.convs.append(c)
+        self.dense = nn.Dense(256, NCLASS, weight_initializer=nn.initializer.NumpyArray(weights["dw"]),
+                              bias_initializer=nn.initializer.NumpyArray(weights["db"]))
+
+    def trainables(self):
+        out = []
+        for c in self.convs:
+            out += c.trainables()
+        return out + self.dense.trainables()
+
+    def forward(self, x):
+        nn = self.nn
+        for i, c in enumerate(self.convs):
+            x = nn.conv2D(x, c.kernel, 1, 1, "same", bias_t=c.bias, activation="leaky_relu", alpha=0.1)
+            if i < 3:
+                x = nn.max_pool2D(x, 2, 2, "same")
+        x = nn.flatten(nn.reduce_mean(x, (2, 3)))
+        return self.dense(x)
+
+    def loss(self, logits, onehot):
+        nn = self.nn
+        return nn.categorical_crossentropy(nn.softmax(logits), onehot).mean()
+
+
+def cnn_forward_oracle(o, w, x):
+    """The same network on the CPU oracle (one rounding per reference operator)."""
+    for i in range(4):
+        x = o.conv2d_fwd(x, w[f"k{i}"], 1, 1, "same", bias=w[f"b{i}"], act=1, alpha=0.1)
+        if i < 3:
+            x = o.pool2d_fwd("max", x, 2, 2, "same")
+    x = o.reduce("mean", x, (2, 3))
+    return o.gemm(x, w["dw"], bias=w["db"])
+
+
+# ---------------------------------------------------------------------------------------------
+# reference arm: the CPU path
+# ---------------------------------------------------------------------------------------------
+def cpu_cnn_images_per_s(target_seconds, seed=1):
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle as o
+    o.build()
+    cores = len(os.sched_getaffinity(0))
+    w = cnn_weights()
+    rng = np.random.default_rng(seed)
+    n = 2
+    x = rng.uniform(0, 1, (n,) + IMG).astype(np.float32)
+    t0 = time.perf_counter()
+    cnn_forward_oracle(o, w, x)
+    per_img = (time.perf_counter() - t0) / n
+    n = int(max(2, min(256, target_seconds / max(per_img, 1e-6))))
+    x = rng.uniform(0, 1, (n,) + IMG).astype(np.float32)
+    t0 = time.perf_counter()
+    cnn_forward_oracle(o, w, x)
+    dt = time.perf_counter() - t0
+    return n / dt, cores, f"{n} of {TOTAL_BATCH} images, forward pass, C oracle with OpenMP on {cores} threads", dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    vals, sample, cores, t_total = [], "", 1, 0.0
+    per_step = max(2.0, min(20.0, 90.0 / max(1, args.steps + args.warmup)))
+    for i in range(args.warmup + args.steps):
+        v, cores, sample, dt = cpu_cnn_images_per_s(per_step)
+        if i >= args.warmup:
+            vals.append(v)
+            t_total += dt
+    value = float(np.mean(vals))
+    line = {"impl": "reference", "metric": "cnn_inference_images_per_s", "value": value, "unit": "images/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * t_total / max(1, args.steps),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(args.gpus),
+            "cpu_baseline": {"value": value, "unit": "images/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus):
+    return {"workload": "small CNN classifier inference, fp32, input [4096,3,128,128] ~U(0,1), batch sharded over the GPUs",
+            "global_batch": TOTAL_BATCH, "micro_batch": MICRO_BATCH, "parallelism": f"dp{n_gpus}",
+            "tf32_passes": int(os.environ.get("LNN_TF32_PASSES", "3")),
+            "l2": "every micro-batch streams > 2 GB of activations through HBM, far beyond the 126 MB L2; no explicit flush"}
+
+
+# ---------------------------------------------------------------------------------------------
+# single-op configurations (N = 1)
+# ---------------------------------------------------------------------------------------------
+def _time_calls(timer, nn, fn, warmup, iters):
+    for _ in range(warmup):
+        fn()
+    nn.devices.wait()
+    timer.start()
+    for _ in range(iters):
+        fn()
+    ms = timer.stop_ms()
+    return ms / iters
+
+
+def bench_ops(nn, dev, peaks, quick):
+    from litenn_b200 import _lib
+    lib = _lib.get_lib()
+    timer = DevTimer(nn, dev)
+    rng = np.random.default_rng(0)
+    passes = _lib.tf32_passes()
+    out = {}
+    iters = 3 if quick else 10
+    tf32_peak = peaks["bf16_tflops"] / 2.0
+
+    def T(a):
+        return nn.Tensor_from_value(a)
+
+    def rec(name, ms, flop=None, nbytes=None, note=None):
+        e = {"ms": round(ms, 4)}
+        if flop is not None:
+            e["tflops"] = round(flop / ms / 1e9, 2)
+            e["frac_of_tf32_peak"] = round(e["tflops"] / tf32_peak, 4)
+            e["tensor_pipe_frac"] = round(passes * e["tflops"] / tf32_peak, 4)
+        if nbytes is not None:
+            e["gbs"] = round(nbytes / ms / 1e6, 1)
+            e["frac_of_hbm"] = round(e["gbs"] / peaks["hbm_gbs"], 4)
+        if note:
+            e["note"] = note
+        out[name] = e
+
+    # ---- matmul 4096^3 forward, dA, dB and Dense [8192,1024]x[1024,4096]+b -------------------
+    n = 4096
+    a, b = T(rng.standard_normal((n, n)).astype(np.float32) / 64), T(rng.standard_normal((n, n)).astype(np.float32) / 64)
+    do = T(np.random.default_rng(1).standard_normal((n, n)).astype(np.float32))
+    c = nn.Tensor((n, n))
+    flop = 2.0 * n ** 3
+
+    def gemm(o_t, a_t, b_t, bias, m, nn_, k, ta, tb, acc):
+        lib.lnn_gemm_f32(dev.index, o_t._ptr(0), a_t._ptr(0), b_t._ptr(0), bias, 1, m, nn_, k, ta, tb, acc, passes)
+
+    rec("matmul_4096_fwd", _time_calls(timer, nn, lambda: gemm(c, a, b, 0, n, n, n, 0, 0, 0), 3, iters), flop)
+    rec("matmul_4096_dA", _time_calls(timer, nn, lambda: gemm(c, do, b, 0, n, n, n, 0, 1, 1), 3, iters), flop)
+    rec("matmul_4096_dB", _time_calls(timer, nn, lambda: gemm(c, a, do, 0, n, n, n, 1, 0, 1), 3, iters), flop)
+    del a, b, do, c
+    x = T(rng.standard_normal((8192, 1024)).astype(np.float32))
+    w = T(rng.standard_normal((1024, 4096)).astype(np.float32) / 32)
+    bias = T(rng.uniform(-0.1, 0.1, (4096,)).astype(np.float32))
+    y = nn.Tensor((8192, 4096))
+    rec("dense_8192x1024x4096_fwd", _time_calls(timer, nn, lambda: gemm(y, x, w, bias._ptr(0), 8192, 4096, 1024, 0, 0, 0), 3, iters),
+        2.0 * 8192 * 1024 * 4096)
+    del x, w, bias, y
+
+    # ---- conv stages ----------------------------------------------------------------------------
+    convs = [("conv3a_256x64x56x56_k3s1", (256, 64, 56, 56), (64, 64, 3, 3), 1, 1),
+             ("conv3b_256x128x56x56_k3s2", (256, 128, 56, 56), (256, 128, 3, 3), 2, 1),
+             ("conv3c_256x256x28x28_k1", (256, 256, 28, 28), (1024, 256, 1, 1), 1, 0)]
+    for name, xs, ws, stride, pad in convs:
+        fan = ws[1] * ws[2] * ws[3]
+        xt = T(rng.standard_normal(xs).astype(np.float32))
+        wt = T((rng.standard_normal(ws) * np.sqrt(2.0 / fan)).astype(np.float32))
+        g, oshape = nn.ops._conv_geom(xt.shape, wt.shape, stride, 1, pad)
+        yt = nn.Tensor(oshape)
+        dyt = T(np.random.default_rng(2).standard_normal(oshape.shape).astype(np.float32))
+        dxt, dwt = nn.Tensor(xs), nn.Tensor(ws)
+        flop = 2.0 * oshape.size * fan
+        rec(name + "_fwd", _time_calls(timer, nn, lambda: lib.lnn_conv2d_fwd(dev.index, ctypes.byref(g), yt._ptr(0), xt._ptr(0), wt._ptr(0), 0, 0, 0.0, 0, passes), 2, iters), flop)
+        rec(name + "_dX", _time_calls(timer, nn, lambda: lib.lnn_conv2d_dx(dev.index, ctypes.byref(g), dxt._ptr(0), dyt._ptr(0), wt._ptr(0), passes), 2, iters), flop)
+        rec(name + "_dW", _time_calls(timer, nn, lambda: lib.lnn_conv2d_dw(dev.index, ctypes.byref(g), dwt._ptr(0), dyt._ptr(0), xt._ptr(0), passes), 2, iters), flop)
+        del xt, wt, yt, dyt, dxt, dwt
+
+    # ---- memory-bound sweep -----------------------------------------------------------------------
+    xp = T(rng.uniform(-1, 1, (256, 128, 112, 112)).astype(np.float32))
+    pool_bytes = (256 * 128 * 112 * 112 + 256 * 128 * 56 * 56) * 4
+    rec("max_pool2D_256x128x112x112", _time_calls(timer, nn, lambda: nn.max_pool2D(xp), 3, iters), nbytes=pool_bytes)
+    rec("avg_pool2D_256x128x112x112", _time_calls(timer, nn, lambda: nn.avg_pool2D(xp), 3, iters), nbytes=pool_bytes)
+    del xp
+    xr = T(rng.uniform(-1, 1, (256, 512, 1024)).astype(np.float32))
+    rb = 256 * 512 * 1024 * 4
+    for opname, fn in (("sum", nn.reduce_sum), ("mean", nn.reduce_mean), ("max", nn.reduce_max)):
+        rec(f"reduce_{opname}_axis1", _time_calls(timer, nn, lambda: fn(xr, (1,)), 3, iters), nbytes=rb + 256 * 1024 * 4)
+        rec(f"reduce_{opname}_all", _time_calls(timer, nn, lambda: fn(xr), 3, iters), nbytes=rb)
+    xr4 = xr.reshape((256, 512, 32, 32))
+    for opname, fn in (("sum", nn.reduce_sum), ("mean", nn.reduce_mean), ("max", nn.reduce_max)):
+        rec(f"reduce_{opname}_axes23_view", _time_calls(timer, nn, lambda: fn(xr4, (2, 3)), 3, iters), nbytes=rb + 256 * 512 * 4,
+            note="axes (2,3) of the [256,512,32,32] view: (2,3) is invalid on the rank-3 tensor in the reference")
+    del xr, xr4
+    xc = T(rng.standard_normal((256, 256, 56, 56)).astype(np.float32))
+    gc, bc = T(rng.uniform(0.5, 1.5, (1, 256, 1, 1)).astype(np.float32)), T(rng.uniform(-0.5, 0.5, (1, 256, 1, 1)).astype(np.float32))
+    yc = nn.Tensor(xc.shape)
+    cb = 2 * 256 * 256 * 56 * 56 * 4
+    rec("chain_lrelu_xg_b_fused", _time_calls(timer, nn, lambda: nn.scale_bias_leaky_relu(xc, gc, bc, 0.1, output_t=yc), 3, iters), nbytes=cb)
+    rec("chain_lrelu_xg_b_3ops", _time_calls(timer, nn, lambda: nn.leaky_relu(xc * gc + bc, 0.1), 3, iters), nbytes=cb,
+        note="the reference's three kernels; GB/s counts algorithmic bytes (x in, y out) only")
+    del xc, gc, bc, yc
+    nn.devices.check_status()
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# main arm
+# ---------------------------------------------------------------------------------------------
+def run_ours(args):
+    dist = Dist()
+    world, rank = dist.world, dist.rank
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    import litenn_b200 as nn
+    from litenn_b200 import _lib, parallel
+    devs = nn.devices.get_all()
+    if not devs:
+        raise SystemExit("no CUDA device: this benchmark has no CPU fallback")
+    dev = devs[dist.local_rank % len(devs)]
+    nn.devices.set_current(dev)
+    lib = _lib.get_lib()
+    peaks = load_peaks()
+    passes = _lib.tf32_passes()
+
+    local_batch = TOTAL_BATCH // world
+    mb = min(MICRO_BATCH, local_batch)
+    n_mb = local_batch // mb
+    begin, end = parallel.shard_bounds(TOTAL_BATCH, world, rank)
+    weights = cnn_weights()
+    model = CNN(nn, weights)
+
+    # synthetic input shard in PINNED host memory + resident device copies
+    img_elems = int(np.prod(IMG))
+    host_ptr = ctypes.c_void_p()
+    lib.lnn_host_alloc(local_batch * img_elems * 4, ctypes.byref(host_ptr))
+    host_x = np.ctypeslib.as_array(ctypes.cast(host_ptr, ctypes.POINTER(ctypes.c_float)), shape=(local_batch,) + IMG)
+    rng = np.random.default_rng(1000 + rank)
+    for i in range(0, local_batch, 256):
+        host_x[i:i + 256] = rng.uniform(0, 1, (min(256, local_batch - i),) + IMG).astype(np.float32)
+    host_out_ptr = ctypes.c_void_p()
+    lib.lnn_host_alloc(local_batch * NCLASS * 4, ctypes.byref(host_out_ptr))
+    resident = []
+    for j in range(n_mb):
+        t = nn.Tensor((mb,) + IMG)
+        lib.lnn_h2d(dev.index, t._ptr(0), host_ptr.value + j * mb * img_elems * 4, mb * img_elems * 4)
+        resident.append(t)
+    stage = nn.Tensor((mb,) + IMG)
+
+    def step_resident():
+        last = None
+        for t in resident:
+            last = model.forward(t)
+        return last
+
+    def step_e2e():
+        for j in range(n_mb):
+            lib.lnn_h2d_async(dev.index, stage._ptr(0), host_ptr.value + j * mb * img_elems * 4, mb * img_elems * 4)
+            logits = model.forward(stage)
+            lib.lnn_d2h_async(dev.index, host_out_ptr.value + j * mb * NCLASS * 4, logits._ptr(0), mb * NCLASS * 4)
+        lib.lnn_sync(dev.index)
+
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+    timer = DevTimer(nn, dev)
+
+    # ---- value: inputs resident in HBM --------------------------------------------------------
+    for _ in range(args.warmup):
+        step_resident()
+    nn.devices.wait()
+    dist.barrier()
+    launches0 = dev.launch_count()
+    m0 = sampler.mark()
+    timer.start()
+    for _ in range(args.steps):
+        step_resident()
+    ms = timer.stop_ms()
+    nn.devices.wait()
+    dist.barrier()
+    m1 = sampler.mark()
+    launches = dev.launch_count() - launches0
+    ms_max = dist.max(ms)
+    value = TOTAL_BATCH * args.steps / (ms_max / 1000.0)
+
+    # ---- e2e: host buffers in, logits out -----------------------------------------------------
+    for _ in range(max(1, args.warmup // 2)):
+        step_e2e()
+    dist.barrier()
+    timer.start()
+    for _ in range(args.steps):
+        step_e2e()
+    ms_e = timer.stop_ms()
+    dist.barrier()
+    ms_e_max = dist.max(ms_e)
+    e2e_value = TOTAL_BATCH * args.steps / (ms_e_max / 1000.0)
+
+    # ---- roofline of the dominant kernel: the implicit-GEMM convolution tile kernel -------------
+    lib.lnn_profile_enable(dev.index, 1)
+    prof_steps = min(args.steps, 3)
+    for _ in range(prof_steps):
+        step_resident()
+    nl, tms = ctypes.c_uint64(), ctypes.c_float()
+    lib.lnn_profile_read(dev.index, 1, ctypes.byref(nl), ctypes.byref(tms))
+    npre, tpre = ctypes.c_uint64(), ctypes.c_float()
+    lib.lnn_profile_read(dev.index, 3, ctypes.byref(npre), ctypes.byref(tpre))
+    lib.lnn_profile_enable(dev.index, 0)
+    conv_flop = (FWD_FLOP_PER_IMAGE - 2 * 256 * 1000) * local_batch * prof_steps       # the four convolutions
+    conv_tflops = conv_flop / (tms.value / 1000.0) / 1e12 if tms.value > 0 else 0.0
+    tf32_peak = peaks["bf16_tflops_sustained"] / 2.0
+    roofline = {"bound": "tensor", "kernel": "tc_kernel<MODE_CONV> (implicit-GEMM conv2D, tcgen05 kind::tf32)",
+                "achieved": round(conv_tflops, 2), "peak": round(tf32_peak, 1), "unit": "TFLOP/s",
+                "frac": round(conv_tflops / tf32_peak, 4), "traffic": None,
+                "issued_frac": round(passes * conv_tflops / tf32_peak, 4),
+                "launches": int(nl.value), "avg_launch_ms": round(tms.value / max(1, nl.value), 4),
+                "prepass_ms_per_step": round(tpre.value / prof_steps, 3),
+                "peak_source": f"dense TF32 taken as half of the {peaks['source']} sustained bf16 cuBLAS rate; "
+                               f"achieved counts algorithmic 2*M*N*K flops, issued_frac counts the {passes} TF32 MMAs per product"}
+
+    # ---- training step (softmax-CE, SGD lr 1e-3, NCCL gradient all-reduce) ---------------------
+    train = None
+    if not args.no_train:
+        if world > 1:
+            uid = parallel.new_unique_id() if rank == 0 else None
+            uid = dist.bcast_bytes(uid, 128)
+            parallel.init_process_rank(world, rank, uid)
+        opt = nn.optimizer.SGD(model.trainables(), lr=1e-3)
+        lab_rng = np.random.default_rng(77 + rank)
+        onehots = []
+        for j in range(n_mb):
+            oh = np.zeros((mb, NCLASS), np.float32)
+            oh[np.arange(mb), lab_rng.integers(0, NCLASS, mb)] = 1
+            onehots.append(nn.Tensor_from_value(oh))
+        scale = 1.0 / n_mb
+
+        def train_step():
+            last = None
+            for t, oh in zip(resident, onehots):
+                loss = model.loss(model.forward(t), oh)
+                if n_mb > 1:
+                    loss = loss * scale
+                loss.backward()
+                last = loss
+            opt.step(multi_gpu_step=True)
+            opt.zero_grad()
+            return last
+
+        tsteps = max(1, min(args.steps, 3))
+        for _ in range(2):
+            last = train_step()
+        nn.devices.wait()
+        dist.barrier()
+        timer.start()
+        for _ in range(tsteps):
+            last = train_step()
+        ms_t = timer.stop_ms()
+        loss_val = float(last.np()[0])
+        dist.barrier()
+        ms_t_max = dist.max(ms_t)
+        train = {"value": round(TOTAL_BATCH * tsteps / (ms_t_max / 1000.0), 1), "unit": "images/s", "steps": tsteps,
+                 "ms_per_step": round(ms_t_max / tsteps, 2), "last_micro_batch_loss": loss_val,
+                 "what": "forward + softmax-CE + backward + SGD(lr 1e-3)" + (" + NCCL all-reduce of 645,416 gradients" if world > 1 else "")}
+        del onehots
+
+    clocks = sampler.summary(m0, m1)
+    sampler.stop()
+    nn.devices.check_status()
+
+    ops = None
+    if rank == 0 and world == 1 and not args.no_ops:
+        del resident[:]
+        ops = bench_ops(nn, dev, peaks, args.quick)
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        v, cores, sample, _ = cpu_cnn_images_per_s(15.0)
+        cpu = {"value": round(v, 3), "unit": "images/s", "cores": cores, "kind": "port", "sample": sample}
+
+    if rank == 0:
+        line = {"metric": "cnn_inference_images_per_s", "value": round(value, 1), "unit": "images/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_max / args.steps, 3),
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": workload_config(world),
+                "e2e": {"value": round(e2e_value, 1), "unit": "images/s", "h2d_bytes_per_step": local_batch * img_elems * 4,
+                        "d2h_bytes_per_step": local_batch * NCLASS * 4, "ms_per_step": round(ms_e_max / args.steps, 3)},
+                "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline,
+                "model_tflops": round(value * FWD_FLOP_PER_IMAGE / 1e12, 2)}
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        if train is not None:
+            line["train"] = train
+        if ops is not None:
+            line["ops"] = ops
+        print(json.dumps(line), flush=True)
+    dist.close()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-ops", action="store_true", help="skip the single-op configurations")
+    ap.add_argument("--no-train", action="store_true", help="skip the training step")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--quick", action="store_true", help="fewer iterations in the single-op configurations")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+        return
+    if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
+        # plain invocation with N > 1: start one rank per GPU
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", "29533", os.path.abspath(__file__)] + sys.argv[1:]
+        raise SystemExit(subprocess.call(cmd))
+    run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
