@@ -145,6 +145,16 @@ enum { LNN_RED_SUM = 0, LNN_RED_MEAN = 1, LNN_RED_MAX = 2, LNN_RED_MIN = 3 };
  * ref: op/reduce.py:166-205,279-301, info/InfoReduction.py:25-50 */
 int lnn_reduce(int dev, int op, uint64_t O, uint64_t I, int64_t outer, int64_t r0,
                int64_t mid, int64_t r1, int64_t inner, int accumulate);
+/* No counterpart in the reference.  lnn_reduce for callers that must not allocate device
+ * memory (a serving loop that cannot afford a cudaMalloc stall, a host application that owns
+ * the whole GPU heap, a process that is already out of memory): same arguments, bit-identical
+ * result, but the partial sums of split rows live in a fixed 1 MiB device array inside the
+ * library (one copy per device, kept until exit).  Refuses with LNN_E_UNSUPPORTED when the
+ * partials need more than 2^18 floats.  The first call on a device looks up the array's
+ * address and should come before any stream capture; calls share the array, so calls made
+ * to overlap on one GPU race. */
+int lnn_reduce_noalloc(int dev, int op, uint64_t O, uint64_t I, int64_t outer, int64_t r0,
+                       int64_t mid, int64_t r1, int64_t inner, int accumulate);
 /* dI += broadcast(dO) [/COLS] (sum, mean) or dO at the first column equal to O (max, min).
  * ref: op/reduce.py:207-216,250-276 (ties: lowest column index wins) */
 int lnn_reduce_bwd(int dev, int op, uint64_t dI, uint64_t I, uint64_t dO, uint64_t O,

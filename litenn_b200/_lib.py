@@ -76,6 +76,7 @@ _SIGNATURES = {
     "lnn_pool2d_fwd": (c_int, [c_int, c_int, c_uint64, c_uint64, c_int64, c_int64] + [c_int] * 8),
     "lnn_pool2d_bwd": (c_int, [c_int, c_int, c_uint64, c_uint64, c_uint64, c_uint64, c_int64, c_int64] + [c_int] * 8),
     "lnn_reduce": (c_int, [c_int, c_int, c_uint64, c_uint64] + [c_int64] * 5 + [c_int]),
+    "lnn_reduce_noalloc": (c_int, [c_int, c_int, c_uint64, c_uint64] + [c_int64] * 5 + [c_int]),
     "lnn_reduce_bwd": (c_int, [c_int, c_int, c_uint64, c_uint64, c_uint64, c_uint64] + [c_int64] * 5),
     "lnn_transpose": (c_int, [c_int, c_uint64, c_uint64, c_int, _I64P, POINTER(c_int), c_int]),
     "lnn_slice_fwd": (c_int, [c_int, c_uint64, c_uint64, c_int, _I64P, _I64P, _I64P, _I64P, c_int]),

@@ -276,6 +276,90 @@ int reduce_impl(lnn::Device* d, float* O, const float* I, int64_t outer, int64_t
   return reduce_impl<OP>(d, O, scratch.as<float>(), outer, parts, 1, 1, mid * inner, acc, mean_div);
 }
 
+
+// ---- reduction without any allocation ---------------------------------------------------------
+// Partial results of split rows live in this fixed device array instead of pooled memory.
+// Every device that loads the library holds its own 1 MiB copy until the process exits.
+constexpr int64_t kStaticScratchFloats = 1 << 18;
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+
+// Device address of g_static_scratch per device slot, resolved once per device.  In host
+// code the symbol itself is only a stand-in; kernels must be given this address.
+float* g_static_scratch_ptr[LNN_MAX_DEVICES] = {nullptr};
+
+int static_scratch_for(lnn::Device* d, int dev, float** out) {
+  if (!g_static_scratch_ptr[dev]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);   // d's device is current
+    if (e != cudaSuccess || !p)
+      return lnn::set_error(LNN_E_CUDA, "cudaGetSymbolAddress(static scratch) failed on device %d: %s",
+                            d->ordinal, cudaGetErrorString(e));
+    g_static_scratch_ptr[dev] = (float*)p;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return LNN_OK;
+}
+
+// Same plan as reduce_impl, with the partial buffers carved from [scratch, scratch + cap).
+template <int OP>
+int reduce_impl_static(lnn::Device* d, float* O, const float* I, int64_t outer, int64_t r0, int64_t mid,
+                       int64_t r1, int64_t inner, int acc, float mean_div, float* scratch, int64_t cap) {
+  RedGeom g;
+  int rc = make_geom(g, outer, r0, mid, r1, inner);
+  if (rc) return rc;
+  Levels L;
+  make_levels(L, r0 * r1);
+  const int64_t cols = r0 * r1;
+  const int64_t kTargetThreads = 1 << 19;
+  if (inner == 1) {
+    int s_block = 0;
+    while (L.n[s_block] > kThreads) ++s_block;
+    const bool split = (g.rows * kThreads < kTargetThreads / 2) && cols > 65536;
+    if (!split) {
+      int tpr = 1;
+      while (tpr < L.n[s_block]) tpr <<= 1;
+      const int rows_per_block = kThreads / tpr;
+      const int64_t blocks = lnn_ceil_div(g.rows, rows_per_block);
+      LNN_REQUIRE(blocks < (1ll << 31), "too many rows");
+      reduce_rowcoop_kernel<OP><<<(unsigned)blocks, kThreads, 0, d->stream>>>(O, I, g, L, s_block, tpr, acc, mean_div);
+      LNN_CHECK_LAUNCH(d);
+      return LNN_OK;
+    }
+    int s = 6;
+    while (s < L.S && g.rows * L.n[s] > kTargetThreads) ++s;
+    const int64_t parts = L.n[s];
+    const int64_t need = (g.rows * parts + 63) & ~63ll;
+    if (need > cap)
+      return lnn::set_error(LNN_E_UNSUPPORTED,
+                            "reduction needs %lld floats of scratch but the static scratch holds %lld "
+                            "(1 MiB in total): use lnn_reduce", (long long)need, (long long)cap);
+    reduce_parts_kernel<OP><<<grid_for(d, g.rows * parts), kThreads, 0, d->stream>>>(
+        nullptr, scratch, I, g, L, s, 1, 0, 0.0f);
+    LNN_CHECK_LAUNCH(d);
+    return reduce_impl_static<OP>(d, O, scratch, outer, parts, mid, 1, 1, acc, mean_div, scratch + need, cap - need);
+  }
+  int s = L.S;
+  if (g.rows < 65536 && cols > 256) {
+    s = 4;
+    while (s < L.S && g.rows * L.n[s] > kTargetThreads) ++s;
+  }
+  const int64_t parts = L.n[s];
+  if (parts == 1) {
+    reduce_parts_kernel<OP><<<grid_for(d, g.rows), kThreads, 0, d->stream>>>(O, nullptr, I, g, L, L.S, 0, acc, mean_div);
+    LNN_CHECK_LAUNCH(d);
+    return LNN_OK;
+  }
+  const int64_t need = (g.rows * parts + 63) & ~63ll;
+  if (need > cap)
+    return lnn::set_error(LNN_E_UNSUPPORTED,
+                          "reduction needs %lld floats of scratch but the static scratch holds %lld "
+                          "(1 MiB in total): use lnn_reduce", (long long)need, (long long)cap);
+  reduce_parts_kernel<OP><<<grid_for(d, g.rows * parts), kThreads, 0, d->stream>>>(
+      nullptr, scratch, I, g, L, s, 0, 0, 0.0f);
+  LNN_CHECK_LAUNCH(d);
+  return reduce_impl_static<OP>(d, O, scratch, outer, parts, 1, 1, mid * inner, acc, mean_div, scratch + need, cap - need);
+}
+
 }  // namespace
 
 extern "C" {
@@ -319,6 +403,42 @@ int lnn_reduce_bwd(int dev, int op, uint64_t dI, uint64_t I, uint64_t dO, uint64
   }
   LNN_CHECK_LAUNCH(d);
   return LNN_OK;
+}
+
+// Reduction for callers that must not allocate device memory: a host thread inside a
+// latency-critical serving loop, a library embedded in an application that has handed the
+// whole GPU heap to its own allocator, or code running after memory has been exhausted --
+// cudaMalloc there either stalls the device or fails.  Same arguments and bit-identical
+// results as lnn_reduce; the partial sums of rows that are split across thread blocks are
+// kept in a fixed 1 MiB device array that belongs to the library (one copy per device,
+// held until the process exits) instead of pooled memory.
+//  * Reductions whose partials do not fit (more than 2^18 floats) are refused with
+//    LNN_E_UNSUPPORTED; nothing is launched in that case.
+//  * The first call on a device resolves the array's device address (one
+//    cudaGetSymbolAddress, no allocation); make that first call before any stream capture.
+//  * All calls share the one array and it keeps whatever the previous call left; every
+//    partial a launch reads has been written by the launch before it, so nothing needs
+//    clearing.  Calls follow each other on the device's single stream; two calls made to
+//    overlap on the GPU (by driving the same device from two threads) would race on it.
+int lnn_reduce_noalloc(int dev, int op, uint64_t O, uint64_t I, int64_t outer, int64_t r0, int64_t mid,
+                       int64_t r1, int64_t inner, int accumulate) {
+  LNN_DEV(d, dev);
+  LNN_REQUIRE(O && I, "null buffer");
+  LNN_REQUIRE(outer >= 1 && r0 >= 1 && mid >= 1 && r1 >= 1 && inner >= 1, "bad reduce extents");
+  float* scratch = nullptr;
+  int rc = static_scratch_for(d, dev, &scratch);
+  if (rc) return rc;
+  float* o = (float*)(uintptr_t)O;
+  const float* i = (const float*)(uintptr_t)I;
+  const float cols_f = (float)(r0 * r1);
+  const int64_t cap = kStaticScratchFloats;
+  switch (op) {
+    case LNN_RED_SUM: return reduce_impl_static<LNN_RED_SUM>(d, o, i, outer, r0, mid, r1, inner, accumulate, 0.0f, scratch, cap);
+    case LNN_RED_MEAN: return reduce_impl_static<LNN_RED_SUM>(d, o, i, outer, r0, mid, r1, inner, accumulate, cols_f, scratch, cap);
+    case LNN_RED_MAX: return reduce_impl_static<LNN_RED_MAX>(d, o, i, outer, r0, mid, r1, inner, accumulate, 0.0f, scratch, cap);
+    case LNN_RED_MIN: return reduce_impl_static<LNN_RED_MIN>(d, o, i, outer, r0, mid, r1, inner, accumulate, 0.0f, scratch, cap);
+  }
+  return lnn::set_error(LNN_E_INVALID, "unknown reduce op %d", op);
 }
 
 }  // extern "C"
