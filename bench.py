@@ -67,7 +67,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.gpu_index)],
+                                          "-lms", "50", "-i", str(self.gpu_index)],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -164,6 +164,7 @@ class DevTimer:
 
     def __init__(self, nn, dev):
         from litenn_b200 import _lib
+        dev._ensure()
         self.lib, self.dev = _lib.get_lib(), dev.index
         self.e0, self.e1 = ctypes.c_uint64(), ctypes.c_uint64()
         self.lib.lnn_event_create(self.dev, ctypes.byref(self.e0))
@@ -200,6 +201,7 @@ class CNN:
 
     def __init__(self, nn, weights):
         self.nn = nn
+        self.training = False      # inference uses the fused conv+bias+lrelu+maxpool entry
         self.convs = []
         for i in range(4):
             c = nn.Conv2D(CHANS[i], CHANS[i + 1], 3, padding="same",
@@ -218,6 +220,9 @@ class CNN:
     def forward(self, x):
         nn = self.nn
         for i, c in enumerate(self.convs):
+            if i < 3 and not self.training:
+                x = nn.conv2D_pool(x, c.kernel, 1, 1, "same", bias_t=c.bias, activation="leaky_relu", alpha=0.1)
+                continue
             x = nn.conv2D(x, c.kernel, 1, 1, "same", bias_t=c.bias, activation="leaky_relu", alpha=0.1)
             if i < 3:
                 x = nn.max_pool2D(x, 2, 2, "same")
@@ -304,20 +309,135 @@ def _time_calls(timer, nn, fn, warmup, iters):
     return ms / iters
 
 
-def bench_ops(nn, dev, peaks, quick):
-    from litenn_b200 import _lib
-    lib = _lib.get_lib()
-    timer = DevTimer(nn, dev)
+def op_cases(nn, dev, lib, passes):
+    """(name, setup) pairs of the single-op configurations; setup() allocates the operands and
+    returns (callable, flop or None, bytes or None, note or None)."""
     rng = np.random.default_rng(0)
-    passes = _lib.tf32_passes()
-    out = {}
-    iters = 3 if quick else 10
-    tf32_peak = peaks["bf16_tflops"] / 2.0
 
     def T(a):
         return nn.Tensor_from_value(a)
 
-    def rec(name, ms, flop=None, nbytes=None, note=None):
+    def gemm(o_t, a_t, b_t, bias, m, n_, k, ta, tb, acc):
+        lib.lnn_gemm_f32(dev.index, o_t._ptr(0), a_t._ptr(0), b_t._ptr(0), bias, 1, m, n_, k, ta, tb, acc, passes)
+
+    cases = []
+    n = 4096
+
+    def mm(kind):
+        def setup():
+            a = T(rng.standard_normal((n, n)).astype(np.float32) / 64)
+            b = T(rng.standard_normal((n, n)).astype(np.float32) / 64)
+            do = T(np.random.default_rng(1).standard_normal((n, n)).astype(np.float32))
+            c = nn.Tensor((n, n))
+            fn = {"fwd": lambda: gemm(c, a, b, 0, n, n, n, 0, 0, 0),
+                  "dA": lambda: gemm(c, do, b, 0, n, n, n, 0, 1, 1),
+                  "dB": lambda: gemm(c, a, do, 0, n, n, n, 1, 0, 1)}[kind]
+            return fn, 2.0 * n ** 3, None, None
+        return setup
+
+    for kind in ("fwd", "dA", "dB"):
+        cases.append((f"matmul_4096_{kind}", mm(kind)))
+
+    def dense_setup():
+        x = T(rng.standard_normal((8192, 1024)).astype(np.float32))
+        w = T(rng.standard_normal((1024, 4096)).astype(np.float32) / 32)
+        bias = T(rng.uniform(-0.1, 0.1, (4096,)).astype(np.float32))
+        y = nn.Tensor((8192, 4096))
+        return (lambda: gemm(y, x, w, bias._ptr(0), 8192, 4096, 1024, 0, 0, 0)), 2.0 * 8192 * 1024 * 4096, None, None
+
+    cases.append(("dense_8192x1024x4096_fwd", dense_setup))
+
+    convs = [("conv3a_256x64x56x56_k3s1", (256, 64, 56, 56), (64, 64, 3, 3), 1, 1),
+             ("conv3b_256x128x56x56_k3s2", (256, 128, 56, 56), (256, 128, 3, 3), 2, 1),
+             ("conv3c_256x256x28x28_k1", (256, 256, 28, 28), (1024, 256, 1, 1), 1, 0),
+             ("conv_config1_8x16x32x32_k3", (8, 16, 32, 32), (32, 16, 3, 3), 1, 1)]
+
+    def conv(xs, ws, stride, pad, kind):
+        def setup():
+            fan = ws[1] * ws[2] * ws[3]
+            xt = T(rng.standard_normal(xs).astype(np.float32))
+            wt = T((rng.standard_normal(ws) * np.sqrt(2.0 / fan)).astype(np.float32))
+            g, oshape = nn.ops._conv_geom(xt.shape, wt.shape, stride, 1, pad)
+            flop = 2.0 * oshape.size * fan
+            if kind == "fwd":
+                yt = nn.Tensor(oshape)
+                return (lambda: lib.lnn_conv2d_fwd(dev.index, ctypes.byref(g), yt._ptr(0), xt._ptr(0), wt._ptr(0), 0, 0, 0.0, 0, passes)), flop, None, None
+            dyt = T(np.random.default_rng(2).standard_normal(oshape.shape).astype(np.float32))
+            if kind == "dX":
+                dxt = nn.Tensor(xs)
+                return (lambda: lib.lnn_conv2d_dx(dev.index, ctypes.byref(g), dxt._ptr(0), dyt._ptr(0), wt._ptr(0), passes)), flop, None, None
+            dwt = nn.Tensor(ws)
+            return (lambda: lib.lnn_conv2d_dw(dev.index, ctypes.byref(g), dwt._ptr(0), dyt._ptr(0), xt._ptr(0), passes)), flop, None, None
+        return setup
+
+    for name, xs, ws, stride, pad in convs:
+        for kind in ("fwd", "dX", "dW"):
+            cases.append((f"{name}_{kind}", conv(xs, ws, stride, pad, kind)))
+
+    pool_bytes = (256 * 128 * 112 * 112 + 256 * 128 * 56 * 56) * 4
+
+    def pool(fn_name):
+        def setup():
+            xp = T(rng.uniform(-1, 1, (256, 128, 112, 112)).astype(np.float32))
+            fn = getattr(nn, fn_name)
+            return (lambda: fn(xp)), None, pool_bytes, None
+        return setup
+
+    cases.append(("max_pool2D_256x128x112x112", pool("max_pool2D")))
+    cases.append(("avg_pool2D_256x128x112x112", pool("avg_pool2D")))
+
+    rb = 256 * 512 * 1024 * 4
+
+    def red(opname, mode):
+        def setup():
+            xr = T(rng.uniform(-1, 1, (256, 512, 1024)).astype(np.float32))
+            fn = getattr(nn, "reduce_" + opname)
+            if mode == "axis1":
+                return (lambda: fn(xr, (1,))), None, rb + 256 * 1024 * 4, None
+            if mode == "all":
+                return (lambda: fn(xr)), None, rb, None
+            x4 = xr.reshape((256, 512, 32, 32))
+            return (lambda: fn(x4, (2, 3))), None, rb + 256 * 512 * 4, \
+                "axes (2,3) of the [256,512,32,32] view: (2,3) is invalid on the rank-3 tensor in the reference"
+        return setup
+
+    for opname in ("sum", "mean", "max"):
+        cases.append((f"reduce_{opname}_axis1", red(opname, "axis1")))
+        cases.append((f"reduce_{opname}_all", red(opname, "all")))
+        cases.append((f"reduce_{opname}_axes23_view", red(opname, "view")))
+
+    cb = 2 * 256 * 256 * 56 * 56 * 4
+
+    def chain(fused):
+        def setup():
+            xc = T(rng.standard_normal((256, 256, 56, 56)).astype(np.float32))
+            gc = T(rng.uniform(0.5, 1.5, (1, 256, 1, 1)).astype(np.float32))
+            bc = T(rng.uniform(-0.5, 0.5, (1, 256, 1, 1)).astype(np.float32))
+            if fused:
+                yc = nn.Tensor(xc.shape)
+                return (lambda: nn.scale_bias_leaky_relu(xc, gc, bc, 0.1, output_t=yc)), None, cb, None
+            return (lambda: nn.leaky_relu(xc * gc + bc, 0.1)), None, cb, \
+                "the reference's three kernels; GB/s counts algorithmic bytes (x in, y out) only"
+        return setup
+
+    cases.append(("chain_lrelu_xg_b_fused", chain(True)))
+    cases.append(("chain_lrelu_xg_b_3ops", chain(False)))
+    return cases
+
+
+def bench_ops(nn, dev, peaks, quick, only=None):
+    from litenn_b200 import _lib
+    lib = _lib.get_lib()
+    timer = DevTimer(nn, dev)
+    passes = _lib.tf32_passes()
+    out = {}
+    iters = 3 if quick else 10
+    tf32_peak = peaks["bf16_tflops"] / 2.0
+    for name, setup in op_cases(nn, dev, lib, passes):
+        if only and not any(o in name for o in only.split(",")):
+            continue
+        fn, flop, nbytes, note = setup()
+        ms = _time_calls(timer, nn, fn, 3, iters)
         e = {"ms": round(ms, 4)}
         if flop is not None:
             e["tflops"] = round(flop / ms / 1e9, 2)
@@ -329,71 +449,7 @@ def bench_ops(nn, dev, peaks, quick):
         if note:
             e["note"] = note
         out[name] = e
-
-    # ---- matmul 4096^3 forward, dA, dB and Dense [8192,1024]x[1024,4096]+b -------------------
-    n = 4096
-    a, b = T(rng.standard_normal((n, n)).astype(np.float32) / 64), T(rng.standard_normal((n, n)).astype(np.float32) / 64)
-    do = T(np.random.default_rng(1).standard_normal((n, n)).astype(np.float32))
-    c = nn.Tensor((n, n))
-    flop = 2.0 * n ** 3
-
-    def gemm(o_t, a_t, b_t, bias, m, nn_, k, ta, tb, acc):
-        lib.lnn_gemm_f32(dev.index, o_t._ptr(0), a_t._ptr(0), b_t._ptr(0), bias, 1, m, nn_, k, ta, tb, acc, passes)
-
-    rec("matmul_4096_fwd", _time_calls(timer, nn, lambda: gemm(c, a, b, 0, n, n, n, 0, 0, 0), 3, iters), flop)
-    rec("matmul_4096_dA", _time_calls(timer, nn, lambda: gemm(c, do, b, 0, n, n, n, 0, 1, 1), 3, iters), flop)
-    rec("matmul_4096_dB", _time_calls(timer, nn, lambda: gemm(c, a, do, 0, n, n, n, 1, 0, 1), 3, iters), flop)
-    del a, b, do, c
-    x = T(rng.standard_normal((8192, 1024)).astype(np.float32))
-    w = T(rng.standard_normal((1024, 4096)).astype(np.float32) / 32)
-    bias = T(rng.uniform(-0.1, 0.1, (4096,)).astype(np.float32))
-    y = nn.Tensor((8192, 4096))
-    rec("dense_8192x1024x4096_fwd", _time_calls(timer, nn, lambda: gemm(y, x, w, bias._ptr(0), 8192, 4096, 1024, 0, 0, 0), 3, iters),
-        2.0 * 8192 * 1024 * 4096)
-    del x, w, bias, y
-
-    # ---- conv stages ----------------------------------------------------------------------------
-    convs = [("conv3a_256x64x56x56_k3s1", (256, 64, 56, 56), (64, 64, 3, 3), 1, 1),
-             ("conv3b_256x128x56x56_k3s2", (256, 128, 56, 56), (256, 128, 3, 3), 2, 1),
-             ("conv3c_256x256x28x28_k1", (256, 256, 28, 28), (1024, 256, 1, 1), 1, 0)]
-    for name, xs, ws, stride, pad in convs:
-        fan = ws[1] * ws[2] * ws[3]
-        xt = T(rng.standard_normal(xs).astype(np.float32))
-        wt = T((rng.standard_normal(ws) * np.sqrt(2.0 / fan)).astype(np.float32))
-        g, oshape = nn.ops._conv_geom(xt.shape, wt.shape, stride, 1, pad)
-        yt = nn.Tensor(oshape)
-        dyt = T(np.random.default_rng(2).standard_normal(oshape.shape).astype(np.float32))
-        dxt, dwt = nn.Tensor(xs), nn.Tensor(ws)
-        flop = 2.0 * oshape.size * fan
-        rec(name + "_fwd", _time_calls(timer, nn, lambda: lib.lnn_conv2d_fwd(dev.index, ctypes.byref(g), yt._ptr(0), xt._ptr(0), wt._ptr(0), 0, 0, 0.0, 0, passes), 2, iters), flop)
-        rec(name + "_dX", _time_calls(timer, nn, lambda: lib.lnn_conv2d_dx(dev.index, ctypes.byref(g), dxt._ptr(0), dyt._ptr(0), wt._ptr(0), passes), 2, iters), flop)
-        rec(name + "_dW", _time_calls(timer, nn, lambda: lib.lnn_conv2d_dw(dev.index, ctypes.byref(g), dwt._ptr(0), dyt._ptr(0), xt._ptr(0), passes), 2, iters), flop)
-        del xt, wt, yt, dyt, dxt, dwt
-
-    # ---- memory-bound sweep -----------------------------------------------------------------------
-    xp = T(rng.uniform(-1, 1, (256, 128, 112, 112)).astype(np.float32))
-    pool_bytes = (256 * 128 * 112 * 112 + 256 * 128 * 56 * 56) * 4
-    rec("max_pool2D_256x128x112x112", _time_calls(timer, nn, lambda: nn.max_pool2D(xp), 3, iters), nbytes=pool_bytes)
-    rec("avg_pool2D_256x128x112x112", _time_calls(timer, nn, lambda: nn.avg_pool2D(xp), 3, iters), nbytes=pool_bytes)
-    del xp
-    xr = T(rng.uniform(-1, 1, (256, 512, 1024)).astype(np.float32))
-    rb = 256 * 512 * 1024 * 4
-    for opname, fn in (("sum", nn.reduce_sum), ("mean", nn.reduce_mean), ("max", nn.reduce_max)):
-        rec(f"reduce_{opname}_axis1", _time_calls(timer, nn, lambda: fn(xr, (1,)), 3, iters), nbytes=rb + 256 * 1024 * 4)
-        rec(f"reduce_{opname}_all", _time_calls(timer, nn, lambda: fn(xr), 3, iters), nbytes=rb)
-    xr4 = xr.reshape((256, 512, 32, 32))
-    for opname, fn in (("sum", nn.reduce_sum), ("mean", nn.reduce_mean), ("max", nn.reduce_max)):
-        rec(f"reduce_{opname}_axes23_view", _time_calls(timer, nn, lambda: fn(xr4, (2, 3)), 3, iters), nbytes=rb + 256 * 512 * 4,
-            note="axes (2,3) of the [256,512,32,32] view: (2,3) is invalid on the rank-3 tensor in the reference")
-    del xr, xr4
-    xc = T(rng.standard_normal((256, 256, 56, 56)).astype(np.float32))
-    gc, bc = T(rng.uniform(0.5, 1.5, (1, 256, 1, 1)).astype(np.float32)), T(rng.uniform(-0.5, 0.5, (1, 256, 1, 1)).astype(np.float32))
-    yc = nn.Tensor(xc.shape)
-    cb = 2 * 256 * 256 * 56 * 56 * 4
-    rec("chain_lrelu_xg_b_fused", _time_calls(timer, nn, lambda: nn.scale_bias_leaky_relu(xc, gc, bc, 0.1, output_t=yc), 3, iters), nbytes=cb)
-    rec("chain_lrelu_xg_b_3ops", _time_calls(timer, nn, lambda: nn.leaky_relu(xc * gc + bc, 0.1), 3, iters), nbytes=cb,
-        note="the reference's three kernels; GB/s counts algorithmic bytes (x in, y out) only")
-    del xc, gc, bc, yc
+        del fn
     nn.devices.check_status()
     return out
 
@@ -498,7 +554,8 @@ def run_ours(args):
     npre, tpre = ctypes.c_uint64(), ctypes.c_float()
     lib.lnn_profile_read(dev.index, 3, ctypes.byref(npre), ctypes.byref(tpre))
     lib.lnn_profile_enable(dev.index, 0)
-    conv_flop = (FWD_FLOP_PER_IMAGE - 2 * 256 * 1000) * local_batch * prof_steps       # the four convolutions
+    # the tile kernel runs convolutions 2-4; the 3-channel input layer runs on the FP32 pipes
+    conv_flop = (FWD_FLOP_PER_IMAGE - 2 * 256 * 1000 - 2 * 32 * 27 * 128 * 128) * local_batch * prof_steps
     conv_tflops = conv_flop / (tms.value / 1000.0) / 1e12 if tms.value > 0 else 0.0
     tf32_peak = peaks["bf16_tflops_sustained"] / 2.0
     roofline = {"bound": "tensor", "kernel": "tc_kernel<MODE_CONV> (implicit-GEMM conv2D, tcgen05 kind::tf32)",
@@ -525,6 +582,8 @@ def run_ours(args):
             oh[np.arange(mb), lab_rng.integers(0, NCLASS, mb)] = 1
             onehots.append(nn.Tensor_from_value(oh))
         scale = 1.0 / n_mb
+
+        model.training = True
 
         def train_step():
             last = None
@@ -556,6 +615,9 @@ def run_ours(args):
         del onehots
 
     clocks = sampler.summary(m0, m1)
+    if clocks["samples"] < 3:       # timed region shorter than a few sampling periods:
+        clocks = sampler.summary(m0, None)   # use every sample from its start to the end of the GPU work
+        clocks["window"] = "timed region through the end of the run"
     sampler.stop()
     nn.devices.check_status()
 
@@ -589,6 +651,7 @@ def run_ours(args):
 
 
 def main():
+    global TOTAL_BATCH
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
@@ -598,11 +661,22 @@ def main():
     ap.add_argument("--no-train", action="store_true", help="skip the training step")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--quick", action="store_true", help="fewer iterations in the single-op configurations")
+    ap.add_argument("--batch", type=int, default=4096,
+                    help="global batch (default 4096, the benchmark configuration; smaller values are for profiling)")
+    ap.add_argument("--ops-only", default=None, metavar="NAMES",
+                    help="run only the single-op configurations whose name contains one of the comma-separated NAMES")
     args = ap.parse_args()
+    TOTAL_BATCH = args.batch
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.ops_only:
+        import litenn_b200 as nn
+        dev = nn.devices.get_all()[0]
+        nn.devices.set_current(dev)
+        print(json.dumps({"ops": bench_ops(nn, dev, load_peaks(), args.quick, args.ops_only)}), flush=True)
         return
     if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
         # plain invocation with N > 1: start one rank per GPU

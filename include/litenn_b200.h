@@ -199,6 +199,11 @@ typedef struct lnn_conv_geom {
  * module/Conv2D.py:58-62 */
 int lnn_conv2d_fwd(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint64_t W,
                    uint64_t bias, int act, float alpha, int accumulate, int tf32_passes);
+/* Inference fusion: Y = max_pool2D(act(conv2D(X, W) + bias), 2, 2, 'same'), Y is
+ * [n, oc, ceil(oh/2), ceil(ow/2)].  Same values as the three separate entries.
+ * ref: op/conv2D.py:9-44 + op/element_wise_op.py:207-221 + op/pool2D.py:47-146 */
+int lnn_conv2d_pool_fwd(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint64_t W,
+                        uint64_t bias, int act, float alpha, int tf32_passes);
 /* dX += conv2D_transpose-like gradient.  ref: op/conv2D.py:46-50, op/unfold2D.py:112-138 */
 int lnn_conv2d_dx(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY, uint64_t W,
                   int tf32_passes);

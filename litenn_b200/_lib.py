@@ -83,6 +83,7 @@ _SIGNATURES = {
     "lnn_slice_bwd": (c_int, [c_int, c_uint64, c_uint64, c_int, _I64P, _I64P, _I64P, _I64P]),
     "lnn_gemm_f32": (c_int, [c_int, c_uint64, c_uint64, c_uint64, c_uint64, c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int]),
     "lnn_conv2d_fwd": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64, c_uint64, c_int, c_float, c_int, c_int]),
+    "lnn_conv2d_pool_fwd": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64, c_uint64, c_int, c_float, c_int]),
     "lnn_conv2d_dx": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64, c_int]),
     "lnn_conv2d_dw": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64, c_int]),
     "lnn_sgd_step": (c_int, [c_int, c_uint64, c_uint64, c_int64, c_float, c_float]),

@@ -58,6 +58,11 @@ struct Scratch {
   template <class T> T* as() { return reinterpret_cast<T*>(p); }
 };
 
+// direct (FP32-pipe) convolution for layers with IC <= 4 (lnn_direct.cu)
+bool conv_direct_applicable(const lnn_conv_geom* g);
+int conv_direct_fwd(Device* d, const lnn_conv_geom* g, float* Y, const float* X, const float* W,
+                    const float* bias, int act, float alpha, int accumulate, int pool);
+
 }  // namespace lnn
 
 #define LNN_CUDA(call)                                                                   \

@@ -206,6 +206,69 @@ bin_kernel(float* __restrict__ X, const float* __restrict__ A, const float* __re
   }
 }
 
+// Fast broadcast path: every operand is the full tensor, one element, or varies along a
+// single contiguous run of axes, so its element index is i, 0 or (i / inner) % size -- no
+// per-axis index decomposition.  With vec != 0 a thread handles four consecutive outputs.
+enum { OPM_FULL = 0, OPM_SCALAR = 1, OPM_AXIS = 2, OPM_GENERIC = 3 };
+struct Operand { int mode; int64_t inner, size; };
+
+__device__ __forceinline__ float op_load1(const float* __restrict__ p, const Operand& o, int64_t i) {
+  if (o.mode == OPM_FULL) return p[i];
+  if (o.mode == OPM_SCALAR) return __ldg(p);
+  return __ldg(p + (i / o.inner) % o.size);
+}
+__device__ __forceinline__ float4 op_load4(const float* __restrict__ p, const Operand& o, int64_t i) {
+  if (o.mode == OPM_FULL) return *reinterpret_cast<const float4*>(p + i);
+  if (o.mode == OPM_SCALAR) { const float v = __ldg(p); return make_float4(v, v, v, v); }
+  if (o.inner == 1) return __ldg(reinterpret_cast<const float4*>(p + i % o.size));
+  const float v = __ldg(p + (i / o.inner) % o.size);
+  return make_float4(v, v, v, v);
+}
+
+template <int OP, int MODE>
+__global__ void __launch_bounds__(kThreads)
+bin_fast_kernel(float* __restrict__ X, const float* __restrict__ A, const float* __restrict__ B,
+                const float* __restrict__ O, const float* __restrict__ dO, int64_t n, Operand oa,
+                Operand ob, int acc, int vec) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  if (vec) {
+    const int64_t n4 = n >> 2;
+    for (int64_t q = tid; q < n4; q += nthreads) {
+      const int64_t i = q << 2;
+      const float4 a = op_load4(A, oa, i), b = op_load4(B, ob, i);
+      float4 r;
+      if (MODE == 0) {
+        r.x = bin_fwd<OP>(a.x, b.x); r.y = bin_fwd<OP>(a.y, b.y);
+        r.z = bin_fwd<OP>(a.z, b.z); r.w = bin_fwd<OP>(a.w, b.w);
+      } else {
+        const float4 o = *reinterpret_cast<const float4*>(O + i);
+        const float4 g = *reinterpret_cast<const float4*>(dO + i);
+        r.x = bin_bwd<OP, MODE - 1>(a.x, b.x, o.x, g.x); r.y = bin_bwd<OP, MODE - 1>(a.y, b.y, o.y, g.y);
+        r.z = bin_bwd<OP, MODE - 1>(a.z, b.z, o.z, g.z); r.w = bin_bwd<OP, MODE - 1>(a.w, b.w, o.w, g.w);
+      }
+      float4* dst = reinterpret_cast<float4*>(X + i);
+      if (acc || MODE != 0) {
+        const float4 x = *dst;
+        r.x = fadd(x.x, r.x); r.y = fadd(x.y, r.y); r.z = fadd(x.z, r.z); r.w = fadd(x.w, r.w);
+      }
+      *dst = r;
+    }
+    return;
+  }
+  for (int64_t i = tid; i < n; i += nthreads) {
+    const float a = op_load1(A, oa, i), b = op_load1(B, ob, i);
+    float r;
+    if (MODE == 0) {
+      r = bin_fwd<OP>(a, b);
+      X[i] = acc ? fadd(X[i], r) : r;
+    } else {
+      r = bin_bwd<OP, MODE - 1>(a, b, O[i], dO[i]);
+      X[i] = fadd(X[i], r);
+    }
+  }
+}
+
 // y (+)= leaky_relu(x*g + b): x[N,C,HW]; each (n,c) plane is contiguous.  One float4 per
 // thread per step; the channel index is recovered per vector (HW % 4 == 0 on this path).
 __global__ void __launch_bounds__(kThreads)
@@ -345,6 +408,32 @@ static int make_bcast(BcastDims& bd, int rank, const int64_t* o_shape, const int
   return LNN_OK;
 }
 
+// Classify one operand of a broadcast: FULL (same shape as the output), SCALAR (one element)
+// or AXIS (its non-broadcast axes are one contiguous run: element = (i / inner) % size).
+static void classify_operand(int rank, const int64_t* o_shape, const int64_t* x_shape, Operand& op) {
+  int64_t x_size = 1, o_size = 1;
+  for (int k = 0; k < rank; ++k) { x_size *= x_shape[k]; o_size *= o_shape[k]; }
+  op.inner = 1; op.size = 1;
+  if (x_size == o_size) { op.mode = OPM_FULL; return; }
+  if (x_size == 1) { op.mode = OPM_SCALAR; return; }
+  // find the run of axes where the operand is not broadcast (ignoring size-1 output axes)
+  int first = -1, last = -1;
+  for (int k = 0; k < rank; ++k)
+    if (x_shape[k] != 1) { if (first < 0) first = k; last = k; }
+  for (int k = first; k <= last; ++k)
+    if (x_shape[k] != o_shape[k]) { op.mode = OPM_GENERIC; return; }
+  for (int k = first; k <= last; ++k) op.size *= o_shape[k];
+  for (int k = last + 1; k < rank; ++k) op.inner *= o_shape[k];
+  op.mode = OPM_AXIS;
+}
+
+static bool operand_vec_ok(const Operand& op, uint64_t ptr) {
+  if (op.mode == OPM_FULL) return (ptr & 15) == 0;
+  if (op.mode == OPM_SCALAR) return true;
+  if (op.mode == OPM_AXIS) return (op.inner % 4 == 0) || (op.inner == 1 && op.size % 4 == 0 && (ptr & 15) == 0);
+  return false;
+}
+
 extern "C" {
 
 int lnn_fill_f32(int dev, uint64_t dst, int64_t count, float value) {
@@ -397,6 +486,21 @@ int lnn_binary_fwd(int dev, int op, uint64_t O, uint64_t A, uint64_t B, int rank
   BcastDims bd; int64_t n; int same;
   int rc = make_bcast(bd, rank, o_shape, a_shape, b_shape, &n, &same);
   if (rc) return rc;
+  Operand oa, ob;
+  classify_operand(rank, o_shape, a_shape, oa);
+  classify_operand(rank, o_shape, b_shape, ob);
+  if (oa.mode != OPM_GENERIC && ob.mode != OPM_GENERIC) {
+    const int vec = (n % 4 == 0) && aligned16(O) && operand_vec_ok(oa, A) && operand_vec_ok(ob, B);
+    const int grid = grid_for(d, vec ? n / 4 : n);
+#define CALL(OPC)                                                                         \
+  bin_fast_kernel<OPC, 0><<<grid, kThreads, 0, d->stream>>>((float*)(uintptr_t)O,         \
+      (const float*)(uintptr_t)A, (const float*)(uintptr_t)B, nullptr, nullptr, n, oa, ob, \
+      accumulate, vec)
+    BIN_DISPATCH(op, CALL)
+#undef CALL
+    LNN_CHECK_LAUNCH(d);
+    return LNN_OK;
+  }
   int grid = grid_for(d, n);
 #define CALL(OPC)                                                                         \
   bin_kernel<OPC, 0><<<grid, kThreads, 0, d->stream>>>((float*)(uintptr_t)O,              \
@@ -417,6 +521,27 @@ int lnn_binary_bwd(int dev, int op, int which, uint64_t dX, uint64_t A, uint64_t
   BcastDims bd; int64_t n; int same;
   int rc = make_bcast(bd, rank, o_shape, a_shape, b_shape, &n, &same);
   if (rc) return rc;
+  Operand oa, ob;
+  classify_operand(rank, o_shape, a_shape, oa);
+  classify_operand(rank, o_shape, b_shape, ob);
+  if (oa.mode != OPM_GENERIC && ob.mode != OPM_GENERIC) {
+    const int vec = (n % 4 == 0) && aligned16(dX) && aligned16(O) && aligned16(dO) &&
+                    operand_vec_ok(oa, A) && operand_vec_ok(ob, B);
+    const int grid = grid_for(d, vec ? n / 4 : n);
+#define CALL(OPC)                                                                         \
+  if (which == 0)                                                                         \
+    bin_fast_kernel<OPC, 1><<<grid, kThreads, 0, d->stream>>>((float*)(uintptr_t)dX,      \
+        (const float*)(uintptr_t)A, (const float*)(uintptr_t)B, (const float*)(uintptr_t)O, \
+        (const float*)(uintptr_t)dO, n, oa, ob, 1, vec);                                  \
+  else                                                                                    \
+    bin_fast_kernel<OPC, 2><<<grid, kThreads, 0, d->stream>>>((float*)(uintptr_t)dX,      \
+        (const float*)(uintptr_t)A, (const float*)(uintptr_t)B, (const float*)(uintptr_t)O, \
+        (const float*)(uintptr_t)dO, n, oa, ob, 1, vec)
+    BIN_DISPATCH(op, CALL)
+#undef CALL
+    LNN_CHECK_LAUNCH(d);
+    return LNN_OK;
+  }
   int grid = grid_for(d, n);
 #define CALL(OPC)                                                                         \
   if (which == 0)                                                                         \

@@ -92,6 +92,57 @@ pool2x2_fwd_kernel(float2* __restrict__ O, const float* __restrict__ I, int64_t 
   }
 }
 
+// Backward of the 2x2 / stride 2 / no left-top padding case: every input element lies in
+// exactly one window, so a thread takes one window pair (two horizontally adjacent outputs),
+// finds the first tap (row-major) equal to the pooled value and adds dO there; avg spreads
+// dO / count.  Same results as the gather form below, one pass, 128-bit accesses.
+template <int MODE>
+__global__ void __launch_bounds__(kThreads)
+pool2x2_bwd_kernel(float* __restrict__ dI, const float* __restrict__ I, const float2* __restrict__ dO,
+                   const float2* __restrict__ O, int64_t total2, int ih, int iw, int oh, int ow2) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t gid = tid; gid < total2; gid += nthreads) {
+    const int x2 = (int)(gid % ow2);
+    const int64_t t = gid / ow2;
+    const int y = (int)(t % oh);
+    const int64_t plane = t / oh;
+    const int64_t off0 = (plane * ih + 2 * y) * (int64_t)iw + 4 * x2;
+    const bool has1 = (2 * y + 1) < ih;
+    const float2 g = dO[gid];
+    float4 ga = make_float4(0.f, 0.f, 0.f, 0.f), gb = ga;       // gradient of the two input rows
+    if (MODE == LNN_POOL_AVG) {
+      const float cnt = has1 ? 4.0f : 2.0f;
+      const float q0 = __fdiv_rn(g.x, cnt), q1 = __fdiv_rn(g.y, cnt);
+      ga = make_float4(q0, q0, q1, q1);
+      gb = ga;
+    } else {
+      const float4 a = *reinterpret_cast<const float4*>(I + off0);
+      float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (has1) b = *reinterpret_cast<const float4*>(I + off0 + iw);
+      const float2 o = O[gid];
+      // window 0: taps a.x, a.y, b.x, b.y in row-major order; window 1: a.z, a.w, b.z, b.w
+      if (a.x == o.x) ga.x = g.x; else if (a.y == o.x) ga.y = g.x;
+      else if (has1 && b.x == o.x) gb.x = g.x; else if (has1 && b.y == o.x) gb.y = g.x;
+      if (a.z == o.y) ga.z = g.y; else if (a.w == o.y) ga.w = g.y;
+      else if (has1 && b.z == o.y) gb.z = g.y; else if (has1 && b.w == o.y) gb.w = g.y;
+    }
+    float4* d0 = reinterpret_cast<float4*>(dI + off0);
+    float4 v = *d0;
+    // the reference adds 0.0 + dO to its accumulator first, then accumulator to dI
+    v.x = __fadd_rn(v.x, __fadd_rn(0.0f, ga.x)); v.y = __fadd_rn(v.y, __fadd_rn(0.0f, ga.y));
+    v.z = __fadd_rn(v.z, __fadd_rn(0.0f, ga.z)); v.w = __fadd_rn(v.w, __fadd_rn(0.0f, ga.w));
+    *d0 = v;
+    if (has1) {
+      float4* d1 = reinterpret_cast<float4*>(dI + off0 + iw);
+      float4 w = *d1;
+      w.x = __fadd_rn(w.x, __fadd_rn(0.0f, gb.x)); w.y = __fadd_rn(w.y, __fadd_rn(0.0f, gb.y));
+      w.z = __fadd_rn(w.z, __fadd_rn(0.0f, gb.z)); w.w = __fadd_rn(w.w, __fadd_rn(0.0f, gb.w));
+      *d1 = w;
+    }
+  }
+}
+
 // Backward, one thread per INPUT element, exactly the reference's gather formulation.
 template <int MODE>
 __global__ void __launch_bounds__(kThreads)
@@ -199,11 +250,26 @@ int lnn_pool2d_bwd(int dev, int mode, uint64_t dI, uint64_t I, uint64_t dO, uint
   LNN_REQUIRE(pool >= 2 && stride >= 1, "pool_size must be >= 2 and stride >= 1");
   const int64_t total = n * c * ih * iw;
   PoolGeom g{ih, iw, oh, ow, pool, stride, padl, padt};
-  const int grid = grid_for(d, total);
   float* di = (float*)(uintptr_t)dI;
   const float* i = (const float*)(uintptr_t)I;
   const float* dout = (const float*)(uintptr_t)dO;
   const float* o = (const float*)(uintptr_t)O;
+  const bool fast = pool == 2 && stride == 2 && padl == 0 && padt == 0 && (iw % 4) == 0 &&
+                    ow == iw / 2 && oh == (ih + 1) / 2 && (dI & 15) == 0 && (dO & 7) == 0 &&
+                    (mode == LNN_POOL_AVG || ((I & 15) == 0 && (O & 7) == 0));
+  if (fast) {
+    const int64_t total2 = n * c * oh * (ow / 2);
+    const int grid2 = grid_for(d, total2);
+    if (mode == LNN_POOL_AVG)
+      pool2x2_bwd_kernel<LNN_POOL_AVG><<<grid2, kThreads, 0, d->stream>>>(di, i, (const float2*)dout, (const float2*)o, total2, ih, iw, oh, ow / 2);
+    else if (mode == LNN_POOL_MAX)
+      pool2x2_bwd_kernel<LNN_POOL_MAX><<<grid2, kThreads, 0, d->stream>>>(di, i, (const float2*)dout, (const float2*)o, total2, ih, iw, oh, ow / 2);
+    else
+      pool2x2_bwd_kernel<LNN_POOL_MIN><<<grid2, kThreads, 0, d->stream>>>(di, i, (const float2*)dout, (const float2*)o, total2, ih, iw, oh, ow / 2);
+    LNN_CHECK_LAUNCH(d);
+    return LNN_OK;
+  }
+  const int grid = grid_for(d, total);
   if (mode == LNN_POOL_AVG)
     pool_bwd_kernel<LNN_POOL_AVG><<<grid, kThreads, 0, d->stream>>>(di, i, dout, o, total, g);
   else if (mode == LNN_POOL_MAX)

@@ -5,22 +5,27 @@
 // The reference reduces a row of n values in stages: h = ceil(n/2); x[c] = x[c] (+) x[c+h]
 // for every c with c+h < n; n = h; until n == 1.  With n_0 = COLS and n_j = ceil(n_{j-1}/2)
 // the value at stage s, column c is V_s(c) = V_{s-1}(c) (+) V_{s-1}(c + n_s) when that
-// partner exists, else V_{s-1}(c).  Here one thread evaluates a whole subtree V_s(c0) by a
-// depth-first walk (a stack of one partial value per level), so the operand pairing, and
-// therefore every rounding, is the reference's.  A row is finished either inside a block
-// (shared-memory stages for the last levels) or, when a row is split over many threads
-// to fill the GPU, by running the same routine again on the partial values -- the tree
-// over n_s partials is by construction the tail of the tree over n_0 values.
+// partner exists, else V_{s-1}(c).  Here one thread evaluates a whole subtree V_s(c0), so
+// the operand pairing, and therefore every rounding, is the reference's:
+//   * any COLS: a depth-first walk with a stack of one partial value per level;
+//   * power-of-two COLS (every benchmark shape): the 2^s leaves c0 + m*n_s form a plain
+//     halving tree over m, evaluated with 16 independent loads in flight per thread.
+// A row is finished inside a warp (shuffles), inside a block (shared memory), or, when a
+// row is split over many threads to fill the GPU, by running the same routine again on the
+// partial values -- the tree over n_s partials is the tail of the tree over n_0 values.
 #include "lnn_common.cuh"
 #include <math_constants.h>
+#include <utility>
 
 namespace {
 
 constexpr int kThreads = 256;
 constexpr int kMaxLevels = 40;
+constexpr int kMaxPow2Levels = 9;      // fast subtree: up to 2^9 leaves per thread
 
 struct Levels {
   int S;                       // number of stages: n[S] == 1
+  int pow2;                    // COLS is a power of two
   int64_t n[kMaxLevels + 1];   // n[0] = COLS, n[j] = ceil(n[j-1]/2)
 };
 
@@ -48,23 +53,21 @@ __device__ __forceinline__ int64_t row_base(const RedGeom& g, int64_t row) {
   return outer_i * g.stride_outer + mid_i * g.stride_mid + inner_i;
 }
 
-// V_s(c0) of one row (base points at the row's column 0).
+__device__ __forceinline__ int64_t leaf_offset(const RedGeom& g, int64_t leaf) {
+  if (g.r0 == 1) return leaf * g.stride_r1;
+  const int64_t q = leaf / g.r1;
+  return q * g.stride_r0 + (leaf - q * g.r1) * g.stride_r1;
+}
+
+// V_s(c0) of one row for any COLS (base points at the row's column 0).
 template <int OP>
-__device__ float subtree(const float* __restrict__ base, int64_t c0, int s, const Levels& L,
-                         const RedGeom& g) {
+__device__ float subtree_dfs(const float* __restrict__ base, int64_t c0, int s, const Levels& L,
+                             const RedGeom& g) {
   float acc[kMaxLevels];
   int64_t leaf = c0;
   uint64_t m = 0;
-  const bool one_group = (g.r0 == 1);
   for (;;) {
-    int64_t off;
-    if (one_group) {
-      off = leaf * g.stride_r1;
-    } else {
-      const int64_t q = leaf / g.r1;
-      off = q * g.stride_r0 + (leaf - q * g.r1) * g.stride_r1;
-    }
-    float v = __ldcs(base + off);
+    float v = __ldcs(base + leaf_offset(g, leaf));
     int64_t cur = leaf;
     int j = 1;
     for (; j <= s; ++j) {
@@ -79,6 +82,152 @@ __device__ float subtree(const float* __restrict__ base, int64_t c0, int s, cons
     if (j > s) return v;
     m = ((m >> (j - 1)) | 1ull) << (j - 1);
     leaf = cur + L.n[j];
+  }
+}
+
+__host__ __device__ constexpr int bit_reverse(int t, int bits) {
+  int r = 0;
+  for (int i = 0; i < bits; ++i) r |= ((t >> i) & 1) << (bits - 1 - i);
+  return r;
+}
+
+// Power-of-two COLS: leaf m of V_s(c0) is column c0 + m*ns (ns = COLS >> s) and the tree is
+// the halving tree over m.  m = a*B + b: the A = 2^LOG_A leaves of one b are loaded together
+// and halved in registers (the high bits of m go first); b then runs in bit-reversed order so
+// that a binary-counter stack, fully unrolled into registers, pairs b with b + B/2 first.
+template <int OP, int LOG_A, int LOG_B>
+__device__ __forceinline__ float subtree_pow2(const float* __restrict__ base, int64_t c0, int64_t ns,
+                                              const RedGeom& g) {
+  constexpr int A = 1 << LOG_A, B = 1 << LOG_B;
+  float stack[LOG_B + 1];
+  float result = 0.0f;
+#pragma unroll
+  for (int t = 0; t < B; ++t) {
+    const int b = bit_reverse(t, LOG_B);
+    float v[A];
+#pragma unroll
+    for (int a = 0; a < A; ++a) v[a] = __ldcs(base + leaf_offset(g, c0 + (int64_t)(a * B + b) * ns));
+#pragma unroll
+    for (int h = A / 2; h >= 1; h >>= 1) {
+#pragma unroll
+      for (int i = 0; i < h; ++i) v[i] = comb<OP>(v[i], v[i + h]);
+    }
+    float w = v[0];
+    bool stored = false;
+#pragma unroll
+    for (int level = 0; level < LOG_B; ++level) {
+      if (!stored) {
+        if ((t >> level) & 1) w = comb<OP>(stack[level], w);
+        else { stack[level] = w; stored = true; }
+      }
+    }
+    if (t == B - 1) result = w;
+  }
+  return result;
+}
+
+template <int OP>
+__device__ __forceinline__ float4 comb4(const float4& a, const float4& b) {
+  return make_float4(comb<OP>(a.x, b.x), comb<OP>(a.y, b.y), comb<OP>(a.z, b.z), comb<OP>(a.w, b.w));
+}
+
+// Four independent subtrees at once from 128-bit loads: the four lanes of a float4 are four
+// adjacent kept rows (inner axis) or four adjacent columns c0..c0+3, whichever is contiguous
+// in memory.  Same tree per lane as subtree_pow2.
+template <int OP, int LOG_A, int LOG_B>
+__device__ __forceinline__ float4 subtree_pow2_v4(const float* __restrict__ base, int64_t c0, int64_t ns,
+                                                  const RedGeom& g) {
+  constexpr int A = 1 << LOG_A, B = 1 << LOG_B;
+  float4 stack[LOG_B + 1];
+  float4 result = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int t = 0; t < B; ++t) {
+    const int b = bit_reverse(t, LOG_B);
+    float4 v[A];
+#pragma unroll
+    for (int a = 0; a < A; ++a)
+      v[a] = __ldcs(reinterpret_cast<const float4*>(base + leaf_offset(g, c0 + (int64_t)(a * B + b) * ns)));
+#pragma unroll
+    for (int h = A / 2; h >= 1; h >>= 1) {
+#pragma unroll
+      for (int i = 0; i < h; ++i) v[i] = comb4<OP>(v[i], v[i + h]);
+    }
+    float4 w = v[0];
+    bool stored = false;
+#pragma unroll
+    for (int level = 0; level < LOG_B; ++level) {
+      if (!stored) {
+        if ((t >> level) & 1) w = comb4<OP>(stack[level], w);
+        else { stack[level] = w; stored = true; }
+      }
+    }
+    if (t == B - 1) result = w;
+  }
+  return result;
+}
+
+// s <= 8 keeps the unrolled body within the register budget (A = 8 float4 loads in flight)
+template <int OP>
+__device__ __forceinline__ float4 subtree_v4(const float* __restrict__ base, int64_t c0, int s,
+                                             const Levels& L, const RedGeom& g) {
+  const int64_t ns = L.n[s];
+  switch (s) {
+    case 0: return subtree_pow2_v4<OP, 0, 0>(base, c0, ns, g);
+    case 1: return subtree_pow2_v4<OP, 1, 0>(base, c0, ns, g);
+    case 2: return subtree_pow2_v4<OP, 2, 0>(base, c0, ns, g);
+    case 3: return subtree_pow2_v4<OP, 3, 0>(base, c0, ns, g);
+    case 4: return subtree_pow2_v4<OP, 3, 1>(base, c0, ns, g);
+    case 5: return subtree_pow2_v4<OP, 3, 2>(base, c0, ns, g);
+    case 6: return subtree_pow2_v4<OP, 3, 3>(base, c0, ns, g);
+    case 7: return subtree_pow2_v4<OP, 3, 4>(base, c0, ns, g);
+    case 8: return subtree_pow2_v4<OP, 3, 5>(base, c0, ns, g);
+    default: return subtree_pow2_v4<OP, 3, 6>(base, c0, ns, g);
+  }
+}
+
+template <int OP>
+__device__ __forceinline__ float subtree(const float* __restrict__ base, int64_t c0, int s,
+                                         const Levels& L, const RedGeom& g) {
+  if (L.pow2 && s <= kMaxPow2Levels) {
+    const int64_t ns = L.n[s];
+    switch (s) {
+      case 0: return subtree_pow2<OP, 0, 0>(base, c0, ns, g);
+      case 1: return subtree_pow2<OP, 1, 0>(base, c0, ns, g);
+      case 2: return subtree_pow2<OP, 2, 0>(base, c0, ns, g);
+      case 3: return subtree_pow2<OP, 3, 0>(base, c0, ns, g);
+      case 4: return subtree_pow2<OP, 4, 0>(base, c0, ns, g);
+      case 5: return subtree_pow2<OP, 4, 1>(base, c0, ns, g);
+      case 6: return subtree_pow2<OP, 4, 2>(base, c0, ns, g);
+      case 7: return subtree_pow2<OP, 4, 3>(base, c0, ns, g);
+      case 8: return subtree_pow2<OP, 4, 4>(base, c0, ns, g);
+      default: return subtree_pow2<OP, 4, 5>(base, c0, ns, g);
+    }
+  }
+  return subtree_dfs<OP>(base, c0, s, L, g);
+}
+
+// inner == 1, power-of-two COLS, n[s] <= 32: one warp per row.  Lane t owns subtree c0 = t
+// (coalesced: neighbouring lanes read neighbouring columns) and the last stages are
+// shuffles: lane t takes lane t+h for h = n[s]/2 ... 1.
+template <int OP>
+__global__ void __launch_bounds__(kThreads)
+reduce_warp_kernel(float* __restrict__ O, const float* __restrict__ I, RedGeom g, Levels L, int s,
+                   int acc, float mean_div) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int parts = (int)L.n[s];
+  for (int64_t row = warp0; row < g.rows; row += nwarps) {
+    float v = 0.0f;
+    if (lane < parts) v = subtree<OP>(I + row_base(g, row), lane, s, L, g);
+    for (int h = parts >> 1; h >= 1; h >>= 1) {
+      const float other = __shfl_down_sync(0xffffffffu, v, h);
+      if (lane < h) v = comb<OP>(v, other);
+    }
+    if (lane == 0) {
+      if (mean_div != 0.0f) v = __fdiv_rn(v, mean_div);
+      O[row] = acc ? __fadd_rn(O[row], v) : v;
+    }
   }
 }
 
@@ -144,6 +293,78 @@ reduce_parts_kernel(float* __restrict__ O, float* __restrict__ P, const float* _
   }
 }
 
+// inner == 1, power-of-two COLS >= 128, contiguous columns: one warp per row with 128-bit
+// loads.  Lane t owns the four subtrees c0 = 4t..4t+3 of the n[s] = 128 partials; the last
+// stages pair c with c+64 ... c+4 by shuffles (lane t with t+16 ... t+1), then c with c+2
+// and c with c+1 inside the lane.
+template <int OP>
+__global__ void __launch_bounds__(kThreads)
+reduce_warp4_kernel(float* __restrict__ O, const float* __restrict__ I, RedGeom g, Levels L, int s,
+                    int acc, float mean_div) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t row = warp0; row < g.rows; row += nwarps) {
+    float4 v = subtree_v4<OP>(I + row_base(g, row), 4 * lane, s, L, g);
+#pragma unroll
+    for (int h = 16; h >= 1; h >>= 1) {
+      float4 o;
+      o.x = __shfl_down_sync(0xffffffffu, v.x, h); o.y = __shfl_down_sync(0xffffffffu, v.y, h);
+      o.z = __shfl_down_sync(0xffffffffu, v.z, h); o.w = __shfl_down_sync(0xffffffffu, v.w, h);
+      if (lane < h) v = comb4<OP>(v, o);
+    }
+    if (lane == 0) {
+      float r = comb<OP>(comb<OP>(v.x, v.z), comb<OP>(v.y, v.w));
+      if (mean_div != 0.0f) r = __fdiv_rn(r, mean_div);
+      O[row] = acc ? __fadd_rn(O[row], r) : r;
+    }
+  }
+}
+
+// 128-bit variant of reduce_parts_kernel.  rows_vec != 0: a thread owns four adjacent kept
+// rows (inner % 4 == 0) of one c0; else four adjacent columns c0..c0+3 of one row (inner == 1,
+// mid == 1).  Either way its four results are adjacent in O / P.
+template <int OP>
+__global__ void __launch_bounds__(kThreads)
+reduce_parts4_kernel(float* __restrict__ O, float* __restrict__ P, const float* __restrict__ I,
+                     RedGeom g, Levels L, int s, int rows_vec, int acc, float mean_div) {
+  const int64_t parts = L.n[s];
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  if (rows_vec) {
+    const int64_t rows4 = g.rows >> 2;
+    const int64_t total = rows4 * parts;
+    const int64_t mi = g.mid * g.inner;
+    for (int64_t gid = tid; gid < total; gid += nthreads) {
+      const int64_t c0 = gid / rows4;
+      const int64_t row = (gid - c0 * rows4) << 2;
+      float4 v = subtree_v4<OP>(I + row_base(g, row), c0, s, L, g);
+      if (parts == 1) {
+        if (mean_div != 0.0f) {
+          v.x = __fdiv_rn(v.x, mean_div); v.y = __fdiv_rn(v.y, mean_div);
+          v.z = __fdiv_rn(v.z, mean_div); v.w = __fdiv_rn(v.w, mean_div);
+        }
+        float4* dst = reinterpret_cast<float4*>(O + row);
+        if (acc) { const float4 o = *dst; v.x = __fadd_rn(o.x, v.x); v.y = __fadd_rn(o.y, v.y); v.z = __fadd_rn(o.z, v.z); v.w = __fadd_rn(o.w, v.w); }
+        *dst = v;
+      } else {
+        const int64_t outer_i = row / mi;
+        const int64_t rem = row - outer_i * mi;
+        *reinterpret_cast<float4*>(P + (outer_i * parts + c0) * mi + rem) = v;
+      }
+    }
+  } else {
+    const int64_t parts4 = parts >> 2;
+    const int64_t total = g.rows * parts4;
+    for (int64_t gid = tid; gid < total; gid += nthreads) {
+      const int64_t row = gid / parts4;
+      const int64_t c0 = (gid - row * parts4) << 2;
+      const float4 v = subtree_v4<OP>(I + row_base(g, row), c0, s, L, g);
+      *reinterpret_cast<float4*>(P + row * parts + c0) = v;     // mid == inner == 1: [row][parts]
+    }
+  }
+}
+
 // dI += dO[row] (/ COLS)   (reduce.py:250-260)
 __global__ void __launch_bounds__(kThreads)
 reduce_bwd_bcast_kernel(float* __restrict__ dI, const float* __restrict__ dO, int64_t total,
@@ -176,8 +397,7 @@ reduce_bwd_select_kernel(float* __restrict__ dI, const float* __restrict__ I,
     const int64_t base = row_base(g, row);
     const float o = O[row];
     for (int64_t c = 0; c < cols; ++c) {
-      const int64_t q = c / g.r1;
-      const int64_t off = base + q * g.stride_r0 + (c - q * g.r1) * g.stride_r1;
+      const int64_t off = base + leaf_offset(g, c);
       if (I[off] == o) {
         dI[off] = __fadd_rn(dI[off], dO[row]);
         break;
@@ -205,6 +425,7 @@ void make_levels(Levels& L, int64_t cols) {
     ++s;
   }
   L.S = s;
+  L.pow2 = (cols & (cols - 1)) == 0;
   for (int j = s + 1; j <= kMaxLevels; ++j) L.n[j] = 1;
 }
 
@@ -216,11 +437,39 @@ inline int grid_for(const lnn::Device* d, int64_t work_items) {
   return (int)blocks;
 }
 
+// Where the partial values of split rows live: pooled memory (lnn_reduce) or a caller-given
+// fixed region (lnn_reduce_noalloc).
+struct PartialSpace {
+  lnn::Device* d;
+  float* fixed = nullptr;       // non-null: bump-allocate from [fixed, fixed + cap)
+  int64_t cap = 0;
+  std::vector<std::pair<void*, uint64_t>> pooled;
+  explicit PartialSpace(lnn::Device* dev) : d(dev) {}
+  ~PartialSpace() { for (auto& b : pooled) lnn::free_bytes(d, b.first, b.second); }
+  int get(int64_t floats, float** out) {
+    if (fixed) {
+      const int64_t need = (floats + 63) & ~63ll;
+      if (need > cap)
+        return lnn::set_error(LNN_E_UNSUPPORTED,
+                              "reduction needs %lld more floats of scratch but the static scratch has %lld "
+                              "left (1 MiB in total): use lnn_reduce", (long long)need, (long long)cap);
+      *out = fixed; fixed += need; cap -= need;
+      return LNN_OK;
+    }
+    void* p = nullptr;
+    int rc = lnn::alloc_bytes(d, (uint64_t)floats * 4, &p);
+    if (rc) return rc;
+    pooled.push_back({p, (uint64_t)floats * 4});
+    *out = (float*)p;
+    return LNN_OK;
+  }
+};
+
 // Plans one reduction as 1..3 launches.  mean_div is the ORIGINAL column count (as float)
 // for mean, 0 otherwise; it is applied only where a row is finished.
 template <int OP>
-int reduce_impl(lnn::Device* d, float* O, const float* I, int64_t outer, int64_t r0, int64_t mid,
-                int64_t r1, int64_t inner, int acc, float mean_div) {
+int reduce_impl(lnn::Device* d, PartialSpace& space, float* O, const float* I, int64_t outer,
+                int64_t r0, int64_t mid, int64_t r1, int64_t inner, int acc, float mean_div) {
   RedGeom g;
   int rc = make_geom(g, outer, r0, mid, r1, inner);
   if (rc) return rc;
@@ -229,10 +478,32 @@ int reduce_impl(lnn::Device* d, float* O, const float* I, int64_t outer, int64_t
   const int64_t cols = r0 * r1;
   const int64_t kTargetThreads = 1 << 19;
   if (inner == 1) {
-    int s_block = 0;                       // smallest s with n[s] <= 256
-    while (L.n[s_block] > kThreads) ++s_block;
     const bool split = (g.rows * kThreads < kTargetThreads / 2) && cols > 65536;
+    // 128-bit paths need contiguous, 16-byte aligned columns
+    const bool cols_vec = L.pow2 && ((((uintptr_t)I) & 15) == 0) &&
+                          (r0 == 1 || (r1 % 4 == 0 && g.stride_r0 % 4 == 0)) && g.stride_mid % 4 == 0 &&
+                          g.stride_outer % 4 == 0;
     if (!split) {
+      if (cols_vec && cols >= 128 && L.S - 7 <= kMaxPow2Levels) {
+        const int s = L.S - 7;                           // 128 partials per row, four per lane
+        int64_t blocks = lnn_ceil_div(g.rows, kThreads / 32);
+        const int64_t cap = (int64_t)d->sm_count * 16;
+        if (blocks > cap) blocks = cap;
+        reduce_warp4_kernel<OP><<<(unsigned)blocks, kThreads, 0, d->stream>>>(O, I, g, L, s, acc, mean_div);
+        LNN_CHECK_LAUNCH(d);
+        return LNN_OK;
+      }
+      if (L.pow2 && L.S - 5 <= kMaxPow2Levels) {
+        const int s = L.S > 5 ? L.S - 5 : 0;           // n[s] = min(cols, 32) partials per row
+        int64_t blocks = lnn_ceil_div(g.rows, kThreads / 32);
+        const int64_t cap = (int64_t)d->sm_count * 16;
+        if (blocks > cap) blocks = cap;
+        reduce_warp_kernel<OP><<<(unsigned)blocks, kThreads, 0, d->stream>>>(O, I, g, L, s, acc, mean_div);
+        LNN_CHECK_LAUNCH(d);
+        return LNN_OK;
+      }
+      int s_block = 0;                       // smallest s with n[s] <= 256
+      while (L.n[s_block] > kThreads) ++s_block;
       int tpr = 1;
       while (tpr < L.n[s_block]) tpr <<= 1;
       const int rows_per_block = kThreads / tpr;
@@ -246,13 +517,18 @@ int reduce_impl(lnn::Device* d, float* O, const float* I, int64_t outer, int64_t
     int s = 6;                             // at least 64 leaves per thread
     while (s < L.S && g.rows * L.n[s] > kTargetThreads) ++s;
     const int64_t parts = L.n[s];
-    lnn::Scratch scratch(d);
-    rc = scratch.get((uint64_t)(g.rows * parts) * sizeof(float));
+    float* part = nullptr;
+    rc = space.get(g.rows * parts, &part);
     if (rc) return rc;
-    reduce_parts_kernel<OP><<<grid_for(d, g.rows * parts), kThreads, 0, d->stream>>>(
-        nullptr, scratch.as<float>(), I, g, L, s, 1, 0, 0.0f);
+    if (cols_vec && mid == 1 && s <= kMaxPow2Levels && parts % 4 == 0 && ((((uintptr_t)part) & 15) == 0)) {
+      reduce_parts4_kernel<OP><<<grid_for(d, g.rows * parts / 4), kThreads, 0, d->stream>>>(
+          nullptr, part, I, g, L, s, 0, 0, 0.0f);
+    } else {
+      reduce_parts_kernel<OP><<<grid_for(d, g.rows * parts), kThreads, 0, d->stream>>>(
+          nullptr, part, I, g, L, s, 1, 0, 0.0f);
+    }
     LNN_CHECK_LAUNCH(d);
-    return reduce_impl<OP>(d, O, scratch.as<float>(), outer, parts, mid, 1, 1, acc, mean_div);
+    return reduce_impl<OP>(d, space, O, part, outer, parts, mid, 1, 1, acc, mean_div);
   }
   // inner > 1: coalesce along the inner axis, one thread per output when there are enough
   int s = L.S;
@@ -261,21 +537,45 @@ int reduce_impl(lnn::Device* d, float* O, const float* I, int64_t outer, int64_t
     while (s < L.S && g.rows * L.n[s] > kTargetThreads) ++s;
   }
   const int64_t parts = L.n[s];
+  // four adjacent kept rows per thread when the inner axis allows 128-bit loads
+  const bool rows_vec = L.pow2 && s <= kMaxPow2Levels && inner % 4 == 0 && ((((uintptr_t)I) & 15) == 0) &&
+                        ((((uintptr_t)O) & 15) == 0);
   if (parts == 1) {
-    reduce_parts_kernel<OP><<<grid_for(d, g.rows), kThreads, 0, d->stream>>>(
-        O, nullptr, I, g, L, L.S, 0, acc, mean_div);
+    if (rows_vec)
+      reduce_parts4_kernel<OP><<<grid_for(d, g.rows / 4), kThreads, 0, d->stream>>>(
+          O, nullptr, I, g, L, L.S, 1, acc, mean_div);
+    else
+      reduce_parts_kernel<OP><<<grid_for(d, g.rows), kThreads, 0, d->stream>>>(
+          O, nullptr, I, g, L, L.S, 0, acc, mean_div);
     LNN_CHECK_LAUNCH(d);
     return LNN_OK;
   }
-  lnn::Scratch scratch(d);
-  rc = scratch.get((uint64_t)(g.rows * parts) * sizeof(float));
+  float* part = nullptr;
+  rc = space.get(g.rows * parts, &part);
   if (rc) return rc;
-  reduce_parts_kernel<OP><<<grid_for(d, g.rows * parts), kThreads, 0, d->stream>>>(
-      nullptr, scratch.as<float>(), I, g, L, s, 0, 0, 0.0f);
+  if (rows_vec && ((((uintptr_t)part) & 15) == 0))
+    reduce_parts4_kernel<OP><<<grid_for(d, g.rows * parts / 4), kThreads, 0, d->stream>>>(
+        nullptr, part, I, g, L, s, 1, 0, 0.0f);
+  else
+    reduce_parts_kernel<OP><<<grid_for(d, g.rows * parts), kThreads, 0, d->stream>>>(
+        nullptr, part, I, g, L, s, 0, 0, 0.0f);
   LNN_CHECK_LAUNCH(d);
-  return reduce_impl<OP>(d, O, scratch.as<float>(), outer, parts, 1, 1, mid * inner, acc, mean_div);
+  return reduce_impl<OP>(d, space, O, part, outer, parts, 1, 1, mid * inner, acc, mean_div);
 }
 
+int reduce_dispatch(lnn::Device* d, PartialSpace& space, int op, uint64_t O, uint64_t I, int64_t outer,
+                    int64_t r0, int64_t mid, int64_t r1, int64_t inner, int accumulate) {
+  float* o = (float*)(uintptr_t)O;
+  const float* i = (const float*)(uintptr_t)I;
+  const float cols_f = (float)(r0 * r1);
+  switch (op) {
+    case LNN_RED_SUM: return reduce_impl<LNN_RED_SUM>(d, space, o, i, outer, r0, mid, r1, inner, accumulate, 0.0f);
+    case LNN_RED_MEAN: return reduce_impl<LNN_RED_SUM>(d, space, o, i, outer, r0, mid, r1, inner, accumulate, cols_f);
+    case LNN_RED_MAX: return reduce_impl<LNN_RED_MAX>(d, space, o, i, outer, r0, mid, r1, inner, accumulate, 0.0f);
+    case LNN_RED_MIN: return reduce_impl<LNN_RED_MIN>(d, space, o, i, outer, r0, mid, r1, inner, accumulate, 0.0f);
+  }
+  return lnn::set_error(LNN_E_INVALID, "unknown reduce op %d", op);
+}
 
 // ---- reduction without any allocation ---------------------------------------------------------
 // Partial results of split rows live in this fixed device array instead of pooled memory.
@@ -300,66 +600,6 @@ int static_scratch_for(lnn::Device* d, int dev, float** out) {
   return LNN_OK;
 }
 
-// Same plan as reduce_impl, with the partial buffers carved from [scratch, scratch + cap).
-template <int OP>
-int reduce_impl_static(lnn::Device* d, float* O, const float* I, int64_t outer, int64_t r0, int64_t mid,
-                       int64_t r1, int64_t inner, int acc, float mean_div, float* scratch, int64_t cap) {
-  RedGeom g;
-  int rc = make_geom(g, outer, r0, mid, r1, inner);
-  if (rc) return rc;
-  Levels L;
-  make_levels(L, r0 * r1);
-  const int64_t cols = r0 * r1;
-  const int64_t kTargetThreads = 1 << 19;
-  if (inner == 1) {
-    int s_block = 0;
-    while (L.n[s_block] > kThreads) ++s_block;
-    const bool split = (g.rows * kThreads < kTargetThreads / 2) && cols > 65536;
-    if (!split) {
-      int tpr = 1;
-      while (tpr < L.n[s_block]) tpr <<= 1;
-      const int rows_per_block = kThreads / tpr;
-      const int64_t blocks = lnn_ceil_div(g.rows, rows_per_block);
-      LNN_REQUIRE(blocks < (1ll << 31), "too many rows");
-      reduce_rowcoop_kernel<OP><<<(unsigned)blocks, kThreads, 0, d->stream>>>(O, I, g, L, s_block, tpr, acc, mean_div);
-      LNN_CHECK_LAUNCH(d);
-      return LNN_OK;
-    }
-    int s = 6;
-    while (s < L.S && g.rows * L.n[s] > kTargetThreads) ++s;
-    const int64_t parts = L.n[s];
-    const int64_t need = (g.rows * parts + 63) & ~63ll;
-    if (need > cap)
-      return lnn::set_error(LNN_E_UNSUPPORTED,
-                            "reduction needs %lld floats of scratch but the static scratch holds %lld "
-                            "(1 MiB in total): use lnn_reduce", (long long)need, (long long)cap);
-    reduce_parts_kernel<OP><<<grid_for(d, g.rows * parts), kThreads, 0, d->stream>>>(
-        nullptr, scratch, I, g, L, s, 1, 0, 0.0f);
-    LNN_CHECK_LAUNCH(d);
-    return reduce_impl_static<OP>(d, O, scratch, outer, parts, mid, 1, 1, acc, mean_div, scratch + need, cap - need);
-  }
-  int s = L.S;
-  if (g.rows < 65536 && cols > 256) {
-    s = 4;
-    while (s < L.S && g.rows * L.n[s] > kTargetThreads) ++s;
-  }
-  const int64_t parts = L.n[s];
-  if (parts == 1) {
-    reduce_parts_kernel<OP><<<grid_for(d, g.rows), kThreads, 0, d->stream>>>(O, nullptr, I, g, L, L.S, 0, acc, mean_div);
-    LNN_CHECK_LAUNCH(d);
-    return LNN_OK;
-  }
-  const int64_t need = (g.rows * parts + 63) & ~63ll;
-  if (need > cap)
-    return lnn::set_error(LNN_E_UNSUPPORTED,
-                          "reduction needs %lld floats of scratch but the static scratch holds %lld "
-                          "(1 MiB in total): use lnn_reduce", (long long)need, (long long)cap);
-  reduce_parts_kernel<OP><<<grid_for(d, g.rows * parts), kThreads, 0, d->stream>>>(
-      nullptr, scratch, I, g, L, s, 0, 0, 0.0f);
-  LNN_CHECK_LAUNCH(d);
-  return reduce_impl_static<OP>(d, O, scratch, outer, parts, 1, 1, mid * inner, acc, mean_div, scratch + need, cap - need);
-}
-
 }  // namespace
 
 extern "C" {
@@ -369,16 +609,8 @@ int lnn_reduce(int dev, int op, uint64_t O, uint64_t I, int64_t outer, int64_t r
   LNN_DEV(d, dev);
   LNN_REQUIRE(O && I, "null buffer");
   LNN_REQUIRE(outer >= 1 && r0 >= 1 && mid >= 1 && r1 >= 1 && inner >= 1, "bad reduce extents");
-  float* o = (float*)(uintptr_t)O;
-  const float* i = (const float*)(uintptr_t)I;
-  const float cols_f = (float)(r0 * r1);
-  switch (op) {
-    case LNN_RED_SUM: return reduce_impl<LNN_RED_SUM>(d, o, i, outer, r0, mid, r1, inner, accumulate, 0.0f);
-    case LNN_RED_MEAN: return reduce_impl<LNN_RED_SUM>(d, o, i, outer, r0, mid, r1, inner, accumulate, cols_f);
-    case LNN_RED_MAX: return reduce_impl<LNN_RED_MAX>(d, o, i, outer, r0, mid, r1, inner, accumulate, 0.0f);
-    case LNN_RED_MIN: return reduce_impl<LNN_RED_MIN>(d, o, i, outer, r0, mid, r1, inner, accumulate, 0.0f);
-  }
-  return lnn::set_error(LNN_E_INVALID, "unknown reduce op %d", op);
+  PartialSpace space(d);
+  return reduce_dispatch(d, space, op, O, I, outer, r0, mid, r1, inner, accumulate);
 }
 
 int lnn_reduce_bwd(int dev, int op, uint64_t dI, uint64_t I, uint64_t dO, uint64_t O, int64_t outer,
@@ -413,7 +645,7 @@ int lnn_reduce_bwd(int dev, int op, uint64_t dI, uint64_t I, uint64_t dO, uint64
 // kept in a fixed 1 MiB device array that belongs to the library (one copy per device,
 // held until the process exits) instead of pooled memory.
 //  * Reductions whose partials do not fit (more than 2^18 floats) are refused with
-//    LNN_E_UNSUPPORTED; nothing is launched in that case.
+//    LNN_E_UNSUPPORTED; nothing more is launched once that is found.
 //  * The first call on a device resolves the array's device address (one
 //    cudaGetSymbolAddress, no allocation); make that first call before any stream capture.
 //  * All calls share the one array and it keeps whatever the previous call left; every
@@ -428,17 +660,10 @@ int lnn_reduce_noalloc(int dev, int op, uint64_t O, uint64_t I, int64_t outer, i
   float* scratch = nullptr;
   int rc = static_scratch_for(d, dev, &scratch);
   if (rc) return rc;
-  float* o = (float*)(uintptr_t)O;
-  const float* i = (const float*)(uintptr_t)I;
-  const float cols_f = (float)(r0 * r1);
-  const int64_t cap = kStaticScratchFloats;
-  switch (op) {
-    case LNN_RED_SUM: return reduce_impl_static<LNN_RED_SUM>(d, o, i, outer, r0, mid, r1, inner, accumulate, 0.0f, scratch, cap);
-    case LNN_RED_MEAN: return reduce_impl_static<LNN_RED_SUM>(d, o, i, outer, r0, mid, r1, inner, accumulate, cols_f, scratch, cap);
-    case LNN_RED_MAX: return reduce_impl_static<LNN_RED_MAX>(d, o, i, outer, r0, mid, r1, inner, accumulate, 0.0f, scratch, cap);
-    case LNN_RED_MIN: return reduce_impl_static<LNN_RED_MIN>(d, o, i, outer, r0, mid, r1, inner, accumulate, 0.0f, scratch, cap);
-  }
-  return lnn::set_error(LNN_E_INVALID, "unknown reduce op %d", op);
+  PartialSpace space(d);
+  space.fixed = scratch;
+  space.cap = kStaticScratchFloats;
+  return reduce_dispatch(d, space, op, O, I, outer, r0, mid, r1, inner, accumulate);
 }
 
 }  // extern "C"

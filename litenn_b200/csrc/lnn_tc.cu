@@ -33,6 +33,17 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "memory");
   return ok;
 }
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
 // Bounded wait.  Returns false when the budget ran out or another role aborted.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int role, int step) {
@@ -146,17 +157,58 @@ __device__ __forceinline__ float apply_act(float v, int act, float alpha) {
 }
 
 // =========================================================================================
-// the tile kernel
+// the tile kernel: persistent, one CTA per SM, two TMEM accumulators
 // =========================================================================================
+struct TileCoord {
+  int m0, n0, bz;                 // GEMM
+  int pb0, pa0, pn0;              // CONV pixel-tile origin (logical output coordinates)
+  int split, oc_t, ic_t, tap, patch0;   // DW
+  int num_kb;
+};
+
 template <int MODE>
-__global__ void __launch_bounds__(kThreadsTc)
+__device__ __forceinline__ TileCoord decode_tile(const TcParams& p, int tile) {
+  TileCoord t;
+  t.m0 = t.n0 = t.bz = t.pb0 = t.pa0 = t.pn0 = t.split = t.oc_t = t.ic_t = t.tap = t.patch0 = 0;
+  t.num_kb = p.num_kb;
+  const int x = tile % p.grid_x;
+  const int r = tile / p.grid_x;
+  const int y = r % p.grid_y;
+  const int z = r / p.grid_y;
+  if (MODE == MODE_GEMM) {
+    t.m0 = x * 128; t.n0 = y * p.bn; t.bz = z;
+  } else if (MODE == MODE_CONV || MODE == MODE_CONVT) {
+    const int bt = x % p.tiles_b;
+    const int at = (x / p.tiles_b) % p.tiles_a;
+    const int nt = x / (p.tiles_b * p.tiles_a);
+    t.pb0 = bt * p.tw; t.pa0 = at * p.th; t.pn0 = nt * p.tn;
+    if (MODE == MODE_CONV) t.n0 = y * p.bn; else t.m0 = y * 128;
+  } else {
+    t.split = x;
+    t.oc_t = y / p.ic_tiles;
+    t.ic_t = y % p.ic_tiles;
+    t.tap = z;
+    t.patch0 = x * p.patches_per_split;
+    t.num_kb = min(p.patches_per_split, p.patches_total - t.patch0);
+    if (t.num_kb < 0) t.num_kb = 0;
+  }
+  return t;
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreadsTc, 1)
 tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
           const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
           const __grid_constant__ TcParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t full_bar[8];
   __shared__ uint64_t empty_bar[8];
-  __shared__ uint64_t accum_bar;
+  __shared__ uint64_t tmem_full_bar[2];
+  __shared__ uint64_t tmem_empty_bar[2];
   __shared__ uint32_t tmem_base_smem;
   __shared__ int abort_flag_smem;
 
@@ -174,31 +226,8 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
   const int nbuf = p.passes == 3 ? 2 : 1;
   const uint32_t a_sz = (uint32_t)((p.a_tile_bytes + 1023) & ~1023);
   const uint32_t b_sz = (uint32_t)((p.b_tile_bytes + 1023) & ~1023);
-  const uint32_t stage_sz = nbuf * (a_sz + b_sz);
-
-  // ---- tile coordinates -----------------------------------------------------------------
-  int m0 = 0, n0 = 0, bz = 0;              // GEMM
-  int pb0 = 0, pa0 = 0, pn0 = 0;           // CONV pixel-tile origin (logical output coords)
-  int split = 0, oc_t = 0, ic_t = 0, tap = 0, patch0 = 0;   // DW
-  int num_kb = p.num_kb;
-  if (MODE == MODE_GEMM) {
-    m0 = blockIdx.x * 128; n0 = blockIdx.y * p.bn; bz = blockIdx.z;
-  } else if (MODE == MODE_CONV) {
-    const int pt = blockIdx.x;
-    const int bt = pt % p.tiles_b;
-    const int at = (pt / p.tiles_b) % p.tiles_a;
-    const int nt = pt / (p.tiles_b * p.tiles_a);
-    pb0 = bt * p.tw; pa0 = at * p.th; pn0 = nt * p.tn;
-    n0 = blockIdx.y * p.bn;
-  } else {
-    split = blockIdx.x;
-    oc_t = blockIdx.y / p.ic_tiles;
-    ic_t = blockIdx.y % p.ic_tiles;
-    tap = blockIdx.z;
-    patch0 = split * p.patches_per_split;
-    num_kb = min(p.patches_per_split, p.patches_total - patch0);
-    if (num_kb < 0) num_kb = 0;
-  }
+  const uint32_t stage_sz = (uint32_t)p.kgroup * nbuf * (a_sz + b_sz);
+  const int num_tiles = p.grid_x * p.grid_y * p.grid_z;
 
   // ---- set-up ---------------------------------------------------------------------------
   if (threadIdx.x == 0) {
@@ -206,11 +235,14 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
       mbar_init(smem_u32(&full_bar[s]), 1);
       mbar_init(smem_u32(&empty_bar[s]), 1);
     }
-    mbar_init(smem_u32(&accum_bar), 1);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&tmem_full_bar[a]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[a]), 4);     // one arrival per epilogue warp
+    }
     fence_barrier_init();
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(&tmem_base_smem), p.tmem_cols);
+    tmem_alloc(smem_u32(&tmem_base_smem), 2u * p.tmem_cols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -219,56 +251,80 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
   const uint32_t tmem_base = tmem_base_smem;
 
   // ---- roles ----------------------------------------------------------------------------
+  // A stage of the ring holds `kgroup` units; a unit is one 32-wide K slab (GEMM), one
+  // (tap, channel block) pair (CONV/CONVT) or one pixel patch (DW).  The two single-thread
+  // roles below are scalar-issue bound, so their loops carry running counters instead of
+  // recomputing positions with divisions.
+  const uint32_t unit_sz = nbuf * (a_sz + b_sz);
+  const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
   if (warp == 0) {
     if (lane == 0) {
-      const uint32_t tx_bytes =
+      const uint32_t unit_tx =
           (uint32_t)nbuf * (uint32_t)(p.a_loads * p.a_load_bytes + p.b_loads * p.b_load_bytes);
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % p.stages;
-        const uint32_t ph = (uint32_t)(kb / p.stages) & 1u;
-        if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1u, abort_flag, p.status, 0, kb)) break;
-        const uint32_t fb = smem_u32(&full_bar[s]);
-        mbar_expect_tx(fb, tx_bytes);
-        const uint32_t sa = tiles + s * stage_sz;
-        const uint32_t sb = sa + nbuf * a_sz;
-        for (int half = 0; half < nbuf; ++half) {
-          const CUtensorMap* ta = half ? &tmAl : &tmAh;
-          const CUtensorMap* tb = half ? &tmBl : &tmBh;
-          const uint32_t da = sa + half * a_sz;
-          const uint32_t db = sb + half * b_sz;
-          if (MODE == MODE_GEMM) {
-            const int k0 = kb * 32;
-            if (p.a_major == 0) {
-              tma_load_3d(da, ta, fb, k0, m0, bz);
-            } else {
-              for (int i = 0; i < p.a_loads; ++i)
-                tma_load_3d(da + i * p.a_load_bytes, ta, fb, m0 + i * 32, k0, bz);
+      uint32_t s = 0, ph = 0;                           // ring position and its phase
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        const TileCoord t = decode_tile<MODE>(p, tile);
+        int units_left = t.num_kb;
+        int k0 = 0;                                     // GEMM: K offset
+        int tp = 0, cbi = 0;                            // CONV: tap, channel block
+        int pidx = t.patch0;                            // DW: patch
+        const int cx = t.pb0 * p.es, cy = t.pa0 * p.es;
+        while (units_left > 0) {
+          const int nun = min(p.kgroup, units_left);
+          if (!mbar_wait(empty0 + 8u * s, ph ^ 1u, abort_flag, p.status, 0, units_left)) { ok = false; break; }
+          const uint32_t fb = full0 + 8u * s;
+          if (p.debug & 2) { mbar_arrive(fb); }         // timing experiment: no loads
+          else {
+            mbar_expect_tx(fb, unit_tx * (uint32_t)nun);
+            uint32_t dst = tiles + s * stage_sz;
+            for (int u = 0; u < nun; ++u, dst += unit_sz) {
+              for (int half = 0; half < nbuf; ++half) {
+                const CUtensorMap* ta = half ? &tmAl : &tmAh;
+                const CUtensorMap* tb = half ? &tmBl : &tmBh;
+                const uint32_t da = dst + half * a_sz;
+                const uint32_t db = dst + nbuf * a_sz + half * b_sz;
+                if (MODE == MODE_GEMM) {
+                  if (p.a_major == 0) {
+                    tma_load_3d(da, ta, fb, k0, t.m0, t.bz);
+                  } else {
+                    for (int i = 0; i < p.a_loads; ++i)
+                      tma_load_3d(da + i * p.a_load_bytes, ta, fb, t.m0 + i * 32, k0, t.bz);
+                  }
+                  if (p.b_major == 0) {
+                    tma_load_3d(db, tb, fb, k0, t.n0, t.bz);
+                  } else {
+                    for (int i = 0; i < p.b_loads; ++i)
+                      tma_load_3d(db + i * p.b_load_bytes, tb, fb, t.n0 + i * 32, k0, t.bz);
+                  }
+                } else if (MODE == MODE_CONV) {
+                  tma_load_4d(da, ta, fb, cbi * p.cb, cx + p.tap_dx[tp], cy + p.tap_dy[tp], t.pn0);
+                  tma_load_3d(db, tb, fb, cbi * p.cb, t.n0, p.tap_w[tp]);
+                } else if (MODE == MODE_CONVT) {
+                  // channels on M: the kernel tile is operand A, the pixel patch operand B
+                  tma_load_3d(da, ta, fb, cbi * p.cb, t.m0, p.tap_w[tp]);
+                  tma_load_4d(db, tb, fb, cbi * p.cb, cx + p.tap_dx[tp], cy + p.tap_dy[tp], t.pn0);
+                } else {
+                  const int bt = pidx % p.tiles_b;
+                  const int at = (pidx / p.tiles_b) % p.tiles_a;
+                  const int nt = pidx / (p.tiles_b * p.tiles_a);
+                  const int ea = p.swz_a >> 2, eb = p.swz_b >> 2;
+                  for (int i = 0; i < p.a_loads; ++i)
+                    tma_load_4d(da + i * p.a_load_bytes, ta, fb, t.oc_t * 128 + i * ea, bt * p.tw,
+                                at * p.th, nt * p.tn);
+                  for (int i = 0; i < p.b_loads; ++i)
+                    tma_load_4d(db + i * p.b_load_bytes, tb, fb, t.ic_t * p.bn + i * eb,
+                                bt * p.tw * p.es + p.tap_dx[t.tap], at * p.th * p.es + p.tap_dy[t.tap],
+                                nt * p.tn);
+                }
+              }
+              k0 += 32;
+              if (++cbi == p.ncb) { cbi = 0; ++tp; }
+              ++pidx;
             }
-            if (p.b_major == 0) {
-              tma_load_3d(db, tb, fb, k0, n0, bz);
-            } else {
-              for (int i = 0; i < p.b_loads; ++i)
-                tma_load_3d(db + i * p.b_load_bytes, tb, fb, n0 + i * 32, k0, bz);
-            }
-          } else if (MODE == MODE_CONV) {
-            const int t = kb / p.ncb;
-            const int cbi = kb - t * p.ncb;
-            tma_load_4d(da, ta, fb, cbi * p.cb, pb0 * p.es + p.tap_dx[t], pa0 * p.es + p.tap_dy[t], pn0);
-            tma_load_3d(db, tb, fb, cbi * p.cb, n0, p.tap_w[t]);
-          } else {
-            const int pidx = patch0 + kb;
-            const int bt = pidx % p.tiles_b;
-            const int at = (pidx / p.tiles_b) % p.tiles_a;
-            const int nt = pidx / (p.tiles_b * p.tiles_a);
-            const int ea = p.swz_a >> 2, eb = p.swz_b >> 2;
-            for (int i = 0; i < p.a_loads; ++i)
-              tma_load_4d(da + i * p.a_load_bytes, ta, fb, oc_t * 128 + i * ea, bt * p.tw,
-                          at * p.th, nt * p.tn);
-            for (int i = 0; i < p.b_loads; ++i)
-              tma_load_4d(db + i * p.b_load_bytes, tb, fb, ic_t * p.bn + i * eb,
-                          bt * p.tw * p.es + p.tap_dx[tap], at * p.th * p.es + p.tap_dy[tap],
-                          nt * p.tn);
           }
+          units_left -= nun;
+          if (++s == (uint32_t)p.stages) { s = 0; ph ^= 1u; }
         }
       }
     }
@@ -282,81 +338,174 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
       const uint32_t a_lbo = p.a_major ? (uint32_t)(p.a_krows * p.swz_a) : 16u;
       const uint32_t b_lbo = p.b_major ? (uint32_t)(p.b_krows * p.swz_b) : 16u;
       const uint32_t a_sbo = (p.a_major ? 4u : 8u) * p.swz_a, b_sbo = (p.b_major ? 4u : 8u) * p.swz_b;
-      const uint32_t a_step = p.a_major ? 8u * p.swz_a : 32u;
-      const uint32_t b_step = p.b_major ? 8u * p.swz_b : 32u;
+      // descriptors with a zero start address; the address field (bits 0-13, 16-byte units)
+      // is added per use -- shared memory addresses stay below 2^18, so no carry leaves it
+      const uint64_t a_desc0 = make_smem_desc(0u, a_lbo, a_sbo, la);
+      const uint64_t b_desc0 = make_smem_desc(0u, b_lbo, b_sbo, lb);
+      const uint64_t a_step16 = (p.a_major ? 8u * p.swz_a : 32u) >> 4;
+      const uint64_t b_step16 = (p.b_major ? 8u * p.swz_b : 32u) >> 4;
+      const uint64_t a_lo16 = a_sz >> 4, b_lo16 = b_sz >> 4;
+      const int ksteps = (p.debug & 1) ? 0 : p.ksteps;     // debug bit 0: no MMAs
+      const uint32_t idesc = p.idesc;
+      uint32_t s = 0, ph = 0;
+      int it = 0;                                       // tiles processed by this CTA
       bool ok = true;
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % p.stages;
-        const uint32_t ph = (uint32_t)(kb / p.stages) & 1u;
-        if (!mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag, p.status, 1, kb)) { ok = false; break; }
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++it) {
+        const TileCoord t = decode_tile<MODE>(p, tile);
+        const int acc = it & 1;
+        const uint32_t acc_ph = (uint32_t)(it >> 1) & 1u;
+        // wait until the epilogue has drained this accumulator (passes at once the first time)
+        if (!mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_ph ^ 1u, abort_flag, p.status, 3, it)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t sa = tiles + s * stage_sz;
-        const uint32_t sb = sa + nbuf * a_sz;
-        for (int ks = 0; ks < p.ksteps; ++ks) {
-          const uint64_t ah = make_smem_desc(sa + ks * a_step, a_lbo, a_sbo, la);
-          const uint64_t bh = make_smem_desc(sb + ks * b_step, b_lbo, b_sbo, lb);
-          umma_tf32(tmem_base, ah, bh, p.idesc, (kb | ks) ? 1u : 0u);
-          if (nbuf == 2) {
-            const uint64_t al = make_smem_desc(sa + a_sz + ks * a_step, a_lbo, a_sbo, la);
-            const uint64_t bl = make_smem_desc(sb + b_sz + ks * b_step, b_lbo, b_sbo, lb);
-            umma_tf32(tmem_base, ah, bl, p.idesc, 1u);
-            umma_tf32(tmem_base, al, bh, p.idesc, 1u);
+        const uint32_t d_tmem = tmem_base + (uint32_t)acc * p.tmem_cols;
+        int units_left = t.num_kb;
+        uint32_t accum = 0u;                            // first MMA of a tile overwrites
+        while (units_left > 0) {
+          const int nun = min(p.kgroup, units_left);
+          if (!mbar_wait(full0 + 8u * s, ph, abort_flag, p.status, 1, units_left)) { ok = false; break; }
+          tc_fence_after();
+          uint32_t ua = tiles + s * stage_sz;
+          for (int u = 0; u < nun; ++u, ua += unit_sz) {
+            uint64_t ah = a_desc0 + (uint64_t)(ua >> 4);
+            uint64_t bh = b_desc0 + (uint64_t)((ua + nbuf * a_sz) >> 4);
+            if (nbuf == 2) {
+              for (int ks = 0; ks < ksteps; ++ks) {
+                umma_tf32(d_tmem, ah, bh, idesc, accum);
+                umma_tf32(d_tmem, ah, bh + b_lo16, idesc, 1u);
+                umma_tf32(d_tmem, ah + a_lo16, bh, idesc, 1u);
+                accum = 1u;
+                ah += a_step16; bh += b_step16;
+              }
+            } else {
+              for (int ks = 0; ks < ksteps; ++ks) {
+                umma_tf32(d_tmem, ah, bh, idesc, accum);
+                accum = 1u;
+                ah += a_step16; bh += b_step16;
+              }
+            }
           }
+          umma_commit(empty0 + 8u * s);                 // frees the stage when these MMAs retire
+          units_left -= nun;
+          if (++s == (uint32_t)p.stages) { s = 0; ph ^= 1u; }
         }
-        umma_commit(smem_u32(&empty_bar[s]));
+        if (ok) umma_commit(smem_u32(&tmem_full_bar[acc]));   // accumulator complete
       }
-      if (ok) umma_commit(smem_u32(&accum_bar));
     }
   } else {
     // ---- epilogue warps: TMEM lane quarter = warp % 4 --------------------------------------
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
-    bool have_acc = true;
-    if (num_kb > 0) {
-      have_acc = mbar_wait(smem_u32(&accum_bar), 0u, abort_flag, p.status, 2, 0);
+    int it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+      const TileCoord t = decode_tile<MODE>(p, tile);
+      const int acc = it & 1;
+      const uint32_t acc_ph = (uint32_t)(it >> 1) & 1u;
+      bool have_acc = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_ph, abort_flag, p.status, 2, it);
       have_acc = __all_sync(0xffffffffu, have_acc);   // tcgen05.ld below is warp-collective
+      if (!have_acc) break;
       tc_fence_after();
-    }
-    if (have_acc) {
+      const uint32_t d_tmem = tmem_base + (uint32_t)acc * p.tmem_cols;
+
+      if (MODE == MODE_CONVT) {
+        // rows = output channels, columns = the pixels of the patch (tn x th x tw, W fastest)
+        const int oc = t.m0 + r;
+        const bool row_ok = oc < p.OC;
+        const float bias_v = (row_ok && p.bias) ? __ldg(p.bias + oc) : 0.0f;
+        float* const obase = p.out + p.out_base + (int64_t)oc * p.out_sc;
+        // running (image, row, column) of the first pixel of the current group of four
+        int tn_i = 0, th_i = 0, tw_i = 0;
+        for (int c0 = 0; c0 < p.bn; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(d_tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+          tmem_ld_wait();
+          if (row_ok && !(p.debug & 4)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              const int q = c0 + j;
+              if (q < p.rows_valid) {
+                float x[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  float tt = __uint_as_float(v[j + e]);
+                  if (p.bias) tt = __fadd_rn(tt, bias_v);
+                  x[e] = apply_act(tt, p.act, p.alpha);
+                }
+                const int n = t.pn0 + tn_i, a = t.pa0 + th_i, b = t.pb0 + tw_i;
+                float* dst = obase + (int64_t)n * p.out_sn + (int64_t)a * p.out_sa + (int64_t)b * p.out_sb;
+                const bool four = (tw_i + 3 < p.tw) && (b + 3 < p.AW) && n < p.NL && a < p.AH;
+                if (four && p.out_sb == 1 && ((((uintptr_t)dst) & 15) == 0)) {
+                  float4* d4 = reinterpret_cast<float4*>(dst);
+                  if (p.accumulate) {
+                    const float4 o = *d4;
+                    x[0] = __fadd_rn(o.x, x[0]); x[1] = __fadd_rn(o.y, x[1]);
+                    x[2] = __fadd_rn(o.z, x[2]); x[3] = __fadd_rn(o.w, x[3]);
+                  }
+                  *d4 = make_float4(x[0], x[1], x[2], x[3]);
+                } else {
+                  int tn_e = tn_i, th_e = th_i, tw_e = tw_i;
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    if (q + e < p.rows_valid) {
+                      const int ne = t.pn0 + tn_e, ae = t.pa0 + th_e, be = t.pb0 + tw_e;
+                      if (ne < p.NL && ae < p.AH && be < p.AW) {
+                        float* de = obase + (int64_t)ne * p.out_sn + (int64_t)ae * p.out_sa + (int64_t)be * p.out_sb;
+                        *de = p.accumulate ? __fadd_rn(*de, x[e]) : x[e];
+                      }
+                    }
+                    if (++tw_e >= p.tw) { tw_e = 0; if (++th_e >= p.th) { th_e = 0; ++tn_e; } }
+                  }
+                }
+              }
+              tw_i += 4;
+              while (tw_i >= p.tw) { tw_i -= p.tw; if (++th_i >= p.th) { th_i = 0; ++tn_i; } }
+            }
+          }
+          __syncwarp();
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
+        continue;
+      }
       bool row_ok;
       int64_t row_off;
       int64_t col_stride = 1;
       int col0 = 0, col_limit = 0;
       if (MODE == MODE_GEMM) {
-        const int64_t m = (int64_t)m0 + r;
+        const int64_t m = (int64_t)t.m0 + r;
         row_ok = m < p.M;
-        row_off = (int64_t)bz * p.batch_stride_c + m * p.ldc;
-        col0 = n0; col_limit = (int)min((int64_t)p.bn, p.N - n0);
+        row_off = (int64_t)t.bz * p.batch_stride_c + m * p.ldc;
+        col0 = t.n0; col_limit = (int)min((int64_t)p.bn, p.N - t.n0);
       } else if (MODE == MODE_CONV) {
         const int hw = p.th * p.tw;
         const int tn_i = r / hw;
         const int rem = r - tn_i * hw;
         const int th_i = rem / p.tw;
         const int tw_i = rem - th_i * p.tw;
-        const int n = pn0 + tn_i, a = pa0 + th_i, b = pb0 + tw_i;
+        const int n = t.pn0 + tn_i, a = t.pa0 + th_i, b = t.pb0 + tw_i;
         row_ok = r < p.rows_valid && n < p.NL && a < p.AH && b < p.AW;
         row_off = p.out_base + (int64_t)n * p.out_sn + (int64_t)a * p.out_sa + (int64_t)b * p.out_sb;
         col_stride = p.out_sc;
-        col0 = n0; col_limit = min(p.bn, p.OC - n0);
+        col0 = t.n0; col_limit = min(p.bn, p.OC - t.n0);
       } else {
         row_ok = true;
-        row_off = (int64_t)split * p.part_stride_split + (int64_t)tap * p.part_stride_tap +
-                  ((int64_t)oc_t * 128 + r) * p.part_ld + (int64_t)ic_t * p.bn;
+        row_off = (int64_t)t.split * p.part_stride_split + (int64_t)t.tap * p.part_stride_tap +
+                  ((int64_t)t.oc_t * 128 + r) * p.part_ld + (int64_t)t.ic_t * p.bn;
         col0 = 0; col_limit = p.bn;
       }
       float* outp = p.out + row_off;
       const bool vec_ok = (MODE != MODE_CONV) && ((((uintptr_t)outp) & 15) == 0);
       for (int c0 = 0; c0 < p.bn; c0 += 32) {
         uint32_t v[32];
-        if (num_kb > 0) {
-          tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+        if (t.num_kb > 0) {
+          tmem_ld32(d_tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
           tmem_ld_wait();
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = 0u;
         }
-        if (!row_ok) {
-          // nothing to store for this lane
+        if (!row_ok || (p.debug & 4)) {
+          // nothing to store for this lane (debug bit 2: timing experiment without stores)
         } else if (MODE == MODE_DW) {
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
@@ -372,9 +521,9 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
             float x[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              float t = __uint_as_float(v[j + e]);
-              if (p.bias) t = __fadd_rn(t, __ldg(p.bias + col0 + c0 + j + e));
-              x[e] = apply_act(t, p.act, p.alpha);
+              float tt = __uint_as_float(v[j + e]);
+              if (p.bias) tt = __fadd_rn(tt, __ldg(p.bias + col0 + c0 + j + e));
+              x[e] = apply_act(tt, p.act, p.alpha);
             }
             float4* dst = reinterpret_cast<float4*>(outp + col0 + c0 + j);
             if (p.accumulate) {
@@ -388,17 +537,21 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             if (c0 + j < col_limit) {
-              float t = __uint_as_float(v[j]);
-              if (p.bias) t = __fadd_rn(t, __ldg(p.bias + col0 + c0 + j));
-              t = apply_act(t, p.act, p.alpha);
+              float tt = __uint_as_float(v[j]);
+              if (p.bias) tt = __fadd_rn(tt, __ldg(p.bias + col0 + c0 + j));
+              tt = apply_act(tt, p.act, p.alpha);
               float* dst = outp + (int64_t)(col0 + c0 + j) * col_stride;
-              if (p.accumulate) t = __fadd_rn(*dst, t);
-              *dst = t;
+              if (p.accumulate) tt = __fadd_rn(*dst, tt);
+              *dst = tt;
             }
           }
         }
         __syncwarp();   // reconverge before the next warp-collective TMEM load
       }
+      // this warp no longer needs the accumulator: let the MMA warp reuse it
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
     }
   }
 
@@ -413,7 +566,7 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
   }
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, p.tmem_cols);
+    tmem_dealloc(tmem_base, 2u * p.tmem_cols);
   }
 }
 
@@ -496,6 +649,33 @@ nchw_to_nhwc_split_kernel(float* __restrict__ hi, float* __restrict__ lo,
       }
     }
     __syncthreads();
+  }
+}
+
+// NCHW -> NHWC for c <= 8 channels padded to exactly 8: thread = pixel.
+__global__ void __launch_bounds__(kThreads)
+nchw_to_nhwc8_split_kernel(float* __restrict__ hi, float* __restrict__ lo, const float* __restrict__ src,
+                           int64_t n, int c, int64_t hw, int want_lo) {
+  const int64_t total = n * hw;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = tid; i < total; i += nthreads) {
+    const int64_t img = i / hw, px = i - img * hw;
+    const float* sp = src + img * (int64_t)c * hw + px;
+    float h[8], l[8];
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch) {
+      h[ch] = 0.0f; l[ch] = 0.0f;
+      if (ch < c) split1(__ldcs(sp + (int64_t)ch * hw), h[ch], l[ch]);
+    }
+    float4* ho = reinterpret_cast<float4*>(hi + i * 8);
+    ho[0] = make_float4(h[0], h[1], h[2], h[3]);
+    ho[1] = make_float4(h[4], h[5], h[6], h[7]);
+    if (want_lo) {
+      float4* lp = reinterpret_cast<float4*>(lo + i * 8);
+      lp[0] = make_float4(l[0], l[1], l[2], l[3]);
+      lp[1] = make_float4(l[4], l[5], l[6], l[7]);
+    }
   }
 }
 
@@ -625,27 +805,39 @@ int launch_tc(lnn::Device* d, dim3 grid, const CUtensorMap& ah, const CUtensorMa
   const int nbuf = p.passes == 3 ? 2 : 1;
   const int a_sz = (p.a_tile_bytes + 1023) & ~1023;
   const int b_sz = (p.b_tile_bytes + 1023) & ~1023;
-  const int stage = nbuf * (a_sz + b_sz);
+  const int unit = nbuf * (a_sz + b_sz);
+  // several small units share one stage so that a barrier round trip covers enough MMAs
+  int kgroup = env_int("LNN_TC_KGROUP", 0);
+  if (kgroup <= 0) kgroup = std::max(1, std::min(p.num_kb, (72 * 1024) / unit));
+  if (MODE == MODE_DW) kgroup = 1;
+  const int stage = kgroup * unit;
+  p.kgroup = kgroup;
   int stages = env_int("LNN_TC_STAGES", 0);
   if (stages <= 0) {
     stages = (kSmemLimit - kSmemSlack) / stage;
-    if (stages > 4) stages = 4;
+    if (stages > 6) stages = 6;
   }
   if (stages > 8) stages = 8;
   if (stages < 1 || stages * stage + kSmemSlack > kSmemLimit)
     return lnn::set_error(LNN_E_UNSUPPORTED, "operand stage of %d bytes does not fit shared memory", stage);
   p.stages = stages;
+  p.debug = env_int("LNN_TC_DEBUG", 0);     // timing experiments only; results are wrong when set
   p.status = d->status_dev;
+  // persistent launch: the logical grid is walked by one CTA per SM
+  p.grid_x = (int)grid.x; p.grid_y = (int)grid.y; p.grid_z = (int)grid.z;
+  const int64_t num_tiles = (int64_t)grid.x * grid.y * grid.z;
+  if (num_tiles >= (1ll << 31)) return lnn::set_error(LNN_E_UNSUPPORTED, "too many tiles");
+  const unsigned ctas = (unsigned)std::min<int64_t>(num_tiles, d->sm_count);
   const int smem = stages * stage + 1024;
-  static bool attr_set[3] = {false, false, false};
+  static bool attr_set[4] = {false, false, false, false};
   if (!attr_set[MODE]) {
     LNN_CUDA(cudaFuncSetAttribute(tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   kSmemLimit - 1024));
     attr_set[MODE] = true;
   }
   {
-    lnn::ProfScope prof(d, MODE);   // LNN_PROF_TC_GEMM / _CONV / _DW equal the mode numbers
-    tc_kernel<MODE><<<grid, kThreadsTc, smem, d->stream>>>(ah, al, bh, bl, p);
+    lnn::ProfScope prof(d, MODE == MODE_CONVT ? (int)LNN_PROF_TC_CONV : MODE);   // slots follow the modes
+    tc_kernel<MODE><<<ctas, kThreadsTc, smem, d->stream>>>(ah, al, bh, bl, p);
   }
   LNN_CHECK_LAUNCH(d);
   return LNN_OK;
@@ -675,24 +867,24 @@ int split_matrix(lnn::Device* d, lnn::Scratch& hi, lnn::Scratch& lo, const float
 struct PixTile { int tw, th, tn, tiles_b, tiles_a, tiles_n; };
 
 // rows of a CONV tile: up to 128 logical output pixels as tn x th x tw
-PixTile plan_conv_tile(int NL, int AH, int AW, int es) {
+PixTile plan_conv_tile(int NL, int AH, int AW, int es, int maxpix) {
   PixTile t;
-  const int wcap = std::min(128, 256 / es);
+  const int wcap = std::min(maxpix, 256 / es);
   if (AW >= wcap) { t.tw = wcap; t.th = 1; t.tn = 1; }
   else {
     t.tw = AW;
-    int hmax = std::min(std::min(AH, 128 / t.tw), 256 / es);
+    int hmax = std::min(std::min(AH, maxpix / t.tw), 256 / es);
     if (hmax < 1) hmax = 1;
     // pick th <= hmax minimising padded rows over the image height
     int best = 1; double best_eff = 0;
     for (int th = 1; th <= hmax; ++th) {
       const int tiles = (AH + th - 1) / th;
-      const double eff = (double)AH / (tiles * th) * (double)(th * t.tw) / 128.0;
+      const double eff = (double)AH / (tiles * th) * (double)(th * t.tw) / (double)maxpix;
       if (eff > best_eff + 1e-9) { best_eff = eff; best = th; }
     }
     t.th = best;
     t.tn = 1;
-    if (t.th == AH) t.tn = std::max(1, std::min(NL, 128 / (t.tw * t.th)));
+    if (t.th == AH) t.tn = std::max(1, std::min(NL, maxpix / (t.tw * t.th)));
   }
   t.tiles_b = (AW + t.tw - 1) / t.tw;
   t.tiles_a = (AH + t.th - 1) / t.th;
@@ -722,9 +914,17 @@ int nhwc_split(lnn::Device* d, lnn::Scratch& hi, lnn::Scratch& lo, const float* 
   if (rc) return rc;
   if (want_lo) { rc = lo.get(bytes); if (rc) return rc; }
   const int64_t hw = (int64_t)h * w;
+  lnn::ProfScope prof(d, LNN_PROF_PREP);
+  if (cp == 8) {
+    // few channels (the network's first layer): one thread per pixel, channel planes read
+    // coalesced, one 32-byte NHWC pixel written per thread
+    nchw_to_nhwc8_split_kernel<<<grid_for(d, (int64_t)n * hw), kThreads, 0, d->stream>>>(
+        hi.as<float>(), want_lo ? lo.as<float>() : nullptr, src, n, c, hw, want_lo);
+    LNN_CHECK_LAUNCH(d);
+    return LNN_OK;
+  }
   const int64_t tiles = (int64_t)n * ((hw + 31) / 32) * ((cp + 31) / 32);
   int64_t grid = std::min<int64_t>(tiles, (int64_t)d->sm_count * 16);
-  lnn::ProfScope prof(d, LNN_PROF_PREP);
   nchw_to_nhwc_split_kernel<<<(unsigned)grid, 256, 0, d->stream>>>(
       hi.as<float>(), want_lo ? lo.as<float>() : nullptr, src, n, c, hw, cp, want_lo);
   LNN_CHECK_LAUNCH(d);
@@ -763,21 +963,38 @@ int launch_conv_like(lnn::Device* d, const float* act_hi, const float* act_lo, i
                      int OCv, float* out, int64_t out_base, int64_t out_sn, int64_t out_sa,
                      int64_t out_sb, int64_t out_sc, const float* bias, int act, float alpha,
                      int accumulate, int passes) {
-  const int cb = chan_block(kp);
+  int cb = chan_block(kp);
+  {
+    const int cb_env = env_int("LNN_TC_CB", 0);          // tuning: channels per unit (8/16/32)
+    if ((cb_env == 8 || cb_env == 16) && cb_env < cb) cb = cb_env;
+  }
   const int swz = cb * 4;
-  PixTile t = plan_conv_tile(NL, AH, AW, es);
-  int bn = std::min(256, (OCv + 15) & ~15);
-  const int bn_env = env_int("LNN_TC_BN", 0);
-  if (bn_env >= 16 && bn_env <= 256 && bn_env % 16 == 0) bn = std::min(bn, bn_env);
+  // Orientation.  A tcgen05.mma costs about max(90, 0.45 * N) clocks whatever M carries, so the
+  // wide operand should sit on N: with more than a few output channels the pixel patch (up to
+  // 256 pixels) goes on N and the channels on M ("channels on M", MODE_CONVT); with very few
+  // output channels the pixels go on M and the channels on N.
+  int orient = env_int("LNN_TC_ORIENT", 0);     // 1 = pixels on M, 2 = channels on M
+  if (orient == 0) orient = (OCv >= 64 && OCv <= 128) ? 2 : 1;
+  const bool chan_m = orient == 2;
+  PixTile t = plan_conv_tile(NL, AH, AW, es, chan_m ? 256 : 128);
+  const int pix = t.tn * t.th * t.tw;
+  int bn;
+  if (chan_m) {
+    bn = std::max(16, (pix + 15) & ~15);
+  } else {
+    bn = std::min(256, (OCv + 15) & ~15);
+    const int bn_env = env_int("LNN_TC_BN", 0);
+    if (bn_env >= 16 && bn_env <= 256 && bn_env % 16 == 0) bn = std::min(bn, bn_env);
+  }
   TcParams p;
   memset(&p, 0, sizeof(p));
-  p.mode = MODE_CONV; p.passes = passes; p.bn = bn;
+  p.mode = chan_m ? MODE_CONVT : MODE_CONV; p.passes = passes; p.bn = bn;
   p.a_major = 0; p.b_major = 0; p.swz_a = swz; p.swz_b = swz;
   p.ksteps = cb / 8;
   p.a_tile_bytes = 128 * swz; p.b_tile_bytes = bn * swz;
   p.a_loads = 1; p.b_loads = 1;
-  p.a_load_bytes = t.tn * t.th * t.tw * swz;
-  p.b_load_bytes = bn * swz;
+  if (chan_m) { p.a_load_bytes = 128 * swz; p.b_load_bytes = pix * swz; }
+  else { p.a_load_bytes = pix * swz; p.b_load_bytes = bn * swz; }
   p.idesc = make_idesc(bn, 0, 0);
   p.tmem_cols = tmem_cols_for(bn);
   p.ncb = kp / cb; p.cb = cb; p.ntaps = ntaps;
@@ -785,30 +1002,34 @@ int launch_conv_like(lnn::Device* d, const float* act_hi, const float* act_lo, i
   p.tw = t.tw; p.th = t.th; p.tn = t.tn;
   p.tiles_b = t.tiles_b; p.tiles_a = t.tiles_a; p.tiles_n = t.tiles_n;
   p.AW = AW; p.AH = AH; p.NL = NL; p.es = es;
-  p.rows_valid = t.tn * t.th * t.tw;
+  p.rows_valid = pix;
   p.out_sn = out_sn; p.out_sa = out_sa; p.out_sb = out_sb; p.out_sc = out_sc; p.out_base = out_base;
   p.OC = OCv;
   p.accumulate = accumulate; p.act = act; p.alpha = alpha; p.bias = bias; p.out = out;
   for (int i = 0; i < ntaps; ++i) { p.tap_dy[i] = dy[i]; p.tap_dx[i] = dx[i]; p.tap_w[i] = widx[i]; }
-  CUtensorMap mah, mal, mbh, mbl;
-  int rc = encode_nhwc(&mah, act_hi, NL, H, W, kp, cb, t.tw, t.th, t.tn, es);
+  CUtensorMap act_h, act_l, w_h, w_l;
+  int rc = encode_nhwc(&act_h, act_hi, NL, H, W, kp, cb, t.tw, t.th, t.tn, es);
   if (rc) return rc;
-  rc = encode_nhwc(&mal, passes == 3 ? act_lo : act_hi, NL, H, W, kp, cb, t.tw, t.th, t.tn, es);
+  rc = encode_nhwc(&act_l, passes == 3 ? act_lo : act_hi, NL, H, W, kp, cb, t.tw, t.th, t.tn, es);
   if (rc) return rc;
   {
     uint64_t dims[3] = {(uint64_t)kp, (uint64_t)wrows, (uint64_t)wtaps};
     uint64_t str[2] = {(uint64_t)kp * 4, (uint64_t)wrows * kp * 4};
-    uint32_t box[3] = {(uint32_t)cb, (uint32_t)bn, 1};
+    uint32_t box[3] = {(uint32_t)cb, (uint32_t)(chan_m ? 128 : bn), 1};
     uint32_t es1[3] = {1, 1, 1};
-    rc = encode_map(&mbh, w_hi, 3, dims, str, box, es1, swz);
+    rc = encode_map(&w_h, w_hi, 3, dims, str, box, es1, swz);
     if (rc) return rc;
-    rc = encode_map(&mbl, passes == 3 ? w_lo : w_hi, 3, dims, str, box, es1, swz);
+    rc = encode_map(&w_l, passes == 3 ? w_lo : w_hi, 3, dims, str, box, es1, swz);
     if (rc) return rc;
   }
   const int64_t ptiles = (int64_t)t.tiles_b * t.tiles_a * t.tiles_n;
   LNN_REQUIRE(ptiles < (1ll << 31), "too many pixel tiles");
+  if (chan_m) {
+    dim3 grid((unsigned)ptiles, (unsigned)((OCv + 127) / 128), 1);
+    return launch_tc<MODE_CONVT>(d, grid, w_h, w_l, act_h, act_l, p);
+  }
   dim3 grid((unsigned)ptiles, (unsigned)((OCv + bn - 1) / bn), 1);
-  return launch_tc<MODE_CONV>(d, grid, mah, mal, mbh, mbl, p);
+  return launch_tc<MODE_CONV>(d, grid, act_h, act_l, w_h, w_l, p);
 }
 
 }  // namespace
@@ -892,6 +1113,10 @@ int lnn_conv2d_fwd(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint
   if (rc) return rc;
   LNN_REQUIRE(Y && X && W, "null buffer");
   LNN_REQUIRE(act == 0 || act == 1, "unknown activation %d", act);
+  if (lnn::conv_direct_applicable(g) && env_int("LNN_CONV_DIRECT", 1))
+    return lnn::conv_direct_fwd(d, g, (float*)(uintptr_t)Y, (const float*)(uintptr_t)X,
+                                (const float*)(uintptr_t)W, (const float*)(uintptr_t)bias, act, alpha,
+                                accumulate, 0);
   const int want_lo = tf32_passes == 3;
   const int cp = chan_pad(g->ic);
   const int taps = g->kh * g->kw;
@@ -913,6 +1138,29 @@ int lnn_conv2d_fwd(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint
                           wl.as<float>(), g->oc, taps, g->oh, g->ow, g->stride, taps, dy, dx, wi,
                           g->oc, (float*)(uintptr_t)Y, 0, (int64_t)g->oc * plane, g->ow, 1, plane,
                           (const float*)(uintptr_t)bias, act, alpha, accumulate, tf32_passes);
+}
+
+int lnn_pool2d_fwd(int dev, int mode, uint64_t O, uint64_t I, int64_t n, int64_t c, int ih, int iw,
+                   int oh, int ow, int pool, int stride, int padl, int padt);
+
+int lnn_conv2d_pool_fwd(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint64_t W,
+                        uint64_t bias, int act, float alpha, int tf32_passes) {
+  LNN_DEV(d, dev);
+  int rc = check_geom(g);
+  if (rc) return rc;
+  LNN_REQUIRE(Y && X && W, "null buffer");
+  LNN_REQUIRE(act == 0 || act == 1, "unknown activation %d", act);
+  if (lnn::conv_direct_applicable(g) && env_int("LNN_CONV_DIRECT", 1))
+    return lnn::conv_direct_fwd(d, g, (float*)(uintptr_t)Y, (const float*)(uintptr_t)X,
+                                (const float*)(uintptr_t)W, (const float*)(uintptr_t)bias, act, alpha, 0, 1);
+  // other layers: convolution into pooled scratch, then the pooling kernel
+  lnn::Scratch tmp(d);
+  rc = tmp.get((uint64_t)g->n * g->oc * g->oh * g->ow * 4);
+  if (rc) return rc;
+  rc = lnn_conv2d_fwd(dev, g, (uint64_t)(uintptr_t)tmp.p, X, W, bias, act, alpha, 0, tf32_passes);
+  if (rc) return rc;
+  return lnn_pool2d_fwd(dev, LNN_POOL_MAX, Y, (uint64_t)(uintptr_t)tmp.p, g->n, g->oc, g->oh, g->ow,
+                        (g->oh + 1) / 2, (g->ow + 1) / 2, 2, 2, 0, 0);
 }
 
 int lnn_conv2d_dx(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY, uint64_t W,

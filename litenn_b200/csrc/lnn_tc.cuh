@@ -1,9 +1,12 @@
 // tcgen05 / TMEM / TMA tile engine shared by matmul and the three convolution passes.
 //
-// One CTA (192 threads) produces one 128 x BN fp32 accumulator tile in tensor memory:
-//   warp 0    : TMA producer  -- cp.async.bulk.tensor loads into a ring of smem stages
-//   warp 1    : MMA issuer    -- one elected thread issues tcgen05.mma.kind::tf32, owns TMEM
-//   warps 2-5 : epilogue      -- tcgen05.ld the accumulator, bias / activation / "+=", store
+// One persistent CTA per SM (192 threads) walks the 128 x BN output tiles round-robin:
+//   warp 0    : TMA producer  -- cp.async.bulk.tensor loads into a ring of smem stages,
+//                                running ahead across tile boundaries
+//   warp 1    : MMA issuer    -- one elected thread issues tcgen05.mma.kind::tf32 into one of
+//                                two TMEM accumulators, owns the TMEM allocation
+//   warps 2-5 : epilogue      -- tcgen05.ld the finished accumulator, bias / activation /
+//                                "+=", store -- while the MMA warp fills the other one
 // fp32 accuracy comes from split-TF32: every operand is pre-split (by an HBM-bound pass)
 // into hi = rna_tf32(x) and lo = rna_tf32(x - hi); the MMA warp issues hi*hi + hi*lo +
 // lo*hi into the same accumulator.  Operands may be K-major or MN-major in shared memory
@@ -26,7 +29,7 @@ constexpr int kMaxTaps = 64;
 constexpr long long kWaitBudget = 1500000000ll;   // ~0.8 s of SM clocks
 constexpr int kAbortDelay = 400000;               // cycles granted to in-flight TMA copies
 
-enum { MODE_GEMM = 0, MODE_CONV = 1, MODE_DW = 2 };
+enum { MODE_GEMM = 0, MODE_CONV = 1, MODE_DW = 2, MODE_CONVT = 3 };
 
 struct TcParams {
   int mode, passes, stages, bn;
@@ -40,6 +43,9 @@ struct TcParams {
   uint32_t idesc;
   uint32_t tmem_cols;
   int num_kb;                    // k-blocks per output tile (GEMM/CONV); patches per split (DW)
+  int grid_x, grid_y, grid_z;    // logical tile grid walked by the persistent CTAs
+  int debug;                     // timing experiments: 1 no MMA, 2 no TMA loads, 4 no stores
+  int kgroup;                    // units (K slabs / tap-channel blocks / patches) per ring stage
   // GEMM
   int64_t M, N;                  // logical output extents
   int64_t ldc, batch_stride_c;

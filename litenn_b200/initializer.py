@@ -21,6 +21,14 @@ class Scalar(Initializer):
     def __str__(self): return f"Scalar ({self.value})"
 
 
+class Uninitialized(Initializer):
+    """Leaves the buffer as allocated: for tensors every element of which the producing kernel
+    overwrites (op outputs), so the zero fill of the default initializer would be wasted."""
+
+    def initialize_buffer(self, buf, shape):
+        pass
+
+
 class NumpyArray(Initializer):
     def __init__(self, np_value):
         self.np_value = np.asarray(np_value, dtype=np.float32)

@@ -9,6 +9,7 @@ import functools
 from collections.abc import Iterable
 
 from . import _lib
+from . import initializer as _initializer
 from .devices import devices
 from .info import (InfoBroadcast, InfoConv2D, InfoReduction, InfoReshape, InfoSlice, InfoTranspose)
 from .shape import TensorAxes, TensorShape
@@ -28,6 +29,14 @@ def _lib_():
     return _lib.get_lib()
 
 
+_UNINIT = _initializer.Uninitialized()
+
+
+def _out(shape):
+    """Result tensor of an op: its kernel writes every element, so no zero fill."""
+    return Tensor(shape, init=_UNINIT)
+
+
 # =============================================================================================
 # element-wise (ref: op/element_wise_op.py)
 # =============================================================================================
@@ -38,7 +47,7 @@ def _ew(name, args, input_t, output_t=None, is_add_to_output=False):
     p0, p1, flag = args
     n = input_t.shape.size
     if output_t is None:
-        output_t = Tensor(input_t.shape)
+        output_t = _out(input_t.shape)
         output_t._set_op_name(name)
         output_t._assign_gradfn(input_t, lambda O_t, dO_t: _ew_grad(name, args, input_t, O_t, dO_t))
     elif output_t.shape.size != n:
@@ -122,7 +131,7 @@ def _bin(name, a_t, b_t, output_t=None, is_add_to_output=False):
     if info.output_shape.rank > _lib.MAX_DIMS:
         raise ValueError(f"broadcast rank {info.output_shape.rank} > {_lib.MAX_DIMS} is not supported")
     if output_t is None:
-        output_t = Tensor(info.output_shape)
+        output_t = _out(info.output_shape)
         output_t._set_op_name(name)
         output_t._assign_gradfn(a_t, lambda O_t, dO_t: _bin_grad(name, info, 0, a_t, b_t, O_t, dO_t))
         output_t._assign_gradfn(b_t, lambda O_t, dO_t: _bin_grad(name, info, 1, a_t, b_t, O_t, dO_t))
@@ -188,7 +197,7 @@ def scale_bias_leaky_relu(x_t, g_t, b_t, alpha=0.1, output_t=None, is_add_to_out
         raise ValueError("expected x (N,C,H,W) and g, b with C elements")
     is_add_to_output = False if output_t is None else is_add_to_output
     if output_t is None:
-        output_t = Tensor(x_t.shape)
+        output_t = _out(x_t.shape)
         output_t._set_op_name("scale_bias_leaky_relu")
     elif output_t.shape.size != x_t.shape.size:
         raise ValueError(f"output_t must have size {x_t.shape.size}")
@@ -270,7 +279,7 @@ def reduce_op(op_type, input_t, axes=None, keepdims=False, output_t=None, is_add
     is_add_to_output = False if output_t is None else is_add_to_output
     op = _reduce_plan(op_type, input_t.shape, TensorAxes(axes, input_t.shape.rank), bool(keepdims))
     if output_t is None:
-        output_t = Tensor(op.info.output_shape)
+        output_t = _out(op.info.output_shape)
         output_t._op = op
         output_t._set_op_name(f"reduce_{op_type}")
         output_t._assign_gradfn(input_t, lambda O_t, dO_t: _reduce_grad(op, input_t, O_t, dO_t))
@@ -331,7 +340,7 @@ def transpose_op(input_t, axes_order, output_t=None, is_add_to_output=False):
     if input_t.shape.rank > _lib.MAX_DIMS:
         raise ValueError(f"rank {input_t.shape.rank} > {_lib.MAX_DIMS} is not supported")
     if output_t is None:
-        output_t = Tensor(info.output_shape)
+        output_t = _out(info.output_shape)
         output_t._set_op_name("transpose")
         output_t._assign_gradfn(input_t, lambda O_t, dO_t: transpose_op(
             dO_t, axes_order.inversed(), output_t=input_t.get_grad(), is_add_to_output=True))
@@ -380,7 +389,7 @@ def slice_op(input_t, slices, output_t=None, is_add_to_output=False):
     if output_t is None:
         if info.output_is_reshaped:
             return input_t.reshape(info.output_shape)
-        output_t = Tensor(info.output_shape)
+        output_t = _out(info.output_shape)
         output_t._set_op_name("slice")
         output_t._assign_gradfn(input_t, lambda O_t, dO_t: _slice_grad(info, input_t, dO_t))
     elif output_t.shape.size != info.output_shape.size:
@@ -419,7 +428,7 @@ def pool2D_op(op_type, input_t, pool_size=2, stride=2, padding="same"):
     N, IC, IH, IW = input_t.shape
     ci = InfoConv2D(IH, IW, pool_size, pool_size, stride, 1, padding)
     geom = (N, IC, IH, IW, ci.OH, ci.OW, pool_size, stride, ci.PADL, ci.PADT)
-    output_t = Tensor((N, IC, ci.OH, ci.OW))
+    output_t = _out((N, IC, ci.OH, ci.OW))
     output_t._set_op_name(f"{op_type}_pool2D")
     output_t._assign_gradfn(input_t, lambda O_t, dO_t: _pool_grad(op_type, geom, input_t, dO_t, O_t))
     for i, dev in _each_device():
@@ -473,7 +482,7 @@ def matmul_op(a_t, b_t, output_t=None, is_add_to_output=False):
     is_add_to_output = False if output_t is None else is_add_to_output
     batch, M, N, K, out_shape = _matmul_shapes(a_t.shape, b_t.shape)
     if output_t is None:
-        output_t = Tensor(out_shape)
+        output_t = _out(out_shape)
         output_t._set_op_name("matmul")
         output_t._assign_gradfn(a_t, lambda O_t, dO_t: _gemm(a_t.get_grad(), dO_t, b_t, None, batch, M, K, N, 0, 1, 1))
         output_t._assign_gradfn(b_t, lambda O_t, dO_t: _gemm(b_t.get_grad(), a_t, dO_t, None, batch, K, N, M, 1, 0, 1))
@@ -498,7 +507,7 @@ def dense(input_t, weight_t, bias_t=None):
     batch, M, N, K, out_shape = _matmul_shapes(input_t.shape, weight_t.shape)
     if bias_t is not None and bias_t.shape.size != N:
         raise ValueError(f"bias must have {N} elements")
-    output_t = Tensor(out_shape)
+    output_t = _out(out_shape)
     output_t._set_op_name("dense")
     output_t._assign_gradfn(input_t, lambda O_t, dO_t: _gemm(input_t.get_grad(), dO_t, weight_t, None, batch, M, K, N, 0, 1, 1))
     output_t._assign_gradfn(weight_t, lambda O_t, dO_t: _gemm(weight_t.get_grad(), input_t, dO_t, None, batch, K, N, M, 1, 0, 1))
@@ -537,7 +546,7 @@ def conv2D(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t=None,
     if bias_t is not None and bias_t.shape.size != g.oc:
         raise ValueError(f"bias must have {g.oc} elements")
     passes = _lib.tf32_passes()
-    output_t = Tensor(out_shape)
+    output_t = _out(out_shape)
     output_t._set_op_name("conv2D")
     act = 1 if activation == "leaky_relu" else 0
 
@@ -577,6 +586,26 @@ def conv2D(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t=None,
     for i, dev in _each_device():
         _lib_().lnn_conv2d_fwd(dev, ctypes.byref(g), output_t._ptr(i), input_t._ptr(i), kernel_t._ptr(i),
                                bias_t._ptr(i) if bias_t is not None else 0, act, float(alpha), 0, passes)
+    return output_t
+
+
+def conv2D_pool(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t=None, activation=None, alpha=0.1):
+    """max_pool2D(activation(conv2D(x, k) + bias), 2, 2, 'same') in one call, for inference:
+    no grad functions are registered (build the chain from nn.conv2D / nn.leaky_relu /
+    nn.max_pool2D to train).  Same values as that chain."""
+    if input_t.shape.rank != 4 or kernel_t.shape.rank != 4:
+        raise ValueError("conv2D_pool expects (N,IC,H,W) input and (OC,IC,KH,KW) kernel")
+    g, out_shape = _conv_geom(input_t.shape, kernel_t.shape, int(stride), int(dilation), padding)
+    if activation not in (None, "leaky_relu"):
+        raise ValueError(f"unknown activation {activation}")
+    if bias_t is not None and bias_t.shape.size != g.oc:
+        raise ValueError(f"bias must have {g.oc} elements")
+    output_t = _out((g.n, g.oc, (g.oh + 1) // 2, (g.ow + 1) // 2))
+    output_t._set_op_name("conv2D_pool")
+    for i, dev in _each_device():
+        _lib_().lnn_conv2d_pool_fwd(dev, ctypes.byref(g), output_t._ptr(i), input_t._ptr(i), kernel_t._ptr(i),
+                                    bias_t._ptr(i) if bias_t is not None else 0,
+                                    1 if activation == "leaky_relu" else 0, float(alpha), _lib.tf32_passes())
     return output_t
 
 

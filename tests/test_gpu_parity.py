@@ -110,6 +110,25 @@ def test_fused_conv_bias_lrelu_equals_unfused(nn_gpu):
     assert_bit_exact(fused, unfused, "conv epilogue fusion")
 
 
+@pytest.mark.parametrize("xs,ws", [((2, 3, 17, 13), (8, 3, 3, 3)), ((2, 3, 32, 32), (32, 3, 3, 3)),
+                                   ((2, 16, 12, 12), (24, 16, 3, 3)), ((1, 4, 9, 9), (5, 4, 5, 5))])
+def test_conv_pool_fusion_equals_chain(nn_gpu, xs, ws):
+    """conv2D_pool (direct FP32 kernel for IC <= 4, tile engine + pooling otherwise) against
+    the unfused chain and the oracle."""
+    import oracle as o
+    nn = nn_gpu
+    rng = np.random.default_rng(12)
+    x = rng.standard_normal(xs).astype(np.float32)
+    w = (rng.standard_normal(ws) * 0.2).astype(np.float32)
+    b = rng.uniform(-0.1, 0.1, (ws[0],)).astype(np.float32)
+    xt, wt, bt = nn.Tensor_from_value(x), nn.Tensor_from_value(w), nn.Tensor_from_value(b)
+    chain = nn.max_pool2D(nn.conv2D(xt, wt, bias_t=bt, activation="leaky_relu", alpha=0.1), 2, 2, "same").np()
+    fused = nn.conv2D_pool(xt, wt, bias_t=bt, activation="leaky_relu", alpha=0.1).np()
+    assert_bit_exact(fused, chain, "conv2D_pool vs chain")
+    want = o.pool2d_fwd("max", o.conv2d_fwd(x, w, 1, 1, "same", bias=b, act=1, alpha=0.1, accum64=True), 2, 2, "same")
+    assert_contraction_close(fused, want, ws[1] * ws[2] * ws[3], "conv2D_pool vs oracle")
+
+
 def test_softmax_ce(nn_gpu):
     ins, outs = load_golden("softmax_ce")["softmax_ce"]
     got = cases.run_case(nn_gpu, "softmax_ce", {}, ins)
