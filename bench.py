@@ -495,7 +495,6 @@ def run_ours(args):
         t = nn.Tensor((mb,) + IMG)
         lib.lnn_h2d(dev.index, t._ptr(0), host_ptr.value + j * mb * img_elems * 4, mb * img_elems * 4)
         resident.append(t)
-    stage = nn.Tensor((mb,) + IMG)
 
     def step_resident():
         last = None
@@ -503,10 +502,26 @@ def run_ours(args):
             last = model.forward(t)
         return last
 
+    stages = [nn.Tensor((mb,) + IMG), nn.Tensor((mb,) + IMG)]
+    for st in stages:
+        st._ptr(0)
+    done_ev = [ctypes.c_uint64(), ctypes.c_uint64()]
+    for ev in done_ev:
+        lib.lnn_event_create(dev.index, ctypes.byref(ev))
+        lib.lnn_event_record(dev.index, ev.value)
+
     def step_e2e():
+        """Host images in, logits out: micro-batch j+1 uploads on the copy stream while j computes."""
+        mb_bytes = mb * img_elems * 4
+        lib.lnn_h2d_prefetch(dev.index, stages[0]._ptr(0), host_ptr.value, mb_bytes, done_ev[0].value)
         for j in range(n_mb):
-            lib.lnn_h2d_async(dev.index, stage._ptr(0), host_ptr.value + j * mb * img_elems * 4, mb * img_elems * 4)
-            logits = model.forward(stage)
+            lib.lnn_wait_prefetch(dev.index)
+            if j + 1 < n_mb:
+                k = (j + 1) & 1
+                lib.lnn_h2d_prefetch(dev.index, stages[k]._ptr(0), host_ptr.value + (j + 1) * mb_bytes, mb_bytes,
+                                     done_ev[k].value)
+            logits = model.forward(stages[j & 1])
+            lib.lnn_event_record(dev.index, done_ev[j & 1].value)
             lib.lnn_d2h_async(dev.index, host_out_ptr.value + j * mb * NCLASS * 4, logits._ptr(0), mb * NCLASS * 4)
         lib.lnn_sync(dev.index)
 

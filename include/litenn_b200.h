@@ -68,6 +68,13 @@ int lnn_sync(int dev);
 /* asynchronous copies on the device stream; host memory should come from lnn_host_alloc */
 int lnn_h2d_async(int dev, uint64_t dst, const void* src, uint64_t bytes);
 int lnn_d2h_async(int dev, void* dst, uint64_t src, uint64_t bytes);
+/* Host->device copy on a second stream, so that the next batch uploads while the current one
+ * computes.  The copy starts after `after_event` (an lnn_event recorded on the compute stream
+ * after the last kernel that read `dst`; 0 = no dependency).  lnn_wait_prefetch makes the
+ * compute stream wait for every prefetch issued so far.  The reference uploads with a
+ * blocking write (minicl/CLBuffer.py:78-80). */
+int lnn_h2d_prefetch(int dev, uint64_t dst, const void* src, uint64_t bytes, uint64_t after_event);
+int lnn_wait_prefetch(int dev);
 int lnn_host_alloc(uint64_t bytes, void** ptr);   /* pinned host memory */
 int lnn_host_free(void* ptr);
 /* number of kernels this library has launched on the device since lnn_init */

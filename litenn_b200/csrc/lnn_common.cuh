@@ -16,6 +16,8 @@ struct Device {
   int ordinal = -1;
   int sm_count = 0;
   cudaStream_t stream = nullptr;
+  cudaStream_t copy_stream = nullptr;            // host->device prefetches that overlap compute
+  cudaEvent_t copy_event = nullptr;
   std::map<uint64_t, std::vector<void*>> pool;   // free buffers by exact byte size
   uint64_t allocated_bytes = 0;                  // live + pooled
   uint64_t pooled_bytes = 0;

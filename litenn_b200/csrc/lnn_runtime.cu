@@ -142,6 +142,8 @@ int lnn_init(int dev) {
                      p.major, p.minor);
   LNN_CUDA(cudaSetDevice(dev));
   LNN_CUDA(cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
+  LNN_CUDA(cudaStreamCreateWithFlags(&d->copy_stream, cudaStreamNonBlocking));
+  LNN_CUDA(cudaEventCreateWithFlags(&d->copy_event, cudaEventDisableTiming));
   LNN_CUDA(cudaMalloc(&d->status_dev, sizeof(int) * 4));
   LNN_CUDA(cudaMemset(d->status_dev, 0, sizeof(int) * 4));
   LNN_CUDA(cudaMallocHost(&d->status_host, sizeof(int) * 4));
@@ -181,6 +183,8 @@ int lnn_shutdown(int dev) {
   cudaFree(d->status_dev);
   cudaFreeHost(d->status_host);
   cudaStreamDestroy(d->stream);
+  cudaStreamDestroy(d->copy_stream);
+  cudaEventDestroy(d->copy_event);
   *d = Device();
   return LNN_OK;
 }
@@ -234,6 +238,22 @@ int lnn_d2h_async(int dev, void* dst, uint64_t src, uint64_t bytes) {
   LNN_DEV(d, dev);
   LNN_REQUIRE(dst && src, "null pointer");
   LNN_CUDA(cudaMemcpyAsync(dst, (const void*)(uintptr_t)src, bytes, cudaMemcpyDeviceToHost, d->stream));
+  return LNN_OK;
+}
+
+int lnn_h2d_prefetch(int dev, uint64_t dst, const void* src, uint64_t bytes, uint64_t after_event) {
+  LNN_DEV(d, dev);
+  LNN_REQUIRE(dst && src, "null pointer");
+  if (after_event)
+    LNN_CUDA(cudaStreamWaitEvent(d->copy_stream, (cudaEvent_t)(uintptr_t)after_event, 0));
+  LNN_CUDA(cudaMemcpyAsync((void*)(uintptr_t)dst, src, bytes, cudaMemcpyHostToDevice, d->copy_stream));
+  return LNN_OK;
+}
+
+int lnn_wait_prefetch(int dev) {
+  LNN_DEV(d, dev);
+  LNN_CUDA(cudaEventRecord(d->copy_event, d->copy_stream));
+  LNN_CUDA(cudaStreamWaitEvent(d->stream, d->copy_event, 0));
   return LNN_OK;
 }
 

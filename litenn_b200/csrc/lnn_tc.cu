@@ -163,6 +163,7 @@ struct TileCoord {
   int m0, n0, bz;                 // GEMM
   int pb0, pa0, pn0;              // CONV pixel-tile origin (logical output coordinates)
   int split, oc_t, ic_t, tap, patch0;   // DW
+  int nb0, nblk;                        // DW: first 32-wide column block and how many this tile owns
   int num_kb;
 };
 
@@ -170,6 +171,7 @@ template <int MODE>
 __device__ __forceinline__ TileCoord decode_tile(const TcParams& p, int tile) {
   TileCoord t;
   t.m0 = t.n0 = t.bz = t.pb0 = t.pa0 = t.pn0 = t.split = t.oc_t = t.ic_t = t.tap = t.patch0 = 0;
+  t.nb0 = t.nblk = 0;
   t.num_kb = p.num_kb;
   const int x = tile % p.grid_x;
   const int r = tile / p.grid_x;
@@ -185,9 +187,9 @@ __device__ __forceinline__ TileCoord decode_tile(const TcParams& p, int tile) {
     if (MODE == MODE_CONV) t.n0 = y * p.bn; else t.m0 = y * 128;
   } else {
     t.split = x;
-    t.oc_t = y / p.ic_tiles;
-    t.ic_t = y % p.ic_tiles;
-    t.tap = z;
+    t.oc_t = y;
+    t.nb0 = z * p.nb_group;                       // columns = (tap, 32-channel block) pairs
+    t.nblk = min(p.nb_group, p.nb_total - t.nb0);
     t.patch0 = x * p.patches_per_split;
     t.num_kb = min(p.patches_per_split, p.patches_total - t.patch0);
     if (t.num_kb < 0) t.num_kb = 0;
@@ -276,7 +278,10 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
           const uint32_t fb = full0 + 8u * s;
           if (p.debug & 2) { mbar_arrive(fb); }         // timing experiment: no loads
           else {
-            mbar_expect_tx(fb, unit_tx * (uint32_t)nun);
+            if (MODE == MODE_DW)
+              mbar_expect_tx(fb, (uint32_t)nbuf * (uint32_t)(p.a_loads * p.a_load_bytes + t.nblk * p.b_load_bytes));
+            else
+              mbar_expect_tx(fb, unit_tx * (uint32_t)nun);
             uint32_t dst = tiles + s * stage_sz;
             for (int u = 0; u < nun; ++u, dst += unit_sz) {
               for (int half = 0; half < nbuf; ++half) {
@@ -312,10 +317,13 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
                   for (int i = 0; i < p.a_loads; ++i)
                     tma_load_4d(da + i * p.a_load_bytes, ta, fb, t.oc_t * 128 + i * ea, bt * p.tw,
                                 at * p.th, nt * p.tn);
-                  for (int i = 0; i < p.b_loads; ++i)
-                    tma_load_4d(db + i * p.b_load_bytes, tb, fb, t.ic_t * p.bn + i * eb,
-                                bt * p.tw * p.es + p.tap_dx[t.tap], at * p.th * p.es + p.tap_dy[t.tap],
+                  int tapi = t.nb0 / p.ic_tiles, icb = t.nb0 - tapi * p.ic_tiles;
+                  for (int i = 0; i < t.nblk; ++i) {
+                    tma_load_4d(db + i * p.b_load_bytes, tb, fb, icb * eb,
+                                bt * p.tw * p.es + p.tap_dx[tapi], at * p.th * p.es + p.tap_dy[tapi],
                                 nt * p.tn);
+                    if (++icb == p.ic_tiles) { icb = 0; ++tapi; }
+                  }
                 }
               }
               k0 += 32;
@@ -489,9 +497,9 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
         col0 = t.n0; col_limit = min(p.bn, p.OC - t.n0);
       } else {
         row_ok = true;
-        row_off = (int64_t)t.split * p.part_stride_split + (int64_t)t.tap * p.part_stride_tap +
-                  ((int64_t)t.oc_t * 128 + r) * p.part_ld + (int64_t)t.ic_t * p.bn;
-        col0 = 0; col_limit = p.bn;
+        row_off = (int64_t)t.split * p.part_stride_split +
+                  ((int64_t)t.oc_t * 128 + r) * p.part_ld + (int64_t)t.nb0 * 32;
+        col0 = 0; col_limit = t.nblk * 32;
       }
       float* outp = p.out + row_off;
       const bool vec_ok = (MODE != MODE_CONV) && ((((uintptr_t)outp) & 15) == 0);
@@ -705,10 +713,10 @@ weight_split_kernel(float* __restrict__ hi, float* __restrict__ lo, const float*
   }
 }
 
-// dW[oc][ic][tap] += sum over splits of P[split][tap][ocp][icp], splits added in order
+// dW[oc][ic][tap] += sum over splits of P[split][oc][(tap, ic block, 32)], splits added in order
 __global__ void __launch_bounds__(kThreads)
 dw_finalize_kernel(float* __restrict__ dW, const float* __restrict__ P, int oc, int ic, int taps,
-                   int splits, int64_t stride_split, int64_t stride_tap, int64_t ld) {
+                   int splits, int64_t stride_split, int icb, int64_t ld) {
   const int64_t total = (int64_t)oc * ic * taps;
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
@@ -717,7 +725,7 @@ dw_finalize_kernel(float* __restrict__ dW, const float* __restrict__ P, int oc, 
     const int64_t t2 = i / taps;
     const int c = (int)(t2 % ic);
     const int o = (int)(t2 / ic);
-    const float* pp = P + (int64_t)t * stride_tap + (int64_t)o * ld + c;
+    const float* pp = P + (int64_t)o * ld + ((int64_t)t * icb + (c >> 5)) * 32 + (c & 31);
     float s = 0.0f;
     for (int k = 0; k < splits; ++k) s = __fadd_rn(s, pp[(int64_t)k * stride_split]);
     dW[i] = __fadd_rn(dW[i], s);
@@ -1233,8 +1241,14 @@ int lnn_conv2d_dw(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY, uin
   // extent of the NHWC copy are zero-filled by the TMA unit
   const int ea = 32, eb = 32;
   const int swa = 128, swb = 128;
-  int bn = std::min(256, (cp + 31) & ~31);
-  const int oc_tiles = (g->oc + 127) / 128, ic_tiles = (cp + bn - 1) / bn;
+  // Columns of the accumulator enumerate (tap, 32-channel block) pairs, so one dY patch in
+  // shared memory serves every tap; a tile owns up to 8 such blocks (N <= 256).
+  const int icb = (cp + 31) / 32;
+  const int nb_total = taps * icb;
+  const int ngroups = (nb_total + 7) / 8;
+  const int nb_group = (nb_total + ngroups - 1) / ngroups;
+  int bn = nb_group * 32;
+  const int oc_tiles = (g->oc + 127) / 128, ic_tiles = icb;
   // pixel patch = one k-block: tw x th output pixels of one image, a multiple of 8 pixels,
   // sized so that two stages of (128 + bn) x pix floats (x2 for hi/lo) fit shared memory
   const int nbuf = want_lo ? 2 : 1;
@@ -1265,14 +1279,13 @@ int lnn_conv2d_dw(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY, uin
   const int64_t patches = (int64_t)tiles_b * tiles_a * tiles_n;
   LNN_REQUIRE(patches < (1ll << 30), "too many pixel patches");
   int64_t want_ctas = (int64_t)d->sm_count * 4;
-  int64_t splits = want_ctas / ((int64_t)taps * oc_tiles * ic_tiles);
+  int64_t splits = want_ctas / ((int64_t)oc_tiles * ngroups);
   splits = std::max<int64_t>(1, std::min<int64_t>(splits, patches));
   const int pps = (int)((patches + splits - 1) / splits);
   splits = (patches + pps - 1) / pps;    // every split owns at least one patch
 
-  const int64_t part_ld = (int64_t)ic_tiles * bn;
-  const int64_t stride_tap = (int64_t)oc_tiles * 128 * part_ld;
-  const int64_t stride_split = stride_tap * taps;
+  const int64_t part_ld = (int64_t)nb_total * 32;
+  const int64_t stride_split = (int64_t)oc_tiles * 128 * part_ld;
   rc = part.get((uint64_t)splits * stride_split * 4);
   if (rc) return rc;
 
@@ -1291,8 +1304,9 @@ int lnn_conv2d_dw(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY, uin
   p.tiles_b = tiles_b; p.tiles_a = tiles_a; p.tiles_n = tiles_n;
   p.es = s;
   p.patches_total = (int)patches; p.patches_per_split = pps; p.num_kb = pps;
-  p.part_stride_split = stride_split; p.part_stride_tap = stride_tap; p.part_ld = part_ld;
+  p.part_stride_split = stride_split; p.part_stride_tap = 0; p.part_ld = part_ld;
   p.oc_tiles = oc_tiles; p.ic_tiles = ic_tiles;
+  p.nb_total = nb_total; p.nb_group = nb_group;
   p.OC = g->oc; p.ICv = g->ic;
   p.out = part.as<float>();
   for (int kh = 0; kh < g->kh; ++kh)
@@ -1312,12 +1326,12 @@ int lnn_conv2d_dw(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY, uin
   if (rc) return rc;
   rc = encode_nhwc(&mbl, want_lo ? xl.as<float>() : xh.as<float>(), g->n, g->ih, g->iw, cp, eb, tw, th, 1, s, true);
   if (rc) return rc;
-  dim3 grid((unsigned)splits, (unsigned)(oc_tiles * ic_tiles), (unsigned)taps);
+  dim3 grid((unsigned)splits, (unsigned)oc_tiles, (unsigned)ngroups);
   rc = launch_tc<MODE_DW>(d, grid, mah, mal, mbh, mbl, p);
   if (rc) return rc;
   dw_finalize_kernel<<<grid_for(d, (int64_t)g->oc * g->ic * taps), kThreads, 0, d->stream>>>(
       (float*)(uintptr_t)dW, part.as<float>(), g->oc, g->ic, taps, (int)splits, stride_split,
-      stride_tap, part_ld);
+      icb, part_ld);
   LNN_CHECK_LAUNCH(d);
   return LNN_OK;
 }

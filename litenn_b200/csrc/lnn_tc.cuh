@@ -64,7 +64,8 @@ struct TcParams {
   int patches_total, patches_per_split;
   int dw_tap_dy, dw_tap_dx;      // unused placeholders (taps come from the arrays below)
   int64_t part_stride_split, part_stride_tap, part_ld;   // partial buffer [split][tap][ocp][icp]
-  int oc_tiles, ic_tiles;
+  int oc_tiles, ic_tiles;        // ic_tiles: 32-channel blocks of the input channels
+  int nb_total, nb_group;        // DW: (tap, channel block) column blocks in total / per tile
   // epilogue
   int accumulate, act;
   float alpha;
