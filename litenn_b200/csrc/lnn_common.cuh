@@ -64,6 +64,9 @@ struct Scratch {
 bool conv_direct_applicable(const lnn_conv_geom* g);
 int conv_direct_fwd(Device* d, const lnn_conv_geom* g, float* Y, const float* X, const float* W,
                     const float* bias, int act, float alpha, int accumulate, int pool);
+// kernel gradient of the same layers (IC <= 4, 3x3): dW += ...
+bool conv_direct_dw_applicable(const lnn_conv_geom* g);
+int conv_direct_dw(Device* d, const lnn_conv_geom* g, float* dW, const float* dY, const float* X);
 
 }  // namespace lnn
 

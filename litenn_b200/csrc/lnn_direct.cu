@@ -9,6 +9,7 @@
 // op/element_wise_op.py:210 leaky_relu, op/pool2D.py:111-146 max pool).
 #include "lnn_common.cuh"
 #include <math_constants.h>
+#include <algorithm>
 
 namespace {
 
@@ -127,9 +128,247 @@ conv_direct_fwd_kernel(float* __restrict__ Y, const float* __restrict__ X, const
   }
 }
 
+// -----------------------------------------------------------------------------------------
+// Kernel gradient of the same layers (IC <= 4, 3x3 taps): dW[oc][ic][kh][kw] += sum over
+// (n, oh, ow) of dY[n][oc][oh][ow] * X[n][ic][oh*s + kh*d - padt][ow*s + kw*d - padl]
+// (litenn/core/op/conv2D.py:52-54).  The contraction runs over tens of millions of pixels
+// but has only OC x IC*9 outputs, so a tensor-core tile would be almost all padding: each
+// lane owns one output channel and keeps its IC*9 sums in registers, a warp walks groups of
+// four pixels of a tile staged in shared memory (dY tile read as one 128-bit load per lane,
+// X values as warp-wide broadcasts), and a block keeps accumulating over all the tiles it
+// visits.  Block partials are combined in a fixed order by dw_direct_finalize_kernel, so the
+// result does not depend on scheduling.
+constexpr int kDwOc = 32;          // output channels per block (one per lane)
+constexpr int kDwTilePix = 128;    // output pixels per tile
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+// asynchronous global -> shared copies; bytes beyond src_bytes are written as zeros
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+constexpr int kDwXPer = 6;         // X-tile elements per thread whose position is precomputed
+
+template <int IC, bool UNIT>
+__global__ void __launch_bounds__(kThreads, 2)
+conv_direct_dw_kernel(float* __restrict__ partial, const float* __restrict__ dY,
+                      const float* __restrict__ X, lnn_conv_geom g, int tw, int th, int pp, int xr,
+                      int xwp, int tiles_w, int tiles_h, int oc_chunks, int slots) {
+  constexpr int T = IC * 9;
+  extern __shared__ __align__(16) float sm[];
+  const int buf_floats = kDwOc * pp + IC * xr * xwp;      // one stage: dY tile [32][pp], X tile [IC][xr][xwp]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int chunk = blockIdx.x % oc_chunks, slot = blockIdx.x / oc_chunks;
+  const int oc0 = chunk * kDwOc;
+  const int tile_pix = th * tw;                            // <= 128: at most one group of four per lane
+  const int s = g.stride, dl = g.dilation;
+  const bool vec_ok = (g.ow % 4 == 0) && ((((uintptr_t)dY) & 15) == 0);
+  const int64_t in_plane = (int64_t)g.ih * g.iw, out_plane = (int64_t)g.oh * g.ow;
+  float acc[T];
+#pragma unroll
+  for (int i = 0; i < T; ++i) acc[i] = 0.0f;
+
+  // positions this thread copies for every tile
+  const int my_p4 = lane * 4;
+  const int my_r = my_p4 / tw, my_c = my_p4 - my_r * tw;
+  const int x_elems = IC * xr * xwp;
+  int x_pos[kDwXPer], x_off[kDwXPer];                      // (row << 16 | column), offset inside the image
+#pragma unroll
+  for (int k = 0; k < kDwXPer; ++k) {
+    const int i = threadIdx.x + k * kThreads;
+    const int cc = i % xwp, t3 = i / xwp;
+    const int rr = t3 % xr, ic = t3 / xr;
+    x_pos[k] = (rr << 16) | cc;
+    x_off[k] = (int)(ic * in_plane) + rr * g.iw + cc;
+  }
+
+  const int64_t items = (int64_t)g.n * tiles_h * tiles_w;
+  auto issue = [&](int64_t item, int b) {
+    const int twi = (int)(item % tiles_w);
+    const int64_t t2 = item / tiles_w;
+    const int thi = (int)(t2 % tiles_h);
+    const int64_t n = t2 / tiles_h;
+    const int oh0 = thi * th, ow0 = twi * tw;
+    float* dys = sm + b * buf_floats;
+    float* xs = dys + kDwOc * pp;
+    if (my_p4 < tile_pix) {
+      const int oh = oh0 + my_r, ow = ow0 + my_c;
+      const int nvalid = (oh < g.oh) ? max(0, min(4, g.ow - ow)) : 0;
+#pragma unroll
+      for (int k = 0; k < kDwOc / (kThreads / 32); ++k) {
+        const int o = warp + k * (kThreads / 32);
+        const int nv = (oc0 + o < g.oc) ? nvalid : 0;
+        const float* q = nv ? dY + (n * g.oc + (oc0 + o)) * out_plane + (int64_t)oh * g.ow + ow : dY;
+        const uint32_t dst = smem_addr(dys + o * pp + my_p4);
+        if (vec_ok) cp_async_16(dst, q, nv * 4);
+        else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) cp_async_4(dst + 4 * e, e < nv ? q + e : dY, e < nv ? 4 : 0);
+        }
+      }
+    }
+    const int ih0 = oh0 * s - g.padt, iw0 = ow0 * s - g.padl;
+    const float* xn = X + n * g.ic * in_plane + (int64_t)ih0 * g.iw + iw0;
+#pragma unroll
+    for (int k = 0; k < kDwXPer; ++k) {
+      const int i = threadIdx.x + k * kThreads;
+      if (i < x_elems) {
+        const int ih = ih0 + (x_pos[k] >> 16), iw = iw0 + (x_pos[k] & 0xffff);
+        const bool ok = ih >= 0 && ih < g.ih && iw >= 0 && iw < g.iw;
+        cp_async_4(smem_addr(xs + i), ok ? xn + x_off[k] : X, ok ? 4 : 0);
+      }
+    }
+    for (int i = threadIdx.x + kDwXPer * kThreads; i < x_elems; i += kThreads) {
+      const int cc = i % xwp, t3 = i / xwp;
+      const int rr = t3 % xr, ic = t3 / xr;
+      const int ih = ih0 + rr, iw = iw0 + cc;
+      const bool ok = ih >= 0 && ih < g.ih && iw >= 0 && iw < g.iw;
+      cp_async_4(smem_addr(xs + i), ok ? xn + ic * in_plane + (int64_t)rr * g.iw + cc : X, ok ? 4 : 0);
+    }
+    cp_async_commit();
+  };
+
+  int b = 0;
+  if (slot < items) issue(slot, 0);
+  for (int64_t item = slot; item < items; item += slots, b ^= 1) {
+    const int64_t next = item + slots;
+    if (next < items) { issue(next, b ^ 1); cp_async_wait<1>(); }
+    else cp_async_wait<0>();
+    __syncthreads();                          // this tile has landed for every thread
+    const float* dys = sm + b * buf_floats;
+    const float* xs = dys + kDwOc * pp;
+    for (int p4 = warp * 4; p4 < tile_pix; p4 += (kThreads / 32) * 4) {
+      const int r = p4 / tw, c = p4 - r * tw;
+      const float4 dy = *reinterpret_cast<const float4*>(dys + lane * pp + p4);
+#pragma unroll
+      for (int ic = 0; ic < IC; ++ic) {
+#pragma unroll
+        for (int kh = 0; kh < 3; ++kh) {
+          const float* xrow = xs + (ic * xr + r * s + kh * dl) * xwp;
+          if (UNIT) {
+            const float4 a = *reinterpret_cast<const float4*>(xrow + c);
+            const float2 b2 = *reinterpret_cast<const float2*>(xrow + c + 4);
+            const float xv[6] = {a.x, a.y, a.z, a.w, b2.x, b2.y};
+#pragma unroll
+            for (int kw = 0; kw < 3; ++kw) {
+              float t = acc[(ic * 3 + kh) * 3 + kw];
+              t = fmaf(dy.x, xv[kw], t);
+              t = fmaf(dy.y, xv[kw + 1], t);
+              t = fmaf(dy.z, xv[kw + 2], t);
+              t = fmaf(dy.w, xv[kw + 3], t);
+              acc[(ic * 3 + kh) * 3 + kw] = t;
+            }
+          } else {
+#pragma unroll
+            for (int kw = 0; kw < 3; ++kw) {
+              const float* xq = xrow + c * s + kw * dl;
+              float t = acc[(ic * 3 + kh) * 3 + kw];
+              t = fmaf(dy.x, xq[0], t);
+              t = fmaf(dy.y, xq[s], t);
+              t = fmaf(dy.z, xq[2 * s], t);
+              t = fmaf(dy.w, xq[3 * s], t);
+              acc[(ic * 3 + kh) * 3 + kw] = t;
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();                          // stage b may be refilled by the next iteration's issue
+  }
+  // combine the eight warps in warp order, then publish this block's partial
+  float* red = sm;                            // [warps][T][32]
+#pragma unroll
+  for (int i = 0; i < T; ++i) red[(warp * T + i) * 32 + lane] = acc[i];
+  __syncthreads();
+  for (int i = threadIdx.x; i < T * 32; i += kThreads) {
+    float v = red[i];
+    for (int w = 1; w < kThreads / 32; ++w) v = __fadd_rn(v, red[w * T * 32 + i]);
+    const int t = i >> 5, o = i & 31;
+    partial[((int64_t)slot * oc_chunks * kDwOc + oc0 + o) * T + t] = v;
+  }
+}
+
+// dW[oc][t] += partial[0][oc][t] + partial[1][oc][t] + ... (slot order)
+__global__ void __launch_bounds__(kThreads)
+dw_direct_finalize_kernel(float* __restrict__ dW, const float* __restrict__ partial, int oc, int T,
+                          int ocp, int slots) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= oc * T) return;
+  float v = 0.0f;
+  for (int k = 0; k < slots; ++k) v = __fadd_rn(v, partial[(int64_t)k * ocp * T + i]);
+  dW[i] = __fadd_rn(dW[i], v);
+}
+
+struct DwPlan { int tw, th, pp, xr, xwp, tiles_w, tiles_h; size_t smem; };
+
+DwPlan plan_dw(const lnn_conv_geom* g) {
+  DwPlan q;
+  q.tw = std::min(kDwTilePix, (g->ow + 3) & ~3);
+  q.th = std::max(1, std::min(g->oh, kDwTilePix / q.tw));
+  q.pp = ((q.th * q.tw + 7) & ~7) + 4;                   // pitch / 4 odd: conflict-free 128-bit reads
+  q.xr = (q.th - 1) * g->stride + 2 * g->dilation + 1;
+  q.xwp = ((q.tw - 1) * g->stride + 2 * g->dilation + 1 + 3) & ~3;
+  q.tiles_w = (g->ow + q.tw - 1) / q.tw;
+  q.tiles_h = (g->oh + q.th - 1) / q.th;
+  const size_t tile = 2 * (size_t)(kDwOc * q.pp + g->ic * q.xr * q.xwp) * sizeof(float);   // two stages
+  const size_t red = (size_t)(kThreads / 32) * g->ic * 9 * 32 * sizeof(float);
+  q.smem = std::max(tile, red);
+  return q;
+}
+
 }  // namespace
 
 namespace lnn {
+
+bool conv_direct_dw_applicable(const lnn_conv_geom* g) {
+  if (g->ic > 4 || g->kh != 3 || g->kw != 3) return false;
+  return plan_dw(g).smem <= 96 * 1024;
+}
+
+int conv_direct_dw(Device* d, const lnn_conv_geom* g, float* dW, const float* dY, const float* X) {
+  const DwPlan q = plan_dw(g);
+  const int oc_chunks = (g->oc + kDwOc - 1) / kDwOc;
+  const int64_t items = (int64_t)g->n * q.tiles_h * q.tiles_w;
+  int slots = (int)std::min<int64_t>(items, std::max(1, d->sm_count * 2 / oc_chunks));
+  const int T = g->ic * 9;
+  Scratch part(d);
+  int rc = part.get((uint64_t)slots * oc_chunks * kDwOc * T * sizeof(float));
+  if (rc) return rc;
+  const bool unit = g->stride == 1 && g->dilation == 1;
+  const unsigned grid = (unsigned)(slots * oc_chunks);
+#define LNN_DW_CASE(IC_, U_)                                                                        \
+  do {                                                                                              \
+    auto kern = conv_direct_dw_kernel<IC_, U_>;                                                     \
+    if (q.smem > 48 * 1024)                                                                         \
+      LNN_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)q.smem)); \
+    kern<<<grid, kThreads, q.smem, d->stream>>>(part.as<float>(), dY, X, *g, q.tw, q.th, q.pp, q.xr, \
+                                                q.xwp, q.tiles_w, q.tiles_h, oc_chunks, slots);     \
+  } while (0)
+  switch (g->ic * 2 + (unit ? 1 : 0)) {
+    case 2: LNN_DW_CASE(1, false); break;
+    case 3: LNN_DW_CASE(1, true); break;
+    case 4: LNN_DW_CASE(2, false); break;
+    case 5: LNN_DW_CASE(2, true); break;
+    case 6: LNN_DW_CASE(3, false); break;
+    case 7: LNN_DW_CASE(3, true); break;
+    case 8: LNN_DW_CASE(4, false); break;
+    default: LNN_DW_CASE(4, true); break;
+  }
+#undef LNN_DW_CASE
+  LNN_CHECK_LAUNCH(d);
+  dw_direct_finalize_kernel<<<(g->oc * T + kThreads - 1) / kThreads, kThreads, 0, d->stream>>>(
+      dW, part.as<float>(), g->oc, T, oc_chunks * kDwOc, slots);
+  LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
+}
 
 // true when the direct kernel handles this geometry
 bool conv_direct_applicable(const lnn_conv_geom* g) {

@@ -109,6 +109,39 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint6
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum)
       : "memory");
 }
+// All MMAs of one k-block (KS steps of K = 8; hi*hi, hi*lo, lo*hi when NBUF == 2), fully
+// unrolled with independent descriptor adds: the issuing thread is a single scalar stream and
+// every dependent instruction between two tcgen05.mma shows up in the MMA rate.
+template <int KS, int NBUF>
+__device__ __forceinline__ void issue_kblock(uint32_t d_tmem, uint64_t ah, uint64_t bh, uint64_t a_step,
+                                             uint64_t b_step, uint64_t a_lo, uint64_t b_lo,
+                                             uint32_t idesc, uint32_t accum_first) {
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+    const uint64_t a = ah + (uint64_t)ks * a_step, b = bh + (uint64_t)ks * b_step;
+    umma_tf32(d_tmem, a, b, idesc, ks == 0 ? accum_first : 1u);
+    if (NBUF == 2) {
+      umma_tf32(d_tmem, a, b + b_lo, idesc, 1u);
+      umma_tf32(d_tmem, a + a_lo, b, idesc, 1u);
+    }
+  }
+}
+template <int NBUF>
+__device__ __forceinline__ void issue_kblock_n(int ksteps, uint32_t d_tmem, uint64_t ah, uint64_t bh,
+                                               uint64_t a_step, uint64_t b_step, uint64_t a_lo,
+                                               uint64_t b_lo, uint32_t idesc, uint32_t accum_first) {
+  switch (ksteps) {
+    case 4: issue_kblock<4, NBUF>(d_tmem, ah, bh, a_step, b_step, a_lo, b_lo, idesc, accum_first); break;
+    case 2: issue_kblock<2, NBUF>(d_tmem, ah, bh, a_step, b_step, a_lo, b_lo, idesc, accum_first); break;
+    case 1: issue_kblock<1, NBUF>(d_tmem, ah, bh, a_step, b_step, a_lo, b_lo, idesc, accum_first); break;
+    case 8: issue_kblock<8, NBUF>(d_tmem, ah, bh, a_step, b_step, a_lo, b_lo, idesc, accum_first); break;
+    default:
+      for (int ks = 0; ks < ksteps; ++ks) {
+        issue_kblock<1, NBUF>(d_tmem, ah, bh, a_step, b_step, a_lo, b_lo, idesc, ks == 0 ? accum_first : 1u);
+        ah += a_step; bh += b_step;
+      }
+  }
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                : "memory");
@@ -374,23 +407,11 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
           tc_fence_after();
           uint32_t ua = tiles + s * stage_sz;
           for (int u = 0; u < nun; ++u, ua += unit_sz) {
-            uint64_t ah = a_desc0 + (uint64_t)(ua >> 4);
-            uint64_t bh = b_desc0 + (uint64_t)((ua + nbuf * a_sz) >> 4);
-            if (nbuf == 2) {
-              for (int ks = 0; ks < ksteps; ++ks) {
-                umma_tf32(d_tmem, ah, bh, idesc, accum);
-                umma_tf32(d_tmem, ah, bh + b_lo16, idesc, 1u);
-                umma_tf32(d_tmem, ah + a_lo16, bh, idesc, 1u);
-                accum = 1u;
-                ah += a_step16; bh += b_step16;
-              }
-            } else {
-              for (int ks = 0; ks < ksteps; ++ks) {
-                umma_tf32(d_tmem, ah, bh, idesc, accum);
-                accum = 1u;
-                ah += a_step16; bh += b_step16;
-              }
-            }
+            const uint64_t ah = a_desc0 + (uint64_t)(ua >> 4);
+            const uint64_t bh = b_desc0 + (uint64_t)((ua + nbuf * a_sz) >> 4);
+            if (nbuf == 2) issue_kblock_n<2>(ksteps, d_tmem, ah, bh, a_step16, b_step16, a_lo16, b_lo16, idesc, accum);
+            else issue_kblock_n<1>(ksteps, d_tmem, ah, bh, a_step16, b_step16, a_lo16, b_lo16, idesc, accum);
+            if (ksteps > 0) accum = 1u;
           }
           umma_commit(empty0 + 8u * s);                 // frees the stage when these MMAs retire
           units_left -= nun;
@@ -568,6 +589,256 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
   __syncthreads();
   if (*abort_flag) {
     // copies issued before the abort may still be landing in this CTA's shared memory
+    const long long t0 = clock64();
+    while (clock64() - t0 < kAbortDelay) { }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2u * p.tmem_cols);
+  }
+}
+
+// =========================================================================================
+// unit-stride convolution with a halo-resident pixel patch
+// =========================================================================================
+// tc_kernel reloads the pixel patch for every tap, so a 3x3 convolution pulls nine copies of
+// it from L2 into shared memory and the operand ring, not the tensor pipe, sets the pace.
+// Here the patch of one 32-channel block is loaded ONCE per tile, halo included, as a flat
+// array of pixels: (th + halo) rows of h_pw pixels, 128 bytes per pixel, 128-byte swizzle.
+// Accumulator column n = h * h_pw + w stands for output pixel (h, w) of the tile; tap
+// (dy, dx) needs patch pixel n + dy' * h_pw + dx', i.e. the SAME array read from a start
+// address shifted by tap_shift rows, which a shared-memory descriptor can express.  Columns
+// with w >= tw are computed and thrown away (they wrap into the next patch row).
+// Channels sit on M (kernel tile = operand A, one unit per tap), pixels on N.
+//   warp 0 : kernel-unit producer      warp 1 : MMA issuer, TMEM owner
+//   warp 6 : patch producer            warps 2-5 : epilogue
+constexpr int kThreadsHalo = 224;
+
+__global__ void __launch_bounds__(kThreadsHalo, 1)
+tc_halo_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
+               const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmBl,
+               const __grid_constant__ TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t a_full_bar[8];
+  __shared__ uint64_t a_empty_bar[8];
+  __shared__ uint64_t b_full_bar[4];
+  __shared__ uint64_t b_empty_bar[4];
+  __shared__ uint64_t tmem_full_bar[2];
+  __shared__ uint64_t tmem_empty_bar[2];
+  __shared__ uint32_t tmem_base_smem;
+  __shared__ int abort_flag_smem;
+
+  if (threadIdx.x == 0) abort_flag_smem = (*(volatile int*)p.status != 0) ? 2 : 0;
+  __syncthreads();
+  if (abort_flag_smem == 2) return;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  volatile int* abort_flag = &abort_flag_smem;
+
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t ring = (raw + 1023u) & ~1023u;
+  const int nbuf = p.passes == 3 ? 2 : 1;
+  const uint32_t a_sz = (uint32_t)p.a_tile_bytes;            // 1024-byte multiples
+  const uint32_t b_sz = (uint32_t)p.h_bbuf;
+  const uint32_t a_unit = nbuf * a_sz, b_stage = nbuf * b_sz;
+  const uint32_t a_ring = ring, b_ring = ring + (uint32_t)p.h_sa * a_unit;
+  const int num_tiles = p.grid_x * p.grid_y;
+  const int a_per_cb = p.cb / p.h_acb;                       // kernel units per (tap, channel block)
+  const uint32_t row_bytes = (uint32_t)p.cb * 4u;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.h_sa; ++s) {
+      mbar_init(smem_u32(&a_full_bar[s]), 1);
+      mbar_init(smem_u32(&a_empty_bar[s]), 1);
+    }
+    for (int s = 0; s < p.h_sb; ++s) {
+      mbar_init(smem_u32(&b_full_bar[s]), 1);
+      mbar_init(smem_u32(&b_empty_bar[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&tmem_full_bar[a]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[a]), 4);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_smem), 2u * p.tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_smem;
+  const uint32_t afull0 = smem_u32(&a_full_bar[0]), aempty0 = smem_u32(&a_empty_bar[0]);
+  const uint32_t bfull0 = smem_u32(&b_full_bar[0]), bempty0 = smem_u32(&b_empty_bar[0]);
+
+  if (warp == 6) {
+    // ---- patch producer -----------------------------------------------------------------
+    if (lane == 0) {
+      const uint32_t tx = (uint32_t)nbuf * (uint32_t)(p.h_pw * p.h_ph) * row_bytes;
+      uint32_t s = 0, ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        const TileCoord t = decode_tile<MODE_CONVT>(p, tile);
+        for (int cbi = 0; cbi < p.ncb; ++cbi) {
+          if (!mbar_wait(bempty0 + 8u * s, ph ^ 1u, abort_flag, p.status, 4, cbi)) { ok = false; break; }
+          const uint32_t fb = bfull0 + 8u * s;
+          mbar_expect_tx(fb, tx);
+          const uint32_t dst = b_ring + s * b_stage;
+          tma_load_4d(dst, &tmBh, fb, cbi * p.cb, t.pb0 + p.h_x0, t.pa0 + p.h_y0, t.pn0);
+          if (nbuf == 2) tma_load_4d(dst + b_sz, &tmBl, fb, cbi * p.cb, t.pb0 + p.h_x0, t.pa0 + p.h_y0, t.pn0);
+          if (++s == (uint32_t)p.h_sb) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 0) {
+    // ---- kernel-unit producer -----------------------------------------------------------
+    if (lane == 0) {
+      const uint32_t tx = (uint32_t)nbuf * (uint32_t)p.a_load_bytes;
+      uint32_t s = 0, ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        const TileCoord t = decode_tile<MODE_CONVT>(p, tile);
+        for (int cbi = 0; ok && cbi < p.ncb; ++cbi) {
+          for (int tp = 0; ok && tp < p.ntaps; ++tp) {
+            for (int h = 0; h < a_per_cb; ++h) {
+              if (!mbar_wait(aempty0 + 8u * s, ph ^ 1u, abort_flag, p.status, 0, tp)) { ok = false; break; }
+              const uint32_t fb = afull0 + 8u * s;
+              if (p.debug & 2) { mbar_arrive(fb); }
+              else {
+              mbar_expect_tx(fb, tx);
+              const uint32_t dst = a_ring + s * a_unit;
+              const int c0 = cbi * p.cb + h * p.h_acb;
+              tma_load_3d(dst, &tmAh, fb, c0, t.m0, p.tap_w[tp]);
+              if (nbuf == 2) tma_load_3d(dst + a_sz, &tmAl, fb, c0, t.m0, p.tap_w[tp]);
+              }
+              if (++s == (uint32_t)p.h_sa) { s = 0; ph ^= 1u; }
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer -----------------------------------------------------------------------
+    if (lane == 0) {
+      const uint32_t a_swz = (uint32_t)p.h_acb * 4u;
+      const uint64_t a_desc0 = make_smem_desc(0u, 16u, 8u * a_swz, layout_of_swizzle((int)a_swz));
+      const uint64_t b_desc0 = make_smem_desc(0u, 16u, 8u * row_bytes, layout_of_swizzle((int)row_bytes));
+      const uint64_t a_lo16 = a_sz >> 4, b_lo16 = b_sz >> 4;
+      const int ksteps = (p.debug & 1) ? 0 : p.h_acb / 8;
+      const uint32_t idesc = p.idesc;
+      uint32_t sa = 0, pha = 0, sb = 0, phb = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_ph = (uint32_t)(it >> 1) & 1u;
+        if (!mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_ph ^ 1u, abort_flag, p.status, 3, it)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)acc * p.tmem_cols;
+        uint32_t accum = 0u;
+        for (int cbi = 0; ok && cbi < p.ncb; ++cbi) {
+          if (!mbar_wait(bfull0 + 8u * sb, phb, abort_flag, p.status, 5, cbi)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t b_base = b_ring + sb * b_stage;
+          for (int tp = 0; ok && tp < p.ntaps; ++tp) {
+            // the tap's window of the patch: same array, start address shifted by whole pixels
+            const uint32_t b_addr = b_base + ((p.debug & 8) ? 0u : (uint32_t)p.tap_shift[tp] * row_bytes);
+            // the swizzle is a function of the absolute shared-memory address, so a start address
+            // that is not a multiple of the 1024-byte pattern needs no base-offset field
+            const uint64_t bdesc = b_desc0 + (uint64_t)(b_addr >> 4);
+            for (int h = 0; h < a_per_cb; ++h) {
+              if (!mbar_wait(afull0 + 8u * sa, pha, abort_flag, p.status, 1, tp)) { ok = false; break; }
+              tc_fence_after();
+              const uint64_t ah = a_desc0 + (uint64_t)((a_ring + sa * a_unit) >> 4);
+              const uint64_t bh = bdesc + (uint64_t)((h * p.h_acb * 4) >> 4);
+              // one MMA step = 8 channels = 32 bytes = 2 descriptor units
+              if (nbuf == 2) issue_kblock_n<2>(ksteps, d_tmem, ah, bh, 2, 2, a_lo16, b_lo16, idesc, accum);
+              else issue_kblock_n<1>(ksteps, d_tmem, ah, bh, 2, 2, a_lo16, b_lo16, idesc, accum);
+              if (ksteps > 0) accum = 1u;
+              umma_commit(aempty0 + 8u * sa);
+              if (++sa == (uint32_t)p.h_sa) { sa = 0; pha ^= 1u; }
+            }
+          }
+          if (ok) umma_commit(bempty0 + 8u * sb);
+          if (++sb == (uint32_t)p.h_sb) { sb = 0; phb ^= 1u; }
+        }
+        if (ok) umma_commit(smem_u32(&tmem_full_bar[acc]));
+      }
+    }
+  } else {
+    // ---- epilogue: lane = output channel, columns = flattened patch positions ---------------
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int ncols = p.th * p.h_pw;                  // columns that can hold a real pixel
+    int it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+      const TileCoord t = decode_tile<MODE_CONVT>(p, tile);
+      const int acc = it & 1;
+      const uint32_t acc_ph = (uint32_t)(it >> 1) & 1u;
+      bool have_acc = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_ph, abort_flag, p.status, 2, it);
+      have_acc = __all_sync(0xffffffffu, have_acc);
+      if (!have_acc) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + (uint32_t)acc * p.tmem_cols;
+      const int oc = t.m0 + r;
+      const bool row_ok = oc < p.OC;
+      const float bias_v = (row_ok && p.bias) ? __ldg(p.bias + oc) : 0.0f;
+      float* const obase = p.out + p.out_base + (int64_t)oc * p.out_sc + (int64_t)t.pn0 * p.out_sn;
+      int h_i = 0, w_i = 0;                           // position of the current group of four
+      for (int c0 = 0; c0 < ncols; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld32(d_tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            const int a = t.pa0 + h_i, b = t.pb0 + w_i;
+            if (c0 + j < ncols && w_i < p.tw && a < p.AH && b < p.AW && !(p.debug & 4)) {
+              float x[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float tt = __uint_as_float(v[j + e]);
+                if (p.bias) tt = __fadd_rn(tt, bias_v);
+                x[e] = apply_act(tt, p.act, p.alpha);
+              }
+              float* dst = obase + (int64_t)a * p.out_sa + (int64_t)b * p.out_sb;
+              const bool four = (w_i + 3 < p.tw) && (b + 3 < p.AW);
+              if (four && p.out_sb == 1 && ((((uintptr_t)dst) & 15) == 0)) {
+                float4* d4 = reinterpret_cast<float4*>(dst);
+                if (p.accumulate) {
+                  const float4 o = *d4;
+                  x[0] = __fadd_rn(o.x, x[0]); x[1] = __fadd_rn(o.y, x[1]);
+                  x[2] = __fadd_rn(o.z, x[2]); x[3] = __fadd_rn(o.w, x[3]);
+                }
+                *d4 = make_float4(x[0], x[1], x[2], x[3]);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  if (w_i + e < p.tw && b + e < p.AW) {
+                    float* de = dst + (int64_t)e * p.out_sb;
+                    *de = p.accumulate ? __fadd_rn(*de, x[e]) : x[e];
+                  }
+                }
+              }
+            }
+            w_i += 4;
+            if (w_i >= p.h_pw) { w_i = 0; ++h_i; }
+          }
+        }
+        __syncwarp();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
     const long long t0 = clock64();
     while (clock64() - t0 < kAbortDelay) { }
     __syncthreads();
@@ -962,6 +1233,134 @@ int check_geom(const lnn_conv_geom* g) {
   return LNN_OK;
 }
 
+// Tiling of the halo-resident kernel: tile = th rows x tw columns of one image, patch =
+// (th + hy) x pw pixels with pw = tw + hx rounded up to 4 (so that groups of four columns never
+// straddle a patch row).  Two patch stages (hi and lo each) plus at least three kernel units
+// must fit shared memory; among the tilings that do, take the one with most real pixels per
+// MMA clock under the measured cost of one tcgen05.mma in this kernel, about max(150, 0.7 * N) clocks.
+struct HaloPlan { bool ok; int tw, th, pw, ph, bn, sa, bbuf, acb; double px_per_clk; };
+
+HaloPlan plan_halo(int AH, int AW, int hx, int hy, int a_rows, int nbuf, int cb) {
+  HaloPlan best;
+  memset(&best, 0, sizeof(best));
+  const int budget = kSmemLimit - kSmemSlack - 1024;
+  const int divs[] = {1, 2, 3, 4, 6, 8};
+  for (int acb = cb; acb >= 16; acb >>= 1) {
+    const int a_unit = nbuf * ((a_rows * acb * 4 + 1023) & ~1023);
+    const int min_sa = 3;
+    for (int di = 0; di < 6; ++di) {
+      int tw = (AW + divs[di] - 1) / divs[di];
+      tw = (tw + 3) & ~3;
+      const int pw = (tw + hx + 3) & ~3;
+      if (pw > 256) continue;
+      for (int th = 1; th <= AH && th * pw <= 256; ++th) {
+        const int bn = std::max(16, (th * pw + 15) & ~15);
+        const int ph = th + hy;
+        if (bn > 256 || ph > 256) continue;
+        const int bbuf = ((bn + hy * pw + hx) * cb * 4 + 1023) & ~1023;
+        int sa = (budget - 2 * nbuf * bbuf) / a_unit;
+        if (sa < min_sa) continue;
+        if (sa > 8) sa = 8;
+        const double tiles = (double)((AW + tw - 1) / tw) * (double)((AH + th - 1) / th);
+        const double cost = std::max(150.0, 0.7 * bn);
+        const double ppc = (double)AH * AW / (tiles * cost);
+        if (!best.ok || ppc > best.px_per_clk * 1.02) {
+          best.ok = true; best.tw = tw; best.th = th; best.pw = pw; best.ph = ph; best.bn = bn;
+          best.sa = sa; best.bbuf = bbuf; best.acb = acb; best.px_per_clk = ppc;
+        }
+      }
+    }
+  }
+  return best;
+}
+
+// Unit-stride convolution through tc_halo_kernel.  Same operands as launch_conv_like with
+// es == 1 and 32-channel blocks; returns LNN_E_UNSUPPORTED (without setting an error) through
+// *taken = 0 when no tiling fits.
+int launch_conv_halo(lnn::Device* d, const float* act_hi, const float* act_lo, int NL, int H, int W,
+                     int kp, const float* w_hi, const float* w_lo, int wrows, int wtaps, int AH,
+                     int AW, int ntaps, const int* dy, const int* dx, const int* widx, int OCv,
+                     float* out, int64_t out_base, int64_t out_sn, int64_t out_sa, int64_t out_sb,
+                     int64_t out_sc, const float* bias, int act, float alpha, int accumulate,
+                     int passes, int* taken) {
+  *taken = 0;
+  const int cb = 32;
+  if (kp % cb != 0 || ntaps < 1) return LNN_OK;
+  int x0 = dx[0], x1 = dx[0], y0 = dy[0], y1 = dy[0];
+  for (int i = 1; i < ntaps; ++i) {
+    x0 = std::min(x0, dx[i]); x1 = std::max(x1, dx[i]);
+    y0 = std::min(y0, dy[i]); y1 = std::max(y1, dy[i]);
+  }
+  const int hx = x1 - x0, hy = y1 - y0;
+  const int nbuf = passes == 3 ? 2 : 1;
+  const int a_rows = std::min(128, (OCv + 7) & ~7);
+  const HaloPlan hp = plan_halo(AH, AW, hx, hy, a_rows, nbuf, cb);
+  // Both kernels turn out to be bound by shared-memory bandwidth (operand reads of the MMAs plus
+  // TMA writes, about 90 bytes per clock), so the resident patch only pays where the per-tap
+  // kernel is at its worst: one tap per ring stage (32 input channels) or so few output
+  // channels that it would put them on N; and only when few accumulator columns are wasted.
+  if (!hp.ok) return LNN_OK;
+  if (env_int("LNN_TC_HALO", 1) != 2 && !(hp.px_per_clk >= 1.15 && (OCv < 64 || kp == 32))) return LNN_OK;
+
+  TcParams p;
+  memset(&p, 0, sizeof(p));
+  p.mode = MODE_CONVT; p.passes = passes; p.bn = hp.bn;
+  p.swz_a = hp.acb * 4; p.swz_b = cb * 4;
+  p.a_tile_bytes = (a_rows * hp.acb * 4 + 1023) & ~1023;
+  p.a_load_bytes = a_rows * hp.acb * 4;
+  p.idesc = make_idesc(hp.bn, 0, 0);
+  p.tmem_cols = tmem_cols_for(hp.bn);
+  p.ncb = kp / cb; p.cb = cb; p.ntaps = ntaps;
+  p.tw = hp.tw; p.th = hp.th; p.tn = 1;
+  p.tiles_b = (AW + hp.tw - 1) / hp.tw; p.tiles_a = (AH + hp.th - 1) / hp.th; p.tiles_n = NL;
+  p.AW = AW; p.AH = AH; p.NL = NL; p.es = 1;
+  p.out_sn = out_sn; p.out_sa = out_sa; p.out_sb = out_sb; p.out_sc = out_sc; p.out_base = out_base;
+  p.OC = OCv;
+  p.accumulate = accumulate; p.act = act; p.alpha = alpha; p.bias = bias; p.out = out;
+  p.h_pw = hp.pw; p.h_ph = hp.ph; p.h_x0 = x0; p.h_y0 = y0; p.h_arows = a_rows; p.h_acb = hp.acb;
+  p.h_sa = hp.sa; p.h_sb = 2; p.h_bbuf = hp.bbuf;
+  p.debug = env_int("LNN_TC_DEBUG", 0);     // timing experiments only; results are wrong when set
+  for (int i = 0; i < ntaps; ++i) {
+    p.tap_dy[i] = dy[i]; p.tap_dx[i] = dx[i]; p.tap_w[i] = widx[i];
+    p.tap_shift[i] = (dy[i] - y0) * hp.pw + (dx[i] - x0);
+  }
+  p.status = d->status_dev;
+  CUtensorMap act_h, act_l, w_h, w_l;
+  int rc = encode_nhwc(&act_h, act_hi, NL, H, W, kp, cb, hp.pw, hp.ph, 1, 1);
+  if (rc) return rc;
+  rc = encode_nhwc(&act_l, passes == 3 ? act_lo : act_hi, NL, H, W, kp, cb, hp.pw, hp.ph, 1, 1);
+  if (rc) return rc;
+  {
+    uint64_t dims[3] = {(uint64_t)kp, (uint64_t)wrows, (uint64_t)wtaps};
+    uint64_t str[2] = {(uint64_t)kp * 4, (uint64_t)wrows * kp * 4};
+    uint32_t box[3] = {(uint32_t)hp.acb, (uint32_t)a_rows, 1};
+    uint32_t es1[3] = {1, 1, 1};
+    rc = encode_map(&w_h, w_hi, 3, dims, str, box, es1, hp.acb * 4);
+    if (rc) return rc;
+    rc = encode_map(&w_l, passes == 3 ? w_lo : w_hi, 3, dims, str, box, es1, hp.acb * 4);
+    if (rc) return rc;
+  }
+  const int64_t ptiles = (int64_t)p.tiles_b * p.tiles_a * p.tiles_n;
+  const int64_t mtiles = (OCv + 127) / 128;
+  LNN_REQUIRE(ptiles * mtiles < (1ll << 31), "too many tiles");
+  p.grid_x = (int)ptiles; p.grid_y = (int)mtiles; p.grid_z = 1;
+  const int smem = p.h_sa * nbuf * p.a_tile_bytes + p.h_sb * nbuf * p.h_bbuf + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    LNN_CUDA(cudaFuncSetAttribute(tc_halo_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  kSmemLimit - 1024));
+    attr_set = true;
+  }
+  const unsigned ctas = (unsigned)std::min<int64_t>(ptiles * mtiles, d->sm_count);
+  {
+    lnn::ProfScope prof(d, (int)LNN_PROF_TC_CONV);
+    tc_halo_kernel<<<ctas, kThreadsHalo, smem, d->stream>>>(w_h, w_l, act_h, act_l, p);
+  }
+  LNN_CHECK_LAUNCH(d);
+  *taken = 1;
+  return LNN_OK;
+}
+
 // Shared launcher of the "pixels on M" implicit GEMM (forward and input gradient).
 // act_hi/lo: NHWC copy [NL][H][W][kp]; w_hi/lo: [taps][rows][kp]; the logical output grid is
 // AH x AW per image; tap t reads the activation at (a*es + dy[t], b*es + dx[t]).
@@ -971,13 +1370,21 @@ int launch_conv_like(lnn::Device* d, const float* act_hi, const float* act_lo, i
                      int OCv, float* out, int64_t out_base, int64_t out_sn, int64_t out_sa,
                      int64_t out_sb, int64_t out_sc, const float* bias, int act, float alpha,
                      int accumulate, int passes) {
+  if (es == 1 && env_int("LNN_TC_HALO", 1) != 0) {
+    int taken = 0;
+    const int rc = launch_conv_halo(d, act_hi, act_lo, NL, H, W, kp, w_hi, w_lo, wrows, wtaps, AH, AW,
+                                    ntaps, dy, dx, widx, OCv, out, out_base, out_sn, out_sa, out_sb,
+                                    out_sc, bias, act, alpha, accumulate, passes, &taken);
+    if (rc) return rc;
+    if (taken) return LNN_OK;
+  }
   int cb = chan_block(kp);
   {
     const int cb_env = env_int("LNN_TC_CB", 0);          // tuning: channels per unit (8/16/32)
     if ((cb_env == 8 || cb_env == 16) && cb_env < cb) cb = cb_env;
   }
   const int swz = cb * 4;
-  // Orientation.  A tcgen05.mma costs about max(90, 0.45 * N) clocks whatever M carries, so the
+  // Orientation.  A tcgen05.mma costs about max(90, 0.7 * N) clocks whatever M carries, so the
   // wide operand should sit on N: with more than a few output channels the pixel patch (up to
   // 256 pixels) goes on N and the channels on M ("channels on M", MODE_CONVT); with very few
   // output channels the pixels go on M and the channels on N.
@@ -1227,6 +1634,9 @@ int lnn_conv2d_dw(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY, uin
   rc = check_passes(tf32_passes);
   if (rc) return rc;
   LNN_REQUIRE(dW && dY && X, "null buffer");
+  if (lnn::conv_direct_dw_applicable(g) && env_int("LNN_CONV_DIRECT", 1))
+    return lnn::conv_direct_dw(d, g, (float*)(uintptr_t)dW, (const float*)(uintptr_t)dY,
+                               (const float*)(uintptr_t)X);
   const int want_lo = tf32_passes == 3;
   const int s = g->stride;
   const int cp = chan_pad(g->ic), ocp = chan_pad(g->oc);

@@ -73,6 +73,16 @@ struct TcParams {
   float* out;
   int* status;
   int tap_dy[kMaxTaps], tap_dx[kMaxTaps], tap_w[kMaxTaps];
+  // halo-resident pixel patch (tc_halo_kernel): the patch of one channel block, with its halo,
+  // is loaded once per tile as a flat array of pixels (row pitch h_pw) and every tap reads it
+  // through a descriptor shifted by tap_shift rows
+  int h_pw, h_ph;                // patch width (multiple of 4) and height in pixels
+  int h_x0, h_y0;                // smallest tap offsets: patch origin relative to the tile origin
+  int h_arows;                   // kernel rows loaded per unit (the rest of the 128 is never stored)
+  int h_acb;                     // channels per kernel unit (<= cb)
+  int h_sa, h_sb;                // ring depths: kernel units, patch stages
+  int h_bbuf;                    // bytes of one (hi or lo) patch buffer, 1024-byte multiple
+  int tap_shift[kMaxTaps];
 };
 
 }  // namespace lnn_tc

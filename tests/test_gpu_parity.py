@@ -129,6 +129,67 @@ def test_conv_pool_fusion_equals_chain(nn_gpu, xs, ws):
     assert_contraction_close(fused, want, ws[1] * ws[2] * ws[3], "conv2D_pool vs oracle")
 
 
+@pytest.mark.parametrize("xs,ws,dil", [((3, 32, 64, 64), (64, 32, 3, 3), 1), ((2, 64, 32, 32), (128, 64, 3, 3), 1),
+                                       ((2, 128, 16, 16), (200, 128, 3, 3), 1), ((2, 32, 30, 27), (48, 32, 3, 3), 1),
+                                       ((2, 32, 40, 40), (64, 32, 3, 3), 2), ((2, 64, 28, 28), (96, 64, 5, 5), 1),
+                                       ((2, 64, 21, 64), (24, 64, 3, 3), 1)])
+def test_conv_halo_kernel(nn_gpu, monkeypatch, xs, ws, dil):
+    """The unit-stride kernel with a halo-resident pixel patch (forced on, then forced off):
+    forward with fused bias + leaky_relu, and the input gradient, against the fp64 oracle."""
+    import oracle as o
+    nn = nn_gpu
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal(xs).astype(np.float32)
+    w = (rng.standard_normal(ws) * 0.1).astype(np.float32)
+    b = rng.uniform(-0.1, 0.1, (ws[0],)).astype(np.float32)
+    want = o.conv2d_fwd(x, w, 1, dil, "same", bias=b, act=1, alpha=0.1, accum64=True)
+    dy = rng.standard_normal(want.shape).astype(np.float32)
+    want_dx = o.conv2d_dx(np.zeros(xs, np.float32), dy, w, xs, 1, dil, "same", accum64=True)
+    results = {}
+    for mode in ("2", "0"):
+        monkeypatch.setenv("LNN_TC_HALO", mode)
+        xt, wt, bt = nn.Tensor_from_value(x), nn.Tensor_from_value(w), nn.Tensor_from_value(b)
+        y = nn.conv2D(xt, wt, dilation=dil, bias_t=bt, activation="leaky_relu", alpha=0.1)
+        assert_contraction_close(y.np(), want, ws[1] * ws[2] * ws[3], f"halo={mode} forward")
+        assert np.abs(y.np() - want).max() <= 2e-5 * np.abs(want).max(), "split-TF32 accuracy"
+        lin = nn.conv2D(xt, wt, dilation=dil)
+        nn.backward({lin: dy}, grad_for_non_trainables=True)
+        assert_contraction_close(xt.get_grad().np(), want_dx, ws[0] * ws[2] * ws[3], f"halo={mode} dX")
+        results[mode] = y.np()
+    nn.devices.check_status()
+    assert_contraction_close(results["2"], results["0"], ws[1] * ws[2] * ws[3], "halo kernel vs per-tap kernel")
+
+
+@pytest.mark.parametrize("xs,ws,stride,dil", [((8, 3, 33, 31), (20, 3, 3, 3), 1, 1), ((4, 3, 40, 44), (40, 3, 3, 3), 2, 1),
+                                              ((4, 1, 24, 24), (8, 1, 3, 3), 1, 2), ((3, 4, 128, 128), (32, 4, 3, 3), 1, 1),
+                                              ((2, 2, 7, 300), (33, 2, 3, 3), 1, 1)])
+def test_conv_direct_dw(nn_gpu, monkeypatch, xs, ws, stride, dil):
+    """Kernel gradient of few-input-channel layers on the FP32 pipes (IC <= 4, 3x3), against the
+    fp64 oracle and against the tile-engine path; a second call must add into dW."""
+    import oracle as o
+    nn = nn_gpu
+    rng = np.random.default_rng(6)
+    x = rng.standard_normal(xs).astype(np.float32)
+    w = (rng.standard_normal(ws) * 0.1).astype(np.float32)
+    y_shape = o.conv2d_fwd(x, w, stride, dil, "same").shape
+    dy = rng.standard_normal(y_shape).astype(np.float32)
+    want = o.conv2d_dw(np.zeros(ws, np.float32), dy, x, stride, dil, "same", accum64=True)
+    K = xs[0] * y_shape[2] * y_shape[3]
+    got = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("LNN_CONV_DIRECT", mode)
+        xt, wt = nn.Tensor_from_value(x), nn.Tensor_from_value(w)
+        y = nn.conv2D(xt, wt, stride=stride, dilation=dil)
+        nn.backward({y: dy}, grad_for_non_trainables=True)
+        got[mode] = wt.get_grad().np()
+        assert_contraction_close(got[mode], want, K, f"direct={mode} dW")
+        if mode == "1":
+            y2 = nn.conv2D(xt, wt, stride=stride, dilation=dil)
+            nn.backward({y2: dy}, grad_for_non_trainables=True)
+            assert_contraction_close(wt.get_grad().np(), 2 * want, K, "dW accumulates")
+    nn.devices.check_status()
+
+
 def test_softmax_ce(nn_gpu):
     ins, outs = load_golden("softmax_ce")["softmax_ce"]
     got = cases.run_case(nn_gpu, "softmax_ce", {}, ins)
