@@ -203,6 +203,7 @@ class CNN:
     def __init__(self, nn, weights):
         self.nn = nn
         self.training = False      # inference uses the fused conv+bias+lrelu+maxpool entry
+        self.packed = os.environ.get("LNN_BENCH_PACKED", "1") != "0"
         self.convs = []
         for i in range(4):
             c = nn.Conv2D(CHANS[i], CHANS[i + 1], 3, padding="same",
@@ -221,8 +222,11 @@ class CNN:
     def forward(self, x):
         nn = self.nn
         for i, c in enumerate(self.convs):
-            if i < 3 and not self.training:
-                x = nn.conv2D_pool(x, c.kernel, 1, 1, "same", bias_t=c.bias, activation="leaky_relu", alpha=0.1)
+            if not self.training:
+                # inference: bias, leaky_relu and the max-pool ride in the convolution's epilogue and the
+                # activation between two convolutions stays in the tensor-core operand format
+                x = nn.conv2D_infer(x, c.kernel, 1, 1, "same", bias_t=c.bias, activation="leaky_relu", alpha=0.1,
+                                    pool=i < 3, packed_output=(i < 3 and self.packed))
                 continue
             x = nn.conv2D(x, c.kernel, 1, 1, "same", bias_t=c.bias, activation="leaky_relu", alpha=0.1)
             if i < 3:

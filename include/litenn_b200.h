@@ -211,6 +211,23 @@ int lnn_conv2d_fwd(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint
  * ref: op/conv2D.py:9-44 + op/element_wise_op.py:207-221 + op/pool2D.py:47-146 */
 int lnn_conv2d_pool_fwd(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint64_t W,
                         uint64_t bias, int act, float alpha, int tf32_passes);
+/* Operand format of the tensor-core convolution: channel-innermost copies of an NCHW activation,
+ * hi = tf32(x) and lo = tf32(x - hi), each [n][h][w][cp] floats with cp = c rounded up to 8 (pad
+ * channels zero); lo may be 0 when only single-pass TF32 will be used.  The reference has no such
+ * format: its conv2D materialises an im2col buffer per call (op/conv2D.py:39-41,
+ * op/unfold2D.py:84-110); this entry is the explicit form of the pre-pass lnn_conv2d_fwd runs. */
+int lnn_nhwc_split(int dev, uint64_t hi, uint64_t lo, uint64_t X, int n, int c, int h, int w);
+/* conv2D forward (+ bias, leaky_relu, optional max_pool2D(2,2,'same')) whose input and / or output
+ * stay in that format, so that a chain of convolutions never writes or re-reads the NCHW
+ * activations between layers.  in_packed: X / X_lo are the packed copies of the input
+ * [n][ih][iw][pad8(ic)].  out_packed: Y / Y_lo receive the packed copies of the (pooled) result
+ * [n][oh'][ow'][pad8(oc)]; otherwise Y is the NCHW result and Y_lo is ignored.  The values are
+ * those of the un-fused entries (the packed result equals lnn_nhwc_split of their output).
+ * ref: op/conv2D.py:9-44, module/Conv2D.py:58-62, op/element_wise_op.py:207-221,
+ * op/pool2D.py:47-146 */
+int lnn_conv2d_fwd_packed(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t Y_lo, uint64_t X,
+                          uint64_t X_lo, uint64_t W, uint64_t bias, int act, float alpha, int pool,
+                          int in_packed, int out_packed, int tf32_passes);
 /* dX += conv2D_transpose-like gradient.  ref: op/conv2D.py:46-50, op/unfold2D.py:112-138 */
 int lnn_conv2d_dx(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY, uint64_t W,
                   int tf32_passes);

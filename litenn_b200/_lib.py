@@ -86,6 +86,9 @@ _SIGNATURES = {
     "lnn_gemm_f32": (c_int, [c_int, c_uint64, c_uint64, c_uint64, c_uint64, c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int]),
     "lnn_conv2d_fwd": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64, c_uint64, c_int, c_float, c_int, c_int]),
     "lnn_conv2d_pool_fwd": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64, c_uint64, c_int, c_float, c_int]),
+    "lnn_nhwc_split": (c_int, [c_int, c_uint64, c_uint64, c_uint64, c_int, c_int, c_int, c_int]),
+    "lnn_conv2d_fwd_packed": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64, c_uint64, c_uint64, c_uint64,
+                                      c_int, c_float, c_int, c_int, c_int, c_int]),
     "lnn_conv2d_dx": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64, c_int]),
     "lnn_conv2d_dw": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64, c_int]),
     "lnn_sgd_step": (c_int, [c_int, c_uint64, c_uint64, c_int64, c_float, c_float]),

@@ -63,7 +63,8 @@ struct Scratch {
 // direct (FP32-pipe) convolution for layers with IC <= 4 (lnn_direct.cu)
 bool conv_direct_applicable(const lnn_conv_geom* g);
 int conv_direct_fwd(Device* d, const lnn_conv_geom* g, float* Y, const float* X, const float* W,
-                    const float* bias, int act, float alpha, int accumulate, int pool);
+                    const float* bias, int act, float alpha, int accumulate, int pool, int packed = 0,
+                    float* Ylo = nullptr, int ocp_out = 0);
 // kernel gradient of the same layers (IC <= 4, 3x3): dW += ...
 bool conv_direct_dw_applicable(const lnn_conv_geom* g);
 int conv_direct_dw(Device* d, const lnn_conv_geom* g, float* dW, const float* dY, const float* X);

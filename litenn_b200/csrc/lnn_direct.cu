@@ -31,7 +31,7 @@ __device__ __forceinline__ float act_apply(float v, int act, float alpha) {
 __global__ void __launch_bounds__(kThreads)
 conv_direct_fwd_kernel(float* __restrict__ Y, const float* __restrict__ X, const float* __restrict__ W,
                        const float* __restrict__ bias, lnn_conv_geom g, int act, float alpha,
-                       int accumulate, int pool) {
+                       int accumulate, int pool, int packed, float* __restrict__ Ylo, int ocp_out) {
   extern __shared__ float wsm[];
   const int taps = g.ic * g.kh * g.kw;
   const int ocp = (g.oc + kOcChunk - 1) / kOcChunk * kOcChunk;
@@ -88,6 +88,42 @@ conv_direct_fwd_kernel(float* __restrict__ Y, const float* __restrict__ X, const
             }
           }
         }
+      }
+      if (packed) {
+        // pooled result written channel-innermost and pre-split for the next convolution:
+        // Y / Ylo are [n][qh][qw][ocp_out], this thread owns 16 consecutive channels of one pixel
+        float hi[kOcChunk], lo[kOcChunk];
+#pragma unroll
+        for (int o = 0; o < kOcChunk; ++o) {
+          const int oc = oc0 + o;
+          float m = 0.0f;
+          if (oc < g.oc) {
+            const float b = bias ? __ldg(bias + oc) : 0.0f;
+            float y00 = a00[o], y01 = a01[o], y10 = a10[o], y11 = a11[o];
+            if (bias) { y00 = __fadd_rn(y00, b); y01 = __fadd_rn(y01, b); y10 = __fadd_rn(y10, b); y11 = __fadd_rn(y11, b); }
+            y00 = act_apply(y00, act, alpha); y01 = act_apply(y01, act, alpha);
+            y10 = act_apply(y10, act, alpha); y11 = act_apply(y11, act, alpha);
+            m = fmaxf(-CUDART_INF_F, y00);
+            if (v01) m = fmaxf(m, y01);
+            if (v10) m = fmaxf(m, y10);
+            if (v01 && v10) m = fmaxf(m, y11);
+          }
+          uint32_t r;
+          asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(m));
+          hi[o] = __uint_as_float(r);
+          asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(__fsub_rn(m, hi[o])));
+          lo[o] = __uint_as_float(r);
+        }
+        const int64_t pix = (n * qh + qy) * qw + qx;
+#pragma unroll
+        for (int o = 0; o < kOcChunk; o += 4) {
+          if (oc0 + o < ocp_out) {
+            *reinterpret_cast<float4*>(Y + pix * ocp_out + oc0 + o) = make_float4(hi[o], hi[o + 1], hi[o + 2], hi[o + 3]);
+            if (Ylo)
+              *reinterpret_cast<float4*>(Ylo + pix * ocp_out + oc0 + o) = make_float4(lo[o], lo[o + 1], lo[o + 2], lo[o + 3]);
+          }
+        }
+        continue;
       }
 #pragma unroll
       for (int o = 0; o < kOcChunk; ++o) {
@@ -377,7 +413,8 @@ bool conv_direct_applicable(const lnn_conv_geom* g) {
 }
 
 int conv_direct_fwd(Device* d, const lnn_conv_geom* g, float* Y, const float* X, const float* W,
-                    const float* bias, int act, float alpha, int accumulate, int pool) {
+                    const float* bias, int act, float alpha, int accumulate, int pool, int packed,
+                    float* Ylo, int ocp_out) {
   const int ocp = (g->oc + kOcChunk - 1) / kOcChunk * kOcChunk;
   const size_t smem = (size_t)g->ic * g->kh * g->kw * ocp * sizeof(float);
   const int64_t quads = (int64_t)g->n * ((g->oh + 1) / 2) * ((g->ow + 1) / 2);
@@ -386,7 +423,7 @@ int conv_direct_fwd(Device* d, const lnn_conv_geom* g, float* Y, const float* X,
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   conv_direct_fwd_kernel<<<(unsigned)blocks, kThreads, smem, d->stream>>>(Y, X, W, bias, *g, act, alpha,
-                                                                         accumulate, pool);
+                                                                         accumulate, pool, packed, Ylo, ocp_out);
   LNN_CHECK_LAUNCH(d);
   return LNN_OK;
 }

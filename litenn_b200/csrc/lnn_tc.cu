@@ -2,6 +2,7 @@
 // and the planners behind lnn_gemm_f32 / lnn_conv2d_fwd / lnn_conv2d_dx / lnn_conv2d_dw.
 #include "lnn_tc.cuh"
 #include <stdlib.h>
+#include <math_constants.h>
 #include <string.h>
 #include <algorithm>
 
@@ -187,6 +188,67 @@ __device__ __forceinline__ float apply_act(float v, int act, float alpha) {
     return __fadd_rn(pos, neg);
   }
   return v;
+}
+
+__device__ __forceinline__ float to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+__device__ __forceinline__ void split1(float x, float& hi, float& lo) {
+  hi = to_tf32(x);
+  lo = to_tf32(__fsub_rn(x, hi));
+}
+
+// Fused max_pool2D(2, 2) of a channels-on-M accumulator: v0 / v1 hold 32 consecutive pixels of
+// two consecutive image rows for this lane's channel (row `a` even, first column `b0` even,
+// `wvalid` of the 32 columns real).  The maximum is taken in the pooling kernel's order
+// (t00, t01, t10, t11 on top of -inf; litenn/core/op/pool2D.py:111-146) after bias and
+// activation, so the value equals the unfused chain bit for bit.
+__device__ __forceinline__ void pooled_store(const TcParams& p, const uint32_t* v0, const uint32_t* v1,
+                                             float bias_v, int oc, int64_t n, int a, int b0, int wvalid) {
+  const bool real = oc < p.OC;
+  if (p.ep_mode == 1 && !real) return;
+  if (p.ep_mode == 2 && oc >= p.ocp) return;
+  float m[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    float t00 = __uint_as_float(v0[2 * j]), t01 = __uint_as_float(v0[2 * j + 1]);
+    float t10 = __uint_as_float(v1[2 * j]), t11 = __uint_as_float(v1[2 * j + 1]);
+    if (p.bias) {
+      t00 = __fadd_rn(t00, bias_v); t01 = __fadd_rn(t01, bias_v);
+      t10 = __fadd_rn(t10, bias_v); t11 = __fadd_rn(t11, bias_v);
+    }
+    t00 = apply_act(t00, p.act, p.alpha); t01 = apply_act(t01, p.act, p.alpha);
+    t10 = apply_act(t10, p.act, p.alpha); t11 = apply_act(t11, p.act, p.alpha);
+    const float mm = fmaxf(fmaxf(fmaxf(fmaxf(-CUDART_INF_F, t00), t01), t10), t11);
+    m[j] = (mm == -CUDART_INF_F) ? 0.0f : mm;
+  }
+  const int npool = min(wvalid, p.AW - b0) >> 1;          // pooled pixels of this chunk that exist
+  const int64_t base = n * p.out_sn + (int64_t)(a >> 1) * p.out_sa + (int64_t)(b0 >> 1) * p.out_sb +
+                       (int64_t)oc * p.out_sc + p.out_base;
+  if (p.ep_mode == 1) {
+    float* dst = p.out + base;                               // 16 consecutive floats of one plane row
+    if (npool == 16 && ((((uintptr_t)dst) & 15) == 0)) {
+#pragma unroll
+      for (int j = 0; j < 16; j += 4)
+        *reinterpret_cast<float4*>(dst + j) = make_float4(m[j], m[j + 1], m[j + 2], m[j + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if (j < npool) dst[j] = m[j];
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      if (j < npool) {
+        float hi = 0.0f, lo = 0.0f;
+        if (real) split1(m[j], hi, lo);                      // pad channels are written as zeros
+        p.out[base + (int64_t)j * p.out_sb] = hi;
+        if (p.out_lo) p.out_lo[base + (int64_t)j * p.out_sb] = lo;
+      }
+    }
+  }
 }
 
 // =========================================================================================
@@ -440,6 +502,30 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
         const int oc = t.m0 + r;
         const bool row_ok = oc < p.OC;
         const float bias_v = (row_ok && p.bias) ? __ldg(p.bias + oc) : 0.0f;
+        if (p.ep_mode != 0) {
+          // fused max pool: tw is a multiple of 32 and th even, so a 32-column chunk is a piece
+          // of one image row and the chunk tw columns later is the row below it
+          const int chunks_per_row = p.tw >> 5;
+          for (int tn_i = 0; tn_i < p.tn; ++tn_i) {
+            for (int th_i = 0; th_i < p.th; th_i += 2) {
+              for (int ch = 0; ch < chunks_per_row; ++ch) {
+                const int c_top = (tn_i * p.th + th_i) * p.tw + ch * 32;
+                uint32_t v0[32], v1[32];
+                tmem_ld32(d_tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c_top, v0);
+                tmem_ld32(d_tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c_top + p.tw), v1);
+                tmem_ld_wait();
+                const int n = t.pn0 + tn_i, a = t.pa0 + th_i, b0 = t.pb0 + ch * 32;
+                if (n < p.NL && a < p.AH && b0 < p.AW && !(p.debug & 4))
+                  pooled_store(p, v0, v1, bias_v, oc, n, a, b0, 32);
+                __syncwarp();
+              }
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
+          continue;
+        }
         float* const obase = p.out + p.out_base + (int64_t)oc * p.out_sc;
         // running (image, row, column) of the first pixel of the current group of four
         int tn_i = 0, th_i = 0, tw_i = 0;
@@ -786,6 +872,26 @@ tc_halo_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
       const int oc = t.m0 + r;
       const bool row_ok = oc < p.OC;
       const float bias_v = (row_ok && p.bias) ? __ldg(p.bias + oc) : 0.0f;
+      if (p.ep_mode != 0) {
+        // fused max pool: th even, tw a multiple of 32; the row below column c is column c + h_pw
+        for (int h_i = 0; h_i < p.th; h_i += 2) {
+          for (int w0 = 0; w0 < p.tw; w0 += 32) {
+            const int c_top = h_i * p.h_pw + w0;
+            uint32_t v0[32], v1[32];
+            tmem_ld32(d_tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c_top, v0);
+            tmem_ld32(d_tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c_top + p.h_pw), v1);
+            tmem_ld_wait();
+            const int a = t.pa0 + h_i, b0 = t.pb0 + w0;
+            if (a < p.AH && b0 < p.AW && !(p.debug & 4))
+              pooled_store(p, v0, v1, bias_v, oc, t.pn0, a, b0, 32);
+            __syncwarp();
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
+        continue;
+      }
       float* const obase = p.out + p.out_base + (int64_t)oc * p.out_sc + (int64_t)t.pn0 * p.out_sn;
       int h_i = 0, w_i = 0;                           // position of the current group of four
       for (int c0 = 0; c0 < ncols; c0 += 32) {
@@ -853,16 +959,6 @@ tc_halo_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
 // operand preparation (HBM-bound)
 // =========================================================================================
 constexpr int kThreads = 256;
-
-__device__ __forceinline__ float to_tf32(float x) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-  return __uint_as_float(r);
-}
-__device__ __forceinline__ void split1(float x, float& hi, float& lo) {
-  hi = to_tf32(x);
-  lo = to_tf32(__fsub_rn(x, hi));
-}
 
 // hi/lo split of a dense [rows][cols] matrix into buffers of row pitch `pitch`
 __global__ void __launch_bounds__(kThreads)
@@ -1186,26 +1282,35 @@ int encode_nhwc(CUtensorMap* tm, const float* base, int n, int h, int w, int cp,
   return encode_map(tm, base, 4, dims, str, box, es, box_c * 4, mn_major);
 }
 
+int nhwc_split_to(lnn::Device* d, float* hi_p, float* lo_p, const float* src, int n, int c, int h,
+                  int w, int cp);
+
 int nhwc_split(lnn::Device* d, lnn::Scratch& hi, lnn::Scratch& lo, const float* src, int n, int c,
                int h, int w, int cp, int want_lo) {
   const uint64_t bytes = (uint64_t)n * h * w * cp * 4;
   int rc = hi.get(bytes);
   if (rc) return rc;
   if (want_lo) { rc = lo.get(bytes); if (rc) return rc; }
+  return nhwc_split_to(d, hi.as<float>(), want_lo ? lo.as<float>() : nullptr, src, n, c, h, w, cp);
+}
+
+// NCHW -> channel-innermost hi (and lo when lo_p is given) copies with channel pitch cp
+int nhwc_split_to(lnn::Device* d, float* hi_p, float* lo_p, const float* src, int n, int c, int h,
+                  int w, int cp) {
+  const int want_lo = lo_p != nullptr;
   const int64_t hw = (int64_t)h * w;
   lnn::ProfScope prof(d, LNN_PROF_PREP);
   if (cp == 8) {
     // few channels (the network's first layer): one thread per pixel, channel planes read
     // coalesced, one 32-byte NHWC pixel written per thread
     nchw_to_nhwc8_split_kernel<<<grid_for(d, (int64_t)n * hw), kThreads, 0, d->stream>>>(
-        hi.as<float>(), want_lo ? lo.as<float>() : nullptr, src, n, c, hw, want_lo);
+        hi_p, lo_p, src, n, c, hw, want_lo);
     LNN_CHECK_LAUNCH(d);
     return LNN_OK;
   }
   const int64_t tiles = (int64_t)n * ((hw + 31) / 32) * ((cp + 31) / 32);
   int64_t grid = std::min<int64_t>(tiles, (int64_t)d->sm_count * 16);
-  nchw_to_nhwc_split_kernel<<<(unsigned)grid, 256, 0, d->stream>>>(
-      hi.as<float>(), want_lo ? lo.as<float>() : nullptr, src, n, c, hw, cp, want_lo);
+  nchw_to_nhwc_split_kernel<<<(unsigned)grid, 256, 0, d->stream>>>(hi_p, lo_p, src, n, c, hw, cp, want_lo);
   LNN_CHECK_LAUNCH(d);
   return LNN_OK;
 }
@@ -1238,9 +1343,12 @@ int check_geom(const lnn_conv_geom* g) {
 // straddle a patch row).  Two patch stages (hi and lo each) plus at least three kernel units
 // must fit shared memory; among the tilings that do, take the one with most real pixels per
 // MMA clock under the measured cost of one tcgen05.mma in this kernel, about max(150, 0.7 * N) clocks.
+// Optional fused pooling / packed output of the channels-on-M kernels (TcParams::ep_mode).
+struct EpiExtra { int ep_mode; float* out_lo; int ocp; };
+
 struct HaloPlan { bool ok; int tw, th, pw, ph, bn, sa, bbuf, acb; double px_per_clk; };
 
-HaloPlan plan_halo(int AH, int AW, int hx, int hy, int a_rows, int nbuf, int cb) {
+HaloPlan plan_halo(int AH, int AW, int hx, int hy, int a_rows, int nbuf, int cb, bool pooled) {
   HaloPlan best;
   memset(&best, 0, sizeof(best));
   const int budget = kSmemLimit - kSmemSlack - 1024;
@@ -1250,10 +1358,11 @@ HaloPlan plan_halo(int AH, int AW, int hx, int hy, int a_rows, int nbuf, int cb)
     const int min_sa = 3;
     for (int di = 0; di < 6; ++di) {
       int tw = (AW + divs[di] - 1) / divs[di];
-      tw = (tw + 3) & ~3;
+      tw = pooled ? ((tw + 31) & ~31) : ((tw + 3) & ~3);     // the fused pool works on 32-column chunks
       const int pw = (tw + hx + 3) & ~3;
       if (pw > 256) continue;
       for (int th = 1; th <= AH && th * pw <= 256; ++th) {
+        if (pooled && (th & 1)) continue;
         const int bn = std::max(16, (th * pw + 15) & ~15);
         const int ph = th + hy;
         if (bn > 256 || ph > 256) continue;
@@ -1282,9 +1391,11 @@ int launch_conv_halo(lnn::Device* d, const float* act_hi, const float* act_lo, i
                      int AW, int ntaps, const int* dy, const int* dx, const int* widx, int OCv,
                      float* out, int64_t out_base, int64_t out_sn, int64_t out_sa, int64_t out_sb,
                      int64_t out_sc, const float* bias, int act, float alpha, int accumulate,
-                     int passes, int* taken) {
+                     int passes, const EpiExtra* ex, int* taken) {
   *taken = 0;
   const int cb = 32;
+  const bool pooled = ex && ex->ep_mode != 0;
+  if (pooled && ((AH | AW) & 1)) return LNN_OK;
   if (kp % cb != 0 || ntaps < 1) return LNN_OK;
   int x0 = dx[0], x1 = dx[0], y0 = dy[0], y1 = dy[0];
   for (int i = 1; i < ntaps; ++i) {
@@ -1294,7 +1405,7 @@ int launch_conv_halo(lnn::Device* d, const float* act_hi, const float* act_lo, i
   const int hx = x1 - x0, hy = y1 - y0;
   const int nbuf = passes == 3 ? 2 : 1;
   const int a_rows = std::min(128, (OCv + 7) & ~7);
-  const HaloPlan hp = plan_halo(AH, AW, hx, hy, a_rows, nbuf, cb);
+  const HaloPlan hp = plan_halo(AH, AW, hx, hy, a_rows, nbuf, cb, pooled);
   // Both kernels turn out to be bound by shared-memory bandwidth (operand reads of the MMAs plus
   // TMA writes, about 90 bytes per clock), so the resident patch only pays where the per-tap
   // kernel is at its worst: one tap per ring stage (32 input channels) or so few output
@@ -1317,6 +1428,7 @@ int launch_conv_halo(lnn::Device* d, const float* act_hi, const float* act_lo, i
   p.out_sn = out_sn; p.out_sa = out_sa; p.out_sb = out_sb; p.out_sc = out_sc; p.out_base = out_base;
   p.OC = OCv;
   p.accumulate = accumulate; p.act = act; p.alpha = alpha; p.bias = bias; p.out = out;
+  if (pooled) { p.ep_mode = ex->ep_mode; p.out_lo = ex->out_lo; p.ocp = ex->ocp; }
   p.h_pw = hp.pw; p.h_ph = hp.ph; p.h_x0 = x0; p.h_y0 = y0; p.h_arows = a_rows; p.h_acb = hp.acb;
   p.h_sa = hp.sa; p.h_sb = 2; p.h_bbuf = hp.bbuf;
   p.debug = env_int("LNN_TC_DEBUG", 0);     // timing experiments only; results are wrong when set
@@ -1369,14 +1481,18 @@ int launch_conv_like(lnn::Device* d, const float* act_hi, const float* act_lo, i
                      int AW, int es, int ntaps, const int* dy, const int* dx, const int* widx,
                      int OCv, float* out, int64_t out_base, int64_t out_sn, int64_t out_sa,
                      int64_t out_sb, int64_t out_sc, const float* bias, int act, float alpha,
-                     int accumulate, int passes) {
+                     int accumulate, int passes, const EpiExtra* ex = nullptr, int* fused = nullptr) {
+  // ex (fused pool / packed output) can only be honoured by the channels-on-M kernels with a
+  // suitable tiling; *fused tells the caller whether it was (nothing is launched when not)
+  const bool pooled = ex && ex->ep_mode != 0;
+  if (fused) *fused = 0;
   if (es == 1 && env_int("LNN_TC_HALO", 1) != 0) {
     int taken = 0;
     const int rc = launch_conv_halo(d, act_hi, act_lo, NL, H, W, kp, w_hi, w_lo, wrows, wtaps, AH, AW,
                                     ntaps, dy, dx, widx, OCv, out, out_base, out_sn, out_sa, out_sb,
-                                    out_sc, bias, act, alpha, accumulate, passes, &taken);
+                                    out_sc, bias, act, alpha, accumulate, passes, ex, &taken);
     if (rc) return rc;
-    if (taken) return LNN_OK;
+    if (taken) { if (fused) *fused = 1; return LNN_OK; }
   }
   int cb = chan_block(kp);
   {
@@ -1392,6 +1508,10 @@ int launch_conv_like(lnn::Device* d, const float* act_hi, const float* act_lo, i
   if (orient == 0) orient = (OCv >= 64 && OCv <= 128) ? 2 : 1;
   const bool chan_m = orient == 2;
   PixTile t = plan_conv_tile(NL, AH, AW, es, chan_m ? 256 : 128);
+  if (pooled) {
+    // 32-column chunks must be pieces of one image row, rows must come in pairs
+    if (!chan_m || es != 1 || (t.tw & 31) || (t.th & 1) || ((AH | AW) & 1)) return LNN_OK;
+  }
   const int pix = t.tn * t.th * t.tw;
   int bn;
   if (chan_m) {
@@ -1421,6 +1541,7 @@ int launch_conv_like(lnn::Device* d, const float* act_hi, const float* act_lo, i
   p.out_sn = out_sn; p.out_sa = out_sa; p.out_sb = out_sb; p.out_sc = out_sc; p.out_base = out_base;
   p.OC = OCv;
   p.accumulate = accumulate; p.act = act; p.alpha = alpha; p.bias = bias; p.out = out;
+  if (pooled) { p.ep_mode = ex->ep_mode; p.out_lo = ex->out_lo; p.ocp = ex->ocp; if (fused) *fused = 1; }
   for (int i = 0; i < ntaps; ++i) { p.tap_dy[i] = dy[i]; p.tap_dx[i] = dx[i]; p.tap_w[i] = widx[i]; }
   CUtensorMap act_h, act_l, w_h, w_l;
   int rc = encode_nhwc(&act_h, act_hi, NL, H, W, kp, cb, t.tw, t.th, t.tn, es);
@@ -1519,8 +1640,25 @@ int lnn_gemm_f32(int dev, uint64_t C, uint64_t A, uint64_t B, uint64_t bias, int
   return launch_tc<MODE_GEMM>(d, grid, mah, mal, mbh, mbl, p);
 }
 
-int lnn_conv2d_fwd(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint64_t W,
-                   uint64_t bias, int act, float alpha, int accumulate, int tf32_passes) {
+int lnn_pool2d_fwd(int dev, int mode, uint64_t O, uint64_t I, int64_t n, int64_t c, int ih, int iw,
+                   int oh, int ow, int pool, int stride, int padl, int padt);
+
+}  // extern "C"
+
+namespace {
+
+struct FwdOpts {
+  uint64_t y_lo = 0, x_lo = 0;
+  int pool = 0;          // Y = max_pool2D(act(conv + bias), 2, 2, 'same')
+  int in_packed = 0;     // X / x_lo are channel-innermost hi / lo copies [n][ih][iw][chan_pad(ic)]
+  int out_packed = 0;    // Y / y_lo receive such copies of the result instead of the NCHW tensor
+};
+
+// conv2D forward with the optional fusions.  Whatever cannot be fused into the convolution's
+// epilogue (odd sizes, tilings that do not pair rows, the pixels-on-M orientation) runs as the
+// separate pooling / repacking kernels, so every combination of options is always available.
+int conv_fwd_impl(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint64_t W, uint64_t bias,
+                  int act, float alpha, int accumulate, int tf32_passes, const FwdOpts& o) {
   LNN_DEV(d, dev);
   int rc = check_geom(g);
   if (rc) return rc;
@@ -1528,16 +1666,31 @@ int lnn_conv2d_fwd(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint
   if (rc) return rc;
   LNN_REQUIRE(Y && X && W, "null buffer");
   LNN_REQUIRE(act == 0 || act == 1, "unknown activation %d", act);
-  if (lnn::conv_direct_applicable(g) && env_int("LNN_CONV_DIRECT", 1))
-    return lnn::conv_direct_fwd(d, g, (float*)(uintptr_t)Y, (const float*)(uintptr_t)X,
-                                (const float*)(uintptr_t)W, (const float*)(uintptr_t)bias, act, alpha,
-                                accumulate, 0);
+  LNN_REQUIRE(!(accumulate && (o.pool || o.out_packed)), "accumulate cannot be combined with pool / packed output");
   const int want_lo = tf32_passes == 3;
+  LNN_REQUIRE(!o.in_packed || !want_lo || o.x_lo, "packed input needs its lo copy for split TF32");
+  const float* biasp = (const float*)(uintptr_t)bias;
+  const int oh_p = o.pool ? (g->oh + 1) / 2 : g->oh, ow_p = o.pool ? (g->ow + 1) / 2 : g->ow;
+  const int ocp = chan_pad(g->oc);
+
+  if (!o.in_packed && lnn::conv_direct_applicable(g) && env_int("LNN_CONV_DIRECT", 1) &&
+      (!o.out_packed || o.pool))
+    return lnn::conv_direct_fwd(d, g, (float*)(uintptr_t)Y, (const float*)(uintptr_t)X,
+                                (const float*)(uintptr_t)W, biasp, act, alpha, accumulate, o.pool,
+                                o.out_packed ? 1 : 0, (float*)(uintptr_t)o.y_lo, ocp);
+
   const int cp = chan_pad(g->ic);
   const int taps = g->kh * g->kw;
   lnn::Scratch xh(d), xl(d), wh(d), wl(d);
-  rc = nhwc_split(d, xh, xl, (const float*)(uintptr_t)X, g->n, g->ic, g->ih, g->iw, cp, want_lo);
-  if (rc) return rc;
+  const float *x_hi, *x_lo;
+  if (o.in_packed) {
+    x_hi = (const float*)(uintptr_t)X;
+    x_lo = want_lo ? (const float*)(uintptr_t)o.x_lo : x_hi;
+  } else {
+    rc = nhwc_split(d, xh, xl, (const float*)(uintptr_t)X, g->n, g->ic, g->ih, g->iw, cp, want_lo);
+    if (rc) return rc;
+    x_hi = xh.as<float>(); x_lo = xl.as<float>();
+  }
   rc = weights_split(d, wh, wl, (const float*)(uintptr_t)W, g->oc, g->ic, taps, cp, 0, want_lo);
   if (rc) return rc;
   int dy[kMaxTaps], dx[kMaxTaps], wi[kMaxTaps];
@@ -1549,33 +1702,84 @@ int lnn_conv2d_fwd(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint
       wi[t] = t;
     }
   const int64_t plane = (int64_t)g->oh * g->ow;
-  return launch_conv_like(d, xh.as<float>(), xl.as<float>(), g->n, g->ih, g->iw, cp, wh.as<float>(),
-                          wl.as<float>(), g->oc, taps, g->oh, g->ow, g->stride, taps, dy, dx, wi,
-                          g->oc, (float*)(uintptr_t)Y, 0, (int64_t)g->oc * plane, g->ow, 1, plane,
-                          (const float*)(uintptr_t)bias, act, alpha, accumulate, tf32_passes);
+  if (o.pool && g->stride == 1) {
+    // try the fused epilogue: pooled NCHW (ep_mode 1) or pooled, packed (ep_mode 2)
+    EpiExtra ex{o.out_packed ? 2 : 1, want_lo ? (float*)(uintptr_t)o.y_lo : nullptr, ocp};
+    const int64_t pplane = (int64_t)oh_p * ow_p;
+    int fused = 0;
+    if (o.out_packed)
+      rc = launch_conv_like(d, x_hi, x_lo, g->n, g->ih, g->iw, cp, wh.as<float>(), wl.as<float>(), g->oc, taps,
+                            g->oh, g->ow, 1, taps, dy, dx, wi, g->oc, (float*)(uintptr_t)Y, 0,
+                            pplane * ocp, (int64_t)ow_p * ocp, ocp, 1, biasp, act, alpha, 0, tf32_passes, &ex, &fused);
+    else
+      rc = launch_conv_like(d, x_hi, x_lo, g->n, g->ih, g->iw, cp, wh.as<float>(), wl.as<float>(), g->oc, taps,
+                            g->oh, g->ow, 1, taps, dy, dx, wi, g->oc, (float*)(uintptr_t)Y, 0,
+                            (int64_t)g->oc * pplane, ow_p, 1, pplane, biasp, act, alpha, 0, tf32_passes, &ex, &fused);
+    if (rc) return rc;
+    if (fused) return LNN_OK;
+  }
+  // un-fused: convolution into its NCHW result (scratch when more steps follow)
+  lnn::Scratch conv_out(d), pool_out(d);
+  float* ydst = (float*)(uintptr_t)Y;
+  if (o.pool || o.out_packed) {
+    rc = conv_out.get((uint64_t)g->n * g->oc * plane * 4);
+    if (rc) return rc;
+    ydst = conv_out.as<float>();
+  }
+  rc = launch_conv_like(d, x_hi, x_lo, g->n, g->ih, g->iw, cp, wh.as<float>(), wl.as<float>(), g->oc, taps,
+                        g->oh, g->ow, g->stride, taps, dy, dx, wi, g->oc, ydst, 0, (int64_t)g->oc * plane,
+                        g->ow, 1, plane, biasp, act, alpha, accumulate, tf32_passes);
+  if (rc) return rc;
+  const float* cur = ydst;
+  if (o.pool) {
+    float* pdst = (float*)(uintptr_t)Y;
+    if (o.out_packed) {
+      rc = pool_out.get((uint64_t)g->n * g->oc * oh_p * ow_p * 4);
+      if (rc) return rc;
+      pdst = pool_out.as<float>();
+    }
+    rc = lnn_pool2d_fwd(dev, LNN_POOL_MAX, (uint64_t)(uintptr_t)pdst, (uint64_t)(uintptr_t)cur, g->n, g->oc,
+                        g->oh, g->ow, oh_p, ow_p, 2, 2, 0, 0);
+    if (rc) return rc;
+    cur = pdst;
+  }
+  if (o.out_packed)
+    return nhwc_split_to(d, (float*)(uintptr_t)Y, want_lo ? (float*)(uintptr_t)o.y_lo : nullptr, cur, g->n,
+                         g->oc, oh_p, ow_p, ocp);
+  return LNN_OK;
 }
 
-int lnn_pool2d_fwd(int dev, int mode, uint64_t O, uint64_t I, int64_t n, int64_t c, int ih, int iw,
-                   int oh, int ow, int pool, int stride, int padl, int padt);
+}  // namespace
+
+extern "C" {
+
+int lnn_conv2d_fwd(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint64_t W,
+                   uint64_t bias, int act, float alpha, int accumulate, int tf32_passes) {
+  return conv_fwd_impl(dev, g, Y, X, W, bias, act, alpha, accumulate, tf32_passes, FwdOpts());
+}
 
 int lnn_conv2d_pool_fwd(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint64_t W,
                         uint64_t bias, int act, float alpha, int tf32_passes) {
+  FwdOpts o;
+  o.pool = 1;
+  return conv_fwd_impl(dev, g, Y, X, W, bias, act, alpha, 0, tf32_passes, o);
+}
+
+int lnn_conv2d_fwd_packed(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t Y_lo, uint64_t X,
+                          uint64_t X_lo, uint64_t W, uint64_t bias, int act, float alpha, int pool,
+                          int in_packed, int out_packed, int tf32_passes) {
+  FwdOpts o;
+  o.y_lo = Y_lo; o.x_lo = X_lo; o.pool = pool; o.in_packed = in_packed; o.out_packed = out_packed;
+  LNN_REQUIRE(!out_packed || tf32_passes == 1 || Y_lo, "packed output needs a lo buffer for split TF32");
+  return conv_fwd_impl(dev, g, Y, X, W, bias, act, alpha, 0, tf32_passes, o);
+}
+
+int lnn_nhwc_split(int dev, uint64_t hi, uint64_t lo, uint64_t X, int n, int c, int h, int w) {
   LNN_DEV(d, dev);
-  int rc = check_geom(g);
-  if (rc) return rc;
-  LNN_REQUIRE(Y && X && W, "null buffer");
-  LNN_REQUIRE(act == 0 || act == 1, "unknown activation %d", act);
-  if (lnn::conv_direct_applicable(g) && env_int("LNN_CONV_DIRECT", 1))
-    return lnn::conv_direct_fwd(d, g, (float*)(uintptr_t)Y, (const float*)(uintptr_t)X,
-                                (const float*)(uintptr_t)W, (const float*)(uintptr_t)bias, act, alpha, 0, 1);
-  // other layers: convolution into pooled scratch, then the pooling kernel
-  lnn::Scratch tmp(d);
-  rc = tmp.get((uint64_t)g->n * g->oc * g->oh * g->ow * 4);
-  if (rc) return rc;
-  rc = lnn_conv2d_fwd(dev, g, (uint64_t)(uintptr_t)tmp.p, X, W, bias, act, alpha, 0, tf32_passes);
-  if (rc) return rc;
-  return lnn_pool2d_fwd(dev, LNN_POOL_MAX, Y, (uint64_t)(uintptr_t)tmp.p, g->n, g->oc, g->oh, g->ow,
-                        (g->oh + 1) / 2, (g->ow + 1) / 2, 2, 2, 0, 0);
+  LNN_REQUIRE(hi && X, "null buffer");
+  LNN_REQUIRE(n > 0 && c > 0 && h > 0 && w > 0, "bad extents");
+  return nhwc_split_to(d, (float*)(uintptr_t)hi, (float*)(uintptr_t)lo, (const float*)(uintptr_t)X, n, c, h,
+                       w, chan_pad(c));
 }
 
 int lnn_conv2d_dx(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY, uint64_t W,

@@ -72,6 +72,12 @@ struct TcParams {
   const float* bias;
   float* out;
   int* status;
+  // fused 2x2/stride-2 max pool (channels-on-M kernels): ep_mode 1 writes the pooled NCHW
+  // tensor, ep_mode 2 writes it channel-innermost and pre-split (out = hi, out_lo = lo, channel
+  // pitch ocp) as the next convolution's operand; the out_s* strides then address pooled pixels
+  int ep_mode;
+  float* out_lo;
+  int ocp;
   int tap_dy[kMaxTaps], tap_dx[kMaxTaps], tap_w[kMaxTaps];
   // halo-resident pixel patch (tc_halo_kernel): the patch of one channel block, with its halo,
   // is loaded once per tile as a flat array of pixels (row pitch h_pw) and every tap reads it

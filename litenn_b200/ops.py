@@ -6,6 +6,8 @@ kernels live in liblitenn_b200.so.  There is no host-side arithmetic fallback.
 """
 import ctypes
 import functools
+
+import numpy as np
 from collections.abc import Iterable
 
 from . import _lib
@@ -589,24 +591,79 @@ def conv2D(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t=None,
     return output_t
 
 
-def conv2D_pool(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t=None, activation=None, alpha=0.1):
-    """max_pool2D(activation(conv2D(x, k) + bias), 2, 2, 'same') in one call, for inference:
-    no grad functions are registered (build the chain from nn.conv2D / nn.leaky_relu /
-    nn.max_pool2D to train).  Same values as that chain."""
+class PackedActivation:
+    """An activation kept in the tensor-core convolution's operand format between the layers of
+    an inference chain: channel-innermost copies hi = tf32(x) and lo = tf32(x - hi), each
+    (N, H, W, C rounded up to 8).  Only conv2D_infer / conv2D_pool consume it; the reference has
+    no counterpart (its conv2D builds an im2col buffer per call, conv2D.py:39-41)."""
+
+    def __init__(self, shape_nchw, hi_t, lo_t):
+        self.shape = TensorShape(shape_nchw)
+        self.hi, self.lo = hi_t, lo_t
+
+    def np(self):
+        """hi + lo as an NCHW array: the fp32 activation up to its last two mantissa bits."""
+        c = self.shape.shape[1]
+        v = self.hi.np().astype(np.float64) + (self.lo.np() if self.lo is not None else 0.0)
+        return np.ascontiguousarray(v[..., :c].transpose(0, 3, 1, 2)).astype(np.float32)
+
+
+def _packed_like(n, c, h, w):
+    cp = (c + 7) & ~7
+    hi = _out((n, h, w, cp))
+    lo = _out((n, h, w, cp)) if _lib.tf32_passes() == 3 else None
+    return PackedActivation((n, c, h, w), hi, lo)
+
+
+def pack_activation(input_t):
+    """NCHW tensor -> PackedActivation (the pre-pass nn.conv2D runs on every call)."""
+    n, c, h, w = input_t.shape.shape
+    out = _packed_like(n, c, h, w)
+    for i, dev in _each_device():
+        _lib_().lnn_nhwc_split(dev, out.hi._ptr(i), out.lo._ptr(i) if out.lo is not None else 0, input_t._ptr(i), n, c, h, w)
+    return out
+
+
+def conv2D_infer(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t=None, activation=None, alpha=0.1,
+                 pool=False, packed_output=False):
+    """Inference convolution: [max_pool2D(]activation(conv2D(x, k) + bias)[, 2, 2, 'same')] in one
+    call, without grad functions.  input_t is a Tensor or a PackedActivation; with
+    packed_output=True the result is a PackedActivation for the next convolution, so the NCHW
+    activation between two layers is never written.  Same values as the un-fused chain
+    (conv2D.py:9-44, Conv2D.py:58-62, element_wise_op.py:207-221, pool2D.py:47-146)."""
+    packed_in = isinstance(input_t, PackedActivation)
     if input_t.shape.rank != 4 or kernel_t.shape.rank != 4:
-        raise ValueError("conv2D_pool expects (N,IC,H,W) input and (OC,IC,KH,KW) kernel")
+        raise ValueError("conv2D expects (N,IC,H,W) input and (OC,IC,KH,KW) kernel")
     g, out_shape = _conv_geom(input_t.shape, kernel_t.shape, int(stride), int(dilation), padding)
     if activation not in (None, "leaky_relu"):
         raise ValueError(f"unknown activation {activation}")
     if bias_t is not None and bias_t.shape.size != g.oc:
         raise ValueError(f"bias must have {g.oc} elements")
-    output_t = _out((g.n, g.oc, (g.oh + 1) // 2, (g.ow + 1) // 2))
-    output_t._set_op_name("conv2D_pool")
+    oh, ow = ((g.oh + 1) // 2, (g.ow + 1) // 2) if pool else (g.oh, g.ow)
+    if packed_output:
+        result = _packed_like(g.n, g.oc, oh, ow)
+        y, y_lo = result.hi, result.lo
+    else:
+        result = y = _out((g.n, g.oc, oh, ow))
+        y_lo = None
+        result._set_op_name("conv2D_infer")
     for i, dev in _each_device():
-        _lib_().lnn_conv2d_pool_fwd(dev, ctypes.byref(g), output_t._ptr(i), input_t._ptr(i), kernel_t._ptr(i),
-                                    bias_t._ptr(i) if bias_t is not None else 0,
-                                    1 if activation == "leaky_relu" else 0, float(alpha), _lib.tf32_passes())
-    return output_t
+        x = input_t.hi._ptr(i) if packed_in else input_t._ptr(i)
+        x_lo = input_t.lo._ptr(i) if (packed_in and input_t.lo is not None) else 0
+        _lib_().lnn_conv2d_fwd_packed(dev, ctypes.byref(g), y._ptr(i), y_lo._ptr(i) if y_lo is not None else 0, x, x_lo,
+                                      kernel_t._ptr(i), bias_t._ptr(i) if bias_t is not None else 0,
+                                      1 if activation == "leaky_relu" else 0, float(alpha), 1 if pool else 0,
+                                      1 if packed_in else 0, 1 if packed_output else 0, _lib.tf32_passes())
+    return result
+
+
+def conv2D_pool(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t=None, activation=None, alpha=0.1,
+                packed_output=False):
+    """max_pool2D(activation(conv2D(x, k) + bias), 2, 2, 'same') in one call, for inference:
+    no grad functions are registered (build the chain from nn.conv2D / nn.leaky_relu /
+    nn.max_pool2D to train).  Same values as that chain."""
+    return conv2D_infer(input_t, kernel_t, stride, dilation, padding, bias_t, activation, alpha, pool=True,
+                        packed_output=packed_output)
 
 
 def _ew_grad_into(dst_zeroed, name, args, I_t, O_t, dO_t):

@@ -190,6 +190,52 @@ def test_conv_direct_dw(nn_gpu, monkeypatch, xs, ws, stride, dil):
     nn.devices.check_status()
 
 
+def _tf32_rna(x):
+    """cvt.rna.tf32.f32 on the host: nearest, ties away from zero, 10 mantissa bits kept."""
+    b = np.ascontiguousarray(x, np.float32).view(np.uint32).astype(np.uint64)
+    return ((b + 0x1000) & 0xFFFFE000).astype(np.uint32).view(np.float32)
+
+
+@pytest.mark.parametrize("xs,ws", [((2, 3, 32, 32), (32, 3, 3, 3)), ((3, 32, 64, 64), (64, 32, 3, 3)),
+                                   ((2, 64, 32, 32), (128, 64, 3, 3)), ((2, 32, 64, 64), (40, 32, 3, 3)),
+                                   ((2, 16, 12, 12), (24, 16, 3, 3)), ((2, 64, 30, 34), (64, 64, 3, 3)),
+                                   ((2, 64, 64, 32), (200, 64, 3, 3))])
+def test_conv_infer_fused_and_packed(nn_gpu, xs, ws):
+    """conv2D_infer: pooled NCHW output, packed output and packed input against the un-fused
+    chain (bit-exact: the fused epilogues apply the same roundings in the same order)."""
+    nn = nn_gpu
+    rng = np.random.default_rng(21)
+    x = rng.standard_normal(xs).astype(np.float32)
+    w = (rng.standard_normal(ws) * 0.1).astype(np.float32)
+    b = rng.uniform(-0.1, 0.1, (ws[0],)).astype(np.float32)
+    xt, wt, bt = nn.Tensor_from_value(x), nn.Tensor_from_value(w), nn.Tensor_from_value(b)
+    kw = dict(bias_t=bt, activation="leaky_relu", alpha=0.1)
+    chain = nn.max_pool2D(nn.conv2D(xt, wt, **kw), 2, 2, "same").np()
+    pooled = nn.conv2D_infer(xt, wt, pool=True, **kw).np()
+    assert_bit_exact(pooled, chain, "pool fused into the epilogue")
+    packed = nn.conv2D_infer(xt, wt, pool=True, packed_output=True, **kw)
+    oc = ws[0]
+    hi = packed.hi.np()
+    want_hi = _tf32_rna(chain)
+    want_lo = _tf32_rna(chain - want_hi)
+    assert_bit_exact(hi[..., :oc].transpose(0, 3, 1, 2), want_hi, "packed hi")
+    assert_bit_exact(packed.lo.np()[..., :oc].transpose(0, 3, 1, 2), want_lo, "packed lo")
+    assert not hi[..., oc:].any() and not packed.lo.np()[..., oc:].any(), "pad channels must be zero"
+    # packed input: same result as the NCHW input, with and without the fused pool
+    xp = nn.pack_activation(xt)
+    got_pool = nn.conv2D_infer(xp, wt, pool=True, **kw).np()
+    got_plain = nn.conv2D_infer(xp, wt, **kw).np()
+    if xs[1] <= 4:
+        # an NCHW input with so few channels takes the FP32-pipe kernel, a packed one the tensor cores
+        K = ws[1] * ws[2] * ws[3]
+        assert_contraction_close(got_pool, chain, K, "packed input, pooled")
+        assert_contraction_close(got_plain, nn.conv2D(xt, wt, **kw).np(), K, "packed input, plain")
+    else:
+        assert_bit_exact(got_pool, chain, "packed input, pooled")
+        assert_bit_exact(got_plain, nn.conv2D(xt, wt, **kw).np(), "packed input, plain")
+    nn.devices.check_status()
+
+
 def test_softmax_ce(nn_gpu):
     ins, outs = load_golden("softmax_ce")["softmax_ce"]
     got = cases.run_case(nn_gpu, "softmax_ce", {}, ins)
