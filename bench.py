@@ -34,7 +34,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 TOTAL_BATCH = 4096
-MICRO_BATCH = 512
+MICRO_BATCH = 1024
 NCU_TRAFFIC_RATIO = 584.6 / 616.7     # dram bytes / (hi + lo operand + output bytes), ncu capture of conv 3a forward
 IMG = (3, 128, 128)
 CHANS = [3, 32, 64, 128, 256]
@@ -689,7 +689,7 @@ def run_ours(args):
 
 
 def main():
-    global TOTAL_BATCH
+    global TOTAL_BATCH, MICRO_BATCH
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
@@ -701,10 +701,12 @@ def main():
     ap.add_argument("--quick", action="store_true", help="fewer iterations in the single-op configurations")
     ap.add_argument("--batch", type=int, default=4096,
                     help="global batch (default 4096, the benchmark configuration; smaller values are for profiling)")
+    ap.add_argument("--micro-batch", type=int, default=MICRO_BATCH, help="images per forward call on one GPU")
     ap.add_argument("--ops-only", default=None, metavar="NAMES",
                     help="run only the single-op configurations whose name contains one of the comma-separated NAMES")
     args = ap.parse_args()
     TOTAL_BATCH = args.batch
+    MICRO_BATCH = args.micro_batch
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
     if args.impl == "reference":
