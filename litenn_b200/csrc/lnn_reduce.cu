@@ -16,6 +16,7 @@
 #include "lnn_common.cuh"
 #include <math_constants.h>
 #include <utility>
+#include <algorithm>
 
 namespace {
 
@@ -285,6 +286,8 @@ reduce_parts_kernel(float* __restrict__ O, float* __restrict__ P, const float* _
     if (parts == 1) {
       if (mean_div != 0.0f) v = __fdiv_rn(v, mean_div);
       O[row] = acc ? __fadd_rn(O[row], v) : v;
+    } else if (c0_fastest) {
+      P[row * parts + c0] = v;                    // inner == 1: partials of a row are contiguous
     } else {
       const int64_t outer_i = row / mi;
       const int64_t rem = row - outer_i * mi;
@@ -360,7 +363,7 @@ reduce_parts4_kernel(float* __restrict__ O, float* __restrict__ P, const float* 
       const int64_t row = gid / parts4;
       const int64_t c0 = (gid - row * parts4) << 2;
       const float4 v = subtree_v4<OP>(I + row_base(g, row), c0, s, L, g);
-      *reinterpret_cast<float4*>(P + row * parts + c0) = v;     // mid == inner == 1: [row][parts]
+      *reinterpret_cast<float4*>(P + row * parts + c0) = v;     // partials of a row are contiguous
     }
   }
 }
@@ -514,13 +517,20 @@ int reduce_impl(lnn::Device* d, PartialSpace& space, float* O, const float* I, i
       LNN_CHECK_LAUNCH(d);
       return LNN_OK;
     }
-    int s = 6;                             // at least 64 leaves per thread
-    while (s < L.S && g.rows * L.n[s] > kTargetThreads) ++s;
+    // enough threads to fill the GPU (a 128-bit thread covers four partials), at least 64 leaves each
+    int64_t target_vals = cols_vec ? 4 * kTargetThreads / 2 : kTargetThreads;
+    if (space.fixed) target_vals = std::min<int64_t>(target_vals, std::max<int64_t>(space.cap / 2, 1024));
+    int s = 6;
+    while (s < L.S && g.rows * L.n[s] > target_vals) ++s;
+    if (L.pow2 && s > kMaxPow2Levels) s = kMaxPow2Levels;   // stay on the unrolled subtree (more partials)
     const int64_t parts = L.n[s];
     float* part = nullptr;
     rc = space.get(g.rows * parts, &part);
     if (rc) return rc;
-    if (cols_vec && mid == 1 && s <= kMaxPow2Levels && parts % 4 == 0 && ((((uintptr_t)part) & 15) == 0)) {
+    // the partials of one kept row are stored contiguously, [row][parts], whatever the position of
+    // the kept axes: the second pass is then a plain row reduction over `parts` columns, the tail
+    // of the same tree
+    if (cols_vec && s <= kMaxPow2Levels && parts % 4 == 0 && ((((uintptr_t)part) & 15) == 0)) {
       reduce_parts4_kernel<OP><<<grid_for(d, g.rows * parts / 4), kThreads, 0, d->stream>>>(
           nullptr, part, I, g, L, s, 0, 0, 0.0f);
     } else {
@@ -528,18 +538,22 @@ int reduce_impl(lnn::Device* d, PartialSpace& space, float* O, const float* I, i
           nullptr, part, I, g, L, s, 1, 0, 0.0f);
     }
     LNN_CHECK_LAUNCH(d);
-    return reduce_impl<OP>(d, space, O, part, outer, parts, mid, 1, 1, acc, mean_div);
+    return reduce_impl<OP>(d, space, O, part, g.rows, 1, 1, parts, 1, acc, mean_div);
   }
   // inner > 1: coalesce along the inner axis, one thread per output when there are enough
+  // four adjacent kept rows per thread when the inner axis allows 128-bit loads
+  const bool vec_possible = L.pow2 && inner % 4 == 0 && ((((uintptr_t)I) & 15) == 0) && ((((uintptr_t)O) & 15) == 0);
   int s = L.S;
-  if (g.rows < 65536 && cols > 256) {
+  // one thread per kept row (or per four) leaves most of the GPU idle when there are few rows:
+  // split the columns as well, down to 16 leaves per thread
+  if (g.rows / (vec_possible ? 4 : 1) < kTargetThreads / 4 && cols > 256) {
+    int64_t target_vals = vec_possible ? 4 * kTargetThreads / 2 : kTargetThreads;
+    if (space.fixed) target_vals = std::min<int64_t>(target_vals, std::max<int64_t>(space.cap / 2, 1024));
     s = 4;
-    while (s < L.S && g.rows * L.n[s] > kTargetThreads) ++s;
+    while (s < L.S && g.rows * L.n[s] > target_vals) ++s;
   }
   const int64_t parts = L.n[s];
-  // four adjacent kept rows per thread when the inner axis allows 128-bit loads
-  const bool rows_vec = L.pow2 && s <= kMaxPow2Levels && inner % 4 == 0 && ((((uintptr_t)I) & 15) == 0) &&
-                        ((((uintptr_t)O) & 15) == 0);
+  const bool rows_vec = vec_possible && s <= kMaxPow2Levels;
   if (parts == 1) {
     if (rows_vec)
       reduce_parts4_kernel<OP><<<grid_for(d, g.rows / 4), kThreads, 0, d->stream>>>(

@@ -61,12 +61,13 @@ def test_noalloc_refuses_oversized_scratch(nn_gpu):
     from litenn_b200 import _lib
     lib = _lib.get_lib()
     dev = nn.devices.get_current()[0]
-    # reducing the leading axis of [200000, 48] is planned with 48 * 6250 = 300000 partials,
-    # more than the 2^18 floats of the static scratch
-    rows, cols = 200000, 48
+    # the planner shrinks the partial count to what the static array holds, but a power-of-two row
+    # is split into subtrees of at most 2^9 leaves: 600 rows of 2^19 columns need 600 * 1024
+    # partials, more than the 2^18 floats of the static scratch
+    rows, cols = 600, 1 << 19
     x = nn.Tensor((rows, cols))
-    out = nn.Tensor((cols,))
+    out = nn.Tensor((rows,))
     with pytest.raises(_lib.LnnError) as ei:
-        lib.lnn_reduce_noalloc(dev.index, _lib.RED["sum"], out._ptr(0), x._ptr(0), 1, 1, 1, rows, cols, 0)
+        lib.lnn_reduce_noalloc(dev.index, _lib.RED["sum"], out._ptr(0), x._ptr(0), rows, 1, 1, cols, 1, 0)
     assert ei.value.code == _lib.E_UNSUPPORTED and "static scratch" in str(ei.value)
     nn.devices.check_status()
