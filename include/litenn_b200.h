@@ -234,6 +234,14 @@ int lnn_conv2d_dx(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY, uin
 /* dW += gradient of the kernel.  ref: op/conv2D.py:52-54 */
 int lnn_conv2d_dw(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY, uint64_t X,
                   int tf32_passes);
+/* The same two gradients from operands that are already in the packed format of lnn_nhwc_split
+ * (dY [n][oh][ow][pad8(oc)], X [n][ih][iw][pad8(ic)], hi and lo each), so that a training step
+ * repacks dY once for both gradients and reuses the copy of X its forward pass made.
+ * ref: op/conv2D.py:46-54 */
+int lnn_conv2d_dx_packed(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY_hi, uint64_t dY_lo,
+                         uint64_t W, int tf32_passes);
+int lnn_conv2d_dw_packed(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY_hi, uint64_t dY_lo,
+                         uint64_t X_hi, uint64_t X_lo, int tf32_passes);
 
 /* ---- optimiser + data-parallel sync --------------------------------------------------- */
 

@@ -91,6 +91,8 @@ _SIGNATURES = {
                                       c_int, c_float, c_int, c_int, c_int, c_int]),
     "lnn_conv2d_dx": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64, c_int]),
     "lnn_conv2d_dw": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64, c_int]),
+    "lnn_conv2d_dx_packed": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64, c_uint64, c_int]),
+    "lnn_conv2d_dw_packed": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64, c_uint64, c_uint64, c_int]),
     "lnn_sgd_step": (c_int, [c_int, c_uint64, c_uint64, c_int64, c_float, c_float]),
     "lnn_nccl_unique_id": (c_int, [c_void_p]),
     "lnn_nccl_init_rank": (c_int, [c_int, c_int, c_int, c_void_p]),

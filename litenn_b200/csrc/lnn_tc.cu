@@ -1782,8 +1782,13 @@ int lnn_nhwc_split(int dev, uint64_t hi, uint64_t lo, uint64_t X, int n, int c, 
                        w, chan_pad(c));
 }
 
-int lnn_conv2d_dx(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY, uint64_t W,
-                  int tf32_passes) {
+}  // extern "C"
+
+namespace {
+
+// dX += ...; dY is NCHW (dy_lo == 0, dy_packed == 0) or the packed hi / lo copies
+int conv_dx_impl(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY, uint64_t dY_lo, int dy_packed,
+                 uint64_t W, int tf32_passes) {
   LNN_DEV(d, dev);
   int rc = check_geom(g);
   if (rc) return rc;
@@ -1791,12 +1796,20 @@ int lnn_conv2d_dx(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY, uin
   if (rc) return rc;
   LNN_REQUIRE(dX && dY && W, "null buffer");
   const int want_lo = tf32_passes == 3;
+  LNN_REQUIRE(!dy_packed || !want_lo || dY_lo, "packed dY needs its lo copy for split TF32");
   const int ocp = chan_pad(g->oc);
   const int taps = g->kh * g->kw;
   const int s = g->stride;
   lnn::Scratch yh(d), yl(d), wh(d), wl(d);
-  rc = nhwc_split(d, yh, yl, (const float*)(uintptr_t)dY, g->n, g->oc, g->oh, g->ow, ocp, want_lo);
-  if (rc) return rc;
+  const float *y_hi, *y_lo;
+  if (dy_packed) {
+    y_hi = (const float*)(uintptr_t)dY;
+    y_lo = want_lo ? (const float*)(uintptr_t)dY_lo : y_hi;
+  } else {
+    rc = nhwc_split(d, yh, yl, (const float*)(uintptr_t)dY, g->n, g->oc, g->oh, g->ow, ocp, want_lo);
+    if (rc) return rc;
+    y_hi = yh.as<float>(); y_lo = yl.as<float>();
+  }
   rc = weights_split(d, wh, wl, (const float*)(uintptr_t)W, g->oc, g->ic, taps, ocp, 1, want_lo);
   if (rc) return rc;
   const int64_t plane = (int64_t)g->ih * g->iw;
@@ -1820,7 +1833,7 @@ int lnn_conv2d_dx(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY, uin
         }
       }
       if (nt == 0) continue;
-      rc = launch_conv_like(d, yh.as<float>(), yl.as<float>(), g->n, g->oh, g->ow, ocp,
+      rc = launch_conv_like(d, y_hi, y_lo, g->n, g->oh, g->ow, ocp,
                             wh.as<float>(), wl.as<float>(), g->ic, taps, AH, AW, 1, nt, dy, dx, wi,
                             g->ic, (float*)(uintptr_t)dX, (int64_t)ph * g->iw + pw,
                             (int64_t)g->ic * plane, (int64_t)s * g->iw, s, plane, nullptr, 0, 0.0f,
@@ -1830,26 +1843,41 @@ int lnn_conv2d_dx(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY, uin
   return LNN_OK;
 }
 
-int lnn_conv2d_dw(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY, uint64_t X,
-                  int tf32_passes) {
+// dW += ...; dY and X are each NCHW or the packed hi / lo copies
+int conv_dw_impl(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY, uint64_t dY_lo, int dy_packed,
+                 uint64_t X, uint64_t X_lo, int x_packed, int tf32_passes) {
   LNN_DEV(d, dev);
   int rc = check_geom(g);
   if (rc) return rc;
   rc = check_passes(tf32_passes);
   if (rc) return rc;
   LNN_REQUIRE(dW && dY && X, "null buffer");
-  if (lnn::conv_direct_dw_applicable(g) && env_int("LNN_CONV_DIRECT", 1))
+  if (!dy_packed && !x_packed && lnn::conv_direct_dw_applicable(g) && env_int("LNN_CONV_DIRECT", 1))
     return lnn::conv_direct_dw(d, g, (float*)(uintptr_t)dW, (const float*)(uintptr_t)dY,
                                (const float*)(uintptr_t)X);
   const int want_lo = tf32_passes == 3;
+  LNN_REQUIRE(!dy_packed || !want_lo || dY_lo, "packed dY needs its lo copy for split TF32");
+  LNN_REQUIRE(!x_packed || !want_lo || X_lo, "packed X needs its lo copy for split TF32");
   const int s = g->stride;
   const int cp = chan_pad(g->ic), ocp = chan_pad(g->oc);
   const int taps = g->kh * g->kw;
-  lnn::Scratch xh(d), xl(d), yh(d), yl(d), part(d);
-  rc = nhwc_split(d, xh, xl, (const float*)(uintptr_t)X, g->n, g->ic, g->ih, g->iw, cp, want_lo);
-  if (rc) return rc;
-  rc = nhwc_split(d, yh, yl, (const float*)(uintptr_t)dY, g->n, g->oc, g->oh, g->ow, ocp, want_lo);
-  if (rc) return rc;
+  lnn::Scratch xh_s(d), xl_s(d), yh_s(d), yl_s(d), part(d);
+  // xh, xl, yh, yl: the hi / lo copies wherever they came from (lo aliases hi for single-pass TF32)
+  const float *xh, *xl, *yh, *yl;
+  if (x_packed) {
+    xh = (const float*)(uintptr_t)X; xl = want_lo ? (const float*)(uintptr_t)X_lo : xh;
+  } else {
+    rc = nhwc_split(d, xh_s, xl_s, (const float*)(uintptr_t)X, g->n, g->ic, g->ih, g->iw, cp, want_lo);
+    if (rc) return rc;
+    xh = xh_s.as<float>(); xl = want_lo ? xl_s.as<float>() : xh;
+  }
+  if (dy_packed) {
+    yh = (const float*)(uintptr_t)dY; yl = want_lo ? (const float*)(uintptr_t)dY_lo : yh;
+  } else {
+    rc = nhwc_split(d, yh_s, yl_s, (const float*)(uintptr_t)dY, g->n, g->oc, g->oh, g->ow, ocp, want_lo);
+    if (rc) return rc;
+    yh = yh_s.as<float>(); yl = want_lo ? yl_s.as<float>() : yh;
+  }
 
   // MN-major tf32 tiles are always 32 channels (128 bytes) wide; channels beyond the padded
   // extent of the NHWC copy are zero-filled by the TMA unit
@@ -1932,13 +1960,13 @@ int lnn_conv2d_dw(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY, uin
     }
   p.ntaps = taps;
   CUtensorMap mah, mal, mbh, mbl;
-  rc = encode_nhwc(&mah, yh.as<float>(), g->n, g->oh, g->ow, ocp, ea, tw, th, 1, 1, true);
+  rc = encode_nhwc(&mah, yh, g->n, g->oh, g->ow, ocp, ea, tw, th, 1, 1, true);
   if (rc) return rc;
-  rc = encode_nhwc(&mal, want_lo ? yl.as<float>() : yh.as<float>(), g->n, g->oh, g->ow, ocp, ea, tw, th, 1, 1, true);
+  rc = encode_nhwc(&mal, yl, g->n, g->oh, g->ow, ocp, ea, tw, th, 1, 1, true);
   if (rc) return rc;
-  rc = encode_nhwc(&mbh, xh.as<float>(), g->n, g->ih, g->iw, cp, eb, tw, th, 1, s, true);
+  rc = encode_nhwc(&mbh, xh, g->n, g->ih, g->iw, cp, eb, tw, th, 1, s, true);
   if (rc) return rc;
-  rc = encode_nhwc(&mbl, want_lo ? xl.as<float>() : xh.as<float>(), g->n, g->ih, g->iw, cp, eb, tw, th, 1, s, true);
+  rc = encode_nhwc(&mbl, xl, g->n, g->ih, g->iw, cp, eb, tw, th, 1, s, true);
   if (rc) return rc;
   dim3 grid((unsigned)splits, (unsigned)oc_tiles, (unsigned)ngroups);
   rc = launch_tc<MODE_DW>(d, grid, mah, mal, mbh, mbl, p);
@@ -1948,6 +1976,30 @@ int lnn_conv2d_dw(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY, uin
       icb, part_ld);
   LNN_CHECK_LAUNCH(d);
   return LNN_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int lnn_conv2d_dx(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY, uint64_t W,
+                  int tf32_passes) {
+  return conv_dx_impl(dev, g, dX, dY, 0, 0, W, tf32_passes);
+}
+
+int lnn_conv2d_dw(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY, uint64_t X,
+                  int tf32_passes) {
+  return conv_dw_impl(dev, g, dW, dY, 0, 0, X, 0, 0, tf32_passes);
+}
+
+int lnn_conv2d_dx_packed(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY_hi, uint64_t dY_lo,
+                         uint64_t W, int tf32_passes) {
+  return conv_dx_impl(dev, g, dX, dY_hi, dY_lo, 1, W, tf32_passes);
+}
+
+int lnn_conv2d_dw_packed(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY_hi, uint64_t dY_lo,
+                         uint64_t X_hi, uint64_t X_lo, int tf32_passes) {
+  return conv_dw_impl(dev, g, dW, dY_hi, dY_lo, 1, X_hi, X_lo, 1, tf32_passes);
 }
 
 }  // extern "C"

@@ -565,15 +565,43 @@ def conv2D(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t=None,
             O_t._pre_act_grad = cached
         return cached[1]
 
-    def grad_x(O_t, dO_t):
+    # Layers that run on the tensor cores read channel-innermost hi/lo copies of their operands.
+    # The copy of the input made for the forward pass is kept for the kernel gradient, and the
+    # copy of dY is made once for both gradients (three repacking passes per layer instead of five).
+    keep_packed = g.ic > 4
+    packed_x = pack_activation(input_t) if keep_packed else None
+
+    def packed_dy(O_t, dO_t):
         d = pre_act_grad(O_t, dO_t)
+        cached = getattr(O_t, "_packed_dy", None)
+        if cached is None or cached[0] is not d:
+            cached = (d, pack_activation(d))
+            O_t._packed_dy = cached
+        return cached[1]
+
+    def _lo(p, i):
+        return p.lo._ptr(i) if p.lo is not None else 0
+
+    def grad_x(O_t, dO_t):
         gx = input_t.get_grad()
+        if keep_packed:
+            pd = packed_dy(O_t, dO_t)
+            for i, dev in _each_device():
+                _lib_().lnn_conv2d_dx_packed(dev, ctypes.byref(g), gx._ptr(i), pd.hi._ptr(i), _lo(pd, i), kernel_t._ptr(i), passes)
+            return
+        d = pre_act_grad(O_t, dO_t)
         for i, dev in _each_device():
             _lib_().lnn_conv2d_dx(dev, ctypes.byref(g), gx._ptr(i), d._ptr(i), kernel_t._ptr(i), passes)
 
     def grad_w(O_t, dO_t):
-        d = pre_act_grad(O_t, dO_t)
         gw = kernel_t.get_grad()
+        if keep_packed:
+            pd = packed_dy(O_t, dO_t)
+            for i, dev in _each_device():
+                _lib_().lnn_conv2d_dw_packed(dev, ctypes.byref(g), gw._ptr(i), pd.hi._ptr(i), _lo(pd, i),
+                                             packed_x.hi._ptr(i), _lo(packed_x, i), passes)
+            return
+        d = pre_act_grad(O_t, dO_t)
         for i, dev in _each_device():
             _lib_().lnn_conv2d_dw(dev, ctypes.byref(g), gw._ptr(i), d._ptr(i), input_t._ptr(i), passes)
 
@@ -586,8 +614,13 @@ def conv2D(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t=None,
     if bias_t is not None:
         output_t._assign_gradfn(bias_t, grad_b)
     for i, dev in _each_device():
-        _lib_().lnn_conv2d_fwd(dev, ctypes.byref(g), output_t._ptr(i), input_t._ptr(i), kernel_t._ptr(i),
-                               bias_t._ptr(i) if bias_t is not None else 0, act, float(alpha), 0, passes)
+        if keep_packed:
+            _lib_().lnn_conv2d_fwd_packed(dev, ctypes.byref(g), output_t._ptr(i), 0, packed_x.hi._ptr(i), _lo(packed_x, i),
+                                          kernel_t._ptr(i), bias_t._ptr(i) if bias_t is not None else 0, act,
+                                          float(alpha), 0, 1, 0, passes)
+        else:
+            _lib_().lnn_conv2d_fwd(dev, ctypes.byref(g), output_t._ptr(i), input_t._ptr(i), kernel_t._ptr(i),
+                                   bias_t._ptr(i) if bias_t is not None else 0, act, float(alpha), 0, passes)
     return output_t
 
 
