@@ -534,45 +534,72 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
           tmem_ld32(d_tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
           tmem_ld_wait();
           if (row_ok && !(p.debug & 4)) {
+            // Phase 1: where each group of four pixels goes, and (for "+=") its old values.  All
+            // loads are issued before any store so that their latencies overlap.
+            float* dsts[8];
+            int pos[8];                                   // tw | th << 8 | tn << 16, or -1: nothing to store
+            uint32_t four_mask = 0, vec_mask = 0;
+            float4 old[8];
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              const int q = c0 + j;
+            for (int gi = 0; gi < 8; ++gi) {
+              const int q = c0 + gi * 4;
+              pos[gi] = -1;
+              old[gi] = make_float4(0.f, 0.f, 0.f, 0.f);
               if (q < p.rows_valid) {
-                float x[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  float tt = __uint_as_float(v[j + e]);
-                  if (p.bias) tt = __fadd_rn(tt, bias_v);
-                  x[e] = apply_act(tt, p.act, p.alpha);
-                }
+                pos[gi] = tw_i | (th_i << 8) | (tn_i << 16);
                 const int n = t.pn0 + tn_i, a = t.pa0 + th_i, b = t.pb0 + tw_i;
                 float* dst = obase + (int64_t)n * p.out_sn + (int64_t)a * p.out_sa + (int64_t)b * p.out_sb;
+                dsts[gi] = dst;
                 const bool four = (tw_i + 3 < p.tw) && (b + 3 < p.AW) && n < p.NL && a < p.AH;
-                if (four && p.out_sb == 1 && ((((uintptr_t)dst) & 15) == 0)) {
-                  float4* d4 = reinterpret_cast<float4*>(dst);
+                if (four) {
+                  four_mask |= 1u << gi;
+                  const bool vec = p.out_sb == 1 && ((((uintptr_t)dst) & 15) == 0);
+                  if (vec) vec_mask |= 1u << gi;
                   if (p.accumulate) {
-                    const float4 o = *d4;
-                    x[0] = __fadd_rn(o.x, x[0]); x[1] = __fadd_rn(o.y, x[1]);
-                    x[2] = __fadd_rn(o.z, x[2]); x[3] = __fadd_rn(o.w, x[3]);
-                  }
-                  *d4 = make_float4(x[0], x[1], x[2], x[3]);
-                } else {
-                  int tn_e = tn_i, th_e = th_i, tw_e = tw_i;
-#pragma unroll
-                  for (int e = 0; e < 4; ++e) {
-                    if (q + e < p.rows_valid) {
-                      const int ne = t.pn0 + tn_e, ae = t.pa0 + th_e, be = t.pb0 + tw_e;
-                      if (ne < p.NL && ae < p.AH && be < p.AW) {
-                        float* de = obase + (int64_t)ne * p.out_sn + (int64_t)ae * p.out_sa + (int64_t)be * p.out_sb;
-                        *de = p.accumulate ? __fadd_rn(*de, x[e]) : x[e];
-                      }
-                    }
-                    if (++tw_e >= p.tw) { tw_e = 0; if (++th_e >= p.th) { th_e = 0; ++tn_e; } }
+                    if (vec) old[gi] = *reinterpret_cast<const float4*>(dst);
+                    else old[gi] = make_float4(dst[0], dst[p.out_sb], dst[2 * p.out_sb], dst[3 * p.out_sb]);
                   }
                 }
               }
               tw_i += 4;
               while (tw_i >= p.tw) { tw_i -= p.tw; if (++th_i >= p.th) { th_i = 0; ++tn_i; } }
+            }
+            // Phase 2: bias, activation, add, store
+#pragma unroll
+            for (int gi = 0; gi < 8; ++gi) {
+              if (pos[gi] < 0) continue;
+              const int j = gi * 4;
+              float x[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float tt = __uint_as_float(v[j + e]);
+                if (p.bias) tt = __fadd_rn(tt, bias_v);
+                x[e] = apply_act(tt, p.act, p.alpha);
+              }
+              float* dst = dsts[gi];
+              if (four_mask & (1u << gi)) {
+                if (p.accumulate) {
+                  x[0] = __fadd_rn(old[gi].x, x[0]); x[1] = __fadd_rn(old[gi].y, x[1]);
+                  x[2] = __fadd_rn(old[gi].z, x[2]); x[3] = __fadd_rn(old[gi].w, x[3]);
+                }
+                if (vec_mask & (1u << gi)) *reinterpret_cast<float4*>(dst) = make_float4(x[0], x[1], x[2], x[3]);
+                else { dst[0] = x[0]; dst[p.out_sb] = x[1]; dst[2 * p.out_sb] = x[2]; dst[3 * p.out_sb] = x[3]; }
+              } else {
+                // a group that crosses the end of a tile row or of the image: element by element
+                int tw_e = pos[gi] & 0xff, th_e = (pos[gi] >> 8) & 0xff, tn_e = pos[gi] >> 16;
+                const int q = c0 + j;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  if (q + e < p.rows_valid) {
+                    const int ne = t.pn0 + tn_e, ae = t.pa0 + th_e, be = t.pb0 + tw_e;
+                    if (ne < p.NL && ae < p.AH && be < p.AW) {
+                      float* de = obase + (int64_t)ne * p.out_sn + (int64_t)ae * p.out_sa + (int64_t)be * p.out_sb;
+                      *de = p.accumulate ? __fadd_rn(*de, x[e]) : x[e];
+                    }
+                  }
+                  if (++tw_e >= p.tw) { tw_e = 0; if (++th_e >= p.th) { th_e = 0; ++tn_e; } }
+                }
+              }
             }
           }
           __syncwarp();
@@ -649,6 +676,14 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
             *dst = make_float4(x[0], x[1], x[2], x[3]);
           }
         } else {
+          // "+=": all old values are loaded before the first store (the compiler cannot reorder a
+          // load past a store through the same pointer with a run-time stride)
+          float oldv[32];
+          if (p.accumulate) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              oldv[j] = (c0 + j < col_limit) ? outp[(int64_t)(col0 + c0 + j) * col_stride] : 0.0f;
+          }
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             if (c0 + j < col_limit) {
@@ -656,7 +691,7 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
               if (p.bias) tt = __fadd_rn(tt, __ldg(p.bias + col0 + c0 + j));
               tt = apply_act(tt, p.act, p.alpha);
               float* dst = outp + (int64_t)(col0 + c0 + j) * col_stride;
-              if (p.accumulate) tt = __fadd_rn(*dst, tt);
+              if (p.accumulate) tt = __fadd_rn(oldv[j], tt);
               *dst = tt;
             }
           }
@@ -899,39 +934,62 @@ tc_halo_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
         tmem_ld32(d_tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
         tmem_ld_wait();
         if (row_ok) {
+          // Phase 1: destinations and (for "+=") old values of the eight groups, all loads first
+          float* dsts[8];
+          int wpos[8];                                  // column inside the tile, or -1: nothing to store
+          uint32_t vec_mask = 0;
+          float4 old[8];
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
+          for (int gi = 0; gi < 8; ++gi) {
             const int a = t.pa0 + h_i, b = t.pb0 + w_i;
-            if (c0 + j < ncols && w_i < p.tw && a < p.AH && b < p.AW && !(p.debug & 4)) {
-              float x[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                float tt = __uint_as_float(v[j + e]);
-                if (p.bias) tt = __fadd_rn(tt, bias_v);
-                x[e] = apply_act(tt, p.act, p.alpha);
-              }
+            wpos[gi] = -1;
+            old[gi] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c0 + gi * 4 < ncols && w_i < p.tw && a < p.AH && b < p.AW && !(p.debug & 4)) {
+              wpos[gi] = w_i;
               float* dst = obase + (int64_t)a * p.out_sa + (int64_t)b * p.out_sb;
+              dsts[gi] = dst;
               const bool four = (w_i + 3 < p.tw) && (b + 3 < p.AW);
-              if (four && p.out_sb == 1 && ((((uintptr_t)dst) & 15) == 0)) {
-                float4* d4 = reinterpret_cast<float4*>(dst);
-                if (p.accumulate) {
-                  const float4 o = *d4;
-                  x[0] = __fadd_rn(o.x, x[0]); x[1] = __fadd_rn(o.y, x[1]);
-                  x[2] = __fadd_rn(o.z, x[2]); x[3] = __fadd_rn(o.w, x[3]);
-                }
-                *d4 = make_float4(x[0], x[1], x[2], x[3]);
-              } else {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  if (w_i + e < p.tw && b + e < p.AW) {
-                    float* de = dst + (int64_t)e * p.out_sb;
-                    *de = p.accumulate ? __fadd_rn(*de, x[e]) : x[e];
-                  }
+              const bool vec = four && p.out_sb == 1 && ((((uintptr_t)dst) & 15) == 0);
+              if (vec) vec_mask |= 1u << gi;
+              if (p.accumulate) {
+                if (vec) old[gi] = *reinterpret_cast<const float4*>(dst);
+                else {
+                  old[gi].x = dst[0];
+                  if (w_i + 1 < p.tw && b + 1 < p.AW) old[gi].y = dst[p.out_sb];
+                  if (w_i + 2 < p.tw && b + 2 < p.AW) old[gi].z = dst[2 * p.out_sb];
+                  if (w_i + 3 < p.tw && b + 3 < p.AW) old[gi].w = dst[3 * p.out_sb];
                 }
               }
             }
             w_i += 4;
             if (w_i >= p.h_pw) { w_i = 0; ++h_i; }
+          }
+          // Phase 2: bias, activation, add, store
+#pragma unroll
+          for (int gi = 0; gi < 8; ++gi) {
+            if (wpos[gi] < 0) continue;
+            const int j = gi * 4;
+            float x[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float tt = __uint_as_float(v[j + e]);
+              if (p.bias) tt = __fadd_rn(tt, bias_v);
+              x[e] = apply_act(tt, p.act, p.alpha);
+            }
+            if (p.accumulate) {
+              x[0] = __fadd_rn(old[gi].x, x[0]); x[1] = __fadd_rn(old[gi].y, x[1]);
+              x[2] = __fadd_rn(old[gi].z, x[2]); x[3] = __fadd_rn(old[gi].w, x[3]);
+            }
+            float* dst = dsts[gi];
+            if (vec_mask & (1u << gi)) {
+              *reinterpret_cast<float4*>(dst) = make_float4(x[0], x[1], x[2], x[3]);
+            } else {
+              const int w0 = wpos[gi];
+              const int b = t.pb0 + w0;
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                if (w0 + e < p.tw && b + e < p.AW) dst[(int64_t)e * p.out_sb] = x[e];
+            }
           }
         }
         __syncwarp();
