@@ -373,8 +373,11 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
           const uint32_t fb = full0 + 8u * s;
           if (p.debug & 2) { mbar_arrive(fb); }         // timing experiment: no loads
           else {
+            // DW: only the 32-channel blocks of dY that hold real output channels are loaded; the
+            // accumulator rows of the others are never read back
+            const int a_valid = MODE == MODE_DW ? min(p.a_loads, (p.OC - t.oc_t * 128 + 31) >> 5) : p.a_loads;
             if (MODE == MODE_DW)
-              mbar_expect_tx(fb, (uint32_t)nbuf * (uint32_t)(p.a_loads * p.a_load_bytes + t.nblk * p.b_load_bytes));
+              mbar_expect_tx(fb, (uint32_t)nbuf * (uint32_t)(a_valid * p.a_load_bytes + t.nblk * p.b_load_bytes));
             else
               mbar_expect_tx(fb, unit_tx * (uint32_t)nun);
             uint32_t dst = tiles + s * stage_sz;
@@ -409,7 +412,7 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
                   const int at = (pidx / p.tiles_b) % p.tiles_a;
                   const int nt = pidx / (p.tiles_b * p.tiles_a);
                   const int ea = p.swz_a >> 2, eb = p.swz_b >> 2;
-                  for (int i = 0; i < p.a_loads; ++i)
+                  for (int i = 0; i < a_valid; ++i)
                     tma_load_4d(da + i * p.a_load_bytes, ta, fb, t.oc_t * 128 + i * ea, bt * p.tw,
                                 at * p.th, nt * p.tn);
                   int tapi = t.nb0 / p.ic_tiles, icb = t.nb0 - tapi * p.ic_tiles;
@@ -1956,23 +1959,26 @@ int conv_dw_impl(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY, uint
   pix_cap = std::min(pix_cap & ~7, 128);
   const int wcap = std::min(pix_cap, 256 / s);
   LNN_REQUIRE(wcap >= 8, "stride too large for the weight-gradient kernel");
-  int tw, th;
-  if (g->ow >= wcap) { tw = wcap & ~7; th = 1; }
-  else {
-    // box width may exceed ow (zero filled); choose (th, tw_box) with tw_box*th % 8 == 0
-    int best_tw = (g->ow + 7) & ~7, best_th = 1;
-    double best_eff = (double)g->ow / best_tw;
-    for (int h = 2; h <= 8 && h <= g->oh && h * s <= 256; ++h) {
+  // Patch = th rows x tw columns of one image with tw*th a multiple of 8 (the box may be wider than
+  // the image: zero filled).  Among the shapes that fit, take the one that wastes the fewest of
+  // its pixels over the whole image (the image width is cut into 1..8 equal pieces), larger first.
+  int tw = 8, th = 1;
+  {
+    // real pixels per clock: a patch of P pixels costs about 60 clocks per pixel of MMAs (three
+    // passes of P/8 instructions) plus about 1500 clocks per ring hand-over (fitted to measurements)
+    double best = -1.0;
+    for (int h = 1; h <= 8 && h <= g->oh && h * s <= 256; ++h) {
       const int mult = 8 / gcd_int(8, h);
-      const int w = ((g->ow + mult - 1) / mult) * mult;
-      if (w * h > pix_cap || w * s > 256) continue;
-      const int tiles = (g->oh + h - 1) / h;
-      const double eff = (double)g->ow / w * (double)g->oh / (tiles * h);
-      if (eff > best_eff + 1e-9 || (eff > best_eff - 1e-9 && w * h > best_tw * best_th)) {
-        best_eff = eff; best_tw = w; best_th = h;
+      for (int k = 1; k <= 8; ++k) {
+        int w = (g->ow + k - 1) / k;
+        w = ((w + mult - 1) / mult) * mult;
+        if (w * h > pix_cap || w * s > 256 || w > wcap) continue;
+        const double tiles = (double)((g->ow + w - 1) / w) * (double)((g->oh + h - 1) / h);
+        const double score = (double)g->ow * g->oh / (tiles * (60.0 * w * h + 1500.0));
+        if (score > best * 1.001) { best = score; tw = w; th = h; }
       }
     }
-    tw = best_tw; th = best_th;
+    LNN_REQUIRE(best > 0, "no pixel patch fits the weight-gradient kernel");
   }
   const int pix = tw * th;
   const int tiles_b = (g->ow + tw - 1) / tw, tiles_a = (g->oh + th - 1) / th, tiles_n = g->n;
