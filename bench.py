@@ -228,9 +228,11 @@ class CNN:
                 x = nn.conv2D_infer(x, c.kernel, 1, 1, "same", bias_t=c.bias, activation="leaky_relu", alpha=0.1,
                                     pool=i < 3, packed_output=(i < 3 and self.packed))
                 continue
-            x = nn.conv2D(x, c.kernel, 1, 1, "same", bias_t=c.bias, activation="leaky_relu", alpha=0.1)
             if i < 3:
-                x = nn.max_pool2D(x, 2, 2, "same")
+                # trainable fused block: same values and gradients as conv2D -> leaky_relu -> max_pool2D
+                x = nn.conv2D_block(x, c.kernel, 1, 1, "same", bias_t=c.bias, activation="leaky_relu", alpha=0.1)
+            else:
+                x = nn.conv2D(x, c.kernel, 1, 1, "same", bias_t=c.bias, activation="leaky_relu", alpha=0.1)
         x = nn.flatten(nn.reduce_mean(x, (2, 3)))
         return self.dense(x)
 

@@ -137,6 +137,13 @@ enum { LNN_POOL_AVG = 0, LNN_POOL_MAX = 1, LNN_POOL_MIN = 2 };
 /* ref: op/pool2D.py:111-146 */
 int lnn_pool2d_fwd(int dev, int mode, uint64_t O, uint64_t I, int64_t n, int64_t c,
                    int ih, int iw, int oh, int ow, int pool, int stride, int padl, int padt);
+/* dZ = gradient of leaky_relu (act = 1) after the gradient of max_pool2D(2, 2) in one pass, written
+ * (not added): Y = leaky_relu(Z) [n,c,ih,iw] is the pooling input, P [n,c,ih/2,iw/2] its output,
+ * dP the gradient of P.  Same roundings as lnn_pool2d_bwd into a zero-filled tensor followed by
+ * lnn_eltwise_bwd(leaky_relu) into another.  Needs even ih, iw % 4 == 0, 16-byte aligned Y / dZ;
+ * LNN_E_UNSUPPORTED otherwise.  ref: op/pool2D.py:147-230 + op/element_wise_op.py:207-221 */
+int lnn_pool2x2_lrelu_bwd(int dev, uint64_t dZ, uint64_t Y, uint64_t P, uint64_t dP, int64_t n,
+                          int64_t c, int ih, int iw, float alpha, int act);
 /* dI += ... ; ref: op/pool2D.py:147-230 (I and O are only read for max/min) */
 int lnn_pool2d_bwd(int dev, int mode, uint64_t dI, uint64_t I, uint64_t dO, uint64_t O,
                    int64_t n, int64_t c, int ih, int iw, int oh, int ow,

@@ -200,6 +200,52 @@ inline int grid_for(const lnn::Device* d, int64_t work_items) {
   return (int)blocks;
 }
 
+// Gradient of max_pool2D(2, 2) followed by the gradient of leaky_relu in one pass, WRITING dZ
+// (the chain of the two un-fused gradient kernels reads and re-writes two zero-filled
+// full-resolution tensors).  Y = leaky_relu(Z) is the pooled tensor's input, P its output, dP the
+// gradient of P.  Per element exactly the roundings of the un-fused chain: the pooling gradient
+// 0 + (0 + dP) at the first window position equal to P in row-major order (pool2D.py:147-230),
+// then 0 + that * ((Y >= 0) + alpha * (Y < 0)) (element_wise_op.py:207-221; sign(Y) == sign(Z)).
+__global__ void __launch_bounds__(kThreads)
+pool2x2_lrelu_bwd_kernel(float* __restrict__ dZ, const float* __restrict__ Y, const float2* __restrict__ dP,
+                         const float2* __restrict__ P, int64_t total2, int ih, int iw, int oh, int ow2,
+                         float alpha, int act) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t gid = tid; gid < total2; gid += nthreads) {
+    const int x2 = (int)(gid % ow2);
+    const int64_t t = gid / ow2;
+    const int y = (int)(t % oh);
+    const int64_t plane = t / oh;
+    const int64_t off0 = (plane * ih + 2 * y) * (int64_t)iw + 4 * x2;
+    const float4 a = __ldcs(reinterpret_cast<const float4*>(Y + off0));
+    const float4 b = __ldcs(reinterpret_cast<const float4*>(Y + off0 + iw));
+    const float2 g = dP[gid];
+    const float2 o = P[gid];
+    float ga[4] = {0.f, 0.f, 0.f, 0.f}, gb[4] = {0.f, 0.f, 0.f, 0.f};
+    if (a.x == o.x) ga[0] = g.x; else if (a.y == o.x) ga[1] = g.x;
+    else if (b.x == o.x) gb[0] = g.x; else if (b.y == o.x) gb[1] = g.x;
+    if (a.z == o.y) ga[2] = g.y; else if (a.w == o.y) ga[3] = g.y;
+    else if (b.z == o.y) gb[2] = g.y; else if (b.w == o.y) gb[3] = g.y;
+    const float ya[4] = {a.x, a.y, a.z, a.w}, yb[4] = {b.x, b.y, b.z, b.w};
+    float ra[4], rb[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float ua = __fadd_rn(0.0f, __fadd_rn(0.0f, ga[e]));
+      float ub = __fadd_rn(0.0f, __fadd_rn(0.0f, gb[e]));
+      if (act) {
+        const float fa = __fadd_rn(ya[e] >= 0.0f ? 1.0f : 0.0f, __fmul_rn(alpha, ya[e] < 0.0f ? 1.0f : 0.0f));
+        const float fb = __fadd_rn(yb[e] >= 0.0f ? 1.0f : 0.0f, __fmul_rn(alpha, yb[e] < 0.0f ? 1.0f : 0.0f));
+        ua = __fadd_rn(0.0f, __fmul_rn(ua, fa));
+        ub = __fadd_rn(0.0f, __fmul_rn(ub, fb));
+      }
+      ra[e] = ua; rb[e] = ub;
+    }
+    __stcs(reinterpret_cast<float4*>(dZ + off0), make_float4(ra[0], ra[1], ra[2], ra[3]));
+    __stcs(reinterpret_cast<float4*>(dZ + off0 + iw), make_float4(rb[0], rb[1], rb[2], rb[3]));
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -276,6 +322,25 @@ int lnn_pool2d_bwd(int dev, int mode, uint64_t dI, uint64_t I, uint64_t dO, uint
     pool_bwd_kernel<LNN_POOL_MAX><<<grid, kThreads, 0, d->stream>>>(di, i, dout, o, total, g);
   else
     pool_bwd_kernel<LNN_POOL_MIN><<<grid, kThreads, 0, d->stream>>>(di, i, dout, o, total, g);
+  LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
+}
+
+
+int lnn_pool2x2_lrelu_bwd(int dev, uint64_t dZ, uint64_t Y, uint64_t P, uint64_t dP, int64_t n, int64_t c,
+                          int ih, int iw, float alpha, int act) {
+  LNN_DEV(d, dev);
+  LNN_REQUIRE(dZ && Y && P && dP, "null buffer");
+  LNN_REQUIRE(n > 0 && c > 0 && ih > 0 && iw > 0, "bad extents");
+  LNN_REQUIRE(act == 0 || act == 1, "unknown activation %d", act);
+  if ((ih & 1) || (iw & 3) || ((dZ | Y) & 15) || ((P | dP) & 7))
+    return lnn::set_error(LNN_E_UNSUPPORTED,
+                          "fused pooling gradient needs an even height, a width that is a multiple of 4 and aligned buffers");
+  const int oh = ih / 2, ow = iw / 2;
+  const int64_t total2 = n * c * oh * (ow / 2);
+  pool2x2_lrelu_bwd_kernel<<<grid_for(d, total2), kThreads, 0, d->stream>>>(
+      (float*)(uintptr_t)dZ, (const float*)(uintptr_t)Y, (const float2*)(uintptr_t)dP,
+      (const float2*)(uintptr_t)P, total2, ih, iw, oh, ow / 2, alpha, act);
   LNN_CHECK_LAUNCH(d);
   return LNN_OK;
 }

@@ -533,7 +533,8 @@ def _conv_geom(input_shape, kernel_shape, stride, dilation, padding):
     return g, TensorShape((N, KO, ci.OH, ci.OW))
 
 
-def conv2D(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t=None, activation=None, alpha=0.1):
+def conv2D(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t=None, activation=None, alpha=0.1,
+           _pooled=False):
     """2-D convolution, input (N,IC,H,W), kernel (OC,IC,KH,KW) (conv2D.py:9-44).
 
     bias_t / activation ('leaky_relu') are optional epilogue fusions that give the same
@@ -551,9 +552,25 @@ def conv2D(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t=None,
     output_t = _out(out_shape)
     output_t._set_op_name("conv2D")
     act = 1 if activation == "leaky_relu" else 0
+    conv_out_t = output_t
+    if _pooled:
+        # conv2D_block: the tensor handed to the caller (and carrying the grad functions) is the
+        # max-pooled one; the full-resolution activation is kept for the backward pass only
+        output_t = _out((g.n, g.oc, g.oh // 2, g.ow // 2))
+        output_t._set_op_name("conv2D_block")
 
     def pre_act_grad(O_t, dO_t):
         # gradient w.r.t. the convolution output (before the fused activation)
+        if _pooled:
+            cached = getattr(O_t, "_pre_act_grad", None)
+            if cached is None or cached[0] is not dO_t:
+                d = _out(conv_out_t.shape)              # every element is written
+                for i, dev in _each_device():
+                    _lib_().lnn_pool2x2_lrelu_bwd(dev, d._ptr(i), conv_out_t._ptr(i), O_t._ptr(i), dO_t._ptr(i),
+                                                  g.n, g.oc, g.oh, g.ow, float(alpha), act)
+                cached = (dO_t, d)
+                O_t._pre_act_grad = cached
+            return cached[1]
         if not act:
             return dO_t
         cached = getattr(O_t, "_pre_act_grad", None)
@@ -615,13 +632,30 @@ def conv2D(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t=None,
         output_t._assign_gradfn(bias_t, grad_b)
     for i, dev in _each_device():
         if keep_packed:
-            _lib_().lnn_conv2d_fwd_packed(dev, ctypes.byref(g), output_t._ptr(i), 0, packed_x.hi._ptr(i), _lo(packed_x, i),
+            _lib_().lnn_conv2d_fwd_packed(dev, ctypes.byref(g), conv_out_t._ptr(i), 0, packed_x.hi._ptr(i), _lo(packed_x, i),
                                           kernel_t._ptr(i), bias_t._ptr(i) if bias_t is not None else 0, act,
                                           float(alpha), 0, 1, 0, passes)
         else:
-            _lib_().lnn_conv2d_fwd(dev, ctypes.byref(g), output_t._ptr(i), input_t._ptr(i), kernel_t._ptr(i),
+            _lib_().lnn_conv2d_fwd(dev, ctypes.byref(g), conv_out_t._ptr(i), input_t._ptr(i), kernel_t._ptr(i),
                                    bias_t._ptr(i) if bias_t is not None else 0, act, float(alpha), 0, passes)
+        if _pooled:
+            _lib_().lnn_pool2d_fwd(dev, _lib.POOL["max"], output_t._ptr(i), conv_out_t._ptr(i), g.n, g.oc, g.oh, g.ow,
+                                   g.oh // 2, g.ow // 2, 2, 2, 0, 0)
     return output_t
+
+
+def conv2D_block(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t=None, activation=None, alpha=0.1):
+    """max_pool2D(activation(conv2D(x, k) + bias), 2, 2, 'same') as ONE trainable op: same values
+    and gradients as the chain nn.conv2D -> nn.leaky_relu -> nn.max_pool2D, but the backward pass
+    computes the gradient of the convolution output from the pooled gradient in a single kernel
+    instead of two zero fills and two read-modify-write passes over full-resolution tensors
+    (pool2D.py:147-230, element_wise_op.py:207-221).  Shapes the fused gradient kernel does not
+    cover (odd height, width not a multiple of 4) run as the chain."""
+    g, _ = _conv_geom(input_t.shape, kernel_t.shape, int(stride), int(dilation), padding)
+    if (g.oh % 2) or (g.ow % 4):
+        y = conv2D(input_t, kernel_t, stride, dilation, padding, bias_t, activation, alpha)
+        return pool2D_op("max", y, 2, 2, "same")
+    return conv2D(input_t, kernel_t, stride, dilation, padding, bias_t, activation, alpha, _pooled=True)
 
 
 class PackedActivation:

@@ -190,6 +190,31 @@ def test_conv_direct_dw(nn_gpu, monkeypatch, xs, ws, stride, dil):
     nn.devices.check_status()
 
 
+@pytest.mark.parametrize("xs,ws", [((2, 3, 32, 32), (16, 3, 3, 3)), ((2, 32, 16, 24), (40, 32, 3, 3)),
+                                   ((2, 8, 10, 10), (8, 8, 3, 3))])
+def test_conv_block_equals_chain(nn_gpu, xs, ws):
+    """conv2D_block (one trainable op, fused pooling + leaky_relu gradient) against the chain
+    conv2D(+bias, leaky_relu) -> max_pool2D: values and all three gradients bit for bit."""
+    nn = nn_gpu
+    rng = np.random.default_rng(31)
+    x = rng.standard_normal(xs).astype(np.float32)
+    w = (rng.standard_normal(ws) * 0.2).astype(np.float32)
+    b = rng.uniform(-0.1, 0.1, (ws[0],)).astype(np.float32)
+    dp = rng.standard_normal((xs[0], ws[0], (xs[2] + 1) // 2, (xs[3] + 1) // 2)).astype(np.float32)
+    res = {}
+    for kind in ("chain", "block"):
+        xt, wt, bt = nn.Tensor_from_value(x), nn.Tensor_from_value(w), nn.Tensor_from_value(b)
+        if kind == "chain":
+            y = nn.max_pool2D(nn.conv2D(xt, wt, bias_t=bt, activation="leaky_relu", alpha=0.1), 2, 2, "same")
+        else:
+            y = nn.conv2D_block(xt, wt, bias_t=bt, activation="leaky_relu", alpha=0.1)
+        nn.backward({y: dp}, grad_for_non_trainables=True)
+        res[kind] = (y.np(), xt.get_grad().np(), wt.get_grad().np(), bt.get_grad().np())
+    for name, a, c in zip(("y", "dx", "dw", "db"), res["block"], res["chain"]):
+        assert_bit_exact(a, c, f"conv2D_block {name}")
+    nn.devices.check_status()
+
+
 def _tf32_rna(x):
     """cvt.rna.tf32.f32 on the host: nearest, ties away from zero, 10 mantissa bits kept."""
     b = np.ascontiguousarray(x, np.float32).view(np.uint32).astype(np.uint64)
