@@ -14,6 +14,11 @@
 // backward GEMMs, and the convolution A-tiles are gathered straight from an NHWC copy of
 // the activations by 4-D tiled TMA (zero fill outside the image = padding).
 //
+// Unit-stride convolutions with few input channels per tap use a second kernel
+// (tc_halo_kernel) that keeps the pixel patch with its halo resident in shared memory and
+// reads every tap through a shifted descriptor.  The channels-on-M kernels can fold a 2x2
+// max-pool into the epilogue and write the result in the next convolution's operand format.
+//
 // Every wait on an mbarrier is bounded: when the budget runs out the role records a
 // status word, raises a CTA-wide abort flag and falls through to the common tear-down
 // (bounded delay for TMA copies still in flight, TMEM dealloc), so a wrong descriptor
@@ -44,7 +49,7 @@ struct TcParams {
   uint32_t tmem_cols;
   int num_kb;                    // k-blocks per output tile (GEMM/CONV); patches per split (DW)
   int grid_x, grid_y, grid_z;    // logical tile grid walked by the persistent CTAs
-  int debug;                     // timing experiments: 1 no MMA, 2 no TMA loads, 4 no stores
+  int debug;                     // timing experiments: 1 no MMA, 2 no TMA loads, 4 no stores, 8 no tap shift
   int kgroup;                    // units (K slabs / tap-channel blocks / patches) per ring stage
   // GEMM
   int64_t M, N;                  // logical output extents
@@ -62,8 +67,7 @@ struct TcParams {
   int ICv;                       // valid columns (DW)
   // DW
   int patches_total, patches_per_split;
-  int dw_tap_dy, dw_tap_dx;      // unused placeholders (taps come from the arrays below)
-  int64_t part_stride_split, part_stride_tap, part_ld;   // partial buffer [split][tap][ocp][icp]
+  int64_t part_stride_split, part_stride_tap, part_ld;   // partial buffer [split][oc_pad128][(tap, block) x 32]
   int oc_tiles, ic_tiles;        // ic_tiles: 32-channel blocks of the input channels
   int nb_total, nb_group;        // DW: (tap, channel block) column blocks in total / per tile
   // epilogue
