@@ -25,6 +25,7 @@ struct Device {
   int* status_dev = nullptr;                     // device status word (bounded waits)
   int* status_host = nullptr;                    // pinned mirror
   void* nccl_comm = nullptr;
+  uint32_t smem_attr_done = 0;                   // kernels whose dynamic shared-memory limit was raised on this device
   bool profiling = false;
   struct ProfSpan { int slot; cudaEvent_t start, stop; };
   std::vector<ProfSpan> prof_spans;

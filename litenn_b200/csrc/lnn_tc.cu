@@ -1265,11 +1265,11 @@ int launch_tc(lnn::Device* d, dim3 grid, const CUtensorMap& ah, const CUtensorMa
   if (num_tiles >= (1ll << 31)) return lnn::set_error(LNN_E_UNSUPPORTED, "too many tiles");
   const unsigned ctas = (unsigned)std::min<int64_t>(num_tiles, d->sm_count);
   const int smem = stages * stage + 1024;
-  static bool attr_set[4] = {false, false, false, false};
-  if (!attr_set[MODE]) {
+  // the opt-in to more than 48 KB of dynamic shared memory is a per-device property of the kernel
+  if (!(d->smem_attr_done & (1u << MODE))) {
     LNN_CUDA(cudaFuncSetAttribute(tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   kSmemLimit - 1024));
-    attr_set[MODE] = true;
+    d->smem_attr_done |= 1u << MODE;
   }
   {
     lnn::ProfScope prof(d, MODE == MODE_CONVT ? (int)LNN_PROF_TC_CONV : MODE);   // slots follow the modes
@@ -1518,11 +1518,10 @@ int launch_conv_halo(lnn::Device* d, const float* act_hi, const float* act_lo, i
   LNN_REQUIRE(ptiles * mtiles < (1ll << 31), "too many tiles");
   p.grid_x = (int)ptiles; p.grid_y = (int)mtiles; p.grid_z = 1;
   const int smem = p.h_sa * nbuf * p.a_tile_bytes + p.h_sb * nbuf * p.h_bbuf + 1024;
-  static bool attr_set = false;
-  if (!attr_set) {
+  if (!(d->smem_attr_done & (1u << 8))) {
     LNN_CUDA(cudaFuncSetAttribute(tc_halo_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   kSmemLimit - 1024));
-    attr_set = true;
+    d->smem_attr_done |= 1u << 8;
   }
   const unsigned ctas = (unsigned)std::min<int64_t>(ptiles * mtiles, d->sm_count);
   {
