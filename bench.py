@@ -204,6 +204,7 @@ class CNN:
         self.nn = nn
         self.training = False      # inference uses the fused conv+bias+lrelu+maxpool entry
         self.packed = os.environ.get("LNN_BENCH_PACKED", "1") != "0"
+        self.block = os.environ.get("LNN_BENCH_BLOCK", "1") != "0"
         self.convs = []
         for i in range(4):
             c = nn.Conv2D(CHANS[i], CHANS[i + 1], 3, padding="same",
@@ -228,11 +229,13 @@ class CNN:
                 x = nn.conv2D_infer(x, c.kernel, 1, 1, "same", bias_t=c.bias, activation="leaky_relu", alpha=0.1,
                                     pool=i < 3, packed_output=(i < 3 and self.packed))
                 continue
-            if i < 3:
+            if i < 3 and self.block:
                 # trainable fused block: same values and gradients as conv2D -> leaky_relu -> max_pool2D
                 x = nn.conv2D_block(x, c.kernel, 1, 1, "same", bias_t=c.bias, activation="leaky_relu", alpha=0.1)
             else:
                 x = nn.conv2D(x, c.kernel, 1, 1, "same", bias_t=c.bias, activation="leaky_relu", alpha=0.1)
+                if i < 3:
+                    x = nn.max_pool2D(x, 2, 2, "same")
         x = nn.flatten(nn.reduce_mean(x, (2, 3)))
         return self.dense(x)
 

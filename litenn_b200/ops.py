@@ -559,14 +559,20 @@ def conv2D(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t=None,
         output_t = _out((g.n, g.oc, g.oh // 2, g.ow // 2))
         output_t._set_op_name("conv2D_block")
 
+    # The grad functions below are stored inside output_t, so they must not capture output_t itself
+    # (a reference cycle would keep the whole chain of activations alive until the cycle collector
+    # runs): they receive it as O_t.  Only the pooled variant needs a second tensor, the
+    # full-resolution activation, which does not refer back to the pooled one.
+    full_res_t = conv_out_t if _pooled else None
+
     def pre_act_grad(O_t, dO_t):
         # gradient w.r.t. the convolution output (before the fused activation)
         if _pooled:
             cached = getattr(O_t, "_pre_act_grad", None)
             if cached is None or cached[0] is not dO_t:
-                d = _out(conv_out_t.shape)              # every element is written
+                d = _out(full_res_t.shape)              # every element is written
                 for i, dev in _each_device():
-                    _lib_().lnn_pool2x2_lrelu_bwd(dev, d._ptr(i), conv_out_t._ptr(i), O_t._ptr(i), dO_t._ptr(i),
+                    _lib_().lnn_pool2x2_lrelu_bwd(dev, d._ptr(i), full_res_t._ptr(i), O_t._ptr(i), dO_t._ptr(i),
                                                   g.n, g.oc, g.oh, g.ow, float(alpha), act)
                 cached = (dO_t, d)
                 O_t._pre_act_grad = cached
