@@ -28,7 +28,11 @@ __device__ __forceinline__ float act_apply(float v, int act, float alpha) {
 
 // W is OIHW.  Shared layout: [ic][kh][kw][ocp] with ocp = OC rounded up to 16.
 // pool != 0: Y is [N][OC][ceil(OH/2)][ceil(OW/2)] = max_pool2D(act(conv + bias), 2, 2, 'same').
-__global__ void __launch_bounds__(kThreads)
+// FAST_IC > 0: 3x3 taps, stride 1, dilation 1 and exactly FAST_IC input channels, everything
+// unrolled (the quad's 4x4 input patch is read once per channel, validity of its rows and columns
+// is decided once per quad); FAST_IC == 0: any geometry.  Same accumulation order in both.
+template <int FAST_IC>
+__global__ void __launch_bounds__(kThreads, 2)
 conv_direct_fwd_kernel(float* __restrict__ Y, const float* __restrict__ X, const float* __restrict__ W,
                        const float* __restrict__ bias, lnn_conv_geom g, int act, float alpha,
                        int accumulate, int pool, int packed, float* __restrict__ Ylo, int ocp_out) {
@@ -58,8 +62,46 @@ conv_direct_fwd_kernel(float* __restrict__ Y, const float* __restrict__ X, const
       float a00[kOcChunk], a01[kOcChunk], a10[kOcChunk], a11[kOcChunk];
 #pragma unroll
       for (int o = 0; o < kOcChunk; ++o) { a00[o] = 0.f; a01[o] = 0.f; a10[o] = 0.f; a11[o] = 0.f; }
+      if (FAST_IC > 0) {
+        const int py = oh0 - g.padt, px = ow0 - g.padl;
+        bool rok[4], cok[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          rok[r] = py + r >= 0 && py + r < g.ih;
+          cok[r] = px + r >= 0 && px + r < g.iw;
+        }
+#pragma unroll 1
+        for (int ic = 0; ic < FAST_IC; ++ic) {     // one channel's patch in registers at a time
+          const float* xp = xin + ic * in_plane + (int64_t)py * g.iw + px;
+          float xv[4][4];
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) xv[r][c] = (rok[r] && cok[c]) ? __ldg(xp + r * g.iw + c) : 0.0f;
+          }
+#pragma unroll
+          for (int kh = 0; kh < 3; ++kh) {
+#pragma unroll
+            for (int kw = 0; kw < 3; ++kw) {
+              const float4* wv = reinterpret_cast<const float4*>(wsm + ((ic * 3 + kh) * 3 + kw) * ocp + oc0);
+#pragma unroll
+              for (int j = 0; j < kOcChunk / 4; ++j) {
+                const float4 w4 = wv[j];
+                const float ww[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  a00[4 * j + e] = fmaf(xv[kh][kw], ww[e], a00[4 * j + e]);
+                  a01[4 * j + e] = fmaf(xv[kh][kw + 1], ww[e], a01[4 * j + e]);
+                  a10[4 * j + e] = fmaf(xv[kh + 1][kw], ww[e], a10[4 * j + e]);
+                  a11[4 * j + e] = fmaf(xv[kh + 1][kw + 1], ww[e], a11[4 * j + e]);
+                }
+              }
+            }
+          }
+        }
+      }
       int tap = 0;
-      for (int ic = 0; ic < g.ic; ++ic) {
+      for (int ic = 0; ic < (FAST_IC > 0 ? 0 : g.ic); ++ic) {
         const float* xp = xin + ic * in_plane;
         for (int kh = 0; kh < g.kh; ++kh) {
           const int ih0 = oh0 * g.stride + kh * g.dilation - g.padt;
@@ -422,8 +464,18 @@ int conv_direct_fwd(Device* d, const lnn_conv_geom* g, float* Y, const float* X,
   const int64_t cap = (int64_t)d->sm_count * 8;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
-  conv_direct_fwd_kernel<<<(unsigned)blocks, kThreads, smem, d->stream>>>(Y, X, W, bias, *g, act, alpha,
-                                                                         accumulate, pool, packed, Ylo, ocp_out);
+  const bool fast = g->kh == 3 && g->kw == 3 && g->stride == 1 && g->dilation == 1;
+#define LNN_FWD_LAUNCH(F_)                                                                               \
+  conv_direct_fwd_kernel<F_><<<(unsigned)blocks, kThreads, smem, d->stream>>>(Y, X, W, bias, *g, act, alpha, \
+                                                                              accumulate, pool, packed, Ylo, ocp_out)
+  switch (fast ? g->ic : 0) {
+    case 1: LNN_FWD_LAUNCH(1); break;
+    case 2: LNN_FWD_LAUNCH(2); break;
+    case 3: LNN_FWD_LAUNCH(3); break;
+    case 4: LNN_FWD_LAUNCH(4); break;
+    default: LNN_FWD_LAUNCH(0); break;
+  }
+#undef LNN_FWD_LAUNCH
   LNN_CHECK_LAUNCH(d);
   return LNN_OK;
 }
