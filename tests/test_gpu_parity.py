@@ -108,6 +108,13 @@ def test_fused_conv_bias_lrelu_equals_unfused(nn_gpu):
     unfused = nn.leaky_relu(nn.conv2D(x, w) + b.reshape((1, -1, 1, 1)), 0.1).np()
     fused = nn.conv2D(x, w, bias_t=b, activation="leaky_relu", alpha=0.1).np()
     assert_bit_exact(fused, unfused, "conv epilogue fusion")
+    # non-finite pre-activations must take the reference's literal form (0 * inf = NaN)
+    bs = ins["b"].copy()
+    bs[:4] = [np.inf, -np.inf, np.nan, 3e38]
+    b2 = nn.Tensor_from_value(bs)
+    unfused = nn.leaky_relu(nn.conv2D(x, w) + b2.reshape((1, -1, 1, 1)), 0.1).np()
+    fused = nn.conv2D(x, w, bias_t=b2, activation="leaky_relu", alpha=0.1).np()
+    assert_bit_exact(fused, unfused, "conv epilogue fusion, non-finite bias")
 
 
 @pytest.mark.parametrize("xs,ws", [((2, 3, 17, 13), (8, 3, 3, 3)), ((2, 3, 32, 32), (32, 3, 3, 3)),
