@@ -19,14 +19,8 @@ constexpr int kMaxWeights = 11 * 1024;     // floats of shared memory for one la
 
 __device__ __forceinline__ float act_apply(float v, int act, float alpha) {
   if (act == 1) {
-    // leaky_relu as the reference writes it: I*(I>=0) + alpha*I*(I<0)
-    // (litenn/core/op/element_wise_op.py:207-221).  For finite I and finite alpha*I that sum is,
-    // bit for bit (signed zeros included), I when I >= 0 and alpha*I otherwise; infinities and
-    // NaN take the literal form, whose 0*inf terms give NaN.
-    const float t = __fmul_rn(alpha, v);
-    if (fabsf(v) < CUDART_INF_F && fabsf(t) < CUDART_INF_F) return v >= 0.0f ? v : t;
     const float pos = __fmul_rn(v, v >= 0.0f ? 1.0f : 0.0f);
-    const float neg = __fmul_rn(t, v < 0.0f ? 1.0f : 0.0f);
+    const float neg = __fmul_rn(__fmul_rn(alpha, v), v < 0.0f ? 1.0f : 0.0f);
     return __fadd_rn(pos, neg);
   }
   return v;
