@@ -149,6 +149,7 @@ conv_direct_fwd_kernel(float* __restrict__ Y, const float* __restrict__ X, const
             if (v01) m = fmaxf(m, y01);
             if (v10) m = fmaxf(m, y10);
             if (v01 && v10) m = fmaxf(m, y11);
+            if (m == -CUDART_INF_F) m = 0.0f;      // a window of NaNs, as the pooling kernel
           }
           uint32_t r;
           asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(m));
@@ -181,6 +182,7 @@ conv_direct_fwd_kernel(float* __restrict__ Y, const float* __restrict__ X, const
             if (v01) m = fmaxf(m, y01);
             if (v10) m = fmaxf(m, y10);
             if (v01 && v10) m = fmaxf(m, y11);
+            if (m == -CUDART_INF_F) m = 0.0f;      // a window of NaNs, as the pooling kernel
             float* dst = Y + (n * g.oc + oc) * pool_plane + (int64_t)qy * qw + qx;
             *dst = accumulate ? __fadd_rn(*dst, m) : m;
           } else {

@@ -314,6 +314,27 @@ def test_conv_infer_fused_and_packed(nn_gpu, xs, ws):
     nn.devices.check_status()
 
 
+@pytest.mark.parametrize("xs,ws", [((2, 3, 32, 32), (32, 3, 3, 3)), ((2, 32, 64, 64), (64, 32, 3, 3)),
+                                   ((2, 64, 32, 32), (128, 64, 3, 3))])
+def test_fused_pool_epilogue_non_finite(nn_gpu, xs, ws):
+    """The fused epilogues reduce the 2x2 window before bias and activation (same bits on finite
+    values); windows with inf / NaN must fall back to the literal order of the chain."""
+    nn = nn_gpu
+    rng = np.random.default_rng(41)
+    x = rng.standard_normal(xs).astype(np.float32)
+    w = (rng.standard_normal(ws) * 0.1).astype(np.float32)
+    b = rng.uniform(-0.1, 0.1, (ws[0],)).astype(np.float32)
+    b[:6] = [np.inf, -np.inf, np.nan, 3e38, -3e38, 0.0]
+    x[0, 0, 5, 5] = np.inf          # a few windows with non-finite convolution results
+    x[1, 1, 9, 4] = np.nan
+    xt, wt, bt = nn.Tensor_from_value(x), nn.Tensor_from_value(w), nn.Tensor_from_value(b)
+    kw = dict(bias_t=bt, activation="leaky_relu", alpha=0.1)
+    chain = nn.max_pool2D(nn.conv2D(xt, wt, **kw), 2, 2, "same").np()
+    fused = nn.conv2D_infer(xt, wt, pool=True, **kw).np()
+    assert_bit_exact(fused, chain, "fused pool epilogue with non-finite values")
+    nn.devices.check_status()
+
+
 def test_softmax_ce(nn_gpu):
     ins, outs = load_golden("softmax_ce")["softmax_ce"]
     got = cases.run_case(nn_gpu, "softmax_ce", {}, ins)
