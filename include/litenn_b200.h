@@ -63,6 +63,13 @@ int lnn_d2h(int dev, void* dst, uint64_t src, uint64_t bytes);
 int lnn_d2d(int dev, uint64_t dst, uint64_t src, uint64_t bytes);
 /* ref: minicl/CLBuffer.py:83-96 (fill), initializer/Scalar.py */
 int lnn_fill_f32(int dev, uint64_t dst, int64_t count, float value);
+/* dst[i] = hash(i + seed) * (high - low) + low with the reference's counter-based PCG hash: the
+ * same bits as its device-side initializer.  ref: initializer/RandomUniform.py:12-28,
+ * CLKernelHelper.py:210-216 */
+int lnn_init_uniform(int dev, uint64_t dst, int64_t count, uint32_t seed, float low, float high);
+/* dst[i] = mean + sqrt(-2 log(rx)) * cos(2 PI ry) * stddev, (rx, ry) the 2-D PCG hash of
+ * (i + seed, 1).  ref: initializer/RandomNormal.py:10-30, CLKernelHelper.py:218-233,250-253 */
+int lnn_init_normal(int dev, uint64_t dst, int64_t count, uint32_t seed, float mean, float stddev);
 /* ref: minicl/CLDevice.py:51-55 (wait = clFinish) */
 int lnn_sync(int dev);
 /* asynchronous copies on the device stream; host memory should come from lnn_host_alloc */

@@ -55,6 +55,8 @@ _SIGNATURES = {
     "lnn_d2h": (c_int, [c_int, c_void_p, c_uint64, c_uint64]),
     "lnn_d2d": (c_int, [c_int, c_uint64, c_uint64, c_uint64]),
     "lnn_fill_f32": (c_int, [c_int, c_uint64, c_int64, c_float]),
+    "lnn_init_uniform": (c_int, [c_int, c_uint64, c_int64, ctypes.c_uint32, c_float, c_float]),
+    "lnn_init_normal": (c_int, [c_int, c_uint64, c_int64, ctypes.c_uint32, c_float, c_float]),
     "lnn_sync": (c_int, [c_int]),
     "lnn_h2d_async": (c_int, [c_int, c_uint64, c_void_p, c_uint64]),
     "lnn_d2h_async": (c_int, [c_int, c_void_p, c_uint64, c_uint64]),

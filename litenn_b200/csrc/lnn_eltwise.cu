@@ -434,7 +434,66 @@ static bool operand_vec_ok(const Operand& op, uint64_t ptr) {
   return false;
 }
 
+namespace {
+
+// Random initializers: counter-based, one hash of (element index + seed) per element, so the
+// result does not depend on the launch geometry.  PCG output functions as the reference uses
+// them (litenn/core/CLKernelHelper.py:210-233; initializer/RandomUniform.py:12-20,
+// RandomNormal.py:10-24); 2^-32 is the reference's 1 / (float)0xffffffff in single precision.
+__device__ __forceinline__ uint32_t pcg_hash(uint32_t v) {
+  const uint32_t state = v * 747796405u + 2891336453u;
+  const uint32_t word = ((state >> ((state >> 28) + 4u)) ^ state) * 277803737u;
+  return (word >> 22) ^ word;
+}
+__device__ __forceinline__ void pcg2d_hash(uint32_t& a, uint32_t& b) {
+  a = a * 1664525u + 1013904223u; b = b * 1664525u + 1013904223u;
+  a += b * 1664525u; b += a * 1664525u;
+  a ^= a >> 16; b ^= b >> 16;
+  a += b * 1664525u; b += a * 1664525u;
+  a ^= a >> 16; b ^= b >> 16;
+}
+constexpr float kUIF = 1.0f / 4294967296.0f;
+
+__global__ void __launch_bounds__(kThreads)
+init_uniform_kernel(float* __restrict__ O, int64_t n, uint32_t seed, float low, float high) {
+  const float range = fsub(high, low);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const float h = fmul(__uint2float_rn(pcg_hash((uint32_t)((uint64_t)i + seed))), kUIF);
+    O[i] = fadd(fmul(h, range), low);
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+init_normal_kernel(float* __restrict__ O, int64_t n, uint32_t seed, float mean, float stddev) {
+  const float two_pi = 2.0f * 3.14159274101257f;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    uint32_t a = (uint32_t)((uint64_t)i + seed), b = 1u;
+    pcg2d_hash(a, b);
+    const float rx = fmul(__uint2float_rn(a), kUIF), ry = fmul(__uint2float_rn(b), kUIF);
+    const float r = fmul(sqrtf(fmul(-2.0f, logf(rx))), cosf(fmul(two_pi, ry)));
+    O[i] = fadd(mean, fmul(r, stddev));
+  }
+}
+
+}  // namespace
+
 extern "C" {
+
+int lnn_init_uniform(int dev, uint64_t dst, int64_t count, uint32_t seed, float low, float high) {
+  LNN_DEV(d, dev);
+  LNN_REQUIRE(dst && count > 0, "bad arguments");
+  init_uniform_kernel<<<grid_for(d, count), kThreads, 0, d->stream>>>((float*)(uintptr_t)dst, count, seed, low, high);
+  LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
+}
+
+int lnn_init_normal(int dev, uint64_t dst, int64_t count, uint32_t seed, float mean, float stddev) {
+  LNN_DEV(d, dev);
+  LNN_REQUIRE(dst && count > 0, "bad arguments");
+  init_normal_kernel<<<grid_for(d, count), kThreads, 0, d->stream>>>((float*)(uintptr_t)dst, count, seed, mean, stddev);
+  LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
+}
 
 int lnn_fill_f32(int dev, uint64_t dst, int64_t count, float value) {
   LNN_DEV(d, dev);

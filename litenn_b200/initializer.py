@@ -1,9 +1,13 @@
-"""Initializers.  Scalar and NumpyArray fill device buffers through the C ABI
-(litenn/core/initializer/Scalar.py, NumpyArray.py).  The random ones draw on the HOST with
-numpy and upload -- the reference generates them on the device with a PCG hash
-(initializer/RandomUniform.py:12-28), whose bit stream is not reproduced here; the
-distributions (uniform range, normal mean/std, He/Glorot fans) are the same."""
+"""Initializers (litenn/core/initializer/*.py).  Scalar and NumpyArray fill device buffers
+through the C ABI; the random ones run on the device with the reference's counter-based PCG
+hash (RandomUniform.py:12-28, RandomNormal.py:10-30) and draw the hash seed the way it does,
+np.random.randint(2**31) at initialisation time, so after the same np.random.seed(...) a
+uniform tensor has the reference's bits and a normal one differs only by the device's log / cos
+rounding.  HeUniform / HeNormal / GlorotUniform / GlorotNormal take (gain, fan_in[, fan_out]) in
+the reference's order; Conv2D / Dense fill in missing fans (Conv2D.py:41-44, Dense.py:28-31)."""
 import numpy as np
+
+from . import _lib
 
 
 class Initializer:
@@ -39,8 +43,15 @@ class NumpyArray(Initializer):
         buf.set(self.np_value.reshape(shape.shape))
 
 
-def _rng():
-    return np.random.default_rng(np.random.randint(2**31))
+def _draw_seed():
+    return int(np.random.randint(2147483648))
+
+
+def _each_device_buffer(buf):
+    from .devices import devices
+    if devices._shallow > 0:
+        return None
+    return buf.device.index, buf.ptr(), buf.size // 4
 
 
 class RandomUniform(Initializer):
@@ -48,7 +59,12 @@ class RandomUniform(Initializer):
         self.low, self.high = low, high
 
     def initialize_buffer(self, buf, shape):
-        buf.set(_rng().uniform(self.low, self.high, shape.shape).astype(np.float32))
+        seed = _draw_seed()
+        tgt = _each_device_buffer(buf)
+        if tgt is not None:
+            _lib.get_lib().lnn_init_uniform(tgt[0], tgt[1], tgt[2], seed, float(np.float32(self.low)), float(np.float32(self.high)))
+
+    def __str__(self): return f"RandomUniform low={self.low}, high={self.high}"
 
 
 class RandomNormal(Initializer):
@@ -56,56 +72,72 @@ class RandomNormal(Initializer):
         self.mean, self.stddev = mean, stddev
 
     def initialize_buffer(self, buf, shape):
-        buf.set(_rng().normal(self.mean, self.stddev, shape.shape).astype(np.float32))
+        seed = _draw_seed()
+        tgt = _each_device_buffer(buf)
+        if tgt is not None:
+            _lib.get_lib().lnn_init_normal(tgt[0], tgt[1], tgt[2], seed, float(np.float32(self.mean)), float(np.float32(self.stddev)))
+
+    def __str__(self): return f"RandomNormal mean={self.mean}, stddev={self.stddev}"
 
 
 def _fans(shape, fan_in, fan_out):
-    """Fans as initializer/He.py:18-31 / Glorot.py derive them: conv kernels (OC,IC,KH,KW)
-    use IC*KH*KW / OC*KH*KW, matrices (in,out) use the two extents."""
-    if fan_in is not None and fan_out is not None:
-        return fan_in, fan_out
+    """Fans when the layer did not set them: conv kernels (OC,IC,KH,KW) use IC*KH*KW /
+    OC*KH*KW (Conv2D.py:41-44), matrices (in,out) the two extents (Dense.py:28-31)."""
     s = shape.shape
     if len(s) == 4:
         rf = s[2] * s[3]
-        return s[1] * rf, s[0] * rf
-    if len(s) >= 2:
-        return s[0], s[1]
-    return s[0], s[0]
+        fi, fo = s[1] * rf, s[0] * rf
+    elif len(s) >= 2:
+        fi, fo = s[0], s[1]
+    else:
+        fi = fo = s[0]
+    return (fan_in if fan_in is not None else fi), (fan_out if fan_out is not None else fo)
 
 
-class HeNormal(Initializer):
-    def __init__(self, fan_in=None, fan_out=None, gain=1.0):
-        self.fan_in, self.fan_out, self.gain = fan_in, fan_out, gain
+class _InitHe(Initializer):
+    """std = gain * sqrt(2 / fan_in); uniform uses +-sqrt(3) * std  (He.py:18-31)."""
 
-    def initialize_buffer(self, buf, shape):
-        fi, _ = _fans(shape, self.fan_in, self.fan_out)
-        buf.set(_rng().normal(0.0, self.gain * np.sqrt(2.0 / fi), shape.shape).astype(np.float32))
+    def __init__(self, type, gain, fan_in):
+        self.type, self.gain, self.fan_in = type, gain, fan_in
 
-
-class HeUniform(Initializer):
-    def __init__(self, fan_in=None, fan_out=None, gain=1.0):
-        self.fan_in, self.fan_out, self.gain = fan_in, fan_out, gain
+    def has_fan_in(self): return True
+    def has_fan_out(self): return False
 
     def initialize_buffer(self, buf, shape):
-        fi, _ = _fans(shape, self.fan_in, self.fan_out)
-        lim = self.gain * np.sqrt(6.0 / fi)
-        buf.set(_rng().uniform(-lim, lim, shape.shape).astype(np.float32))
+        fi, _ = _fans(shape, self.fan_in, None)
+        std = self.gain * np.sqrt(2.0 / fi)
+        if self.type == "uniform":
+            a = np.sqrt(3.0) * std
+            RandomUniform(-a, a).initialize_buffer(buf, shape)
+        else:
+            RandomNormal(0.0, std).initialize_buffer(buf, shape)
+
+    def __str__(self): return f"InitHe type={self.type}, gain={self.gain}, fan_in={self.fan_in}"
 
 
-class GlorotNormal(Initializer):
-    def __init__(self, fan_in=None, fan_out=None, gain=1.0):
-        self.fan_in, self.fan_out, self.gain = fan_in, fan_out, gain
+class _InitGlorot(Initializer):
+    """std = gain * sqrt(2 / (fan_in + fan_out)); uniform uses +-sqrt(3) * std  (Glorot.py:18-33)."""
+
+    def __init__(self, type, gain, fan_in, fan_out):
+        self.type, self.gain, self.fan_in, self.fan_out = type, gain, fan_in, fan_out
+
+    def has_fan_in(self): return True
+    def has_fan_out(self): return True
 
     def initialize_buffer(self, buf, shape):
         fi, fo = _fans(shape, self.fan_in, self.fan_out)
-        buf.set(_rng().normal(0.0, self.gain * np.sqrt(2.0 / (fi + fo)), shape.shape).astype(np.float32))
+        std = self.gain * np.sqrt(2.0 / (fi + fo))
+        if self.type == "uniform":
+            a = np.sqrt(3.0) * std
+            RandomUniform(-a, a).initialize_buffer(buf, shape)
+        else:
+            RandomNormal(0.0, std).initialize_buffer(buf, shape)
+
+    def __str__(self):
+        return f"InitGlorot type={self.type}, gain={self.gain}, fan_in={self.fan_in}, fan_out={self.fan_out}"
 
 
-class GlorotUniform(Initializer):
-    def __init__(self, fan_in=None, fan_out=None, gain=1.0):
-        self.fan_in, self.fan_out, self.gain = fan_in, fan_out, gain
-
-    def initialize_buffer(self, buf, shape):
-        fi, fo = _fans(shape, self.fan_in, self.fan_out)
-        lim = self.gain * np.sqrt(6.0 / (fi + fo))
-        buf.set(_rng().uniform(-lim, lim, shape.shape).astype(np.float32))
+def HeUniform(gain=2.0, fan_in=None): return _InitHe("uniform", gain, fan_in)
+def HeNormal(gain=1.0, fan_in=None): return _InitHe("normal", gain, fan_in)
+def GlorotUniform(gain=1.0, fan_in=None, fan_out=None): return _InitGlorot("uniform", gain, fan_in, fan_out)
+def GlorotNormal(gain=1.0, fan_in=None, fan_out=None): return _InitGlorot("normal", gain, fan_in, fan_out)

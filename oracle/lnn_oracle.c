@@ -449,3 +449,46 @@ void lnn_o_sgd(float* V, const float* G, i64 n, float lr, float gscale) {
     V[i] += a;
   }
 }
+
+/* ---- random initializers --------------------------------------------------------------- */
+/* The reference fills a tensor on the device from a counter-based hash of the element index
+ * (litenn/core/initializer/RandomUniform.py:12-20, RandomNormal.py:10-24) with the PCG output
+ * functions of litenn/core/CLKernelHelper.py:210-233 (the "pcg" and "pcg2d" hashes published
+ * by Jarzynski & Olano, "Hash Functions for GPU Rendering").  Restated here from the
+ * published algorithm; UIF = 1 / (float)0xffffffff = 2^-32 in single precision. */
+static uint32_t pcg_hash(uint32_t v) {
+  const uint32_t state = v * 747796405u + 2891336453u;
+  const uint32_t word = ((state >> ((state >> 28) + 4u)) ^ state) * 277803737u;
+  return (word >> 22) ^ word;
+}
+static void pcg2d_hash(uint32_t* x, uint32_t* y) {
+  uint32_t a = *x * 1664525u + 1013904223u, b = *y * 1664525u + 1013904223u;
+  a += b * 1664525u; b += a * 1664525u;
+  a ^= a >> 16; b ^= b >> 16;
+  a += b * 1664525u; b += a * 1664525u;
+  a ^= a >> 16; b ^= b >> 16;
+  *x = a; *y = b;
+}
+static const float kUIF = 1.0f / 4294967296.0f;
+
+/* O[i] = hash(i + seed) * (high - low) + low            (RandomUniform.py:16-19) */
+void lnn_o_init_uniform(float* O, i64 n, uint32_t seed, float low, float high) {
+  const float range = high - low;
+  for (i64 i = 0; i < n; ++i) {
+    const float h = (float)pcg_hash((uint32_t)((uint64_t)i + seed)) * kUIF;
+    O[i] = h * range + low;
+  }
+}
+
+/* Box-Muller on the two outputs of the 2-D hash of (i + seed, 1):
+ * O[i] = mean + sqrt(-2 log(rx)) * cos(2 PI ry) * stddev      (RandomNormal.py:14-23) */
+void lnn_o_init_normal(float* O, i64 n, uint32_t seed, float mean, float stddev) {
+  const float two_pi = 2.0f * 3.14159274101257f;
+  for (i64 i = 0; i < n; ++i) {
+    uint32_t a = (uint32_t)((uint64_t)i + seed), b = 1u;
+    pcg2d_hash(&a, &b);
+    const float rx = (float)a * kUIF, ry = (float)b * kUIF;
+    const float r = sqrtf(-2.0f * (float)log((double)rx)) * (float)cos((double)(two_pi * ry));
+    O[i] = mean + r * stddev;
+  }
+}

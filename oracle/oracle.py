@@ -249,3 +249,28 @@ def sgd(V, G, lr, gscale=1.0):
     V, G = _f(V).copy(), _f(G)
     lib().lnn_o_sgd(_p(V), _p(G), I64(V.size), F32(lr), F32(gscale))
     return V
+
+
+def init_uniform(shape, seed, low=0.0, high=1.0):
+    """RandomUniform as the reference's device kernel fills it (RandomUniform.py:12-28)."""
+    out = np.empty(shape, np.float32)
+    lib().lnn_o_init_uniform(_p(out), I64(out.size), ctypes.c_uint32(seed), F32(low), F32(high))
+    return out
+
+
+def init_normal(shape, seed, mean=0.0, stddev=1.0):
+    """RandomNormal (Box-Muller on the 2-D PCG hash, RandomNormal.py:10-30)."""
+    out = np.empty(shape, np.float32)
+    lib().lnn_o_init_normal(_p(out), I64(out.size), ctypes.c_uint32(seed), F32(mean), F32(stddev))
+    return out
+
+
+def he_uniform_limits(gain, fan_in):
+    """(low, high) of HeUniform: a = sqrt(3) * gain * sqrt(2 / fan_in)  (He.py:23-27)."""
+    a = np.sqrt(3.0) * (gain * np.sqrt(2.0 / fan_in))
+    return -a, a
+
+
+def glorot_std(gain, fan_in, fan_out):
+    """stddev of GlorotNormal: gain * sqrt(2 / (fan_in + fan_out))  (Glorot.py:25)."""
+    return gain * np.sqrt(2.0 / (fan_in + fan_out))

@@ -79,6 +79,25 @@ CONV_CASES = [  # (x_shape, w_shape, stride, dilation, padding, integer_valued)
 ]
 
 
+# random initializers (initializer/RandomUniform.py, RandomNormal.py, He.py, Glorot.py): the seed
+# of the device-side hash is np.random.randint(2**31) drawn at initialisation time, so a case
+# fixes numpy's legacy generator with np_seed first
+INIT_CASES = [
+    {"kind": "uniform", "args": (-0.5, 0.75), "shape": (5000,), "np_seed": 11},
+    {"kind": "uniform", "args": (0.0, 1.0), "shape": (3, 7, 49), "np_seed": 12},
+    {"kind": "normal", "args": (0.0, 1.0), "shape": (4096,), "np_seed": 13},
+    {"kind": "normal", "args": (0.5, 0.02), "shape": (777,), "np_seed": 14},
+    {"kind": "he_uniform", "args": (2.0, 36), "shape": (8, 4, 3, 3), "np_seed": 15},
+    {"kind": "glorot_normal", "args": (1.0, 64, 10), "shape": (64, 10), "np_seed": 16},
+]
+
+
+def init_seed(np_seed):
+    """The hash seed an initializer draws after np.random.seed(np_seed)."""
+    np.random.seed(np_seed)
+    return int(np.random.randint(2147483648))
+
+
 def _rng(name):
     seed = int.from_bytes(name.encode(), "little") % (2**32)
     return np.random.default_rng(seed)
@@ -106,6 +125,8 @@ def all_cases():
         cases.append((f"matmul_{i}", "matmul", {"a_shape": sa, "b_shape": sb, "integer": integer}))
     for i, (sx, sw, s, d, p, integer) in enumerate(CONV_CASES):
         cases.append((f"conv_{i}", "conv", {"x_shape": sx, "w_shape": sw, "stride": s, "dilation": d, "padding": p, "integer": integer}))
+    for i, p in enumerate(INIT_CASES):
+        cases.append((f"init_{p['kind']}_{i}", "init", p))
     cases.append(("conv_config1", "conv_config1", {}))
     cases.append(("chain", "chain", {}))
     cases.append(("softmax_ce", "softmax_ce", {}))
@@ -166,6 +187,8 @@ def make_inputs(name, family, p):
         return {"x": r0.standard_normal((8, 16, 32, 32)).astype(f32),
                 "w": (r0.standard_normal((32, 16, 3, 3)) * np.sqrt(2.0 / 144)).astype(f32),
                 "b": r0.uniform(-0.1, 0.1, (32,)).astype(f32)}
+    if family == "init":
+        return {"np_seed": np.array([p["np_seed"]], np.int64), "hash_seed": np.array([init_seed(p["np_seed"])], np.int64)}
     if family == "chain":
         return {"x": r.standard_normal((3, 8, 6, 10)).astype(f32), "g": r.uniform(0.5, 1.5, (1, 8, 1, 1)).astype(f32),
                 "b": r.uniform(-0.5, 0.5, (1, 8, 1, 1)).astype(f32)}
@@ -267,6 +290,13 @@ def run_case(nn, family, p, inp):
         x, w, b = T(inp["x"]), T(inp["w"]), T(inp["b"])
         y = nn.conv2D(x, w, stride=1, dilation=1, padding="same") + b.reshape((1, -1, 1, 1))
         out["y"] = y.np()
+    elif family == "init":
+        ini = nn.initializer
+        make = {"uniform": lambda a: ini.RandomUniform(*a), "normal": lambda a: ini.RandomNormal(*a),
+                "he_uniform": lambda a: ini.HeUniform(gain=a[0], fan_in=a[1]),
+                "glorot_normal": lambda a: ini.GlorotNormal(gain=a[0], fan_in=a[1], fan_out=a[2])}[p["kind"]]
+        np.random.seed(int(inp["np_seed"][0]))
+        out["v"] = nn.Tensor(p["shape"], init=make(p["args"])).np()
     elif family == "chain":
         x, g, b = T(inp["x"]), T(inp["g"]), T(inp["b"])
         out["y"] = nn.leaky_relu(x * g + b, 0.1).np()

@@ -232,8 +232,42 @@ def _strip_hash_helpers(source):
     return source[:start] + source[end:]
 
 
+_VEC_CAST_RE = re.compile(r"\((uint2|uint3|float2|float3)\)\s*\(([^()]*)\)")
+_VEC_FIELD_RE = re.compile(r"\b([A-Za-z_]\w*)\.([xyz])\b")
+
+
+def _uses_hash(source):
+    """True when the kernel itself calls one of the PCG hash helpers (the random initializers,
+    initializer/RandomUniform.py:12-20, RandomNormal.py:10-24)."""
+    start = source.find("//---------- PCG hashes")
+    if start < 0:
+        return False
+    tail = source.find("float hash_float_float2(float2 p)", start)
+    end = source.find("}", tail) + 1
+    return "hash_" in source[end:]
+
+
+def _hash_dialect_to_gnu_c(source):
+    """OpenCL vector syntax of the hash helpers -> GNU C vector extensions, nothing else:
+    (uint2)(a, b) becomes the compound literal (uint2){a, b} and v.x / v.y / v.z become
+    v[0] / v[1] / v[2].  The arithmetic text is left as the reference wrote it."""
+    source = _VEC_CAST_RE.sub(lambda m: "(%s){%s}" % (m.group(1), m.group(2)), source)
+    return _VEC_FIELD_RE.sub(lambda m: "%s[%d]" % (m.group(1), "xyz".index(m.group(2))), source)
+
+
+HASH_PRELUDE = r"""
+typedef unsigned int uint2 __attribute__((vector_size(8),  aligned(4)));
+typedef unsigned int uint3 __attribute__((vector_size(16), aligned(4)));
+typedef float float3 __attribute__((vector_size(16), aligned(4)));
+static inline float dot(float2 a, float2 b) { return a[0] * b[0] + a[1] * b[1]; }
+"""
+
+
 def BuildProgram(program, devices, options=None):
-    program.source = _strip_hash_helpers(program.source)
+    if _uses_hash(program.source):
+        program.source = HASH_PRELUDE + _hash_dialect_to_gnu_c(program.source)
+    else:
+        program.source = _strip_hash_helpers(program.source)
     m = _PARAM_RE.search(program.source)
     if not m:
         raise CLException(_Enum(ERROR.BUILD_PROGRAM_FAILURE), "no __kernel found")

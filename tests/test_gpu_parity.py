@@ -335,6 +335,20 @@ def test_fused_pool_epilogue_non_finite(nn_gpu, xs, ws):
     nn.devices.check_status()
 
 
+@pytest.mark.parametrize("name,family,p", _cases("init"))
+def test_random_initializers(nn_gpu, name, family, p):
+    """Device-side random initializers against tensors the unmodified reference initialised
+    after the same np.random.seed: the uniform family bit for bit (integer hash times 2^-32),
+    the normal family to the rounding of the device's logf / cosf."""
+    ins, outs = load_golden(family)[name]
+    got = cases.run_case(nn_gpu, family, p, ins)["v"]
+    if p["kind"] in ("uniform", "he_uniform"):
+        assert_bit_exact(got, outs["v"], name)
+    else:
+        std = p["args"][1] if p["kind"] == "normal" else float(np.std(outs["v"]))
+        np.testing.assert_allclose(got, outs["v"], rtol=2e-5, atol=1e-5 * std, err_msg=name)
+
+
 def test_softmax_ce(nn_gpu):
     ins, outs = load_golden("softmax_ce")["softmax_ce"]
     got = cases.run_case(nn_gpu, "softmax_ce", {}, ins)

@@ -135,6 +135,28 @@ def test_conv(name, p):
     assert_bit_exact(dw, outs["dw"], name + " dw")
 
 
+def _init_oracle(p, hash_seed):
+    kind, a = p["kind"], p["args"]
+    if kind == "uniform":
+        return o.init_uniform(p["shape"], hash_seed, a[0], a[1])
+    if kind == "normal":
+        return o.init_normal(p["shape"], hash_seed, a[0], a[1])
+    if kind == "he_uniform":
+        lo, hi = o.he_uniform_limits(a[0], a[1])
+        return o.init_uniform(p["shape"], hash_seed, lo, hi)
+    return o.init_normal(p["shape"], hash_seed, 0.0, o.glorot_std(a[0], a[1], a[2]))
+
+
+@pytest.mark.parametrize("name,p", _cases("init"))
+def test_init(name, p):
+    """Random initializers: the oracle's restatement of the PCG hashes against tensors the
+    unmodified reference initialised (bit-exact: log / cos are the double functions rounded once
+    in both)."""
+    ins, outs = load_golden("init")[name]
+    assert int(ins["hash_seed"][0]) == cases.init_seed(p["np_seed"])
+    assert_bit_exact(_init_oracle(p, int(ins["hash_seed"][0])), outs["v"], name)
+
+
 def test_conv_config1():
     ins, outs = load_golden("conv_config1")["conv_config1"]
     y = o.conv2d_fwd(ins["x"], ins["w"], 1, 1, "same", bias=ins["b"])
