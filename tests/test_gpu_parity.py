@@ -349,6 +349,48 @@ def test_random_initializers(nn_gpu, name, family, p):
         np.testing.assert_allclose(got, outs["v"], rtol=2e-5, atol=1e-5 * std, err_msg=name)
 
 
+def _random_conv_geometries(count, seed):
+    rng = np.random.default_rng(seed)
+    out = []
+    for _ in range(count):
+        k = int(rng.choice([1, 3, 3, 5]))
+        out.append((int(rng.integers(1, 4)), int(rng.choice([3, 8, 16, 32, 40, 64])), int(rng.integers(k + 2, 41)),
+                    int(rng.integers(k + 2, 41)), int(rng.choice([8, 24, 64, 100, 130])), k,
+                    int(rng.choice([1, 1, 2])), int(rng.choice([1, 1, 2]))))
+    return out
+
+
+@pytest.mark.parametrize("n,ic,h,w,oc,k,stride,dil", _random_conv_geometries(24, 2024))
+def test_conv_random_geometries(nn_gpu, n, ic, h, w, oc, k, stride, dil):
+    """Seeded random geometries (channel counts off the 8/32 grid, odd sizes, strides, dilations,
+    1x1 to 5x5 taps): forward with fused bias + leaky_relu, dX and dW against the fp64 oracle,
+    and the inference entry with fused pool and packed output against the un-fused chain."""
+    import oracle as o
+    nn = nn_gpu
+    rng = np.random.default_rng(n * 1000003 + ic * 10007 + h * 101 + w)
+    x = rng.standard_normal((n, ic, h, w)).astype(np.float32)
+    wt_np = (rng.standard_normal((oc, ic, k, k)) * 0.1).astype(np.float32)
+    b = rng.uniform(-0.1, 0.1, (oc,)).astype(np.float32)
+    want = o.conv2d_fwd(x, wt_np, stride, dil, "same", bias=b, act=1, alpha=0.1, accum64=True)
+    lin = o.conv2d_fwd(x, wt_np, stride, dil, "same", accum64=True)
+    dy = rng.standard_normal(lin.shape).astype(np.float32)
+    want_dx = o.conv2d_dx(np.zeros_like(x), dy, wt_np, x.shape, stride, dil, "same", accum64=True)
+    want_dw = o.conv2d_dw(np.zeros_like(wt_np), dy, x, stride, dil, "same", accum64=True)
+    xt, wt, bt = nn.Tensor_from_value(x), nn.Tensor_from_value(wt_np), nn.Tensor_from_value(b)
+    kw = dict(stride=stride, dilation=dil, bias_t=bt, activation="leaky_relu", alpha=0.1)
+    y = nn.conv2D(xt, wt, **kw)
+    assert_contraction_close(y.np(), want, ic * k * k, "forward")
+    z = nn.conv2D(xt, wt, stride=stride, dilation=dil)
+    nn.backward({z: dy}, grad_for_non_trainables=True)
+    assert_contraction_close(xt.get_grad().np(), want_dx, oc * k * k, "dX")
+    assert_contraction_close(wt.get_grad().np(), want_dw, n * lin.shape[2] * lin.shape[3], "dW")
+    chain = nn.max_pool2D(y, 2, 2, "same").np()
+    assert_bit_exact(nn.conv2D_infer(xt, wt, pool=True, **kw).np(), chain, "fused pool")
+    packed = nn.conv2D_infer(xt, wt, pool=True, packed_output=True, **kw)
+    assert_bit_exact(packed.hi.np()[..., :oc].transpose(0, 3, 1, 2), _tf32_rna(chain), "packed hi")
+    nn.devices.check_status()
+
+
 def test_softmax_ce(nn_gpu):
     ins, outs = load_golden("softmax_ce")["softmax_ce"]
     got = cases.run_case(nn_gpu, "softmax_ce", {}, ins)
