@@ -328,7 +328,9 @@ reduce_warp4_kernel(float* __restrict__ O, const float* __restrict__ I, RedGeom 
 // rows (inner % 4 == 0) of one c0; else four adjacent columns c0..c0+3 of one row (inner == 1,
 // mid == 1).  Either way its four results are adjacent in O / P.
 template <int OP>
-__global__ void __launch_bounds__(kThreads)
+// 4 blocks per SM (64 registers): the few spills of the counter stack cost less than the lost
+// occupancy (measured: 0.67 -> 0.76 of the copy bandwidth on the axis-1 case; 6 blocks: 0.59)
+__global__ void __launch_bounds__(kThreads, 4)
 reduce_parts4_kernel(float* __restrict__ O, float* __restrict__ P, const float* __restrict__ I,
                      RedGeom g, Levels L, int s, int rows_vec, int acc, float mean_div) {
   const int64_t parts = L.n[s];
@@ -486,8 +488,11 @@ int reduce_impl(lnn::Device* d, PartialSpace& space, float* O, const float* I, i
     const bool cols_vec = L.pow2 && ((((uintptr_t)I) & 15) == 0) &&
                           (r0 == 1 || (r1 % 4 == 0 && g.stride_r0 % 4 == 0)) && g.stride_mid % 4 == 0 &&
                           g.stride_outer % 4 == 0;
+    // a handful of long rows (the last pass of an all-axes reduction): one warp per row would be a
+    // single latency-bound chain, so those take the block-per-row kernel below
+    const bool few_long_rows = g.rows <= 32 && cols >= 2048;
     if (!split) {
-      if (cols_vec && cols >= 128 && L.S - 7 <= kMaxPow2Levels) {
+      if (!few_long_rows && cols_vec && cols >= 128 && L.S - 7 <= kMaxPow2Levels) {
         const int s = L.S - 7;                           // 128 partials per row, four per lane
         int64_t blocks = lnn_ceil_div(g.rows, kThreads / 32);
         const int64_t cap = (int64_t)d->sm_count * 16;
@@ -496,7 +501,7 @@ int reduce_impl(lnn::Device* d, PartialSpace& space, float* O, const float* I, i
         LNN_CHECK_LAUNCH(d);
         return LNN_OK;
       }
-      if (L.pow2 && L.S - 5 <= kMaxPow2Levels) {
+      if (!few_long_rows && L.pow2 && L.S - 5 <= kMaxPow2Levels) {
         const int s = L.S > 5 ? L.S - 5 : 0;           // n[s] = min(cols, 32) partials per row
         int64_t blocks = lnn_ceil_div(g.rows, kThreads / 32);
         const int64_t cap = (int64_t)d->sm_count * 16;
