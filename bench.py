@@ -262,6 +262,7 @@ def cpu_cnn_images_per_s(target_seconds, seed=1):
     import oracle as o
     o.build()
     cores = len(os.sched_getaffinity(0))
+    cores = o.set_threads(cores)          # torchrun exports OMP_NUM_THREADS=1
     w = cnn_weights()
     rng = np.random.default_rng(seed)
     n = 2

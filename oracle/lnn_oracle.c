@@ -492,3 +492,15 @@ void lnn_o_init_normal(float* O, i64 n, uint32_t seed, float mean, float stddev)
     O[i] = mean + r * stddev;
   }
 }
+
+/* ---- threading ----------------------------------------------------------------------------- */
+#ifdef _OPENMP
+#include <omp.h>
+/* Launchers such as torchrun export OMP_NUM_THREADS=1; the timed CPU baseline asks for the host
+ * threads it is allowed to use explicitly. */
+void lnn_o_set_threads(int n) { if (n > 0) omp_set_num_threads(n); }
+int lnn_o_get_max_threads(void) { return omp_get_max_threads(); }
+#else
+void lnn_o_set_threads(int n) { (void)n; }
+int lnn_o_get_max_threads(void) { return 1; }
+#endif

@@ -274,3 +274,9 @@ def he_uniform_limits(gain, fan_in):
 def glorot_std(gain, fan_in, fan_out):
     """stddev of GlorotNormal: gain * sqrt(2 / (fan_in + fan_out))  (Glorot.py:25)."""
     return gain * np.sqrt(2.0 / (fan_in + fan_out))
+
+
+def set_threads(n):
+    """OpenMP threads used by the oracle's loops (the environment may have pinned it to 1)."""
+    lib().lnn_o_set_threads(INT(n))
+    return int(lib().lnn_o_get_max_threads())
