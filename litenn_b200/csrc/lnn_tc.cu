@@ -1219,6 +1219,12 @@ inline int env_int(const char* name, int dflt) {
   return (e && *e) ? atoi(e) : dflt;
 }
 
+// Timing-experiment bits (skip MMAs / loads / stores / tap shifts).  They make results wrong, so
+// they are honoured only when LNN_TC_EXPERIMENTS=1 is set as well.
+inline int debug_bits() {
+  return env_int("LNN_TC_EXPERIMENTS", 0) == 1 ? env_int("LNN_TC_DEBUG", 0) : 0;
+}
+
 inline uint32_t make_idesc(int bn, int a_major, int b_major) {
   // c_format F32 (bits 4-5 = 1), a/b format TF32 (= 2) at bits 7-9 / 10-12, majors at 15 / 16,
   // N >> 3 at bits 17-22, M >> 4 at bits 24-28.
@@ -1257,7 +1263,7 @@ int launch_tc(lnn::Device* d, dim3 grid, const CUtensorMap& ah, const CUtensorMa
   if (stages < 1 || stages * stage + kSmemSlack > kSmemLimit)
     return lnn::set_error(LNN_E_UNSUPPORTED, "operand stage of %d bytes does not fit shared memory", stage);
   p.stages = stages;
-  p.debug = env_int("LNN_TC_DEBUG", 0);     // timing experiments only; results are wrong when set
+  p.debug = debug_bits();     // timing experiments only; results are wrong when set
   p.status = d->status_dev;
   // persistent launch: the logical grid is walked by one CTA per SM
   p.grid_x = (int)grid.x; p.grid_y = (int)grid.y; p.grid_z = (int)grid.z;
@@ -1492,7 +1498,7 @@ int launch_conv_halo(lnn::Device* d, const float* act_hi, const float* act_lo, i
   if (pooled) { p.ep_mode = ex->ep_mode; p.out_lo = ex->out_lo; p.ocp = ex->ocp; }
   p.h_pw = hp.pw; p.h_ph = hp.ph; p.h_x0 = x0; p.h_y0 = y0; p.h_arows = a_rows; p.h_acb = hp.acb;
   p.h_sa = hp.sa; p.h_sb = 2; p.h_bbuf = hp.bbuf;
-  p.debug = env_int("LNN_TC_DEBUG", 0);     // timing experiments only; results are wrong when set
+  p.debug = debug_bits();     // timing experiments only; results are wrong when set
   for (int i = 0; i < ntaps; ++i) {
     p.tap_dy[i] = dy[i]; p.tap_dx[i] = dx[i]; p.tap_w[i] = widx[i];
     p.tap_shift[i] = (dy[i] - y0) * hp.pw + (dx[i] - x0);
