@@ -1021,6 +1021,55 @@ tc_halo_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
 // =========================================================================================
 constexpr int kThreads = 256;
 
+// NCHW -> channel-innermost hi/lo copies, 128-bit on both sides: a tile of 32 channels x 128
+// pixels is read as float4 along the pixels and written as float4 along the channels (the row
+// pitch of 129 floats makes the transposed shared-memory reads conflict-free).  Needs hw % 4 == 0
+// and 16-byte aligned buffers; cp is a multiple of 8.
+__global__ void __launch_bounds__(256)
+nchw_to_nhwc_split_vec_kernel(float* __restrict__ hi, float* __restrict__ lo,
+                              const float* __restrict__ src, int64_t n, int c, int64_t hw, int cp,
+                              int want_lo) {
+  __shared__ float tile[32][129];
+  const int64_t tiles_p = (hw + 127) / 128;
+  const int tiles_c = (cp + 31) / 32;
+  const int64_t total = n * tiles_p * tiles_c;
+  for (int64_t t = blockIdx.x; t < total; t += gridDim.x) {
+    const int tc = (int)(t % tiles_c);
+    const int64_t t2 = t / tiles_c;
+    const int64_t tp = t2 % tiles_p;
+    const int64_t img = t2 / tiles_p;
+    const float* sp = src + img * (int64_t)c * hw;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int idx = threadIdx.x + k * 256;
+      const int chl = idx >> 5, p4 = idx & 31;
+      const int ch = tc * 32 + chl;
+      const int64_t px = tp * 128 + p4 * 4;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (ch < c && px < hw) v = __ldcs(reinterpret_cast<const float4*>(sp + (int64_t)ch * hw + px));
+      tile[chl][p4 * 4 + 0] = v.x; tile[chl][p4 * 4 + 1] = v.y;
+      tile[chl][p4 * 4 + 2] = v.z; tile[chl][p4 * 4 + 3] = v.w;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int item = threadIdx.x + k * 256;
+      const int cq = item & 7, pl = item >> 3;
+      const int64_t px = tp * 128 + pl;
+      const int ch = tc * 32 + cq * 4;
+      if (px < hw && ch < cp) {
+        float h[4], l[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) split1(tile[cq * 4 + e][pl], h[e], l[e]);
+        const int64_t o = (img * hw + px) * cp + ch;
+        __stcs(reinterpret_cast<float4*>(hi + o), make_float4(h[0], h[1], h[2], h[3]));
+        if (want_lo) __stcs(reinterpret_cast<float4*>(lo + o), make_float4(l[0], l[1], l[2], l[3]));
+      }
+    }
+    __syncthreads();
+  }
+}
+
 // hi/lo split of a dense [rows][cols] matrix into buffers of row pitch `pitch`
 __global__ void __launch_bounds__(kThreads)
 split_rows_kernel(float* __restrict__ hi, float* __restrict__ lo, const float* __restrict__ src,
@@ -1372,6 +1421,14 @@ int nhwc_split_to(lnn::Device* d, float* hi_p, float* lo_p, const float* src, in
     // coalesced, one 32-byte NHWC pixel written per thread
     nchw_to_nhwc8_split_kernel<<<grid_for(d, (int64_t)n * hw), kThreads, 0, d->stream>>>(
         hi_p, lo_p, src, n, c, hw, want_lo);
+    LNN_CHECK_LAUNCH(d);
+    return LNN_OK;
+  }
+  const bool vec = (hw % 4 == 0) && ((((uintptr_t)src | (uintptr_t)hi_p | (uintptr_t)lo_p) & 15) == 0);
+  if (vec) {
+    const int64_t tiles = (int64_t)n * ((hw + 127) / 128) * ((cp + 31) / 32);
+    const int64_t grid = std::min<int64_t>(tiles, (int64_t)d->sm_count * 8);
+    nchw_to_nhwc_split_vec_kernel<<<(unsigned)grid, 256, 0, d->stream>>>(hi_p, lo_p, src, n, c, hw, cp, want_lo);
     LNN_CHECK_LAUNCH(d);
     return LNN_OK;
   }
