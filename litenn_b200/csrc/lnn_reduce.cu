@@ -371,6 +371,22 @@ reduce_parts4_kernel(float* __restrict__ O, float* __restrict__ P, const float* 
 }
 
 // dI += dO[row] (/ COLS)   (reduce.py:250-260)
+// The common case of the same gradient: the reduced axes are the trailing ones (inner == 1,
+// r0 == 1), so I is [rows][cols] and four consecutive elements share a row (cols % 4 == 0).
+__global__ void __launch_bounds__(kThreads)
+reduce_bwd_bcast_rows4_kernel(float4* __restrict__ dI, const float* __restrict__ dO, int64_t total4,
+                              int64_t cols4, float mean_div) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t gid = tid; gid < total4; gid += nthreads) {
+    float v = __ldg(dO + gid / cols4);
+    if (mean_div != 0.0f) v = __fdiv_rn(v, mean_div);
+    float4 o = dI[gid];
+    o.x = __fadd_rn(o.x, v); o.y = __fadd_rn(o.y, v); o.z = __fadd_rn(o.z, v); o.w = __fadd_rn(o.w, v);
+    dI[gid] = o;
+  }
+}
+
 __global__ void __launch_bounds__(kThreads)
 reduce_bwd_bcast_kernel(float* __restrict__ dI, const float* __restrict__ dO, int64_t total,
                         RedGeom g, float mean_div) {
@@ -640,6 +656,13 @@ int lnn_reduce_bwd(int dev, int op, uint64_t dI, uint64_t I, uint64_t dO, uint64
   int rc = make_geom(g, outer, r0, mid, r1, inner);
   if (rc) return rc;
   const int64_t total = g.rows * r0 * r1;
+  if ((op == LNN_RED_SUM || op == LNN_RED_MEAN) && inner == 1 && r0 == 1 && r1 % 4 == 0 && (dI & 15) == 0) {
+    const float mean_div_rows = op == LNN_RED_MEAN ? (float)(r0 * r1) : 0.0f;
+    reduce_bwd_bcast_rows4_kernel<<<grid_for(d, total / 4), kThreads, 0, d->stream>>>(
+        (float4*)(uintptr_t)dI, (const float*)(uintptr_t)dO, total / 4, r1 / 4, mean_div_rows);
+    LNN_CHECK_LAUNCH(d);
+    return LNN_OK;
+  }
   if (op == LNN_RED_SUM || op == LNN_RED_MEAN) {
     reduce_bwd_bcast_kernel<<<grid_for(d, total), kThreads, 0, d->stream>>>(
         (float*)(uintptr_t)dI, (const float*)(uintptr_t)dO, total, g,
