@@ -522,6 +522,7 @@ def run_ours(args):
         lib.lnn_event_record(dev.index, ev.value)
 
     e2e_state = {"slot": 0, "primed": False}
+    in_flight = []
 
     def upload(j, slot):
         mb_bytes = mb * img_elems * 4
@@ -543,10 +544,14 @@ def run_ours(args):
                 upload(0, slot ^ 1)               # first micro-batch of the next step
             logits = model.forward(stages[slot])
             lib.lnn_event_record(dev.index, done_ev[slot].value)
-            lib.lnn_d2h_async(dev.index, host_out_ptr.value + j * mb * NCLASS * 4, logits._ptr(0), mb * NCLASS * 4)
+            # the logits travel to pinned host memory on the read-back stream while the next
+            # micro-batch computes; the tensors stay alive until the copies have finished
+            lib.lnn_d2h_readback(dev.index, host_out_ptr.value + j * mb * NCLASS * 4, logits._ptr(0), mb * NCLASS * 4)
+            in_flight.append(logits)
             e2e_state["slot"] = slot ^ 1
         e2e_state["primed"] = more_steps_follow
-        lib.lnn_sync(dev.index)                   # the step's logits are in host memory
+        lib.lnn_wait_readback(dev.index)          # the step's logits are in host memory
+        del in_flight[:]
 
     sampler = ClockSampler(dev.index)
     sampler.start()

@@ -82,6 +82,12 @@ int lnn_d2h_async(int dev, void* dst, uint64_t src, uint64_t bytes);
  * blocking write (minicl/CLBuffer.py:78-80). */
 int lnn_h2d_prefetch(int dev, uint64_t dst, const void* src, uint64_t bytes, uint64_t after_event);
 int lnn_wait_prefetch(int dev);
+/* The mirror image for results: a device->host copy ordered after the work enqueued so far but
+ * on its own stream, so that the next batch's kernels do not wait for it; the source buffer must
+ * stay allocated until lnn_wait_readback (which blocks the host) returns.  `dst` should be
+ * pinned (lnn_host_alloc).  ref: minicl/CLBuffer.py:99-115 is the blocking form */
+int lnn_d2h_readback(int dev, void* dst, uint64_t src, uint64_t bytes);
+int lnn_wait_readback(int dev);
 int lnn_host_alloc(uint64_t bytes, void** ptr);   /* pinned host memory */
 int lnn_host_free(void* ptr);
 /* number of kernels this library has launched on the device since lnn_init */

@@ -62,6 +62,8 @@ _SIGNATURES = {
     "lnn_d2h_async": (c_int, [c_int, c_void_p, c_uint64, c_uint64]),
     "lnn_h2d_prefetch": (c_int, [c_int, c_uint64, c_void_p, c_uint64, c_uint64]),
     "lnn_wait_prefetch": (c_int, [c_int]),
+    "lnn_d2h_readback": (c_int, [c_int, c_void_p, c_uint64, c_uint64]),
+    "lnn_wait_readback": (c_int, [c_int]),
     "lnn_host_alloc": (c_int, [c_uint64, POINTER(c_void_p)]),
     "lnn_host_free": (c_int, [c_void_p]),
     "lnn_launch_count": (c_int, [c_int, POINTER(c_uint64)]),

@@ -18,6 +18,8 @@ struct Device {
   cudaStream_t stream = nullptr;
   cudaStream_t copy_stream = nullptr;            // host->device prefetches that overlap compute
   cudaEvent_t copy_event = nullptr;
+  cudaStream_t readback_stream = nullptr;        // device->host reads that overlap the next batch's compute
+  cudaEvent_t readback_event = nullptr;
   std::map<uint64_t, std::vector<void*>> pool;   // free buffers by exact byte size
   uint64_t allocated_bytes = 0;                  // live + pooled
   uint64_t pooled_bytes = 0;

@@ -144,6 +144,8 @@ int lnn_init(int dev) {
   LNN_CUDA(cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
   LNN_CUDA(cudaStreamCreateWithFlags(&d->copy_stream, cudaStreamNonBlocking));
   LNN_CUDA(cudaEventCreateWithFlags(&d->copy_event, cudaEventDisableTiming));
+  LNN_CUDA(cudaStreamCreateWithFlags(&d->readback_stream, cudaStreamNonBlocking));
+  LNN_CUDA(cudaEventCreateWithFlags(&d->readback_event, cudaEventDisableTiming));
   LNN_CUDA(cudaMalloc(&d->status_dev, sizeof(int) * 4));
   LNN_CUDA(cudaMemset(d->status_dev, 0, sizeof(int) * 4));
   LNN_CUDA(cudaMallocHost(&d->status_host, sizeof(int) * 4));
@@ -185,6 +187,8 @@ int lnn_shutdown(int dev) {
   cudaStreamDestroy(d->stream);
   cudaStreamDestroy(d->copy_stream);
   cudaEventDestroy(d->copy_event);
+  cudaStreamDestroy(d->readback_stream);
+  cudaEventDestroy(d->readback_event);
   *d = Device();
   return LNN_OK;
 }
@@ -254,6 +258,23 @@ int lnn_wait_prefetch(int dev) {
   LNN_DEV(d, dev);
   LNN_CUDA(cudaEventRecord(d->copy_event, d->copy_stream));
   LNN_CUDA(cudaStreamWaitEvent(d->stream, d->copy_event, 0));
+  return LNN_OK;
+}
+
+int lnn_d2h_readback(int dev, void* dst, uint64_t src, uint64_t bytes) {
+  LNN_DEV(d, dev);
+  LNN_REQUIRE(dst && src, "null pointer");
+  // ordered after everything enqueued on the compute stream so far, but on its own stream: the
+  // compute stream goes on with the next batch while the result travels to the host
+  LNN_CUDA(cudaEventRecord(d->readback_event, d->stream));
+  LNN_CUDA(cudaStreamWaitEvent(d->readback_stream, d->readback_event, 0));
+  LNN_CUDA(cudaMemcpyAsync(dst, (const void*)(uintptr_t)src, bytes, cudaMemcpyDeviceToHost, d->readback_stream));
+  return LNN_OK;
+}
+
+int lnn_wait_readback(int dev) {
+  LNN_DEV(d, dev);
+  LNN_CUDA(cudaStreamSynchronize(d->readback_stream));
   return LNN_OK;
 }
 
