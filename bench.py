@@ -302,7 +302,7 @@ def run_reference(args):
 def workload_config(n_gpus):
     return {"workload": "small CNN classifier inference, fp32, input [4096,3,128,128] ~U(0,1), batch sharded over the GPUs",
             "global_batch": TOTAL_BATCH, "micro_batch": MICRO_BATCH, "parallelism": f"dp{n_gpus}",
-            "tf32_passes": int(os.environ.get("LNN_TF32_PASSES", "3")),
+            "precision": {1: "tf32", 2: "split fp16 (hi*hi + hi*lo + lo*hi, kind::f16)", 3: "split tf32"}[int(os.environ.get("LNN_PRECISION", "2"))],
             "l2": "every micro-batch streams > 2 GB of activations through HBM, far beyond the 126 MB L2; no explicit flush"}
 
 
@@ -440,7 +440,7 @@ def bench_ops(nn, dev, peaks, quick, only=None):
     from litenn_b200 import _lib
     lib = _lib.get_lib()
     timer = DevTimer(nn, dev)
-    passes = _lib.tf32_passes()
+    passes = _lib.precision()
     out = {}
     iters = 3 if quick else 10
     tf32_peak = peaks["bf16_tflops"] / 2.0
@@ -482,7 +482,7 @@ def run_ours(args):
     nn.devices.set_current(dev)
     lib = _lib.get_lib()
     peaks = load_peaks()
-    passes = _lib.tf32_passes()
+    passes = _lib.precision()
 
     local_batch = TOTAL_BATCH // world
     mb = min(MICRO_BATCH, local_batch)

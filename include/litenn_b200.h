@@ -203,14 +203,22 @@ int lnn_slice_bwd(int dev, uint64_t dI, uint64_t dO, int rank, const int64_t* in
 
 /* ---- contractions (tcgen05 tile engine) ----------------------------------------------- */
 
+/* `precision` of the contraction entries: every fp32 operand is split into two parts of 11
+ * significant bits each and hi*hi + hi*lo + lo*hi is accumulated in fp32 on the tensor cores.
+ *   2 = split FP16 (default of the host layer): x / s = hi + lo in fp16 with s an exact power of
+ *       two taken from the operand's largest magnitude; fp32-level accuracy, tcgen05 kind::f16
+ *   3 = split TF32: x = hi + lo in tf32; same accuracy at any magnitude, tcgen05 kind::tf32,
+ *       twice the instructions and operand bytes of 2
+ *   1 = plain TF32 (hi only), about 1e-3 relative */
+
 /* C[b] (+)= op(A[b]) * op(B[b]) (+ bias[n]) for b < batch, row-major fp32.
  * trans_a = 0: A is [M,K]; 1: A is stored [K,M].  trans_b = 0: B is [K,N]; 1: stored [N,K].
- * bias may be 0.  tf32_passes: 3 = split-TF32 (fp32-level accuracy), 1 = plain TF32.
+ * bias may be 0.
  * ref: op/matmul.py:8-164 (forward), :64-72 (gradients = the transposed variants),
  *      module/Dense.py:44-48 (bias) */
 int lnn_gemm_f32(int dev, uint64_t C, uint64_t A, uint64_t B, uint64_t bias,
                  int64_t batch, int64_t m, int64_t n, int64_t k,
-                 int trans_a, int trans_b, int accumulate, int tf32_passes);
+                 int trans_a, int trans_b, int accumulate, int precision);
 
 /* geometry shared by the three convolution entry points (NCHW / OIHW) */
 typedef struct lnn_conv_geom {
@@ -225,18 +233,24 @@ typedef struct lnn_conv_geom {
  * Y (+)= conv2D(X, W) (+ bias).  ref: op/conv2D.py:9-44, op/unfold2D.py:84-111,
  * module/Conv2D.py:58-62 */
 int lnn_conv2d_fwd(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint64_t W,
-                   uint64_t bias, int act, float alpha, int accumulate, int tf32_passes);
+                   uint64_t bias, int act, float alpha, int accumulate, int precision);
 /* Inference fusion: Y = max_pool2D(act(conv2D(X, W) + bias), 2, 2, 'same'), Y is
  * [n, oc, ceil(oh/2), ceil(ow/2)].  Same values as the three separate entries.
  * ref: op/conv2D.py:9-44 + op/element_wise_op.py:207-221 + op/pool2D.py:47-146 */
 int lnn_conv2d_pool_fwd(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint64_t W,
-                        uint64_t bias, int act, float alpha, int tf32_passes);
-/* Operand format of the tensor-core convolution: channel-innermost copies of an NCHW activation,
- * hi = tf32(x) and lo = tf32(x - hi), each [n][h][w][cp] floats with cp = c rounded up to 8 (pad
- * channels zero); lo may be 0 when only single-pass TF32 will be used.  The reference has no such
- * format: its conv2D materialises an im2col buffer per call (op/conv2D.py:39-41,
- * op/unfold2D.py:84-110); this entry is the explicit form of the pre-pass lnn_conv2d_fwd runs. */
-int lnn_nhwc_split(int dev, uint64_t hi, uint64_t lo, uint64_t X, int n, int c, int h, int w);
+                        uint64_t bias, int act, float alpha, int precision);
+/* Operand format of the tensor-core convolution: channel-innermost copies hi and lo of an NCHW
+ * activation, each [n][h][w][cp] with cp = c rounded up to 8 (pad channels zero).  precision 3 / 1:
+ * fp32 elements, hi = tf32(x), lo = tf32(x - hi) (lo may be 0 for precision 1).  precision 2: fp16
+ * elements of x / s, and the hi buffer ends with a 16-byte trailer that holds the fp32 bit pattern
+ * of the tensor's largest magnitude, from which every consumer derives s.  lnn_packed_bytes gives
+ * the two buffer sizes.  The reference has no such format: its conv2D materialises an im2col
+ * buffer per call (op/conv2D.py:39-41, op/unfold2D.py:84-110); lnn_nhwc_split is the explicit
+ * form of the pre-pass lnn_conv2d_fwd runs. */
+int lnn_packed_bytes(int64_t n, int64_t c, int64_t h, int64_t w, int precision, uint64_t* hi_bytes,
+                     uint64_t* lo_bytes);
+int lnn_nhwc_split(int dev, uint64_t hi, uint64_t lo, uint64_t X, int n, int c, int h, int w,
+                   int precision);
 /* conv2D forward (+ bias, leaky_relu, optional max_pool2D(2,2,'same')) whose input and / or output
  * stay in that format, so that a chain of convolutions never writes or re-reads the NCHW
  * activations between layers.  in_packed: X / X_lo are the packed copies of the input
@@ -247,21 +261,21 @@ int lnn_nhwc_split(int dev, uint64_t hi, uint64_t lo, uint64_t X, int n, int c, 
  * op/pool2D.py:47-146 */
 int lnn_conv2d_fwd_packed(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t Y_lo, uint64_t X,
                           uint64_t X_lo, uint64_t W, uint64_t bias, int act, float alpha, int pool,
-                          int in_packed, int out_packed, int tf32_passes);
+                          int in_packed, int out_packed, int precision);
 /* dX += conv2D_transpose-like gradient.  ref: op/conv2D.py:46-50, op/unfold2D.py:112-138 */
 int lnn_conv2d_dx(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY, uint64_t W,
-                  int tf32_passes);
+                  int precision);
 /* dW += gradient of the kernel.  ref: op/conv2D.py:52-54 */
 int lnn_conv2d_dw(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY, uint64_t X,
-                  int tf32_passes);
+                  int precision);
 /* The same two gradients from operands that are already in the packed format of lnn_nhwc_split
  * (dY [n][oh][ow][pad8(oc)], X [n][ih][iw][pad8(ic)], hi and lo each), so that a training step
  * repacks dY once for both gradients and reuses the copy of X its forward pass made.
  * ref: op/conv2D.py:46-54 */
 int lnn_conv2d_dx_packed(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY_hi, uint64_t dY_lo,
-                         uint64_t W, int tf32_passes);
+                         uint64_t W, int precision);
 int lnn_conv2d_dw_packed(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY_hi, uint64_t dY_lo,
-                         uint64_t X_hi, uint64_t X_lo, int tf32_passes);
+                         uint64_t X_hi, uint64_t X_lo, int precision);
 
 /* ---- optimiser + data-parallel sync --------------------------------------------------- */
 

@@ -91,7 +91,8 @@ _SIGNATURES = {
     "lnn_gemm_f32": (c_int, [c_int, c_uint64, c_uint64, c_uint64, c_uint64, c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int]),
     "lnn_conv2d_fwd": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64, c_uint64, c_int, c_float, c_int, c_int]),
     "lnn_conv2d_pool_fwd": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64, c_uint64, c_int, c_float, c_int]),
-    "lnn_nhwc_split": (c_int, [c_int, c_uint64, c_uint64, c_uint64, c_int, c_int, c_int, c_int]),
+    "lnn_packed_bytes": (c_int, [c_int64, c_int64, c_int64, c_int64, c_int, POINTER(c_uint64), POINTER(c_uint64)]),
+    "lnn_nhwc_split": (c_int, [c_int, c_uint64, c_uint64, c_uint64, c_int, c_int, c_int, c_int, c_int]),
     "lnn_conv2d_fwd_packed": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64, c_uint64, c_uint64, c_uint64,
                                       c_int, c_float, c_int, c_int, c_int, c_int]),
     "lnn_conv2d_dx": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64, c_int]),
@@ -152,9 +153,14 @@ def i64_array(values, pad_to=None, pad_value=1):
     return (c_int64 * len(vals))(*vals)
 
 
-def tf32_passes():
-    """Number of TF32 MMA passes per product: 3 = split-TF32 (default), 1 = plain TF32."""
-    v = int(os.environ.get("LNN_TF32_PASSES", "3"))
-    if v not in (1, 3):
-        raise ValueError("LNN_TF32_PASSES must be 1 or 3")
+def precision():
+    """Operand split of the tensor-core contractions (the `precision` argument of the C entries):
+    2 = split FP16 (default), 3 = split TF32, 1 = plain TF32.  LNN_PRECISION overrides it."""
+    v = int(os.environ.get("LNN_PRECISION", "2"))
+    if v not in (1, 2, 3):
+        raise ValueError("LNN_PRECISION must be 1, 2 or 3")
     return v
+
+
+# older name of the same setting
+tf32_passes = precision

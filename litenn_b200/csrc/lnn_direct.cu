@@ -49,6 +49,7 @@ conv_direct_fwd_kernel(float* __restrict__ Y, const float* __restrict__ X, const
   const int64_t quads = (int64_t)g.n * qh * qw;
   const int64_t in_plane = (int64_t)g.ih * g.iw, out_plane = (int64_t)g.oh * g.ow;
   const int64_t pool_plane = (int64_t)qh * qw;
+  uint32_t amax = 0u;                       // packed == 2: largest magnitude this thread wrote
   for (int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q < quads;
        q += (int64_t)gridDim.x * blockDim.x) {
     const int qx = (int)(q % qw);
@@ -134,6 +135,8 @@ conv_direct_fwd_kernel(float* __restrict__ Y, const float* __restrict__ X, const
       if (packed) {
         // pooled result written channel-innermost and pre-split for the next convolution:
         // Y / Ylo are [n][qh][qw][ocp_out], this thread owns 16 consecutive channels of one pixel
+        // (packed == 2: the fp32 values themselves go to Y and their largest magnitude, as a bit
+        // pattern, to the word Ylo points at -- the fp16 split needs it before it can run)
         float hi[kOcChunk], lo[kOcChunk];
 #pragma unroll
         for (int o = 0; o < kOcChunk; ++o) {
@@ -151,18 +154,23 @@ conv_direct_fwd_kernel(float* __restrict__ Y, const float* __restrict__ X, const
             if (v01 && v10) m = fmaxf(m, y11);
             if (m == -CUDART_INF_F) m = 0.0f;      // a window of NaNs, as the pooling kernel
           }
-          uint32_t r;
-          asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(m));
-          hi[o] = __uint_as_float(r);
-          asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(__fsub_rn(m, hi[o])));
-          lo[o] = __uint_as_float(r);
+          if (packed == 2) {
+            hi[o] = m; lo[o] = 0.0f;
+            amax = max(amax, __float_as_uint(m) & 0x7fffffffu);
+          } else {
+            uint32_t r;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(m));
+            hi[o] = __uint_as_float(r);
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(__fsub_rn(m, hi[o])));
+            lo[o] = __uint_as_float(r);
+          }
         }
         const int64_t pix = (n * qh + qy) * qw + qx;
 #pragma unroll
         for (int o = 0; o < kOcChunk; o += 4) {
           if (oc0 + o < ocp_out) {
             *reinterpret_cast<float4*>(Y + pix * ocp_out + oc0 + o) = make_float4(hi[o], hi[o + 1], hi[o + 2], hi[o + 3]);
-            if (Ylo)
+            if (Ylo && packed == 1)
               *reinterpret_cast<float4*>(Ylo + pix * ocp_out + oc0 + o) = make_float4(lo[o], lo[o + 1], lo[o + 2], lo[o + 3]);
           }
         }
@@ -205,6 +213,12 @@ conv_direct_fwd_kernel(float* __restrict__ Y, const float* __restrict__ X, const
         }
       }
     }
+  }
+  if (packed == 2) {
+    // one atomic per warp for the whole launch
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0 && amax != 0u) atomicMax(reinterpret_cast<unsigned int*>(Ylo), amax);
   }
 }
 

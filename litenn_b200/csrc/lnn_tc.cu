@@ -1,12 +1,21 @@
 // tcgen05 tile engine: device kernel, operand pre-split passes, tensor-map construction
 // and the planners behind lnn_gemm_f32 / lnn_conv2d_fwd / lnn_conv2d_dx / lnn_conv2d_dw.
 #include "lnn_tc.cuh"
+#include <cuda_fp16.h>
 #include <stdlib.h>
 #include <math_constants.h>
 #include <string.h>
 #include <algorithm>
 
 using namespace lnn_tc;
+
+// Timing experiments (skip MMAs / loads / stores / tap shifts; the results are wrong by design)
+// exist only in builds made with -DLNN_TC_EXPERIMENTS.
+#ifdef LNN_TC_EXPERIMENTS
+#define LNN_DBG(p, bit) (((p).debug & (bit)) != 0)
+#else
+#define LNN_DBG(p, bit) false
+#endif
 
 // =========================================================================================
 // device helpers (inline PTX)
@@ -110,38 +119,61 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint6
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum)
       : "memory");
 }
-// All MMAs of one k-block (KS steps of K = 8; hi*hi, hi*lo, lo*hi when NBUF == 2), fully
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                         uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum)
+      : "memory");
+}
+template <bool F16>
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                     uint32_t accum) {
+  if (F16) umma_f16(tmem_d, adesc, bdesc, idesc, accum);
+  else umma_tf32(tmem_d, adesc, bdesc, idesc, accum);
+}
+// All MMAs of one k-block (KS steps of 32 bytes of K; hi*hi, hi*lo, lo*hi when NBUF == 2), fully
 // unrolled with independent descriptor adds: the issuing thread is a single scalar stream and
 // every dependent instruction between two tcgen05.mma shows up in the MMA rate.
-template <int KS, int NBUF>
+template <int KS, int NBUF, bool F16>
 __device__ __forceinline__ void issue_kblock(uint32_t d_tmem, uint64_t ah, uint64_t bh, uint64_t a_step,
                                              uint64_t b_step, uint64_t a_lo, uint64_t b_lo,
                                              uint32_t idesc, uint32_t accum_first) {
 #pragma unroll
   for (int ks = 0; ks < KS; ++ks) {
     const uint64_t a = ah + (uint64_t)ks * a_step, b = bh + (uint64_t)ks * b_step;
-    umma_tf32(d_tmem, a, b, idesc, ks == 0 ? accum_first : 1u);
+    umma<F16>(d_tmem, a, b, idesc, ks == 0 ? accum_first : 1u);
     if (NBUF == 2) {
-      umma_tf32(d_tmem, a, b + b_lo, idesc, 1u);
-      umma_tf32(d_tmem, a + a_lo, b, idesc, 1u);
+      umma<F16>(d_tmem, a, b + b_lo, idesc, 1u);
+      umma<F16>(d_tmem, a + a_lo, b, idesc, 1u);
     }
   }
 }
-template <int NBUF>
+template <int NBUF, bool F16>
 __device__ __forceinline__ void issue_kblock_n(int ksteps, uint32_t d_tmem, uint64_t ah, uint64_t bh,
                                                uint64_t a_step, uint64_t b_step, uint64_t a_lo,
                                                uint64_t b_lo, uint32_t idesc, uint32_t accum_first) {
   switch (ksteps) {
-    case 4: issue_kblock<4, NBUF>(d_tmem, ah, bh, a_step, b_step, a_lo, b_lo, idesc, accum_first); break;
-    case 2: issue_kblock<2, NBUF>(d_tmem, ah, bh, a_step, b_step, a_lo, b_lo, idesc, accum_first); break;
-    case 1: issue_kblock<1, NBUF>(d_tmem, ah, bh, a_step, b_step, a_lo, b_lo, idesc, accum_first); break;
-    case 8: issue_kblock<8, NBUF>(d_tmem, ah, bh, a_step, b_step, a_lo, b_lo, idesc, accum_first); break;
+    case 4: issue_kblock<4, NBUF, F16>(d_tmem, ah, bh, a_step, b_step, a_lo, b_lo, idesc, accum_first); break;
+    case 2: issue_kblock<2, NBUF, F16>(d_tmem, ah, bh, a_step, b_step, a_lo, b_lo, idesc, accum_first); break;
+    case 1: issue_kblock<1, NBUF, F16>(d_tmem, ah, bh, a_step, b_step, a_lo, b_lo, idesc, accum_first); break;
+    case 8: issue_kblock<8, NBUF, F16>(d_tmem, ah, bh, a_step, b_step, a_lo, b_lo, idesc, accum_first); break;
     default:
       for (int ks = 0; ks < ksteps; ++ks) {
-        issue_kblock<1, NBUF>(d_tmem, ah, bh, a_step, b_step, a_lo, b_lo, idesc, ks == 0 ? accum_first : 1u);
+        issue_kblock<1, NBUF, F16>(d_tmem, ah, bh, a_step, b_step, a_lo, b_lo, idesc, ks == 0 ? accum_first : 1u);
         ah += a_step; bh += b_step;
       }
   }
+}
+// precision dispatch: fp16 split always carries hi and lo; tf32 may be hi only
+__device__ __forceinline__ void issue_unit(int esz, int nbuf, int ksteps, uint32_t d_tmem, uint64_t ah,
+                                           uint64_t bh, uint64_t a_step, uint64_t b_step, uint64_t a_lo,
+                                           uint64_t b_lo, uint32_t idesc, uint32_t accum_first) {
+  if (esz == 2) issue_kblock_n<2, true>(ksteps, d_tmem, ah, bh, a_step, b_step, a_lo, b_lo, idesc, accum_first);
+  else if (nbuf == 2) issue_kblock_n<2, false>(ksteps, d_tmem, ah, bh, a_step, b_step, a_lo, b_lo, idesc, accum_first);
+  else issue_kblock_n<1, false>(ksteps, d_tmem, ah, bh, a_step, b_step, a_lo, b_lo, idesc, accum_first);
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
@@ -200,21 +232,62 @@ __device__ __forceinline__ void split1(float x, float& hi, float& lo) {
   lo = to_tf32(__fsub_rn(x, hi));
 }
 
+// ---- fp16 split: exact power-of-two scaling -----------------------------------------------
+// The scale exponent of a tensor follows from the bit pattern of its largest magnitude:
+// x * 2^-e lies in [2^14, 2^15) for that element, so no element overflows fp16 and every element
+// within 2^17 of the largest keeps 22 significant bits in hi + lo (smaller ones keep an absolute
+// error of 2^-25 on that scale).  Zero, infinite and NaN maxima give e = 0: the values then go
+// through fp16 as they are and non-finite inputs stay non-finite.
+__device__ __forceinline__ int exp_of_amax(uint32_t bits) {
+  int E = (int)((bits >> 23) & 0xffu);
+  if (bits == 0u || E == 255) return 0;
+  if (E == 0) E = 1;
+  return E - 127 - 14;
+}
+// 2^k as a float for -149 <= k <= 127
+__device__ __forceinline__ float pow2f_int(int k) {
+  return k >= -126 ? __int_as_float((k + 127) << 23) : __int_as_float(1 << (k + 149));
+}
+// multiplication by 2^k in two exact steps whose factors are always representable
+struct Pow2Scale {
+  float f1, f2;
+  __device__ __forceinline__ explicit Pow2Scale(int k) {
+    const int k1 = k / 2;
+    f1 = pow2f_int(k1); f2 = pow2f_int(k - k1);
+  }
+  __device__ __forceinline__ float operator()(float v) const { return __fmul_rn(__fmul_rn(v, f1), f2); }
+};
+__device__ __forceinline__ void split_half(float xs, __half& hi, __half& lo) {
+  hi = __float2half_rn(xs);
+  lo = __float2half_rn(__fsub_rn(xs, __half2float(hi)));
+}
+// largest magnitude of a warp's values into *dst (bit patterns of non-negative floats order like
+// unsigned integers; a NaN pattern is larger than infinity, which is what exp_of_amax expects)
+__device__ __forceinline__ void warp_amax_commit(uint32_t bits, uint32_t* dst) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) bits = max(bits, __shfl_xor_sync(0xffffffffu, bits, o));
+  if ((threadIdx.x & 31) == 0 && bits != 0u) atomicMax(dst, bits);
+}
+
 // Fused max_pool2D(2, 2) of a channels-on-M accumulator: v0 / v1 hold 32 consecutive pixels of
 // two consecutive image rows for this lane's channel (row `a` even, first column `b0` even,
 // `wvalid` of the 32 columns real).  The maximum is taken in the pooling kernel's order
 // (t00, t01, t10, t11 on top of -inf; litenn/core/op/pool2D.py:111-146) after bias and
 // activation, so the value equals the unfused chain bit for bit.
-__device__ __forceinline__ void pooled_store(const TcParams& p, const uint32_t* v0, const uint32_t* v1,
-                                             float bias_v, int oc, int64_t n, int a, int b0, int wvalid) {
+// ep_mode 3 collects the largest magnitude written by this thread in `amax`; the caller
+// commits it once per warp when the kernel ends.
+__device__ __forceinline__ void pooled_store(const TcParams& p, const Pow2Scale& sc, const uint32_t* v0,
+                                             const uint32_t* v1, float bias_v, int oc, int64_t n, int a,
+                                             int b0, int wvalid, uint32_t& amax) {
   const bool real = oc < p.OC;
   if (p.ep_mode == 1 && !real) return;
-  if (p.ep_mode == 2 && oc >= p.ocp) return;
+  if (p.ep_mode >= 2 && oc >= p.ocp) return;
   float m[16];
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
     float t00 = __uint_as_float(v0[2 * j]), t01 = __uint_as_float(v0[2 * j + 1]);
     float t10 = __uint_as_float(v1[2 * j]), t11 = __uint_as_float(v1[2 * j + 1]);
+    if (p.esz == 2) { t00 = sc(t00); t01 = sc(t01); t10 = sc(t10); t11 = sc(t11); }
     if (p.bias) {
       t00 = __fadd_rn(t00, bias_v); t01 = __fadd_rn(t01, bias_v);
       t10 = __fadd_rn(t10, bias_v); t11 = __fadd_rn(t11, bias_v);
@@ -238,7 +311,7 @@ __device__ __forceinline__ void pooled_store(const TcParams& p, const uint32_t* 
       for (int j = 0; j < 16; ++j)
         if (j < npool) dst[j] = m[j];
     }
-  } else {
+  } else if (p.ep_mode == 2) {
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
       if (j < npool) {
@@ -246,6 +319,15 @@ __device__ __forceinline__ void pooled_store(const TcParams& p, const uint32_t* 
         if (real) split1(m[j], hi, lo);                      // pad channels are written as zeros
         p.out[base + (int64_t)j * p.out_sb] = hi;
         if (p.out_lo) p.out_lo[base + (int64_t)j * p.out_sb] = lo;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      if (j < npool) {
+        const float v = real ? m[j] : 0.0f;                  // pad channels are written as zeros
+        p.out[base + (int64_t)j * p.out_sb] = v;
+        amax = max(amax, __float_as_uint(v) & 0x7fffffffu);
       }
     }
   }
@@ -320,7 +402,7 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
 
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles = (raw + 1023u) & ~1023u;      // operand ring, 1024-byte aligned
-  const int nbuf = p.passes == 3 ? 2 : 1;
+  const int nbuf = p.passes == 1 ? 1 : 2;
   const uint32_t a_sz = (uint32_t)((p.a_tile_bytes + 1023) & ~1023);
   const uint32_t b_sz = (uint32_t)((p.b_tile_bytes + 1023) & ~1023);
   const uint32_t stage_sz = (uint32_t)p.kgroup * nbuf * (a_sz + b_sz);
@@ -371,11 +453,13 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
           const int nun = min(p.kgroup, units_left);
           if (!mbar_wait(empty0 + 8u * s, ph ^ 1u, abort_flag, p.status, 0, units_left)) { ok = false; break; }
           const uint32_t fb = full0 + 8u * s;
-          if (p.debug & 2) { mbar_arrive(fb); }         // timing experiment: no loads
+          if (LNN_DBG(p, 2)) { mbar_arrive(fb); }       // timing experiment: no loads
           else {
-            // DW: only the 32-channel blocks of dY that hold real output channels are loaded; the
+            // elements per 128/64/32-byte row of an MN-major box
+            const int ea = p.swz_a / p.esz, eb = p.swz_b / p.esz;
+            // DW: only the channel blocks of dY that hold real output channels are loaded; the
             // accumulator rows of the others are never read back
-            const int a_valid = MODE == MODE_DW ? min(p.a_loads, (p.OC - t.oc_t * 128 + 31) >> 5) : p.a_loads;
+            const int a_valid = MODE == MODE_DW ? min(p.a_loads, (p.OC - t.oc_t * 128 + ea - 1) / ea) : p.a_loads;
             if (MODE == MODE_DW)
               mbar_expect_tx(fb, (uint32_t)nbuf * (uint32_t)(a_valid * p.a_load_bytes + t.nblk * p.b_load_bytes));
             else
@@ -392,13 +476,13 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
                     tma_load_3d(da, ta, fb, k0, t.m0, t.bz);
                   } else {
                     for (int i = 0; i < p.a_loads; ++i)
-                      tma_load_3d(da + i * p.a_load_bytes, ta, fb, t.m0 + i * 32, k0, t.bz);
+                      tma_load_3d(da + i * p.a_load_bytes, ta, fb, t.m0 + i * ea, k0, t.bz);
                   }
                   if (p.b_major == 0) {
                     tma_load_3d(db, tb, fb, k0, t.n0, t.bz);
                   } else {
                     for (int i = 0; i < p.b_loads; ++i)
-                      tma_load_3d(db + i * p.b_load_bytes, tb, fb, t.n0 + i * 32, k0, t.bz);
+                      tma_load_3d(db + i * p.b_load_bytes, tb, fb, t.n0 + i * eb, k0, t.bz);
                   }
                 } else if (MODE == MODE_CONV) {
                   tma_load_4d(da, ta, fb, cbi * p.cb, cx + p.tap_dx[tp], cy + p.tap_dy[tp], t.pn0);
@@ -411,7 +495,6 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
                   const int bt = pidx % p.tiles_b;
                   const int at = (pidx / p.tiles_b) % p.tiles_a;
                   const int nt = pidx / (p.tiles_b * p.tiles_a);
-                  const int ea = p.swz_a >> 2, eb = p.swz_b >> 2;
                   for (int i = 0; i < a_valid; ++i)
                     tma_load_4d(da + i * p.a_load_bytes, ta, fb, t.oc_t * 128 + i * ea, bt * p.tw,
                                 at * p.th, nt * p.tn);
@@ -424,7 +507,7 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
                   }
                 }
               }
-              k0 += 32;
+              k0 += p.kunit;
               if (++cbi == p.ncb) { cbi = 0; ++tp; }
               ++pidx;
             }
@@ -436,22 +519,26 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      // K-major: 8-row swizzle atoms, SBO = 8 rows.  MN-major tf32 only exists as the
-      // "128-byte swizzle with 32-byte atoms" layout: 4 k-rows per atom (SBO = 4 rows), the
-      // 32-element MN blocks LBO apart.
-      const uint32_t la = p.a_major ? 1u : layout_of_swizzle(p.swz_a);
-      const uint32_t lb = p.b_major ? 1u : layout_of_swizzle(p.swz_b);
+      // K-major: 8-row swizzle atoms, SBO = 8 rows.  MN-major: rows of one swizzle span along
+      // MN, k-rows stacked; fp16 uses the ordinary 128/64/32-byte swizzles (atoms of 8 k-rows,
+      // SBO = 8 rows), tf32 only exists as the "128-byte swizzle with 32-byte atoms" layout
+      // (4 k-rows per atom, SBO = 4 rows); the MN blocks are LBO apart.  One instruction
+      // consumes 32 bytes of K: 8 (tf32) or 16 (fp16) k-rows of an MN-major tile.
+      const bool f16 = p.esz == 2;
+      const uint32_t la = (p.a_major && !f16) ? 1u : layout_of_swizzle(p.swz_a);
+      const uint32_t lb = (p.b_major && !f16) ? 1u : layout_of_swizzle(p.swz_b);
       const uint32_t a_lbo = p.a_major ? (uint32_t)(p.a_krows * p.swz_a) : 16u;
       const uint32_t b_lbo = p.b_major ? (uint32_t)(p.b_krows * p.swz_b) : 16u;
-      const uint32_t a_sbo = (p.a_major ? 4u : 8u) * p.swz_a, b_sbo = (p.b_major ? 4u : 8u) * p.swz_b;
+      const uint32_t mn_atom = f16 ? 8u : 4u, mn_step = f16 ? 16u : 8u;
+      const uint32_t a_sbo = (p.a_major ? mn_atom : 8u) * p.swz_a, b_sbo = (p.b_major ? mn_atom : 8u) * p.swz_b;
       // descriptors with a zero start address; the address field (bits 0-13, 16-byte units)
       // is added per use -- shared memory addresses stay below 2^18, so no carry leaves it
       const uint64_t a_desc0 = make_smem_desc(0u, a_lbo, a_sbo, la);
       const uint64_t b_desc0 = make_smem_desc(0u, b_lbo, b_sbo, lb);
-      const uint64_t a_step16 = (p.a_major ? 8u * p.swz_a : 32u) >> 4;
-      const uint64_t b_step16 = (p.b_major ? 8u * p.swz_b : 32u) >> 4;
+      const uint64_t a_step16 = (p.a_major ? mn_step * p.swz_a : 32u) >> 4;
+      const uint64_t b_step16 = (p.b_major ? mn_step * p.swz_b : 32u) >> 4;
       const uint64_t a_lo16 = a_sz >> 4, b_lo16 = b_sz >> 4;
-      const int ksteps = (p.debug & 1) ? 0 : p.ksteps;     // debug bit 0: no MMAs
+      const int ksteps = LNN_DBG(p, 1) ? 0 : p.ksteps;     // experiment bit 0: no MMAs
       const uint32_t idesc = p.idesc;
       uint32_t s = 0, ph = 0;
       int it = 0;                                       // tiles processed by this CTA
@@ -474,8 +561,7 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
           for (int u = 0; u < nun; ++u, ua += unit_sz) {
             const uint64_t ah = a_desc0 + (uint64_t)(ua >> 4);
             const uint64_t bh = b_desc0 + (uint64_t)((ua + nbuf * a_sz) >> 4);
-            if (nbuf == 2) issue_kblock_n<2>(ksteps, d_tmem, ah, bh, a_step16, b_step16, a_lo16, b_lo16, idesc, accum);
-            else issue_kblock_n<1>(ksteps, d_tmem, ah, bh, a_step16, b_step16, a_lo16, b_lo16, idesc, accum);
+            issue_unit(p.esz, nbuf, ksteps, d_tmem, ah, bh, a_step16, b_step16, a_lo16, b_lo16, idesc, accum);
             if (ksteps > 0) accum = 1u;
           }
           umma_commit(empty0 + 8u * s);                 // frees the stage when these MMAs retire
@@ -489,6 +575,10 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
     // ---- epilogue warps: TMEM lane quarter = warp % 4 --------------------------------------
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
+    // fp16 split: the accumulator holds the product of the scaled operands
+    const bool scaled = p.esz == 2;
+    const Pow2Scale sc(scaled ? exp_of_amax(__ldg(p.amax_a)) + exp_of_amax(__ldg(p.amax_b)) : 0);
+    uint32_t amax_acc = 0u;
     int it = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
       const TileCoord t = decode_tile<MODE>(p, tile);
@@ -518,8 +608,8 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
                 tmem_ld32(d_tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c_top + p.tw), v1);
                 tmem_ld_wait();
                 const int n = t.pn0 + tn_i, a = t.pa0 + th_i, b0 = t.pb0 + ch * 32;
-                if (n < p.NL && a < p.AH && b0 < p.AW && !(p.debug & 4))
-                  pooled_store(p, v0, v1, bias_v, oc, n, a, b0, 32);
+                if (n < p.NL && a < p.AH && b0 < p.AW && !LNN_DBG(p, 4))
+                  pooled_store(p, sc, v0, v1, bias_v, oc, n, a, b0, 32, amax_acc);
                 __syncwarp();
               }
             }
@@ -536,7 +626,7 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
           uint32_t v[32];
           tmem_ld32(d_tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
           tmem_ld_wait();
-          if (row_ok && !(p.debug & 4)) {
+          if (row_ok && !LNN_DBG(p, 4)) {
             // Phase 1: where each group of four pixels goes, and (for "+=") its old values.  All
             // loads are issued before any store so that their latencies overlap.
             float* dsts[8];
@@ -576,6 +666,7 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 float tt = __uint_as_float(v[j + e]);
+                if (scaled) tt = sc(tt);
                 if (p.bias) tt = __fadd_rn(tt, bias_v);
                 x[e] = apply_act(tt, p.act, p.alpha);
               }
@@ -635,8 +726,8 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
       } else {
         row_ok = true;
         row_off = (int64_t)t.split * p.part_stride_split +
-                  ((int64_t)t.oc_t * 128 + r) * p.part_ld + (int64_t)t.nb0 * 32;
-        col0 = 0; col_limit = t.nblk * 32;
+                  ((int64_t)t.oc_t * 128 + r) * p.part_ld + (int64_t)t.nb0 * (p.swz_b / p.esz);
+        col0 = 0; col_limit = t.nblk * (p.swz_b / p.esz);
       }
       float* outp = p.out + row_off;
       const bool vec_ok = (MODE != MODE_CONV) && ((((uintptr_t)outp) & 15) == 0);
@@ -649,8 +740,12 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = 0u;
         }
-        if (!row_ok || (p.debug & 4)) {
-          // nothing to store for this lane (debug bit 2: timing experiment without stores)
+        if (scaled) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(sc(__uint_as_float(v[j])));
+        }
+        if (!row_ok || LNN_DBG(p, 4)) {
+          // nothing to store for this lane (experiment bit 2: no stores)
         } else if (MODE == MODE_DW) {
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
@@ -706,6 +801,8 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
     }
+    __syncwarp();
+    if (p.ep_mode == 3) warp_amax_commit(amax_acc, p.amax_out);
   }
 
   // ---- tear-down ------------------------------------------------------------------------
@@ -763,14 +860,14 @@ tc_halo_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
 
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t ring = (raw + 1023u) & ~1023u;
-  const int nbuf = p.passes == 3 ? 2 : 1;
+  const int nbuf = p.passes == 1 ? 1 : 2;
   const uint32_t a_sz = (uint32_t)p.a_tile_bytes;            // 1024-byte multiples
   const uint32_t b_sz = (uint32_t)p.h_bbuf;
   const uint32_t a_unit = nbuf * a_sz, b_stage = nbuf * b_sz;
   const uint32_t a_ring = ring, b_ring = ring + (uint32_t)p.h_sa * a_unit;
   const int num_tiles = p.grid_x * p.grid_y;
   const int a_per_cb = p.cb / p.h_acb;                       // kernel units per (tap, channel block)
-  const uint32_t row_bytes = (uint32_t)p.cb * 4u;
+  const uint32_t row_bytes = (uint32_t)(p.cb * p.esz);        // one pixel of the patch
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.h_sa; ++s) {
@@ -830,13 +927,13 @@ tc_halo_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
             for (int h = 0; h < a_per_cb; ++h) {
               if (!mbar_wait(aempty0 + 8u * s, ph ^ 1u, abort_flag, p.status, 0, tp)) { ok = false; break; }
               const uint32_t fb = afull0 + 8u * s;
-              if (p.debug & 2) { mbar_arrive(fb); }
+              if (LNN_DBG(p, 2)) { mbar_arrive(fb); }
               else {
-              mbar_expect_tx(fb, tx);
-              const uint32_t dst = a_ring + s * a_unit;
-              const int c0 = cbi * p.cb + h * p.h_acb;
-              tma_load_3d(dst, &tmAh, fb, c0, t.m0, p.tap_w[tp]);
-              if (nbuf == 2) tma_load_3d(dst + a_sz, &tmAl, fb, c0, t.m0, p.tap_w[tp]);
+                mbar_expect_tx(fb, tx);
+                const uint32_t dst = a_ring + s * a_unit;
+                const int c0 = cbi * p.cb + h * p.h_acb;
+                tma_load_3d(dst, &tmAh, fb, c0, t.m0, p.tap_w[tp]);
+                if (nbuf == 2) tma_load_3d(dst + a_sz, &tmAl, fb, c0, t.m0, p.tap_w[tp]);
               }
               if (++s == (uint32_t)p.h_sa) { s = 0; ph ^= 1u; }
             }
@@ -847,11 +944,11 @@ tc_halo_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
   } else if (warp == 1) {
     // ---- MMA issuer -----------------------------------------------------------------------
     if (lane == 0) {
-      const uint32_t a_swz = (uint32_t)p.h_acb * 4u;
+      const uint32_t a_swz = (uint32_t)(p.h_acb * p.esz);
       const uint64_t a_desc0 = make_smem_desc(0u, 16u, 8u * a_swz, layout_of_swizzle((int)a_swz));
       const uint64_t b_desc0 = make_smem_desc(0u, 16u, 8u * row_bytes, layout_of_swizzle((int)row_bytes));
       const uint64_t a_lo16 = a_sz >> 4, b_lo16 = b_sz >> 4;
-      const int ksteps = (p.debug & 1) ? 0 : p.h_acb / 8;
+      const int ksteps = LNN_DBG(p, 1) ? 0 : (int)(a_swz / 32u);   // one instruction = 32 bytes of K
       const uint32_t idesc = p.idesc;
       uint32_t sa = 0, pha = 0, sb = 0, phb = 0;
       int it = 0;
@@ -869,7 +966,7 @@ tc_halo_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
           const uint32_t b_base = b_ring + sb * b_stage;
           for (int tp = 0; ok && tp < p.ntaps; ++tp) {
             // the tap's window of the patch: same array, start address shifted by whole pixels
-            const uint32_t b_addr = b_base + ((p.debug & 8) ? 0u : (uint32_t)p.tap_shift[tp] * row_bytes);
+            const uint32_t b_addr = b_base + (LNN_DBG(p, 8) ? 0u : (uint32_t)p.tap_shift[tp] * row_bytes);
             // the swizzle is a function of the absolute shared-memory address, so a start address
             // that is not a multiple of the 1024-byte pattern needs no base-offset field
             const uint64_t bdesc = b_desc0 + (uint64_t)(b_addr >> 4);
@@ -877,10 +974,9 @@ tc_halo_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
               if (!mbar_wait(afull0 + 8u * sa, pha, abort_flag, p.status, 1, tp)) { ok = false; break; }
               tc_fence_after();
               const uint64_t ah = a_desc0 + (uint64_t)((a_ring + sa * a_unit) >> 4);
-              const uint64_t bh = bdesc + (uint64_t)((h * p.h_acb * 4) >> 4);
-              // one MMA step = 8 channels = 32 bytes = 2 descriptor units
-              if (nbuf == 2) issue_kblock_n<2>(ksteps, d_tmem, ah, bh, 2, 2, a_lo16, b_lo16, idesc, accum);
-              else issue_kblock_n<1>(ksteps, d_tmem, ah, bh, 2, 2, a_lo16, b_lo16, idesc, accum);
+              const uint64_t bh = bdesc + (uint64_t)((h * p.h_acb * p.esz) >> 4);
+              // one MMA step = 32 bytes of channels = 2 descriptor units
+              issue_unit(p.esz, nbuf, ksteps, d_tmem, ah, bh, 2, 2, a_lo16, b_lo16, idesc, accum);
               if (ksteps > 0) accum = 1u;
               umma_commit(aempty0 + 8u * sa);
               if (++sa == (uint32_t)p.h_sa) { sa = 0; pha ^= 1u; }
@@ -897,6 +993,9 @@ tc_halo_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
     const int ncols = p.th * p.h_pw;                  // columns that can hold a real pixel
+    const bool scaled = p.esz == 2;
+    const Pow2Scale sc(scaled ? exp_of_amax(__ldg(p.amax_a)) + exp_of_amax(__ldg(p.amax_b)) : 0);
+    uint32_t amax_acc = 0u;
     int it = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
       const TileCoord t = decode_tile<MODE_CONVT>(p, tile);
@@ -920,8 +1019,8 @@ tc_halo_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
             tmem_ld32(d_tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c_top + p.h_pw), v1);
             tmem_ld_wait();
             const int a = t.pa0 + h_i, b0 = t.pb0 + w0;
-            if (a < p.AH && b0 < p.AW && !(p.debug & 4))
-              pooled_store(p, v0, v1, bias_v, oc, t.pn0, a, b0, 32);
+            if (a < p.AH && b0 < p.AW && !LNN_DBG(p, 4))
+              pooled_store(p, sc, v0, v1, bias_v, oc, t.pn0, a, b0, 32, amax_acc);
             __syncwarp();
           }
         }
@@ -947,7 +1046,7 @@ tc_halo_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
             const int a = t.pa0 + h_i, b = t.pb0 + w_i;
             wpos[gi] = -1;
             old[gi] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (c0 + gi * 4 < ncols && w_i < p.tw && a < p.AH && b < p.AW && !(p.debug & 4)) {
+            if (c0 + gi * 4 < ncols && w_i < p.tw && a < p.AH && b < p.AW && !LNN_DBG(p, 4)) {
               wpos[gi] = w_i;
               float* dst = obase + (int64_t)a * p.out_sa + (int64_t)b * p.out_sb;
               dsts[gi] = dst;
@@ -976,6 +1075,7 @@ tc_halo_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               float tt = __uint_as_float(v[j + e]);
+              if (scaled) tt = sc(tt);
               if (p.bias) tt = __fadd_rn(tt, bias_v);
               x[e] = apply_act(tt, p.act, p.alpha);
             }
@@ -1001,6 +1101,8 @@ tc_halo_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
     }
+    __syncwarp();
+    if (p.ep_mode == 3) warp_amax_commit(amax_acc, p.amax_out);
   }
 
   tc_fence_before();
@@ -1021,14 +1123,64 @@ tc_halo_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
 // =========================================================================================
 constexpr int kThreads = 256;
 
+// Largest magnitude of a tensor as an fp32 bit pattern (*out must be zero before the launch).
+__global__ void __launch_bounds__(kThreads)
+absmax_kernel(const float* __restrict__ src, int64_t n, uint32_t* __restrict__ out) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  uint32_t m = 0u;
+  if ((((uintptr_t)src) & 15) == 0) {
+    const int64_t n4 = n >> 2;
+    for (int64_t i = tid; i < n4; i += nthreads) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(src) + i);
+      m = max(max(m, v.x & 0x7fffffffu), max(v.y & 0x7fffffffu, max(v.z & 0x7fffffffu, v.w & 0x7fffffffu)));
+    }
+    for (int64_t i = (n4 << 2) + tid; i < n; i += nthreads) m = max(m, __float_as_uint(src[i]) & 0x7fffffffu);
+  } else {
+    for (int64_t i = tid; i < n; i += nthreads) m = max(m, __float_as_uint(src[i]) & 0x7fffffffu);
+  }
+  warp_amax_commit(m, out);
+}
+
+// What a split pass needs per thread: the tf32 split needs nothing, the fp16 split the two
+// factors of 2^-e with e the scale exponent of the tensor.
+template <bool F16> struct Splitter;
+template <> struct Splitter<false> {
+  typedef float T;
+  __device__ __forceinline__ explicit Splitter(const uint32_t*) {}
+  __device__ __forceinline__ void operator()(float x, float& h, float& l) const { split1(x, h, l); }
+  static __device__ __forceinline__ float zero() { return 0.0f; }
+};
+template <> struct Splitter<true> {
+  typedef __half T;
+  Pow2Scale sc;
+  __device__ __forceinline__ explicit Splitter(const uint32_t* amax) : sc(-exp_of_amax(__ldg(amax))) {}
+  __device__ __forceinline__ void operator()(float x, __half& h, __half& l) const { split_half(sc(x), h, l); }
+  static __device__ __forceinline__ __half zero() { return __float2half_rn(0.0f); }
+};
+// N consecutive elements as one vector store (N * sizeof(T) = 8 or 16 bytes)
+template <class T, int N> __device__ __forceinline__ void store_vec(T* dst, const T* v, bool streaming) {
+  if (sizeof(T) * N == 16) {
+    const float4 q = *reinterpret_cast<const float4*>(v);
+    if (streaming) __stcs(reinterpret_cast<float4*>(dst), q); else *reinterpret_cast<float4*>(dst) = q;
+  } else {
+    const float2 q = *reinterpret_cast<const float2*>(v);
+    if (streaming) __stcs(reinterpret_cast<float2*>(dst), q); else *reinterpret_cast<float2*>(dst) = q;
+  }
+}
+
 // NCHW -> channel-innermost hi/lo copies, 128-bit on both sides: a tile of 32 channels x 128
-// pixels is read as float4 along the pixels and written as float4 along the channels (the row
-// pitch of 129 floats makes the transposed shared-memory reads conflict-free).  Needs hw % 4 == 0
-// and 16-byte aligned buffers; cp is a multiple of 8.
+// pixels is read as float4 along the pixels and written as 16-byte vectors along the channels (the
+// row pitch of 129 floats makes the transposed shared-memory reads conflict-free).  Needs
+// hw % 4 == 0 and 16-byte aligned buffers; cp is a multiple of 8.
+template <bool F16>
 __global__ void __launch_bounds__(256)
-nchw_to_nhwc_split_vec_kernel(float* __restrict__ hi, float* __restrict__ lo,
+nchw_to_nhwc_split_vec_kernel(typename Splitter<F16>::T* __restrict__ hi, typename Splitter<F16>::T* __restrict__ lo,
                               const float* __restrict__ src, int64_t n, int c, int64_t hw, int cp,
-                              int want_lo) {
+                              int want_lo, const uint32_t* __restrict__ amax) {
+  typedef typename Splitter<F16>::T T;
+  constexpr int CV = F16 ? 8 : 4;                    // channels per 16-byte store
+  const Splitter<F16> split(amax);
   __shared__ float tile[32][129];
   const int64_t tiles_p = (hw + 127) / 128;
   const int tiles_c = (cp + 31) / 32;
@@ -1052,18 +1204,19 @@ nchw_to_nhwc_split_vec_kernel(float* __restrict__ hi, float* __restrict__ lo,
     }
     __syncthreads();
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
+    for (int k = 0; k < 4 * 4 / CV; ++k) {
       const int item = threadIdx.x + k * 256;
-      const int cq = item & 7, pl = item >> 3;
+      const int cq = item & (32 / CV - 1), pl = item / (32 / CV);
       const int64_t px = tp * 128 + pl;
-      const int ch = tc * 32 + cq * 4;
+      const int ch = tc * 32 + cq * CV;
       if (px < hw && ch < cp) {
-        float h[4], l[4];
+        __align__(16) T h[CV];
+        __align__(16) T l[CV];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) split1(tile[cq * 4 + e][pl], h[e], l[e]);
+        for (int e = 0; e < CV; ++e) split(tile[cq * CV + e][pl], h[e], l[e]);
         const int64_t o = (img * hw + px) * cp + ch;
-        __stcs(reinterpret_cast<float4*>(hi + o), make_float4(h[0], h[1], h[2], h[3]));
-        if (want_lo) __stcs(reinterpret_cast<float4*>(lo + o), make_float4(l[0], l[1], l[2], l[3]));
+        store_vec<T, CV>(hi + o, h, true);
+        if (want_lo) store_vec<T, CV>(lo + o, l, true);
       }
     }
     __syncthreads();
@@ -1071,38 +1224,65 @@ nchw_to_nhwc_split_vec_kernel(float* __restrict__ hi, float* __restrict__ lo,
 }
 
 // hi/lo split of a dense [rows][cols] matrix into buffers of row pitch `pitch`
+template <bool F16>
 __global__ void __launch_bounds__(kThreads)
-split_rows_kernel(float* __restrict__ hi, float* __restrict__ lo, const float* __restrict__ src,
-                  int64_t rows, int64_t cols, int64_t pitch, int want_lo) {
+split_rows_kernel(typename Splitter<F16>::T* __restrict__ hi, typename Splitter<F16>::T* __restrict__ lo,
+                  const float* __restrict__ src, int64_t rows, int64_t cols, int64_t pitch, int want_lo,
+                  const uint32_t* __restrict__ amax) {
+  typedef typename Splitter<F16>::T T;
+  const Splitter<F16> split(amax);
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
-  if (pitch == cols && (cols & 3) == 0) {
+  if (pitch == cols && (cols & 3) == 0 && (((uintptr_t)src) & 15) == 0) {
     const int64_t n4 = rows * cols / 4;
     for (int64_t i = tid; i < n4; i += nthreads) {
       const float4 v = __ldcs(reinterpret_cast<const float4*>(src) + i);
-      float4 h, l;
-      split1(v.x, h.x, l.x); split1(v.y, h.y, l.y); split1(v.z, h.z, l.z); split1(v.w, h.w, l.w);
-      reinterpret_cast<float4*>(hi)[i] = h;
-      if (want_lo) reinterpret_cast<float4*>(lo)[i] = l;
+      __align__(16) T h[4];
+      __align__(16) T l[4];
+      split(v.x, h[0], l[0]); split(v.y, h[1], l[1]); split(v.z, h[2], l[2]); split(v.w, h[3], l[3]);
+      store_vec<T, 4>(hi + 4 * i, h, false);
+      if (want_lo) store_vec<T, 4>(lo + 4 * i, l, false);
     }
   } else {
     const int64_t n = rows * pitch;
     for (int64_t i = tid; i < n; i += nthreads) {
       const int64_t r = i / pitch, c = i - r * pitch;
-      float h = 0.0f, l = 0.0f;
-      if (c < cols) split1(src[r * cols + c], h, l);
+      T h = Splitter<F16>::zero(), l = Splitter<F16>::zero();
+      if (c < cols) split(src[r * cols + c], h, l);
       hi[i] = h;
       if (want_lo) lo[i] = l;
     }
   }
 }
 
+// fp32 channel-innermost tensor -> its fp16 hi/lo copies (same layout), element by element
+__global__ void __launch_bounds__(kThreads)
+half_split_kernel(__half* __restrict__ hi, __half* __restrict__ lo, const float* __restrict__ src,
+                  int64_t n8, const uint32_t* __restrict__ amax) {
+  const Splitter<true> split(amax);
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = tid; i < n8; i += nthreads) {
+    const float4 a = __ldcs(reinterpret_cast<const float4*>(src) + 2 * i);
+    const float4 b = __ldcs(reinterpret_cast<const float4*>(src) + 2 * i + 1);
+    __align__(16) __half h[8];
+    __align__(16) __half l[8];
+    split(a.x, h[0], l[0]); split(a.y, h[1], l[1]); split(a.z, h[2], l[2]); split(a.w, h[3], l[3]);
+    split(b.x, h[4], l[4]); split(b.y, h[5], l[5]); split(b.z, h[6], l[6]); split(b.w, h[7], l[7]);
+    store_vec<__half, 8>(hi + 8 * i, h, false);
+    store_vec<__half, 8>(lo + 8 * i, l, false);
+  }
+}
+
 // NCHW -> NHWC with channel padding to cp, split into hi/lo.  One block transposes a
 // [32 channels] x [32 pixels] tile of one image through shared memory.
+template <bool F16>
 __global__ void __launch_bounds__(256)
-nchw_to_nhwc_split_kernel(float* __restrict__ hi, float* __restrict__ lo,
+nchw_to_nhwc_split_kernel(typename Splitter<F16>::T* __restrict__ hi, typename Splitter<F16>::T* __restrict__ lo,
                           const float* __restrict__ src, int64_t n, int c, int64_t hw, int cp,
-                          int want_lo) {
+                          int want_lo, const uint32_t* __restrict__ amax) {
+  typedef typename Splitter<F16>::T T;
+  const Splitter<F16> split(amax);
   __shared__ float tile[32][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int64_t tiles_p = (hw + 31) / 32;
@@ -1126,8 +1306,8 @@ nchw_to_nhwc_split_kernel(float* __restrict__ hi, float* __restrict__ lo,
       const int64_t px = tp * 32 + ty + k * 8;
       const int ch = tc * 32 + tx;
       if (px < hw && ch < cp) {
-        float h, l;
-        split1(tile[tx][ty + k * 8], h, l);
+        T h, l;
+        split(tile[tx][ty + k * 8], h, l);
         const int64_t o = (img * hw + px) * cp + ch;
         hi[o] = h;
         if (want_lo) lo[o] = l;
@@ -1138,37 +1318,44 @@ nchw_to_nhwc_split_kernel(float* __restrict__ hi, float* __restrict__ lo,
 }
 
 // NCHW -> NHWC for c <= 8 channels padded to exactly 8: thread = pixel.
+template <bool F16>
 __global__ void __launch_bounds__(kThreads)
-nchw_to_nhwc8_split_kernel(float* __restrict__ hi, float* __restrict__ lo, const float* __restrict__ src,
-                           int64_t n, int c, int64_t hw, int want_lo) {
+nchw_to_nhwc8_split_kernel(typename Splitter<F16>::T* __restrict__ hi, typename Splitter<F16>::T* __restrict__ lo,
+                           const float* __restrict__ src, int64_t n, int c, int64_t hw, int want_lo,
+                           const uint32_t* __restrict__ amax) {
+  typedef typename Splitter<F16>::T T;
+  constexpr int CV = F16 ? 8 : 4;
+  const Splitter<F16> split(amax);
   const int64_t total = n * hw;
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = tid; i < total; i += nthreads) {
     const int64_t img = i / hw, px = i - img * hw;
     const float* sp = src + img * (int64_t)c * hw + px;
-    float h[8], l[8];
+    __align__(16) T h[8];
+    __align__(16) T l[8];
 #pragma unroll
     for (int ch = 0; ch < 8; ++ch) {
-      h[ch] = 0.0f; l[ch] = 0.0f;
-      if (ch < c) split1(__ldcs(sp + (int64_t)ch * hw), h[ch], l[ch]);
+      h[ch] = Splitter<F16>::zero(); l[ch] = Splitter<F16>::zero();
+      if (ch < c) split(__ldcs(sp + (int64_t)ch * hw), h[ch], l[ch]);
     }
-    float4* ho = reinterpret_cast<float4*>(hi + i * 8);
-    ho[0] = make_float4(h[0], h[1], h[2], h[3]);
-    ho[1] = make_float4(h[4], h[5], h[6], h[7]);
-    if (want_lo) {
-      float4* lp = reinterpret_cast<float4*>(lo + i * 8);
-      lp[0] = make_float4(l[0], l[1], l[2], l[3]);
-      lp[1] = make_float4(l[4], l[5], l[6], l[7]);
+#pragma unroll
+    for (int q = 0; q < 8; q += CV) {
+      store_vec<T, CV>(hi + i * 8 + q, h + q, false);
+      if (want_lo) store_vec<T, CV>(lo + i * 8 + q, l + q, false);
     }
   }
 }
 
 // Kernel OIHW -> [tap][rows][kp] hi/lo.  transpose_io = 0: rows = oc, k = ic (forward);
 // 1: rows = ic, k = oc (input gradient).  k is zero-padded to kp.
+template <bool F16>
 __global__ void __launch_bounds__(kThreads)
-weight_split_kernel(float* __restrict__ hi, float* __restrict__ lo, const float* __restrict__ w,
-                    int oc, int ic, int taps, int kp, int transpose_io, int want_lo) {
+weight_split_kernel(typename Splitter<F16>::T* __restrict__ hi, typename Splitter<F16>::T* __restrict__ lo,
+                    const float* __restrict__ w, int oc, int ic, int taps, int kp, int transpose_io,
+                    int want_lo, const uint32_t* __restrict__ amax) {
+  typedef typename Splitter<F16>::T T;
+  const Splitter<F16> split(amax);
   const int rows = transpose_io ? ic : oc;
   const int64_t total = (int64_t)taps * rows * kp;
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -1179,21 +1366,21 @@ weight_split_kernel(float* __restrict__ hi, float* __restrict__ lo, const float*
     const int64_t t2 = i / kp;
     const int row = (int)(t2 % rows);
     const int t = (int)(t2 / rows);
-    float h = 0.0f, l = 0.0f;
+    T h = Splitter<F16>::zero(), l = Splitter<F16>::zero();
     if (k < kvalid) {
       const int o = transpose_io ? k : row;
       const int c = transpose_io ? row : k;
-      split1(w[((int64_t)o * ic + c) * taps + t], h, l);
+      split(w[((int64_t)o * ic + c) * taps + t], h, l);
     }
     hi[i] = h;
     if (want_lo) lo[i] = l;
   }
 }
 
-// dW[oc][ic][tap] += sum over splits of P[split][oc][(tap, ic block, 32)], splits added in order
+// dW[oc][ic][tap] += sum over splits of P[split][oc][(tap, ic block, eb)], splits added in order
 __global__ void __launch_bounds__(kThreads)
 dw_finalize_kernel(float* __restrict__ dW, const float* __restrict__ P, int oc, int ic, int taps,
-                   int splits, int64_t stride_split, int icb, int64_t ld) {
+                   int splits, int64_t stride_split, int icb, int64_t ld, int eb) {
   const int64_t total = (int64_t)oc * ic * taps;
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
@@ -1202,7 +1389,7 @@ dw_finalize_kernel(float* __restrict__ dW, const float* __restrict__ P, int oc, 
     const int64_t t2 = i / taps;
     const int c = (int)(t2 % ic);
     const int o = (int)(t2 / ic);
-    const float* pp = P + (int64_t)o * ld + ((int64_t)t * icb + (c >> 5)) * 32 + (c & 31);
+    const float* pp = P + (int64_t)o * ld + ((int64_t)t * icb + c / eb) * eb + c % eb;
     float s = 0.0f;
     for (int k = 0; k < splits; ++k) s = __fadd_rn(s, pp[(int64_t)k * stride_split]);
     dW[i] = __fadd_rn(dW[i], s);
@@ -1230,7 +1417,8 @@ int get_encode() {
 }
 
 // dims/box/estr have `rank` entries, innermost first; strides_bytes has rank-1 entries.
-int encode_map(CUtensorMap* tm, const void* base, int rank, const uint64_t* dims,
+// esz = 2: fp16 elements, 4: fp32 (tf32) elements
+int encode_map(CUtensorMap* tm, const void* base, int esz, int rank, const uint64_t* dims,
                const uint64_t* strides_bytes, const uint32_t* box, const uint32_t* estr,
                int swz_bytes, bool mn_major = false) {
   int rc = get_encode();
@@ -1242,12 +1430,14 @@ int encode_map(CUtensorMap* tm, const void* base, int rank, const uint64_t* dims
   for (int i = 0; i < rank; ++i)
     if (bx[i] < 1 || bx[i] > 256)
       return lnn::set_error(LNN_E_UNSUPPORTED, "TMA box extent %u (dim %d) outside 1..256", bx[i], i);
-  // MN-major tf32 operands use the 128-byte swizzle whose atom is 32 bytes
-  const CUtensorMapSwizzle sw = mn_major         ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
-                              : swz_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
-                              : swz_bytes == 64  ? CU_TENSOR_MAP_SWIZZLE_64B
-                                                 : CU_TENSOR_MAP_SWIZZLE_32B;
-  CUresult r = g_encode(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, (void*)base, gd, gs,
+  // MN-major tf32 operands use the 128-byte swizzle whose atom is 32 bytes; fp16 operands use
+  // the ordinary swizzles in either orientation
+  const CUtensorMapSwizzle sw = (mn_major && esz == 4) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                              : swz_bytes == 128       ? CU_TENSOR_MAP_SWIZZLE_128B
+                              : swz_bytes == 64        ? CU_TENSOR_MAP_SWIZZLE_64B
+                                                       : CU_TENSOR_MAP_SWIZZLE_32B;
+  CUresult r = g_encode(tm, esz == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                        (cuuint32_t)rank, (void*)base, gd, gs,
                         bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
@@ -1268,16 +1458,38 @@ inline int env_int(const char* name, int dflt) {
   return (e && *e) ? atoi(e) : dflt;
 }
 
-// Timing-experiment bits (skip MMAs / loads / stores / tap shifts).  They make results wrong, so
-// they are honoured only when LNN_TC_EXPERIMENTS=1 is set as well.
-inline int debug_bits() {
-  return env_int("LNN_TC_EXPERIMENTS", 0) == 1 ? env_int("LNN_TC_DEBUG", 0) : 0;
+// Planner overrides for A/B measurements, read from the environment once per process.
+struct Knobs {
+  int halo, orient, kgroup, stages, cb, bn, direct, debug;
+  Knobs() {
+    halo = env_int("LNN_TC_HALO", 1);          // 0 off, 1 planner's rule, 2 whenever a tiling fits
+    orient = env_int("LNN_TC_ORIENT", 0);      // 1 pixels on M, 2 channels on M
+    kgroup = env_int("LNN_TC_KGROUP", 0);
+    stages = env_int("LNN_TC_STAGES", 0);
+    cb = env_int("LNN_TC_CB", 0);
+    bn = env_int("LNN_TC_BN", 0);
+    direct = env_int("LNN_CONV_DIRECT", 1);
+#ifdef LNN_TC_EXPERIMENTS
+    debug = env_int("LNN_TC_DEBUG", 0);
+#else
+    debug = 0;
+#endif
+  }
+};
+inline const Knobs& knobs() {
+  static const Knobs k;
+  return k;
 }
 
-inline uint32_t make_idesc(int bn, int a_major, int b_major) {
-  // c_format F32 (bits 4-5 = 1), a/b format TF32 (= 2) at bits 7-9 / 10-12, majors at 15 / 16,
-  // N >> 3 at bits 17-22, M >> 4 at bits 24-28.
-  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)a_major << 15) |
+// precision (the `tf32_passes` argument of the entry points): 1 = plain TF32, 3 = split TF32,
+// 2 = split FP16
+inline int esz_of(int precision) { return precision == 2 ? 2 : 4; }
+
+inline uint32_t make_idesc(int bn, int a_major, int b_major, int esz) {
+  // c_format F32 (bits 4-5 = 1), a/b format (F16 = 0, TF32 = 2) at bits 7-9 / 10-12, majors at
+  // 15 / 16, N >> 3 at bits 17-22, M >> 4 at bits 24-28.
+  const uint32_t fmt = esz == 2 ? 0u : 2u;
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)a_major << 15) |
          ((uint32_t)b_major << 16) | ((uint32_t)(bn >> 3) << 17) | ((128u >> 4) << 24);
 }
 
@@ -1293,17 +1505,17 @@ constexpr int kSmemSlack = 2048;   // alignment slack + static barriers
 template <int MODE>
 int launch_tc(lnn::Device* d, dim3 grid, const CUtensorMap& ah, const CUtensorMap& al,
               const CUtensorMap& bh, const CUtensorMap& bl, TcParams& p) {
-  const int nbuf = p.passes == 3 ? 2 : 1;
+  const int nbuf = p.passes == 1 ? 1 : 2;
   const int a_sz = (p.a_tile_bytes + 1023) & ~1023;
   const int b_sz = (p.b_tile_bytes + 1023) & ~1023;
   const int unit = nbuf * (a_sz + b_sz);
   // several small units share one stage so that a barrier round trip covers enough MMAs
-  int kgroup = env_int("LNN_TC_KGROUP", 0);
+  int kgroup = knobs().kgroup;
   if (kgroup <= 0) kgroup = std::max(1, std::min(p.num_kb, (72 * 1024) / unit));
   if (MODE == MODE_DW) kgroup = 1;
   const int stage = kgroup * unit;
   p.kgroup = kgroup;
-  int stages = env_int("LNN_TC_STAGES", 0);
+  int stages = knobs().stages;
   if (stages <= 0) {
     stages = (kSmemLimit - kSmemSlack) / stage;
     if (stages > 6) stages = 6;
@@ -1312,7 +1524,7 @@ int launch_tc(lnn::Device* d, dim3 grid, const CUtensorMap& ah, const CUtensorMa
   if (stages < 1 || stages * stage + kSmemSlack > kSmemLimit)
     return lnn::set_error(LNN_E_UNSUPPORTED, "operand stage of %d bytes does not fit shared memory", stage);
   p.stages = stages;
-  p.debug = debug_bits();     // timing experiments only; results are wrong when set
+  p.debug = knobs().debug;
   p.status = d->status_dev;
   // persistent launch: the logical grid is walked by one CTA per SM
   p.grid_x = (int)grid.x; p.grid_y = (int)grid.y; p.grid_z = (int)grid.z;
@@ -1334,22 +1546,64 @@ int launch_tc(lnn::Device* d, dim3 grid, const CUtensorMap& ah, const CUtensorMa
   return LNN_OK;
 }
 
-int check_passes(int tf32_passes) {
-  LNN_REQUIRE(tf32_passes == 1 || tf32_passes == 3, "tf32_passes must be 1 or 3");
+int check_passes(int precision) {
+  LNN_REQUIRE(precision >= 1 && precision <= 3,
+              "precision must be 1 (TF32), 2 (split FP16) or 3 (split TF32)");
   return LNN_OK;
 }
 
-// Split a dense [rows][cols] matrix (per batch entry) into hi/lo scratch with padded pitch.
-int split_matrix(lnn::Device* d, lnn::Scratch& hi, lnn::Scratch& lo, const float* src,
-                 int64_t rows, int64_t cols, int64_t* pitch_out, int want_lo) {
-  const int64_t pitch = (cols + 3) & ~3ll;
-  int rc = hi.get((uint64_t)rows * pitch * 4);
-  if (rc) return rc;
-  if (want_lo) { rc = lo.get((uint64_t)rows * pitch * 4); if (rc) return rc; }
-  lnn::ProfScope prof(d, LNN_PROF_PREP);
-  split_rows_kernel<<<grid_for(d, rows * pitch / 4 + 1), kThreads, 0, d->stream>>>(
-      hi.as<float>(), want_lo ? lo.as<float>() : nullptr, src, rows, cols, pitch, want_lo);
+// Largest magnitude of `count` floats into *amax (zeroed first, on the stream).
+int launch_absmax(lnn::Device* d, uint32_t* amax, const float* src, int64_t count) {
+  LNN_CUDA(cudaMemsetAsync(amax, 0, sizeof(uint32_t), d->stream));
+  absmax_kernel<<<grid_for(d, count / 4 + 1), kThreads, 0, d->stream>>>(src, count, amax);
   LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
+}
+
+// A packed fp16 operand keeps the fp32 bit pattern of its tensor's largest magnitude in a
+// 16-byte trailer behind the hi copy.
+inline uint64_t half_trailer_offset(uint64_t elems) { return (elems * 2 + 15) & ~15ull; }
+inline uint64_t packed_hi_bytes(uint64_t elems, int precision) {
+  return precision == 2 ? half_trailer_offset(elems) + 16 : elems * 4;
+}
+inline uint64_t packed_lo_bytes(uint64_t elems, int precision) {
+  return precision == 1 ? 0 : elems * (uint64_t)esz_of(precision);
+}
+inline uint32_t* trailer_of(const void* hi, uint64_t elems) {
+  return (uint32_t*)((uint8_t*)hi + half_trailer_offset(elems));
+}
+
+// One operand of a contraction: hi / lo copies and, for the fp16 split, the largest magnitude.
+struct Operand {
+  const void* hi = nullptr; const void* lo = nullptr; const uint32_t* amax = nullptr;
+};
+
+// Split a dense [rows][cols] matrix (per batch entry) into hi/lo scratch with padded pitch
+// (in elements; rows start on 16-byte boundaries).
+int split_matrix(lnn::Device* d, lnn::Scratch& hi, lnn::Scratch& lo, Operand* op, const float* src,
+                 int64_t rows, int64_t cols, int64_t* pitch_out, int precision) {
+  const int esz = esz_of(precision);
+  const int want_lo = precision != 1;
+  const int64_t align = 16 / esz;
+  const int64_t pitch = (cols + align - 1) / align * align;
+  const uint64_t elems = (uint64_t)rows * pitch;
+  int rc = hi.get(packed_hi_bytes(elems, precision));
+  if (rc) return rc;
+  if (want_lo) { rc = lo.get(packed_lo_bytes(elems, precision)); if (rc) return rc; }
+  lnn::ProfScope prof(d, LNN_PROF_PREP);
+  if (esz == 2) {
+    uint32_t* amax = trailer_of(hi.p, elems);
+    rc = launch_absmax(d, amax, src, rows * cols);
+    if (rc) return rc;
+    split_rows_kernel<true><<<grid_for(d, rows * pitch / 4 + 1), kThreads, 0, d->stream>>>(
+        hi.as<__half>(), lo.as<__half>(), src, rows, cols, pitch, 1, amax);
+    op->amax = amax;
+  } else {
+    split_rows_kernel<false><<<grid_for(d, rows * pitch / 4 + 1), kThreads, 0, d->stream>>>(
+        hi.as<float>(), want_lo ? lo.as<float>() : nullptr, src, rows, cols, pitch, want_lo, nullptr);
+  }
+  LNN_CHECK_LAUNCH(d);
+  op->hi = hi.p; op->lo = want_lo ? lo.p : hi.p;
   *pitch_out = pitch;
   return LNN_OK;
 }
@@ -1385,42 +1639,46 @@ PixTile plan_conv_tile(int NL, int AH, int AW, int es, int maxpix) {
 
 int gcd_int(int a, int b) { while (b) { int t = a % b; a = b; b = t; } return a; }
 int chan_pad(int c) { return (c + 7) & ~7; }
-int chan_block(int cp) { return (cp % 32 == 0) ? 32 : ((cp % 16 == 0) ? 16 : 8); }
+// channels per unit: one swizzle row of 128, 64 or 32 bytes (a block wider than the padded
+// channel count is zero-filled by the TMA unit)
+int chan_block(int cp, int esz) {
+  const int full = 128 / esz;
+  return (cp % full == 0) ? full : ((cp % (full / 2) == 0) ? full / 2 : full / 4);
+}
 
 // 4-D map over an NHWC activation copy [N][H][W][cp]
-int encode_nhwc(CUtensorMap* tm, const float* base, int n, int h, int w, int cp, int box_c,
+int encode_nhwc(CUtensorMap* tm, const void* base, int esz, int n, int h, int w, int cp, int box_c,
                 int box_w, int box_h, int box_n, int estride, bool mn_major = false) {
   uint64_t dims[4] = {(uint64_t)cp, (uint64_t)w, (uint64_t)h, (uint64_t)n};
-  uint64_t str[3] = {(uint64_t)cp * 4, (uint64_t)w * cp * 4, (uint64_t)h * w * cp * 4};
+  uint64_t str[3] = {(uint64_t)cp * esz, (uint64_t)w * cp * esz, (uint64_t)h * w * cp * esz};
   uint32_t box[4] = {(uint32_t)box_c, (uint32_t)(box_w * estride), (uint32_t)(box_h * estride),
                      (uint32_t)box_n};
   uint32_t es[4] = {1, (uint32_t)estride, (uint32_t)estride, 1};
-  return encode_map(tm, base, 4, dims, str, box, es, box_c * 4, mn_major);
+  return encode_map(tm, base, esz, 4, dims, str, box, es, box_c * esz, mn_major);
 }
 
-int nhwc_split_to(lnn::Device* d, float* hi_p, float* lo_p, const float* src, int n, int c, int h,
-                  int w, int cp);
-
-int nhwc_split(lnn::Device* d, lnn::Scratch& hi, lnn::Scratch& lo, const float* src, int n, int c,
-               int h, int w, int cp, int want_lo) {
-  const uint64_t bytes = (uint64_t)n * h * w * cp * 4;
-  int rc = hi.get(bytes);
-  if (rc) return rc;
-  if (want_lo) { rc = lo.get(bytes); if (rc) return rc; }
-  return nhwc_split_to(d, hi.as<float>(), want_lo ? lo.as<float>() : nullptr, src, n, c, h, w, cp);
-}
-
-// NCHW -> channel-innermost hi (and lo when lo_p is given) copies with channel pitch cp
-int nhwc_split_to(lnn::Device* d, float* hi_p, float* lo_p, const float* src, int n, int c, int h,
-                  int w, int cp) {
+// NCHW -> channel-innermost hi (and lo when lo_p is given) copies with channel pitch cp.  For the
+// fp16 split `amax` receives the tensor's largest magnitude first (a second read of the source).
+int nhwc_split_to(lnn::Device* d, void* hi_p, void* lo_p, uint32_t* amax, const float* src, int n, int c,
+                  int h, int w, int cp, int precision) {
   const int want_lo = lo_p != nullptr;
+  const bool f16 = precision == 2;
   const int64_t hw = (int64_t)h * w;
   lnn::ProfScope prof(d, LNN_PROF_PREP);
+  if (f16) {
+    LNN_REQUIRE(amax && lo_p, "the fp16 split needs a lo buffer and a word for the largest magnitude");
+    const int rc = launch_absmax(d, amax, src, (int64_t)n * c * hw);
+    if (rc) return rc;
+  }
   if (cp == 8) {
     // few channels (the network's first layer): one thread per pixel, channel planes read
-    // coalesced, one 32-byte NHWC pixel written per thread
-    nchw_to_nhwc8_split_kernel<<<grid_for(d, (int64_t)n * hw), kThreads, 0, d->stream>>>(
-        hi_p, lo_p, src, n, c, hw, want_lo);
+    // coalesced, one NHWC pixel written per thread
+    if (f16)
+      nchw_to_nhwc8_split_kernel<true><<<grid_for(d, (int64_t)n * hw), kThreads, 0, d->stream>>>(
+          (__half*)hi_p, (__half*)lo_p, src, n, c, hw, want_lo, amax);
+    else
+      nchw_to_nhwc8_split_kernel<false><<<grid_for(d, (int64_t)n * hw), kThreads, 0, d->stream>>>(
+          (float*)hi_p, (float*)lo_p, src, n, c, hw, want_lo, nullptr);
     LNN_CHECK_LAUNCH(d);
     return LNN_OK;
   }
@@ -1428,28 +1686,74 @@ int nhwc_split_to(lnn::Device* d, float* hi_p, float* lo_p, const float* src, in
   if (vec) {
     const int64_t tiles = (int64_t)n * ((hw + 127) / 128) * ((cp + 31) / 32);
     const int64_t grid = std::min<int64_t>(tiles, (int64_t)d->sm_count * 8);
-    nchw_to_nhwc_split_vec_kernel<<<(unsigned)grid, 256, 0, d->stream>>>(hi_p, lo_p, src, n, c, hw, cp, want_lo);
+    if (f16)
+      nchw_to_nhwc_split_vec_kernel<true><<<(unsigned)grid, 256, 0, d->stream>>>(
+          (__half*)hi_p, (__half*)lo_p, src, n, c, hw, cp, want_lo, amax);
+    else
+      nchw_to_nhwc_split_vec_kernel<false><<<(unsigned)grid, 256, 0, d->stream>>>(
+          (float*)hi_p, (float*)lo_p, src, n, c, hw, cp, want_lo, nullptr);
     LNN_CHECK_LAUNCH(d);
     return LNN_OK;
   }
   const int64_t tiles = (int64_t)n * ((hw + 31) / 32) * ((cp + 31) / 32);
   int64_t grid = std::min<int64_t>(tiles, (int64_t)d->sm_count * 16);
-  nchw_to_nhwc_split_kernel<<<(unsigned)grid, 256, 0, d->stream>>>(hi_p, lo_p, src, n, c, hw, cp, want_lo);
+  if (f16)
+    nchw_to_nhwc_split_kernel<true><<<(unsigned)grid, 256, 0, d->stream>>>(
+        (__half*)hi_p, (__half*)lo_p, src, n, c, hw, cp, want_lo, amax);
+  else
+    nchw_to_nhwc_split_kernel<false><<<(unsigned)grid, 256, 0, d->stream>>>(
+        (float*)hi_p, (float*)lo_p, src, n, c, hw, cp, want_lo, nullptr);
   LNN_CHECK_LAUNCH(d);
   return LNN_OK;
 }
 
-int weights_split(lnn::Device* d, lnn::Scratch& hi, lnn::Scratch& lo, const float* w, int oc, int ic,
-                  int taps, int kp, int transpose_io, int want_lo) {
-  const int rows = transpose_io ? ic : oc;
-  const uint64_t bytes = (uint64_t)taps * rows * kp * 4;
-  int rc = hi.get(bytes);
+// Packed copies of an NCHW activation into scratch
+int nhwc_split(lnn::Device* d, lnn::Scratch& hi, lnn::Scratch& lo, Operand* op, const float* src, int n,
+               int c, int h, int w, int cp, int precision) {
+  const uint64_t elems = (uint64_t)n * h * w * cp;
+  const int want_lo = precision != 1;
+  int rc = hi.get(packed_hi_bytes(elems, precision));
   if (rc) return rc;
-  if (want_lo) { rc = lo.get(bytes); if (rc) return rc; }
+  if (want_lo) { rc = lo.get(packed_lo_bytes(elems, precision)); if (rc) return rc; }
+  uint32_t* amax = precision == 2 ? trailer_of(hi.p, elems) : nullptr;
+  rc = nhwc_split_to(d, hi.p, want_lo ? lo.p : nullptr, amax, src, n, c, h, w, cp, precision);
+  if (rc) return rc;
+  op->hi = hi.p; op->lo = want_lo ? lo.p : hi.p; op->amax = amax;
+  return LNN_OK;
+}
+
+// A caller-supplied packed activation (hi / lo copies [n][h][w][cp], see lnn_packed_bytes)
+int packed_operand(Operand* op, uint64_t hi, uint64_t lo, uint64_t elems, int precision) {
+  LNN_REQUIRE(hi, "null packed buffer");
+  LNN_REQUIRE(precision == 1 || lo, "a packed operand needs its lo copy unless precision is 1");
+  op->hi = (const void*)(uintptr_t)hi;
+  op->lo = precision == 1 ? op->hi : (const void*)(uintptr_t)lo;
+  op->amax = precision == 2 ? trailer_of(op->hi, elems) : nullptr;
+  return LNN_OK;
+}
+
+int weights_split(lnn::Device* d, lnn::Scratch& hi, lnn::Scratch& lo, Operand* op, const float* w, int oc,
+                  int ic, int taps, int kp, int transpose_io, int precision) {
+  const int rows = transpose_io ? ic : oc;
+  const int want_lo = precision != 1;
+  const uint64_t elems = (uint64_t)taps * rows * kp;
+  int rc = hi.get(packed_hi_bytes(elems, precision));
+  if (rc) return rc;
+  if (want_lo) { rc = lo.get(packed_lo_bytes(elems, precision)); if (rc) return rc; }
   lnn::ProfScope prof(d, LNN_PROF_PREP);
-  weight_split_kernel<<<grid_for(d, (int64_t)taps * rows * kp), kThreads, 0, d->stream>>>(
-      hi.as<float>(), want_lo ? lo.as<float>() : nullptr, w, oc, ic, taps, kp, transpose_io, want_lo);
+  if (precision == 2) {
+    uint32_t* amax = trailer_of(hi.p, elems);
+    rc = launch_absmax(d, amax, w, (int64_t)oc * ic * taps);
+    if (rc) return rc;
+    weight_split_kernel<true><<<grid_for(d, (int64_t)elems), kThreads, 0, d->stream>>>(
+        hi.as<__half>(), lo.as<__half>(), w, oc, ic, taps, kp, transpose_io, 1, amax);
+    op->amax = amax;
+  } else {
+    weight_split_kernel<false><<<grid_for(d, (int64_t)elems), kThreads, 0, d->stream>>>(
+        hi.as<float>(), want_lo ? lo.as<float>() : nullptr, w, oc, ic, taps, kp, transpose_io, want_lo, nullptr);
+  }
   LNN_CHECK_LAUNCH(d);
+  op->hi = hi.p; op->lo = want_lo ? lo.p : hi.p;
   return LNN_OK;
 }
 
@@ -1468,17 +1772,17 @@ int check_geom(const lnn_conv_geom* g) {
 // must fit shared memory; among the tilings that do, take the one with most real pixels per
 // MMA clock under the measured cost of one tcgen05.mma in this kernel, about max(150, 0.7 * N) clocks.
 // Optional fused pooling / packed output of the channels-on-M kernels (TcParams::ep_mode).
-struct EpiExtra { int ep_mode; float* out_lo; int ocp; };
+struct EpiExtra { int ep_mode; float* out_lo; int ocp; uint32_t* amax_out; };
 
 struct HaloPlan { bool ok; int tw, th, pw, ph, bn, sa, bbuf, acb; double px_per_clk; };
 
-HaloPlan plan_halo(int AH, int AW, int hx, int hy, int a_rows, int nbuf, int cb, bool pooled) {
+HaloPlan plan_halo(int AH, int AW, int hx, int hy, int a_rows, int nbuf, int cb, int esz, bool pooled) {
   HaloPlan best;
   memset(&best, 0, sizeof(best));
   const int budget = kSmemLimit - kSmemSlack - 1024;
   const int divs[] = {1, 2, 3, 4, 6, 8};
-  for (int acb = cb; acb >= 16; acb >>= 1) {
-    const int a_unit = nbuf * ((a_rows * acb * 4 + 1023) & ~1023);
+  for (int acb = cb; acb * esz >= 64; acb >>= 1) {
+    const int a_unit = nbuf * ((a_rows * acb * esz + 1023) & ~1023);
     const int min_sa = 3;
     for (int di = 0; di < 6; ++di) {
       int tw = (AW + divs[di] - 1) / divs[di];
@@ -1490,7 +1794,7 @@ HaloPlan plan_halo(int AH, int AW, int hx, int hy, int a_rows, int nbuf, int cb,
         const int bn = std::max(16, (th * pw + 15) & ~15);
         const int ph = th + hy;
         if (bn > 256 || ph > 256) continue;
-        const int bbuf = ((bn + hy * pw + hx) * cb * 4 + 1023) & ~1023;
+        const int bbuf = ((bn + hy * pw + hx) * cb * esz + 1023) & ~1023;
         int sa = (budget - 2 * nbuf * bbuf) / a_unit;
         if (sa < min_sa) continue;
         if (sa > 8) sa = 8;
@@ -1507,77 +1811,95 @@ HaloPlan plan_halo(int AH, int AW, int hx, int hy, int a_rows, int nbuf, int cb,
   return best;
 }
 
+// Everything a convolution-like launch needs besides the operands.
+struct ConvLaunch {
+  int NL, H, W, kp;                  // activation copy [NL][H][W][kp]
+  int wrows, wtaps;                  // kernel copy [wtaps][wrows][kp]
+  int AH, AW, es;                    // logical output grid per image, coordinate multiplier
+  int ntaps; const int *dy, *dx, *widx;
+  int OCv;
+  float* out; int64_t out_base, out_sn, out_sa, out_sb, out_sc;
+  const float* bias; int act; float alpha; int accumulate;
+  int precision;
+};
+
+void fill_common(TcParams& p, const ConvLaunch& c, const Operand& act, const Operand& w, bool act_is_b) {
+  p.passes = c.precision; p.esz = esz_of(c.precision);
+  p.ntaps = c.ntaps;
+  p.AW = c.AW; p.AH = c.AH; p.NL = c.NL; p.es = c.es;
+  p.out_sn = c.out_sn; p.out_sa = c.out_sa; p.out_sb = c.out_sb; p.out_sc = c.out_sc; p.out_base = c.out_base;
+  p.OC = c.OCv;
+  p.accumulate = c.accumulate; p.act = c.act; p.alpha = c.alpha; p.bias = c.bias; p.out = c.out;
+  p.amax_a = act_is_b ? w.amax : act.amax;
+  p.amax_b = act_is_b ? act.amax : w.amax;
+  for (int i = 0; i < c.ntaps; ++i) { p.tap_dy[i] = c.dy[i]; p.tap_dx[i] = c.dx[i]; p.tap_w[i] = c.widx[i]; }
+}
+
+int encode_weights(CUtensorMap* h, CUtensorMap* l, const Operand& w, const ConvLaunch& c, int box_k, int box_rows) {
+  const int esz = esz_of(c.precision);
+  uint64_t dims[3] = {(uint64_t)c.kp, (uint64_t)c.wrows, (uint64_t)c.wtaps};
+  uint64_t str[2] = {(uint64_t)c.kp * esz, (uint64_t)c.wrows * c.kp * esz};
+  uint32_t box[3] = {(uint32_t)box_k, (uint32_t)box_rows, 1};
+  uint32_t es1[3] = {1, 1, 1};
+  int rc = encode_map(h, w.hi, esz, 3, dims, str, box, es1, box_k * esz);
+  if (rc) return rc;
+  return encode_map(l, w.lo, esz, 3, dims, str, box, es1, box_k * esz);
+}
+
 // Unit-stride convolution through tc_halo_kernel.  Same operands as launch_conv_like with
-// es == 1 and 32-channel blocks; returns LNN_E_UNSUPPORTED (without setting an error) through
-// *taken = 0 when no tiling fits.
-int launch_conv_halo(lnn::Device* d, const float* act_hi, const float* act_lo, int NL, int H, int W,
-                     int kp, const float* w_hi, const float* w_lo, int wrows, int wtaps, int AH,
-                     int AW, int ntaps, const int* dy, const int* dx, const int* widx, int OCv,
-                     float* out, int64_t out_base, int64_t out_sn, int64_t out_sa, int64_t out_sb,
-                     int64_t out_sc, const float* bias, int act, float alpha, int accumulate,
-                     int passes, const EpiExtra* ex, int* taken) {
+// es == 1 and one swizzle row of channels per pixel; *taken = 0 (nothing launched, no error)
+// when no tiling fits or the planner prefers the per-tap kernel.
+int launch_conv_halo(lnn::Device* d, const Operand& act, const Operand& w, const ConvLaunch& c,
+                     const EpiExtra* ex, int* taken) {
   *taken = 0;
-  const int cb = 32;
+  const int esz = esz_of(c.precision);
+  const int cb = chan_block(c.kp, esz);
   const bool pooled = ex && ex->ep_mode != 0;
-  if (pooled && ((AH | AW) & 1)) return LNN_OK;
-  if (kp % cb != 0 || ntaps < 1) return LNN_OK;
-  int x0 = dx[0], x1 = dx[0], y0 = dy[0], y1 = dy[0];
-  for (int i = 1; i < ntaps; ++i) {
-    x0 = std::min(x0, dx[i]); x1 = std::max(x1, dx[i]);
-    y0 = std::min(y0, dy[i]); y1 = std::max(y1, dy[i]);
+  if (pooled && ((c.AH | c.AW) & 1)) return LNN_OK;
+  if (c.kp % cb != 0 || cb * esz < 64 || c.ntaps < 1) return LNN_OK;
+  int x0 = c.dx[0], x1 = c.dx[0], y0 = c.dy[0], y1 = c.dy[0];
+  for (int i = 1; i < c.ntaps; ++i) {
+    x0 = std::min(x0, c.dx[i]); x1 = std::max(x1, c.dx[i]);
+    y0 = std::min(y0, c.dy[i]); y1 = std::max(y1, c.dy[i]);
   }
   const int hx = x1 - x0, hy = y1 - y0;
-  const int nbuf = passes == 3 ? 2 : 1;
-  const int a_rows = std::min(128, (OCv + 7) & ~7);
-  const HaloPlan hp = plan_halo(AH, AW, hx, hy, a_rows, nbuf, cb, pooled);
+  const int nbuf = c.precision == 1 ? 1 : 2;
+  const int a_rows = std::min(128, (c.OCv + 7) & ~7);
+  const HaloPlan hp = plan_halo(c.AH, c.AW, hx, hy, a_rows, nbuf, cb, esz, pooled);
   // Both kernels turn out to be bound by shared-memory bandwidth (operand reads of the MMAs plus
   // TMA writes, about 90 bytes per clock), so the resident patch only pays where the per-tap
-  // kernel is at its worst: one tap per ring stage (32 input channels) or so few output
+  // kernel is at its worst: one tap per ring stage (a single channel block) or so few output
   // channels that it would put them on N; and only when few accumulator columns are wasted.
   if (!hp.ok) return LNN_OK;
-  if (env_int("LNN_TC_HALO", 1) != 2 && !(hp.px_per_clk >= 1.15 && (OCv < 64 || kp == 32))) return LNN_OK;
+  if (knobs().halo != 2 && !(hp.px_per_clk >= 1.15 && (c.OCv < 64 || c.kp == cb))) return LNN_OK;
 
   TcParams p;
   memset(&p, 0, sizeof(p));
-  p.mode = MODE_CONVT; p.passes = passes; p.bn = hp.bn;
-  p.swz_a = hp.acb * 4; p.swz_b = cb * 4;
-  p.a_tile_bytes = (a_rows * hp.acb * 4 + 1023) & ~1023;
-  p.a_load_bytes = a_rows * hp.acb * 4;
-  p.idesc = make_idesc(hp.bn, 0, 0);
+  fill_common(p, c, act, w, true);
+  p.mode = MODE_CONVT; p.bn = hp.bn;
+  p.swz_a = hp.acb * esz; p.swz_b = cb * esz;
+  p.a_tile_bytes = (a_rows * hp.acb * esz + 1023) & ~1023;
+  p.a_load_bytes = a_rows * hp.acb * esz;
+  p.idesc = make_idesc(hp.bn, 0, 0, esz);
   p.tmem_cols = tmem_cols_for(hp.bn);
-  p.ncb = kp / cb; p.cb = cb; p.ntaps = ntaps;
+  p.ncb = c.kp / cb; p.cb = cb;
   p.tw = hp.tw; p.th = hp.th; p.tn = 1;
-  p.tiles_b = (AW + hp.tw - 1) / hp.tw; p.tiles_a = (AH + hp.th - 1) / hp.th; p.tiles_n = NL;
-  p.AW = AW; p.AH = AH; p.NL = NL; p.es = 1;
-  p.out_sn = out_sn; p.out_sa = out_sa; p.out_sb = out_sb; p.out_sc = out_sc; p.out_base = out_base;
-  p.OC = OCv;
-  p.accumulate = accumulate; p.act = act; p.alpha = alpha; p.bias = bias; p.out = out;
-  if (pooled) { p.ep_mode = ex->ep_mode; p.out_lo = ex->out_lo; p.ocp = ex->ocp; }
+  p.tiles_b = (c.AW + hp.tw - 1) / hp.tw; p.tiles_a = (c.AH + hp.th - 1) / hp.th; p.tiles_n = c.NL;
+  if (pooled) { p.ep_mode = ex->ep_mode; p.out_lo = ex->out_lo; p.ocp = ex->ocp; p.amax_out = ex->amax_out; }
   p.h_pw = hp.pw; p.h_ph = hp.ph; p.h_x0 = x0; p.h_y0 = y0; p.h_arows = a_rows; p.h_acb = hp.acb;
   p.h_sa = hp.sa; p.h_sb = 2; p.h_bbuf = hp.bbuf;
-  p.debug = debug_bits();     // timing experiments only; results are wrong when set
-  for (int i = 0; i < ntaps; ++i) {
-    p.tap_dy[i] = dy[i]; p.tap_dx[i] = dx[i]; p.tap_w[i] = widx[i];
-    p.tap_shift[i] = (dy[i] - y0) * hp.pw + (dx[i] - x0);
-  }
+  p.debug = knobs().debug;
+  for (int i = 0; i < c.ntaps; ++i) p.tap_shift[i] = (c.dy[i] - y0) * hp.pw + (c.dx[i] - x0);
   p.status = d->status_dev;
   CUtensorMap act_h, act_l, w_h, w_l;
-  int rc = encode_nhwc(&act_h, act_hi, NL, H, W, kp, cb, hp.pw, hp.ph, 1, 1);
+  int rc = encode_nhwc(&act_h, act.hi, esz, c.NL, c.H, c.W, c.kp, cb, hp.pw, hp.ph, 1, 1);
   if (rc) return rc;
-  rc = encode_nhwc(&act_l, passes == 3 ? act_lo : act_hi, NL, H, W, kp, cb, hp.pw, hp.ph, 1, 1);
+  rc = encode_nhwc(&act_l, act.lo, esz, c.NL, c.H, c.W, c.kp, cb, hp.pw, hp.ph, 1, 1);
   if (rc) return rc;
-  {
-    uint64_t dims[3] = {(uint64_t)kp, (uint64_t)wrows, (uint64_t)wtaps};
-    uint64_t str[2] = {(uint64_t)kp * 4, (uint64_t)wrows * kp * 4};
-    uint32_t box[3] = {(uint32_t)hp.acb, (uint32_t)a_rows, 1};
-    uint32_t es1[3] = {1, 1, 1};
-    rc = encode_map(&w_h, w_hi, 3, dims, str, box, es1, hp.acb * 4);
-    if (rc) return rc;
-    rc = encode_map(&w_l, passes == 3 ? w_lo : w_hi, 3, dims, str, box, es1, hp.acb * 4);
-    if (rc) return rc;
-  }
+  rc = encode_weights(&w_h, &w_l, w, c, hp.acb, a_rows);
+  if (rc) return rc;
   const int64_t ptiles = (int64_t)p.tiles_b * p.tiles_a * p.tiles_n;
-  const int64_t mtiles = (OCv + 127) / 128;
+  const int64_t mtiles = (c.OCv + 127) / 128;
   LNN_REQUIRE(ptiles * mtiles < (1ll << 31), "too many tiles");
   p.grid_x = (int)ptiles; p.grid_y = (int)mtiles; p.grid_z = 1;
   const int smem = p.h_sa * nbuf * p.a_tile_bytes + p.h_sb * nbuf * p.h_bbuf + 1024;
@@ -1596,98 +1918,83 @@ int launch_conv_halo(lnn::Device* d, const float* act_hi, const float* act_lo, i
   return LNN_OK;
 }
 
-// Shared launcher of the "pixels on M" implicit GEMM (forward and input gradient).
-// act_hi/lo: NHWC copy [NL][H][W][kp]; w_hi/lo: [taps][rows][kp]; the logical output grid is
-// AH x AW per image; tap t reads the activation at (a*es + dy[t], b*es + dx[t]).
-int launch_conv_like(lnn::Device* d, const float* act_hi, const float* act_lo, int NL, int H, int W,
-                     int kp, const float* w_hi, const float* w_lo, int wrows, int wtaps, int AH,
-                     int AW, int es, int ntaps, const int* dy, const int* dx, const int* widx,
-                     int OCv, float* out, int64_t out_base, int64_t out_sn, int64_t out_sa,
-                     int64_t out_sb, int64_t out_sc, const float* bias, int act, float alpha,
-                     int accumulate, int passes, const EpiExtra* ex = nullptr, int* fused = nullptr) {
+// Shared launcher of the implicit GEMM (forward and input gradient): tap t reads the
+// activation at (a*es + dy[t], b*es + dx[t]) for output pixel (a, b) of the logical grid.
+int launch_conv_like(lnn::Device* d, const Operand& act, const Operand& w, const ConvLaunch& c,
+                     const EpiExtra* ex = nullptr, int* fused = nullptr) {
   // ex (fused pool / packed output) can only be honoured by the channels-on-M kernels with a
   // suitable tiling; *fused tells the caller whether it was (nothing is launched when not)
   const bool pooled = ex && ex->ep_mode != 0;
+  const int esz = esz_of(c.precision);
   if (fused) *fused = 0;
-  if (es == 1 && env_int("LNN_TC_HALO", 1) != 0) {
+  if (c.es == 1 && knobs().halo != 0) {
     int taken = 0;
-    const int rc = launch_conv_halo(d, act_hi, act_lo, NL, H, W, kp, w_hi, w_lo, wrows, wtaps, AH, AW,
-                                    ntaps, dy, dx, widx, OCv, out, out_base, out_sn, out_sa, out_sb,
-                                    out_sc, bias, act, alpha, accumulate, passes, ex, &taken);
+    const int rc = launch_conv_halo(d, act, w, c, ex, &taken);
     if (rc) return rc;
     if (taken) { if (fused) *fused = 1; return LNN_OK; }
   }
-  int cb = chan_block(kp);
+  int cb = chan_block(c.kp, esz);
   {
-    const int cb_env = env_int("LNN_TC_CB", 0);          // tuning: channels per unit (8/16/32)
-    if ((cb_env == 8 || cb_env == 16) && cb_env < cb) cb = cb_env;
+    const int cb_env = knobs().cb;                       // tuning: channels per unit
+    if (cb_env > 0 && cb_env < cb && (cb_env * esz == 32 || cb_env * esz == 64)) cb = cb_env;
   }
-  const int swz = cb * 4;
+  const int swz = cb * esz;
   // Orientation.  A tcgen05.mma costs about max(90, 0.7 * N) clocks whatever M carries, so the
   // wide operand should sit on N: with more than a few output channels the pixel patch (up to
   // 256 pixels) goes on N and the channels on M ("channels on M", MODE_CONVT); with very few
   // output channels the pixels go on M and the channels on N.
-  int orient = env_int("LNN_TC_ORIENT", 0);     // 1 = pixels on M, 2 = channels on M
-  if (orient == 0) orient = (OCv >= 64 && OCv <= 128) ? 2 : 1;
+  int orient = knobs().orient;
+  if (orient == 0) orient = (c.OCv >= 64 && c.OCv <= 128) ? 2 : 1;
   const bool chan_m = orient == 2;
-  PixTile t = plan_conv_tile(NL, AH, AW, es, chan_m ? 256 : 128);
+  PixTile t = plan_conv_tile(c.NL, c.AH, c.AW, c.es, chan_m ? 256 : 128);
   if (pooled) {
     // 32-column chunks must be pieces of one image row, rows must come in pairs
-    if (!chan_m || es != 1 || (t.tw & 31) || (t.th & 1) || ((AH | AW) & 1)) return LNN_OK;
+    if (!chan_m || c.es != 1 || (t.tw & 31) || (t.th & 1) || ((c.AH | c.AW) & 1)) return LNN_OK;
   }
   const int pix = t.tn * t.th * t.tw;
   int bn;
   if (chan_m) {
     bn = std::max(16, (pix + 15) & ~15);
   } else {
-    bn = std::min(256, (OCv + 15) & ~15);
-    const int bn_env = env_int("LNN_TC_BN", 0);
+    bn = std::min(256, (c.OCv + 15) & ~15);
+    const int bn_env = knobs().bn;
     if (bn_env >= 16 && bn_env <= 256 && bn_env % 16 == 0) bn = std::min(bn, bn_env);
   }
   TcParams p;
   memset(&p, 0, sizeof(p));
-  p.mode = chan_m ? MODE_CONVT : MODE_CONV; p.passes = passes; p.bn = bn;
+  fill_common(p, c, act, w, chan_m);
+  p.mode = chan_m ? MODE_CONVT : MODE_CONV; p.bn = bn;
   p.a_major = 0; p.b_major = 0; p.swz_a = swz; p.swz_b = swz;
-  p.ksteps = cb / 8;
+  p.ksteps = swz / 32;
   p.a_tile_bytes = 128 * swz; p.b_tile_bytes = bn * swz;
   p.a_loads = 1; p.b_loads = 1;
   if (chan_m) { p.a_load_bytes = 128 * swz; p.b_load_bytes = pix * swz; }
   else { p.a_load_bytes = pix * swz; p.b_load_bytes = bn * swz; }
-  p.idesc = make_idesc(bn, 0, 0);
+  p.idesc = make_idesc(bn, 0, 0, esz);
   p.tmem_cols = tmem_cols_for(bn);
-  p.ncb = kp / cb; p.cb = cb; p.ntaps = ntaps;
-  p.num_kb = ntaps * p.ncb;
+  p.ncb = (c.kp + cb - 1) / cb; p.cb = cb;
+  p.num_kb = c.ntaps * p.ncb;
   p.tw = t.tw; p.th = t.th; p.tn = t.tn;
   p.tiles_b = t.tiles_b; p.tiles_a = t.tiles_a; p.tiles_n = t.tiles_n;
-  p.AW = AW; p.AH = AH; p.NL = NL; p.es = es;
   p.rows_valid = pix;
-  p.out_sn = out_sn; p.out_sa = out_sa; p.out_sb = out_sb; p.out_sc = out_sc; p.out_base = out_base;
-  p.OC = OCv;
-  p.accumulate = accumulate; p.act = act; p.alpha = alpha; p.bias = bias; p.out = out;
-  if (pooled) { p.ep_mode = ex->ep_mode; p.out_lo = ex->out_lo; p.ocp = ex->ocp; if (fused) *fused = 1; }
-  for (int i = 0; i < ntaps; ++i) { p.tap_dy[i] = dy[i]; p.tap_dx[i] = dx[i]; p.tap_w[i] = widx[i]; }
-  CUtensorMap act_h, act_l, w_h, w_l;
-  int rc = encode_nhwc(&act_h, act_hi, NL, H, W, kp, cb, t.tw, t.th, t.tn, es);
-  if (rc) return rc;
-  rc = encode_nhwc(&act_l, passes == 3 ? act_lo : act_hi, NL, H, W, kp, cb, t.tw, t.th, t.tn, es);
-  if (rc) return rc;
-  {
-    uint64_t dims[3] = {(uint64_t)kp, (uint64_t)wrows, (uint64_t)wtaps};
-    uint64_t str[2] = {(uint64_t)kp * 4, (uint64_t)wrows * kp * 4};
-    uint32_t box[3] = {(uint32_t)cb, (uint32_t)(chan_m ? 128 : bn), 1};
-    uint32_t es1[3] = {1, 1, 1};
-    rc = encode_map(&w_h, w_hi, 3, dims, str, box, es1, swz);
-    if (rc) return rc;
-    rc = encode_map(&w_l, passes == 3 ? w_lo : w_hi, 3, dims, str, box, es1, swz);
-    if (rc) return rc;
+  if (pooled) {
+    p.ep_mode = ex->ep_mode; p.out_lo = ex->out_lo; p.ocp = ex->ocp; p.amax_out = ex->amax_out;
+    if (fused) *fused = 1;
   }
+  CUtensorMap act_h, act_l, w_h, w_l;
+  int rc = encode_nhwc(&act_h, act.hi, esz, c.NL, c.H, c.W, c.kp, cb, t.tw, t.th, t.tn, c.es);
+  if (rc) return rc;
+  rc = encode_nhwc(&act_l, act.lo, esz, c.NL, c.H, c.W, c.kp, cb, t.tw, t.th, t.tn, c.es);
+  if (rc) return rc;
+  rc = encode_weights(&w_h, &w_l, w, c, cb, chan_m ? 128 : bn);
+  if (rc) return rc;
   const int64_t ptiles = (int64_t)t.tiles_b * t.tiles_a * t.tiles_n;
   LNN_REQUIRE(ptiles < (1ll << 31), "too many pixel tiles");
   if (chan_m) {
-    dim3 grid((unsigned)ptiles, (unsigned)((OCv + 127) / 128), 1);
+    dim3 grid((unsigned)ptiles, (unsigned)((c.OCv + 127) / 128), 1);
     return launch_tc<MODE_CONVT>(d, grid, w_h, w_l, act_h, act_l, p);
   }
-  dim3 grid((unsigned)ptiles, (unsigned)((OCv + bn - 1) / bn), 1);
+  dim3 grid((unsigned)ptiles, (unsigned)((c.OCv + bn - 1) / bn), 1);
   return launch_tc<MODE_CONV>(d, grid, act_h, act_l, w_h, w_l, p);
 }
 
@@ -1704,34 +2011,39 @@ int lnn_gemm_f32(int dev, uint64_t C, uint64_t A, uint64_t B, uint64_t bias, int
   LNN_REQUIRE(batch < 65536, "batch too large");
   int rc = check_passes(tf32_passes);
   if (rc) return rc;
-  const int want_lo = tf32_passes == 3;
+  const int esz = esz_of(tf32_passes);
   // A is stored [m][k] (K-major) or [k][m] (MN-major); same for B with n.
   const int64_t a_rows = trans_a ? k : m, a_cols = trans_a ? m : k;
   const int64_t b_rows = trans_b ? n : k, b_cols = trans_b ? k : n;
   lnn::Scratch ah(d), al(d), bh(d), bl(d);
+  Operand oa, ob;
   int64_t a_pitch, b_pitch;
-  rc = split_matrix(d, ah, al, (const float*)(uintptr_t)A, batch * a_rows, a_cols, &a_pitch, want_lo);
+  rc = split_matrix(d, ah, al, &oa, (const float*)(uintptr_t)A, batch * a_rows, a_cols, &a_pitch, tf32_passes);
   if (rc) return rc;
-  rc = split_matrix(d, bh, bl, (const float*)(uintptr_t)B, batch * b_rows, b_cols, &b_pitch, want_lo);
+  rc = split_matrix(d, bh, bl, &ob, (const float*)(uintptr_t)B, batch * b_rows, b_cols, &b_pitch, tf32_passes);
   if (rc) return rc;
 
-  int bn = (int)std::min<int64_t>(256, (n + 31) & ~31ll);
-  const int bn_env = env_int("LNN_TC_BN", 0);
-  if (bn_env >= 32 && bn_env <= 256 && bn_env % 32 == 0) bn = std::min(bn, bn_env);
+  // one unit = one 128-byte swizzle row of K: 32 tf32 or 64 fp16 elements; an MN-major operand
+  // is loaded as boxes of one such row along MN by `kunit` k-rows
+  const int e128 = 128 / esz;
+  int bn = (int)std::min<int64_t>(256, (n + e128 - 1) / e128 * e128);
+  const int bn_env = knobs().bn;
+  if (bn_env >= e128 && bn_env <= 256 && bn_env % e128 == 0) bn = std::min(bn, bn_env);
   TcParams p;
   memset(&p, 0, sizeof(p));
-  p.mode = MODE_GEMM; p.passes = tf32_passes; p.bn = bn;
+  p.mode = MODE_GEMM; p.passes = tf32_passes; p.esz = esz; p.bn = bn;
+  p.amax_a = oa.amax; p.amax_b = ob.amax;
   p.a_major = trans_a ? 1 : 0;
   p.b_major = trans_b ? 0 : 1;
-  p.swz_a = 128; p.swz_b = 128; p.ksteps = 4;
+  p.swz_a = 128; p.swz_b = 128; p.ksteps = 4; p.kunit = e128;
   p.a_tile_bytes = 128 * 128; p.b_tile_bytes = bn * 128;
   if (p.a_major == 0) { p.a_loads = 1; p.a_load_bytes = 128 * 128; }
-  else { p.a_loads = 4; p.a_load_bytes = 32 * 128; p.a_krows = 32; }
+  else { p.a_loads = 128 / e128; p.a_load_bytes = e128 * 128; p.a_krows = e128; }
   if (p.b_major == 0) { p.b_loads = 1; p.b_load_bytes = bn * 128; }
-  else { p.b_loads = bn / 32; p.b_load_bytes = 32 * 128; p.b_krows = 32; }
-  p.idesc = make_idesc(bn, p.a_major, p.b_major);
+  else { p.b_loads = bn / e128; p.b_load_bytes = e128 * 128; p.b_krows = e128; }
+  p.idesc = make_idesc(bn, p.a_major, p.b_major, esz);
   p.tmem_cols = tmem_cols_for(bn);
-  p.num_kb = (int)((k + 31) / 32);
+  p.num_kb = (int)((k + e128 - 1) / e128);
   p.M = m; p.N = n; p.ldc = n; p.batch_stride_c = m * n;
   p.accumulate = accumulate; p.act = 0; p.alpha = 0.0f;
   p.bias = (const float*)(uintptr_t)bias;
@@ -1741,22 +2053,22 @@ int lnn_gemm_f32(int dev, uint64_t C, uint64_t A, uint64_t B, uint64_t bias, int
   {
     // innermost-first dims: (cols, rows, batch)
     uint64_t dims[3] = {(uint64_t)a_cols, (uint64_t)a_rows, (uint64_t)batch};
-    uint64_t str[2] = {(uint64_t)a_pitch * 4, (uint64_t)a_rows * a_pitch * 4};
-    uint32_t box[3] = {32, (uint32_t)(p.a_major ? 32 : 128), 1};
+    uint64_t str[2] = {(uint64_t)a_pitch * esz, (uint64_t)a_rows * a_pitch * esz};
+    uint32_t box[3] = {(uint32_t)e128, (uint32_t)(p.a_major ? e128 : 128), 1};
     uint32_t es[3] = {1, 1, 1};
-    rc = encode_map(&mah, ah.p, 3, dims, str, box, es, 128, p.a_major != 0);
+    rc = encode_map(&mah, oa.hi, esz, 3, dims, str, box, es, 128, p.a_major != 0);
     if (rc) return rc;
-    rc = encode_map(&mal, want_lo ? al.p : ah.p, 3, dims, str, box, es, 128, p.a_major != 0);
+    rc = encode_map(&mal, oa.lo, esz, 3, dims, str, box, es, 128, p.a_major != 0);
     if (rc) return rc;
   }
   {
     uint64_t dims[3] = {(uint64_t)b_cols, (uint64_t)b_rows, (uint64_t)batch};
-    uint64_t str[2] = {(uint64_t)b_pitch * 4, (uint64_t)b_rows * b_pitch * 4};
-    uint32_t box[3] = {32, (uint32_t)(p.b_major ? 32 : bn), 1};
+    uint64_t str[2] = {(uint64_t)b_pitch * esz, (uint64_t)b_rows * b_pitch * esz};
+    uint32_t box[3] = {(uint32_t)e128, (uint32_t)(p.b_major ? e128 : bn), 1};
     uint32_t es[3] = {1, 1, 1};
-    rc = encode_map(&mbh, bh.p, 3, dims, str, box, es, 128, p.b_major != 0);
+    rc = encode_map(&mbh, ob.hi, esz, 3, dims, str, box, es, 128, p.b_major != 0);
     if (rc) return rc;
-    rc = encode_map(&mbl, want_lo ? bl.p : bh.p, 3, dims, str, box, es, 128, p.b_major != 0);
+    rc = encode_map(&mbl, ob.lo, esz, 3, dims, str, box, es, 128, p.b_major != 0);
     if (rc) return rc;
   }
   dim3 grid((unsigned)((m + 127) / 128), (unsigned)((n + bn - 1) / bn), (unsigned)batch);
@@ -1765,6 +2077,17 @@ int lnn_gemm_f32(int dev, uint64_t C, uint64_t A, uint64_t B, uint64_t bias, int
 
 int lnn_pool2d_fwd(int dev, int mode, uint64_t O, uint64_t I, int64_t n, int64_t c, int ih, int iw,
                    int oh, int ow, int pool, int stride, int padl, int padt);
+
+int lnn_packed_bytes(int64_t n, int64_t c, int64_t h, int64_t w, int tf32_passes, uint64_t* hi_bytes,
+                     uint64_t* lo_bytes) {
+  int rc = check_passes(tf32_passes);
+  if (rc) return rc;
+  LNN_REQUIRE(n > 0 && c > 0 && h > 0 && w > 0 && hi_bytes && lo_bytes, "bad arguments");
+  const uint64_t elems = (uint64_t)n * h * w * chan_pad((int)c);
+  *hi_bytes = packed_hi_bytes(elems, tf32_passes);
+  *lo_bytes = packed_lo_bytes(elems, tf32_passes);
+  return LNN_OK;
+}
 
 }  // extern "C"
 
@@ -1777,44 +2100,74 @@ struct FwdOpts {
   int out_packed = 0;    // Y / y_lo receive such copies of the result instead of the NCHW tensor
 };
 
+// fp32 channel-innermost tensor (its largest magnitude already in the trailer of `hi`) -> fp16 copies
+int half_split_packed(lnn::Device* d, void* hi, void* lo, const float* src, uint64_t elems) {
+  lnn::ProfScope prof(d, LNN_PROF_PREP);
+  half_split_kernel<<<grid_for(d, (int64_t)(elems / 8)), kThreads, 0, d->stream>>>(
+      (__half*)hi, (__half*)lo, src, (int64_t)(elems / 8), trailer_of(hi, elems));
+  LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
+}
+
 // conv2D forward with the optional fusions.  Whatever cannot be fused into the convolution's
 // epilogue (odd sizes, tilings that do not pair rows, the pixels-on-M orientation) runs as the
 // separate pooling / repacking kernels, so every combination of options is always available.
 int conv_fwd_impl(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint64_t W, uint64_t bias,
-                  int act, float alpha, int accumulate, int tf32_passes, const FwdOpts& o) {
+                  int act, float alpha, int accumulate, int precision, const FwdOpts& o) {
   LNN_DEV(d, dev);
   int rc = check_geom(g);
   if (rc) return rc;
-  rc = check_passes(tf32_passes);
+  rc = check_passes(precision);
   if (rc) return rc;
   LNN_REQUIRE(Y && X && W, "null buffer");
   LNN_REQUIRE(act == 0 || act == 1, "unknown activation %d", act);
   LNN_REQUIRE(!(accumulate && (o.pool || o.out_packed)), "accumulate cannot be combined with pool / packed output");
-  const int want_lo = tf32_passes == 3;
-  LNN_REQUIRE(!o.in_packed || !want_lo || o.x_lo, "packed input needs its lo copy for split TF32");
+  const int want_lo = precision != 1;
+  const bool f16 = precision == 2;
+  LNN_REQUIRE(!o.out_packed || !want_lo || o.y_lo, "packed output needs a lo buffer unless precision is 1");
   const float* biasp = (const float*)(uintptr_t)bias;
   const int oh_p = o.pool ? (g->oh + 1) / 2 : g->oh, ow_p = o.pool ? (g->ow + 1) / 2 : g->ow;
   const int ocp = chan_pad(g->oc);
+  const uint64_t out_elems = (uint64_t)g->n * oh_p * ow_p * ocp;   // of a packed result
+  float* const y_lo = want_lo ? (float*)(uintptr_t)o.y_lo : nullptr;
 
-  if (!o.in_packed && lnn::conv_direct_applicable(g) && env_int("LNN_CONV_DIRECT", 1) &&
-      (!o.out_packed || o.pool))
+  // fp16 packed output: the kernels write the fp32 channel-innermost result and its largest
+  // magnitude, then one element-wise pass splits it (the scale must be known before the split)
+  lnn::Scratch raw(d);
+  auto raw_target = [&](float** dst, uint32_t** amax) -> int {
+    int r = raw.get(out_elems * 4);
+    if (r) return r;
+    *dst = raw.as<float>();
+    *amax = trailer_of((void*)(uintptr_t)Y, out_elems);
+    LNN_CUDA(cudaMemsetAsync(*amax, 0, sizeof(uint32_t), d->stream));
+    return LNN_OK;
+  };
+
+  if (!o.in_packed && lnn::conv_direct_applicable(g) && knobs().direct && (!o.out_packed || o.pool)) {
+    if (o.out_packed && f16) {
+      float* dst; uint32_t* amax;
+      rc = raw_target(&dst, &amax);
+      if (rc) return rc;
+      rc = lnn::conv_direct_fwd(d, g, dst, (const float*)(uintptr_t)X, (const float*)(uintptr_t)W, biasp, act,
+                                alpha, 0, o.pool, 2, (float*)amax, ocp);
+      if (rc) return rc;
+      return half_split_packed(d, (void*)(uintptr_t)Y, y_lo, dst, out_elems);
+    }
     return lnn::conv_direct_fwd(d, g, (float*)(uintptr_t)Y, (const float*)(uintptr_t)X,
                                 (const float*)(uintptr_t)W, biasp, act, alpha, accumulate, o.pool,
-                                o.out_packed ? 1 : 0, (float*)(uintptr_t)o.y_lo, ocp);
+                                o.out_packed ? 1 : 0, y_lo, ocp);
+  }
 
   const int cp = chan_pad(g->ic);
   const int taps = g->kh * g->kw;
   lnn::Scratch xh(d), xl(d), wh(d), wl(d);
-  const float *x_hi, *x_lo;
-  if (o.in_packed) {
-    x_hi = (const float*)(uintptr_t)X;
-    x_lo = want_lo ? (const float*)(uintptr_t)o.x_lo : x_hi;
-  } else {
-    rc = nhwc_split(d, xh, xl, (const float*)(uintptr_t)X, g->n, g->ic, g->ih, g->iw, cp, want_lo);
-    if (rc) return rc;
-    x_hi = xh.as<float>(); x_lo = xl.as<float>();
-  }
-  rc = weights_split(d, wh, wl, (const float*)(uintptr_t)W, g->oc, g->ic, taps, cp, 0, want_lo);
+  Operand ox, ow;
+  if (o.in_packed)
+    rc = packed_operand(&ox, X, o.x_lo, (uint64_t)g->n * g->ih * g->iw * cp, precision);
+  else
+    rc = nhwc_split(d, xh, xl, &ox, (const float*)(uintptr_t)X, g->n, g->ic, g->ih, g->iw, cp, precision);
+  if (rc) return rc;
+  rc = weights_split(d, wh, wl, &ow, (const float*)(uintptr_t)W, g->oc, g->ic, taps, cp, 0, precision);
   if (rc) return rc;
   int dy[kMaxTaps], dx[kMaxTaps], wi[kMaxTaps];
   for (int kh = 0; kh < g->kh; ++kh)
@@ -1825,21 +2178,39 @@ int conv_fwd_impl(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint6
       wi[t] = t;
     }
   const int64_t plane = (int64_t)g->oh * g->ow;
+  ConvLaunch c;
+  memset(&c, 0, sizeof(c));
+  c.NL = g->n; c.H = g->ih; c.W = g->iw; c.kp = cp; c.wrows = g->oc; c.wtaps = taps;
+  c.AH = g->oh; c.AW = g->ow; c.es = g->stride; c.ntaps = taps; c.dy = dy; c.dx = dx; c.widx = wi;
+  c.OCv = g->oc; c.bias = biasp; c.act = act; c.alpha = alpha; c.precision = precision;
   if (o.pool && g->stride == 1) {
-    // try the fused epilogue: pooled NCHW (ep_mode 1) or pooled, packed (ep_mode 2)
-    EpiExtra ex{o.out_packed ? 2 : 1, want_lo ? (float*)(uintptr_t)o.y_lo : nullptr, ocp};
+    // try the fused epilogue: pooled NCHW (ep_mode 1) or pooled, channel-innermost (2: tf32 hi/lo
+    // written directly, 3: fp32 + largest magnitude for the fp16 split)
     const int64_t pplane = (int64_t)oh_p * ow_p;
+    EpiExtra ex{1, nullptr, ocp, nullptr};
+    ConvLaunch cf = c;
+    cf.es = 1; cf.accumulate = 0; cf.out_base = 0;
+    if (o.out_packed) {
+      cf.out = (float*)(uintptr_t)Y;
+      if (f16) {
+        ex.ep_mode = 3;
+        rc = raw_target(&cf.out, &ex.amax_out);
+        if (rc) return rc;
+      } else {
+        ex.ep_mode = 2; ex.out_lo = y_lo;
+      }
+      cf.out_sn = pplane * ocp; cf.out_sa = (int64_t)ow_p * ocp; cf.out_sb = ocp; cf.out_sc = 1;
+    } else {
+      cf.out = (float*)(uintptr_t)Y;
+      cf.out_sn = (int64_t)g->oc * pplane; cf.out_sa = ow_p; cf.out_sb = 1; cf.out_sc = pplane;
+    }
     int fused = 0;
-    if (o.out_packed)
-      rc = launch_conv_like(d, x_hi, x_lo, g->n, g->ih, g->iw, cp, wh.as<float>(), wl.as<float>(), g->oc, taps,
-                            g->oh, g->ow, 1, taps, dy, dx, wi, g->oc, (float*)(uintptr_t)Y, 0,
-                            pplane * ocp, (int64_t)ow_p * ocp, ocp, 1, biasp, act, alpha, 0, tf32_passes, &ex, &fused);
-    else
-      rc = launch_conv_like(d, x_hi, x_lo, g->n, g->ih, g->iw, cp, wh.as<float>(), wl.as<float>(), g->oc, taps,
-                            g->oh, g->ow, 1, taps, dy, dx, wi, g->oc, (float*)(uintptr_t)Y, 0,
-                            (int64_t)g->oc * pplane, ow_p, 1, pplane, biasp, act, alpha, 0, tf32_passes, &ex, &fused);
+    rc = launch_conv_like(d, ox, ow, cf, &ex, &fused);
     if (rc) return rc;
-    if (fused) return LNN_OK;
+    if (fused) {
+      if (o.out_packed && f16) return half_split_packed(d, (void*)(uintptr_t)Y, y_lo, cf.out, out_elems);
+      return LNN_OK;
+    }
   }
   // un-fused: convolution into its NCHW result (scratch when more steps follow)
   lnn::Scratch conv_out(d), pool_out(d);
@@ -1849,9 +2220,9 @@ int conv_fwd_impl(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint6
     if (rc) return rc;
     ydst = conv_out.as<float>();
   }
-  rc = launch_conv_like(d, x_hi, x_lo, g->n, g->ih, g->iw, cp, wh.as<float>(), wl.as<float>(), g->oc, taps,
-                        g->oh, g->ow, g->stride, taps, dy, dx, wi, g->oc, ydst, 0, (int64_t)g->oc * plane,
-                        g->ow, 1, plane, biasp, act, alpha, accumulate, tf32_passes);
+  c.out = ydst; c.out_base = 0; c.out_sn = (int64_t)g->oc * plane; c.out_sa = g->ow; c.out_sb = 1; c.out_sc = plane;
+  c.accumulate = accumulate;
+  rc = launch_conv_like(d, ox, ow, c);
   if (rc) return rc;
   const float* cur = ydst;
   if (o.pool) {
@@ -1867,8 +2238,8 @@ int conv_fwd_impl(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint6
     cur = pdst;
   }
   if (o.out_packed)
-    return nhwc_split_to(d, (float*)(uintptr_t)Y, want_lo ? (float*)(uintptr_t)o.y_lo : nullptr, cur, g->n,
-                         g->oc, oh_p, ow_p, ocp);
+    return nhwc_split_to(d, (void*)(uintptr_t)Y, y_lo, f16 ? trailer_of((void*)(uintptr_t)Y, out_elems) : nullptr,
+                         cur, g->n, g->oc, oh_p, ow_p, ocp, precision);
   return LNN_OK;
 }
 
@@ -1893,16 +2264,21 @@ int lnn_conv2d_fwd_packed(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t 
                           int in_packed, int out_packed, int tf32_passes) {
   FwdOpts o;
   o.y_lo = Y_lo; o.x_lo = X_lo; o.pool = pool; o.in_packed = in_packed; o.out_packed = out_packed;
-  LNN_REQUIRE(!out_packed || tf32_passes == 1 || Y_lo, "packed output needs a lo buffer for split TF32");
   return conv_fwd_impl(dev, g, Y, X, W, bias, act, alpha, 0, tf32_passes, o);
 }
 
-int lnn_nhwc_split(int dev, uint64_t hi, uint64_t lo, uint64_t X, int n, int c, int h, int w) {
+int lnn_nhwc_split(int dev, uint64_t hi, uint64_t lo, uint64_t X, int n, int c, int h, int w, int tf32_passes) {
   LNN_DEV(d, dev);
   LNN_REQUIRE(hi && X, "null buffer");
   LNN_REQUIRE(n > 0 && c > 0 && h > 0 && w > 0, "bad extents");
-  return nhwc_split_to(d, (float*)(uintptr_t)hi, (float*)(uintptr_t)lo, (const float*)(uintptr_t)X, n, c, h,
-                       w, chan_pad(c));
+  int rc = check_passes(tf32_passes);
+  if (rc) return rc;
+  LNN_REQUIRE(tf32_passes == 1 || lo, "the lo buffer is required unless precision is 1");
+  const int cp = chan_pad(c);
+  void* hp = (void*)(uintptr_t)hi;
+  return nhwc_split_to(d, hp, tf32_passes == 1 ? nullptr : (void*)(uintptr_t)lo,
+                       tf32_passes == 2 ? trailer_of(hp, (uint64_t)n * h * w * cp) : nullptr,
+                       (const float*)(uintptr_t)X, n, c, h, w, cp, tf32_passes);
 }
 
 }  // extern "C"
@@ -1911,29 +2287,24 @@ namespace {
 
 // dX += ...; dY is NCHW (dy_lo == 0, dy_packed == 0) or the packed hi / lo copies
 int conv_dx_impl(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY, uint64_t dY_lo, int dy_packed,
-                 uint64_t W, int tf32_passes) {
+                 uint64_t W, int precision) {
   LNN_DEV(d, dev);
   int rc = check_geom(g);
   if (rc) return rc;
-  rc = check_passes(tf32_passes);
+  rc = check_passes(precision);
   if (rc) return rc;
   LNN_REQUIRE(dX && dY && W, "null buffer");
-  const int want_lo = tf32_passes == 3;
-  LNN_REQUIRE(!dy_packed || !want_lo || dY_lo, "packed dY needs its lo copy for split TF32");
   const int ocp = chan_pad(g->oc);
   const int taps = g->kh * g->kw;
   const int s = g->stride;
   lnn::Scratch yh(d), yl(d), wh(d), wl(d);
-  const float *y_hi, *y_lo;
-  if (dy_packed) {
-    y_hi = (const float*)(uintptr_t)dY;
-    y_lo = want_lo ? (const float*)(uintptr_t)dY_lo : y_hi;
-  } else {
-    rc = nhwc_split(d, yh, yl, (const float*)(uintptr_t)dY, g->n, g->oc, g->oh, g->ow, ocp, want_lo);
-    if (rc) return rc;
-    y_hi = yh.as<float>(); y_lo = yl.as<float>();
-  }
-  rc = weights_split(d, wh, wl, (const float*)(uintptr_t)W, g->oc, g->ic, taps, ocp, 1, want_lo);
+  Operand oy, ow;
+  if (dy_packed)
+    rc = packed_operand(&oy, dY, dY_lo, (uint64_t)g->n * g->oh * g->ow * ocp, precision);
+  else
+    rc = nhwc_split(d, yh, yl, &oy, (const float*)(uintptr_t)dY, g->n, g->oc, g->oh, g->ow, ocp, precision);
+  if (rc) return rc;
+  rc = weights_split(d, wh, wl, &ow, (const float*)(uintptr_t)W, g->oc, g->ic, taps, ocp, 1, precision);
   if (rc) return rc;
   const int64_t plane = (int64_t)g->ih * g->iw;
   // One launch per residue class (ih % s, iw % s): within a class every tap that reaches an
@@ -1956,11 +2327,14 @@ int conv_dx_impl(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY, uint
         }
       }
       if (nt == 0) continue;
-      rc = launch_conv_like(d, y_hi, y_lo, g->n, g->oh, g->ow, ocp,
-                            wh.as<float>(), wl.as<float>(), g->ic, taps, AH, AW, 1, nt, dy, dx, wi,
-                            g->ic, (float*)(uintptr_t)dX, (int64_t)ph * g->iw + pw,
-                            (int64_t)g->ic * plane, (int64_t)s * g->iw, s, plane, nullptr, 0, 0.0f,
-                            1, tf32_passes);
+      ConvLaunch c;
+      memset(&c, 0, sizeof(c));
+      c.NL = g->n; c.H = g->oh; c.W = g->ow; c.kp = ocp; c.wrows = g->ic; c.wtaps = taps;
+      c.AH = AH; c.AW = AW; c.es = 1; c.ntaps = nt; c.dy = dy; c.dx = dx; c.widx = wi;
+      c.OCv = g->ic; c.out = (float*)(uintptr_t)dX; c.out_base = (int64_t)ph * g->iw + pw;
+      c.out_sn = (int64_t)g->ic * plane; c.out_sa = (int64_t)s * g->iw; c.out_sb = s; c.out_sc = plane;
+      c.accumulate = 1; c.precision = precision;
+      rc = launch_conv_like(d, oy, ow, c);
       if (rc) return rc;
     }
   return LNN_OK;
@@ -1968,75 +2342,74 @@ int conv_dx_impl(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY, uint
 
 // dW += ...; dY and X are each NCHW or the packed hi / lo copies
 int conv_dw_impl(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY, uint64_t dY_lo, int dy_packed,
-                 uint64_t X, uint64_t X_lo, int x_packed, int tf32_passes) {
+                 uint64_t X, uint64_t X_lo, int x_packed, int precision) {
   LNN_DEV(d, dev);
   int rc = check_geom(g);
   if (rc) return rc;
-  rc = check_passes(tf32_passes);
+  rc = check_passes(precision);
   if (rc) return rc;
   LNN_REQUIRE(dW && dY && X, "null buffer");
-  if (!dy_packed && !x_packed && lnn::conv_direct_dw_applicable(g) && env_int("LNN_CONV_DIRECT", 1))
+  if (!dy_packed && !x_packed && lnn::conv_direct_dw_applicable(g) && knobs().direct)
     return lnn::conv_direct_dw(d, g, (float*)(uintptr_t)dW, (const float*)(uintptr_t)dY,
                                (const float*)(uintptr_t)X);
-  const int want_lo = tf32_passes == 3;
-  LNN_REQUIRE(!dy_packed || !want_lo || dY_lo, "packed dY needs its lo copy for split TF32");
-  LNN_REQUIRE(!x_packed || !want_lo || X_lo, "packed X needs its lo copy for split TF32");
+  const int esz = esz_of(precision);
   const int s = g->stride;
   const int cp = chan_pad(g->ic), ocp = chan_pad(g->oc);
   const int taps = g->kh * g->kw;
   lnn::Scratch xh_s(d), xl_s(d), yh_s(d), yl_s(d), part(d);
-  // xh, xl, yh, yl: the hi / lo copies wherever they came from (lo aliases hi for single-pass TF32)
-  const float *xh, *xl, *yh, *yl;
-  if (x_packed) {
-    xh = (const float*)(uintptr_t)X; xl = want_lo ? (const float*)(uintptr_t)X_lo : xh;
-  } else {
-    rc = nhwc_split(d, xh_s, xl_s, (const float*)(uintptr_t)X, g->n, g->ic, g->ih, g->iw, cp, want_lo);
-    if (rc) return rc;
-    xh = xh_s.as<float>(); xl = want_lo ? xl_s.as<float>() : xh;
-  }
-  if (dy_packed) {
-    yh = (const float*)(uintptr_t)dY; yl = want_lo ? (const float*)(uintptr_t)dY_lo : yh;
-  } else {
-    rc = nhwc_split(d, yh_s, yl_s, (const float*)(uintptr_t)dY, g->n, g->oc, g->oh, g->ow, ocp, want_lo);
-    if (rc) return rc;
-    yh = yh_s.as<float>(); yl = want_lo ? yl_s.as<float>() : yh;
-  }
+  Operand ox, oy;
+  if (x_packed)
+    rc = packed_operand(&ox, X, X_lo, (uint64_t)g->n * g->ih * g->iw * cp, precision);
+  else
+    rc = nhwc_split(d, xh_s, xl_s, &ox, (const float*)(uintptr_t)X, g->n, g->ic, g->ih, g->iw, cp, precision);
+  if (rc) return rc;
+  if (dy_packed)
+    rc = packed_operand(&oy, dY, dY_lo, (uint64_t)g->n * g->oh * g->ow * ocp, precision);
+  else
+    rc = nhwc_split(d, yh_s, yl_s, &oy, (const float*)(uintptr_t)dY, g->n, g->oc, g->oh, g->ow, ocp, precision);
+  if (rc) return rc;
 
-  // MN-major tf32 tiles are always 32 channels (128 bytes) wide; channels beyond the padded
-  // extent of the NHWC copy are zero-filled by the TMA unit
-  const int ea = 32, eb = 32;
-  const int swa = 128, swb = 128;
-  // Columns of the accumulator enumerate (tap, 32-channel block) pairs, so one dY patch in
-  // shared memory serves every tap; a tile owns up to 8 such blocks (N <= 256).
-  const int icb = (cp + 31) / 32;
+  // MN-major tiles: one swizzle row of channels wide.  tf32 rows are always 128 bytes (32
+  // channels); fp16 rows are 128 or 64 bytes (64 or 32 channels) so that layers with 32
+  // channels do not compute 32 columns of zeros.  Channels beyond the padded extent of the
+  // NHWC copy are zero-filled by the TMA unit.
+  const int ea = 128 / esz;
+  const int eb = (esz == 2 && cp <= 32) ? 32 : 128 / esz;
+  const int swa = ea * esz, swb = eb * esz;
+  // Columns of the accumulator enumerate (tap, channel block) pairs, so one dY patch in
+  // shared memory serves every tap; a tile owns up to 256 columns.
+  const int icb = (cp + eb - 1) / eb;
   const int nb_total = taps * icb;
-  const int ngroups = (nb_total + 7) / 8;
+  const int nb_max = 256 / eb;
+  const int ngroups = (nb_total + nb_max - 1) / nb_max;
   const int nb_group = (nb_total + ngroups - 1) / ngroups;
-  int bn = nb_group * 32;
+  int bn = nb_group * eb;
   const int oc_tiles = (g->oc + 127) / 128, ic_tiles = icb;
-  // pixel patch = one k-block: tw x th output pixels of one image, a multiple of 8 pixels,
-  // sized so that two stages of (128 + bn) x pix floats (x2 for hi/lo) fit shared memory
-  const int nbuf = want_lo ? 2 : 1;
-  int pix_cap = ((kSmemLimit - kSmemSlack) / 2) / (nbuf * (128 + bn) * 4);
-  pix_cap = std::min(pix_cap & ~7, 128);
+  // pixel patch = one k-block: tw x th output pixels of one image, a multiple of one
+  // instruction's K (8 tf32 / 16 fp16 pixels), sized so that two stages of (128 + bn) x pix
+  // elements (x2 for hi/lo) fit shared memory
+  const int kq = 32 / esz;
+  const int nbuf = precision == 1 ? 1 : 2;
+  int pix_cap = ((kSmemLimit - kSmemSlack) / 2) / (nbuf * (128 + bn) * esz);
+  pix_cap = std::min(pix_cap / kq * kq, 128);
   const int wcap = std::min(pix_cap, 256 / s);
-  LNN_REQUIRE(wcap >= 8, "stride too large for the weight-gradient kernel");
-  // Patch = th rows x tw columns of one image with tw*th a multiple of 8 (the box may be wider than
+  LNN_REQUIRE(wcap >= kq, "stride too large for the weight-gradient kernel");
+  // Patch = th rows x tw columns of one image with tw*th a multiple of kq (the box may be wider than
   // the image: zero filled).  Among the shapes that fit, take the one that wastes the fewest of
   // its pixels over the whole image (the image width is cut into 1..8 equal pieces), larger first.
-  int tw = 8, th = 1;
+  int tw = kq, th = 1;
   {
-    // real pixels per clock: a patch of P pixels costs about 60 clocks per pixel of MMAs (three
-    // passes of P/8 instructions) plus about 1500 clocks per ring hand-over (fitted to measurements)
+    // real pixels per clock: a patch of P pixels costs about 480 clocks per instruction K of MMAs
+    // (three passes) plus about 1500 clocks per ring hand-over (fitted to measurements)
     double best = -1.0;
     for (int h = 1; h <= 8 && h <= g->oh && h * s <= 256; ++h) {
-      const int mult = 8 / gcd_int(8, h);
+      const int mult = kq / gcd_int(kq, h);
       for (int k = 1; k <= 8; ++k) {
         int w = (g->ow + k - 1) / k;
         w = ((w + mult - 1) / mult) * mult;
         if (w * h > pix_cap || w * s > 256 || w > wcap) continue;
         const double tiles = (double)((g->ow + w - 1) / w) * (double)((g->oh + h - 1) / h);
-        const double score = (double)g->ow * g->oh / (tiles * (60.0 * w * h + 1500.0));
+        const double score = (double)g->ow * g->oh / (tiles * (480.0 / kq * w * h + 1500.0));
         if (score > best * 1.001) { best = score; tw = w; th = h; }
       }
     }
@@ -2052,21 +2425,22 @@ int conv_dw_impl(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY, uint
   const int pps = (int)((patches + splits - 1) / splits);
   splits = (patches + pps - 1) / pps;    // every split owns at least one patch
 
-  const int64_t part_ld = (int64_t)nb_total * 32;
+  const int64_t part_ld = (int64_t)nb_total * eb;
   const int64_t stride_split = (int64_t)oc_tiles * 128 * part_ld;
   rc = part.get((uint64_t)splits * stride_split * 4);
   if (rc) return rc;
 
   TcParams p;
   memset(&p, 0, sizeof(p));
-  p.mode = MODE_DW; p.passes = tf32_passes; p.bn = bn;
+  p.mode = MODE_DW; p.passes = precision; p.esz = esz; p.bn = bn;
+  p.amax_a = oy.amax; p.amax_b = ox.amax;
   p.a_major = 1; p.b_major = 1; p.swz_a = swa; p.swz_b = swb;
-  p.ksteps = pix / 8;
+  p.ksteps = pix / kq;
   p.a_loads = 128 / ea; p.b_loads = bn / eb;
   p.a_load_bytes = pix * swa; p.b_load_bytes = pix * swb;
   p.a_tile_bytes = p.a_loads * p.a_load_bytes; p.b_tile_bytes = p.b_loads * p.b_load_bytes;
   p.a_krows = pix; p.b_krows = pix;
-  p.idesc = make_idesc(bn, 1, 1);
+  p.idesc = make_idesc(bn, 1, 1, esz);
   p.tmem_cols = tmem_cols_for(bn);
   p.tw = tw; p.th = th; p.tn = 1;
   p.tiles_b = tiles_b; p.tiles_a = tiles_a; p.tiles_n = tiles_n;
@@ -2086,20 +2460,20 @@ int conv_dw_impl(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY, uint
     }
   p.ntaps = taps;
   CUtensorMap mah, mal, mbh, mbl;
-  rc = encode_nhwc(&mah, yh, g->n, g->oh, g->ow, ocp, ea, tw, th, 1, 1, true);
+  rc = encode_nhwc(&mah, oy.hi, esz, g->n, g->oh, g->ow, ocp, ea, tw, th, 1, 1, true);
   if (rc) return rc;
-  rc = encode_nhwc(&mal, yl, g->n, g->oh, g->ow, ocp, ea, tw, th, 1, 1, true);
+  rc = encode_nhwc(&mal, oy.lo, esz, g->n, g->oh, g->ow, ocp, ea, tw, th, 1, 1, true);
   if (rc) return rc;
-  rc = encode_nhwc(&mbh, xh, g->n, g->ih, g->iw, cp, eb, tw, th, 1, s, true);
+  rc = encode_nhwc(&mbh, ox.hi, esz, g->n, g->ih, g->iw, cp, eb, tw, th, 1, s, true);
   if (rc) return rc;
-  rc = encode_nhwc(&mbl, xl, g->n, g->ih, g->iw, cp, eb, tw, th, 1, s, true);
+  rc = encode_nhwc(&mbl, ox.lo, esz, g->n, g->ih, g->iw, cp, eb, tw, th, 1, s, true);
   if (rc) return rc;
   dim3 grid((unsigned)splits, (unsigned)oc_tiles, (unsigned)ngroups);
   rc = launch_tc<MODE_DW>(d, grid, mah, mal, mbh, mbl, p);
   if (rc) return rc;
   dw_finalize_kernel<<<grid_for(d, (int64_t)g->oc * g->ic * taps), kThreads, 0, d->stream>>>(
       (float*)(uintptr_t)dW, part.as<float>(), g->oc, g->ic, taps, (int)splits, stride_split,
-      icb, part_ld);
+      icb, part_ld, eb);
   LNN_CHECK_LAUNCH(d);
   return LNN_OK;
 }

@@ -3,16 +3,23 @@
 // One persistent CTA per SM (192 threads) walks the 128 x BN output tiles round-robin:
 //   warp 0    : TMA producer  -- cp.async.bulk.tensor loads into a ring of smem stages,
 //                                running ahead across tile boundaries
-//   warp 1    : MMA issuer    -- one elected thread issues tcgen05.mma.kind::tf32 into one of
-//                                two TMEM accumulators, owns the TMEM allocation
-//   warps 2-5 : epilogue      -- tcgen05.ld the finished accumulator, bias / activation /
+//   warp 1    : MMA issuer    -- one elected thread issues tcgen05.mma (kind::f16 or kind::tf32)
+//                                into one of two TMEM accumulators, owns the TMEM allocation
+//   warps 2-5 : epilogue      -- tcgen05.ld the finished accumulator, scale / bias / activation /
 //                                "+=", store -- while the MMA warp fills the other one
-// fp32 accuracy comes from split-TF32: every operand is pre-split (by an HBM-bound pass)
-// into hi = rna_tf32(x) and lo = rna_tf32(x - hi); the MMA warp issues hi*hi + hi*lo +
-// lo*hi into the same accumulator.  Operands may be K-major or MN-major in shared memory
-// (both are native to tcgen05 for tf32), so no transposes are materialised for the
-// backward GEMMs, and the convolution A-tiles are gathered straight from an NHWC copy of
-// the activations by 4-D tiled TMA (zero fill outside the image = padding).
+// fp32 accuracy comes from a split of every operand into two 11-bit-significand halves by an
+// HBM-bound pre-pass; the MMA warp issues hi*hi + hi*lo + lo*hi into the same fp32 accumulator.
+//   precision 2 (default): hi = fp16(x / s), lo = fp16(x / s - hi) with s an exact power of two
+//       taken from the tensor's largest magnitude (so that |x / s| < 2^15); kind::f16, K = 16 per
+//       instruction, 2 bytes per element; the accumulator is multiplied by s_a * s_b on the way out
+//   precision 3: hi = rna_tf32(x), lo = rna_tf32(x - hi); kind::tf32, K = 8, 4 bytes per element
+//   precision 1: hi only (plain TF32)
+// An fp16 and a tf32 value carry the same 11 significant bits, so 2 and 3 split x the same way;
+// the fp16 form moves half the bytes and needs half the instructions for the same K.
+// Operands may be K-major or MN-major in shared memory (both are native to tcgen05 for these
+// types), so no transposes are materialised for the backward GEMMs, and the convolution
+// A-tiles are gathered straight from an NHWC copy of the activations by 4-D tiled TMA (zero
+// fill outside the image = padding).
 //
 // Unit-stride convolutions with few input channels per tap use a second kernel
 // (tc_halo_kernel) that keeps the pixel patch with its halo resident in shared memory and
@@ -40,7 +47,9 @@ struct TcParams {
   int mode, passes, stages, bn;
   int a_major, b_major;          // 0 = K-major, 1 = MN-major
   int swz_a, swz_b;              // bytes per smem row of the operand tiles (32/64/128)
-  int ksteps;                    // MMA steps (K = 8) per k-block
+  int esz;                       // bytes per operand element: 2 (fp16 split) or 4 (tf32)
+  int kunit;                     // GEMM: K elements per unit (one 128-byte row)
+  int ksteps;                    // MMA steps (32 bytes of K) per k-block
   int a_tile_bytes, b_tile_bytes;// bytes of one (hi or lo) operand tile
   int a_loads, b_loads;          // TMA boxes per operand tile
   int a_load_bytes, b_load_bytes;// bytes per box
@@ -76,9 +85,16 @@ struct TcParams {
   const float* bias;
   float* out;
   int* status;
+  // fp16 split: largest magnitudes (fp32 bit patterns) of the two operand tensors; the
+  // accumulator is scaled by the product of the powers of two derived from them
+  const uint32_t* amax_a;
+  const uint32_t* amax_b;
+  uint32_t* amax_out;            // ep_mode 3: largest magnitude of what this launch wrote
   // fused 2x2/stride-2 max pool (channels-on-M kernels): ep_mode 1 writes the pooled NCHW
-  // tensor, ep_mode 2 writes it channel-innermost and pre-split (out = hi, out_lo = lo, channel
-  // pitch ocp) as the next convolution's operand; the out_s* strides then address pooled pixels
+  // tensor, ep_mode 2 writes it channel-innermost and pre-split in tf32 (out = hi, out_lo = lo,
+  // channel pitch ocp) as the next convolution's operand, ep_mode 3 writes it channel-innermost
+  // in fp32 and records its largest magnitude (the fp16 split needs that before it can run);
+  // the out_s* strides then address pooled pixels
   int ep_mode;
   float* out_lo;
   int ocp;

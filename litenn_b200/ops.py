@@ -471,7 +471,7 @@ def _matmul_shapes(a_shape, b_shape):
 
 
 def _gemm(out_t, a_t, b_t, bias_t, batch, m, n, k, trans_a, trans_b, accumulate):
-    passes = _lib.tf32_passes()
+    passes = _lib.precision()
     for i, dev in _each_device():
         _lib_().lnn_gemm_f32(dev, out_t._ptr(i), a_t._ptr(i), b_t._ptr(i), bias_t._ptr(i) if bias_t is not None else 0,
                              batch, m, n, k, int(trans_a), int(trans_b), int(accumulate), passes)
@@ -548,7 +548,7 @@ def conv2D(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t=None,
         raise ValueError(f"unknown activation {activation}")
     if bias_t is not None and bias_t.shape.size != g.oc:
         raise ValueError(f"bias must have {g.oc} elements")
-    passes = _lib.tf32_passes()
+    passes = _lib.precision()
     output_t = _out(out_shape)
     output_t._set_op_name("conv2D")
     act = 1 if activation == "leaky_relu" else 0
@@ -666,26 +666,70 @@ def conv2D_block(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t
 
 class PackedActivation:
     """An activation kept in the tensor-core convolution's operand format between the layers of
-    an inference chain: channel-innermost copies hi = tf32(x) and lo = tf32(x - hi), each
-    (N, H, W, C rounded up to 8).  Only conv2D_infer / conv2D_pool consume it; the reference has
-    no counterpart (its conv2D builds an im2col buffer per call, conv2D.py:39-41)."""
+    an inference chain: channel-innermost copies hi and lo, each (N, H, W, C rounded up to 8).
+    Split FP16 (the default precision): fp16 values of x / s with s a power of two derived from
+    the tensor's largest magnitude, whose bit pattern sits in a trailer behind hi.  Split TF32:
+    hi = tf32(x), lo = tf32(x - hi) as fp32.  Only conv2D_infer / conv2D_pool and the gradient
+    entries consume it; the reference has no counterpart (its conv2D builds an im2col buffer per
+    call, conv2D.py:39-41).  hi / lo are flat fp32-typed tensors used as raw storage."""
 
-    def __init__(self, shape_nchw, hi_t, lo_t):
+    def __init__(self, shape_nchw, hi_t, lo_t, precision):
         self.shape = TensorShape(shape_nchw)
-        self.hi, self.lo = hi_t, lo_t
+        self.hi, self.lo, self.precision = hi_t, lo_t, precision
+
+    def _elems(self):
+        n, c, h, w = self.shape.shape
+        return n * h * w * ((c + 7) & ~7)
+
+    def _part(self, t):
+        n, c, h, w = self.shape.shape
+        elems = self._elems()
+        if self.precision == 2:
+            v = t.np().view(np.uint8)[:elems * 2].view(np.float16)
+        else:
+            v = t.np().reshape(-1)[:elems]
+        return v.reshape(n, h, w, (c + 7) & ~7)
+
+    def hi_np(self):
+        """The stored hi elements, (N, H, W, C padded to 8): float16 (split FP16) or float32."""
+        return self._part(self.hi)
+
+    def lo_np(self):
+        return self._part(self.lo) if self.lo is not None else None
+
+    def scale_exponent(self):
+        """e such that the activation is (hi + lo) * 2**e (0 unless split FP16)."""
+        if self.precision != 2:
+            return 0
+        off = (self._elems() * 2 + 15) & ~15
+        return scale_exponent_of(int(self.hi.np().view(np.uint8)[off:off + 4].view(np.uint32)[0]))
 
     def np(self):
-        """hi + lo as an NCHW array: the fp32 activation up to its last two mantissa bits."""
+        """(hi + lo) * 2**e as an NCHW array: the fp32 activation up to its last two mantissa bits."""
         c = self.shape.shape[1]
-        v = self.hi.np().astype(np.float64) + (self.lo.np() if self.lo is not None else 0.0)
+        v = self.hi_np().astype(np.float64)
+        if self.lo is not None:
+            v = v + self.lo_np()
+        v = v * 2.0 ** self.scale_exponent()
         return np.ascontiguousarray(v[..., :c].transpose(0, 3, 1, 2)).astype(np.float32)
 
 
+def scale_exponent_of(amax_bits):
+    """Scale exponent of the split-FP16 format from the fp32 bit pattern of a tensor's largest
+    magnitude: that element times 2**-e lies in [2**14, 2**15); 0 for zero / non-finite maxima."""
+    e = (amax_bits >> 23) & 0xFF
+    if amax_bits == 0 or e == 255:
+        return 0
+    return (e if e > 0 else 1) - 127 - 14     # (max / min are tensor ops in this module)
+
+
 def _packed_like(n, c, h, w):
-    cp = (c + 7) & ~7
-    hi = _out((n, h, w, cp))
-    lo = _out((n, h, w, cp)) if _lib.tf32_passes() == 3 else None
-    return PackedActivation((n, c, h, w), hi, lo)
+    prec = _lib.precision()
+    hb, lb = ctypes.c_uint64(), ctypes.c_uint64()
+    _lib_().lnn_packed_bytes(n, c, h, w, prec, ctypes.byref(hb), ctypes.byref(lb))
+    hi = _out(((hb.value + 3) // 4,))
+    lo = _out(((lb.value + 3) // 4,)) if lb.value else None
+    return PackedActivation((n, c, h, w), hi, lo, prec)
 
 
 def pack_activation(input_t):
@@ -693,7 +737,8 @@ def pack_activation(input_t):
     n, c, h, w = input_t.shape.shape
     out = _packed_like(n, c, h, w)
     for i, dev in _each_device():
-        _lib_().lnn_nhwc_split(dev, out.hi._ptr(i), out.lo._ptr(i) if out.lo is not None else 0, input_t._ptr(i), n, c, h, w)
+        _lib_().lnn_nhwc_split(dev, out.hi._ptr(i), out.lo._ptr(i) if out.lo is not None else 0, input_t._ptr(i),
+                               n, c, h, w, out.precision)
     return out
 
 
@@ -726,7 +771,7 @@ def conv2D_infer(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t
         _lib_().lnn_conv2d_fwd_packed(dev, ctypes.byref(g), y._ptr(i), y_lo._ptr(i) if y_lo is not None else 0, x, x_lo,
                                       kernel_t._ptr(i), bias_t._ptr(i) if bias_t is not None else 0,
                                       1 if activation == "leaky_relu" else 0, float(alpha), 1 if pool else 0,
-                                      1 if packed_in else 0, 1 if packed_output else 0, _lib.tf32_passes())
+                                      1 if packed_in else 0, 1 if packed_output else 0, _lib.precision())
     return result
 
 

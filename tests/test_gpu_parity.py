@@ -274,6 +274,19 @@ def _tf32_rna(x):
     return ((b + 0x1000) & 0xFFFFE000).astype(np.uint32).view(np.float32)
 
 
+def _expected_split(x, precision):
+    """hi, lo and scale exponent the packed operand format must hold for the fp32 array x."""
+    x = np.ascontiguousarray(x, np.float32)
+    if precision != 2:
+        hi = _tf32_rna(x)
+        return hi, _tf32_rna(x - hi), 0
+    from litenn_b200.ops import scale_exponent_of
+    e = scale_exponent_of(int(np.abs(x).max().astype(np.float32).view(np.uint32)))
+    xs = np.ldexp(x, -e).astype(np.float32)          # exact: a power of two
+    hi = xs.astype(np.float16)                       # round to nearest even, as cvt.rn.f16.f32
+    return hi, (xs - hi.astype(np.float32)).astype(np.float16), e
+
+
 @pytest.mark.parametrize("xs,ws", [((2, 3, 32, 32), (32, 3, 3, 3)), ((3, 32, 64, 64), (64, 32, 3, 3)),
                                    ((2, 64, 32, 32), (128, 64, 3, 3)), ((2, 32, 64, 64), (40, 32, 3, 3)),
                                    ((2, 16, 12, 12), (24, 16, 3, 3)), ((2, 64, 30, 34), (64, 64, 3, 3)),
@@ -293,12 +306,12 @@ def test_conv_infer_fused_and_packed(nn_gpu, xs, ws):
     assert_bit_exact(pooled, chain, "pool fused into the epilogue")
     packed = nn.conv2D_infer(xt, wt, pool=True, packed_output=True, **kw)
     oc = ws[0]
-    hi = packed.hi.np()
-    want_hi = _tf32_rna(chain)
-    want_lo = _tf32_rna(chain - want_hi)
+    hi, lo = packed.hi_np(), packed.lo_np()
+    want_hi, want_lo, want_e = _expected_split(chain, packed.precision)
+    assert packed.scale_exponent() == want_e
     assert_bit_exact(hi[..., :oc].transpose(0, 3, 1, 2), want_hi, "packed hi")
-    assert_bit_exact(packed.lo.np()[..., :oc].transpose(0, 3, 1, 2), want_lo, "packed lo")
-    assert not hi[..., oc:].any() and not packed.lo.np()[..., oc:].any(), "pad channels must be zero"
+    assert_bit_exact(lo[..., :oc].transpose(0, 3, 1, 2), want_lo, "packed lo")
+    assert not hi[..., oc:].any() and not lo[..., oc:].any(), "pad channels must be zero"
     # packed input: same result as the NCHW input, with and without the fused pool
     xp = nn.pack_activation(xt)
     got_pool = nn.conv2D_infer(xp, wt, pool=True, **kw).np()
@@ -387,7 +400,8 @@ def test_conv_random_geometries(nn_gpu, n, ic, h, w, oc, k, stride, dil):
     chain = nn.max_pool2D(y, 2, 2, "same").np()
     assert_bit_exact(nn.conv2D_infer(xt, wt, pool=True, **kw).np(), chain, "fused pool")
     packed = nn.conv2D_infer(xt, wt, pool=True, packed_output=True, **kw)
-    assert_bit_exact(packed.hi.np()[..., :oc].transpose(0, 3, 1, 2), _tf32_rna(chain), "packed hi")
+    assert_bit_exact(packed.hi_np()[..., :oc].transpose(0, 3, 1, 2), _expected_split(chain, packed.precision)[0],
+                     "packed hi")
     nn.devices.check_status()
 
 
