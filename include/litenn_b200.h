@@ -92,8 +92,14 @@ int lnn_host_alloc(uint64_t bytes, void** ptr);   /* pinned host memory */
 int lnn_host_free(void* ptr);
 /* number of kernels this library has launched on the device since lnn_init */
 int lnn_launch_count(int dev, uint64_t* count);
-/* read-and-clear the device status word that bounded waits set when they give up */
+/* Read-and-clear the device status word that bounded waits in the tile kernels set when they
+ * give up ({LNN_E_TIMEOUT, role, tile, step}).  While the word is set, later tile kernels return
+ * at once, so their outputs are not results; lnn_sync and lnn_d2h read the word with the
+ * synchronisation they perform anyway and return LNN_E_TIMEOUT (clearing it) when it is set.
+ * The reference has no counterpart: an OpenCL kernel that waits forever hangs the queue. */
 int lnn_device_status(int dev, int* status);
+/* Test hook: writes the status word from the host, as if a wait had expired (no kernel runs). */
+int lnn_debug_set_status(int dev, int code, int role, int tile, int step);
 /* CUDA events on the device stream (for timing on the stream the kernels run on) */
 int lnn_event_create(int dev, uint64_t* ev);
 int lnn_event_record(int dev, uint64_t ev);
@@ -282,6 +288,23 @@ int lnn_conv2d_dw_packed(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t 
 /* V += -lr * (G * gscale)   (momentum 0 form of the reference's two kernels, with the
  * 1/ndev of gradient averaging folded into gscale).  ref: optimizer/SGD.py:42-83 */
 int lnn_sgd_step(int dev, uint64_t V, uint64_t G, int64_t n, float lr, float gscale);
+
+/* One update of a parameter tensor V from its gradient G with the optimizer's state tensors:
+ * SGD with momentum (S1 = accumulator; nesterov optional), RMSprop (S1 = mean square, beta1 = rho),
+ * Adam (S1 = first, S2 = second moment).  The learning rate is decayed by 1/(1 + lr_decay*iteration)
+ * and dropped per element where hash(index + seed) <= lr_dropout, as the reference's kernels do
+ * (SGD evaluates that in both of its kernels: seed_a for the accumulator, seed_b for the update).
+ * ref: optimizer/SGD.py:42-83, optimizer/RMSprop.py:37-69, optimizer/Adam.py:43-84,
+ *      optimizer/Optimizer.py:160-203 */
+enum { LNN_OPT_SGD = 0, LNN_OPT_RMSPROP = 1, LNN_OPT_ADAM = 2 };
+typedef struct lnn_opt_params {
+  float lr, lr_decay, lr_dropout, gscale;
+  float beta1, beta2;          /* SGD: momentum in beta1; RMSprop: rho in beta1 */
+  uint32_t iteration, seed_a, seed_b;
+  int nesterov;
+} lnn_opt_params;
+int lnn_optimizer_step(int dev, int kind, uint64_t V, uint64_t G, uint64_t S1, uint64_t S2, int64_t n,
+                       const lnn_opt_params* p);
 
 /* NCCL (loaded with dlopen on first use).  One communicator per device slot.
  * ref: optimizer/Optimizer.py:149-153 (host-staged replica averaging, replaced by a

@@ -68,6 +68,7 @@ _SIGNATURES = {
     "lnn_host_free": (c_int, [c_void_p]),
     "lnn_launch_count": (c_int, [c_int, POINTER(c_uint64)]),
     "lnn_device_status": (c_int, [c_int, POINTER(c_int)]),
+    "lnn_debug_set_status": (c_int, [c_int, c_int, c_int, c_int, c_int]),
     "lnn_event_create": (c_int, [c_int, POINTER(c_uint64)]),
     "lnn_event_record": (c_int, [c_int, c_uint64]),
     "lnn_event_elapsed_ms": (c_int, [c_int, c_uint64, c_uint64, POINTER(c_float)]),
@@ -100,6 +101,7 @@ _SIGNATURES = {
     "lnn_conv2d_dx_packed": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64, c_uint64, c_int]),
     "lnn_conv2d_dw_packed": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64, c_uint64, c_uint64, c_int]),
     "lnn_sgd_step": (c_int, [c_int, c_uint64, c_uint64, c_int64, c_float, c_float]),
+    "lnn_optimizer_step": (c_int, [c_int, c_int, c_uint64, c_uint64, c_uint64, c_uint64, c_int64, c_void_p]),
     "lnn_nccl_unique_id": (c_int, [c_void_p]),
     "lnn_nccl_init_rank": (c_int, [c_int, c_int, c_int, c_void_p]),
     "lnn_nccl_init_all": (c_int, [POINTER(c_int), c_int]),

@@ -436,6 +436,51 @@ static bool operand_vec_ok(const Operand& op, uint64_t ptr) {
 
 namespace {
 
+__device__ __forceinline__ uint32_t pcg_hash(uint32_t v);
+
+// One optimizer update per element, the reference's two or three kernels per tensor in one pass
+// with the same operations in the same order (litenn/core/optimizer/SGD.py:42-83,
+// RMSprop.py:37-69, Adam.py:43-84) and its learning-rate prologue (Optimizer.py:186-203):
+// decay by 1 / (1 + lr_decay * iteration), then dropout of the step where the hash of
+// (element index + seed) is <= lr_dropout.  SGD evaluates that prologue in both of its kernels,
+// each with its own seed.  g is G * gscale when gscale != 1 (gradient averaging over replicas).
+template <int KIND>
+__global__ void __launch_bounds__(kThreads)
+opt_kernel(float* __restrict__ V, const float* __restrict__ G, float* __restrict__ S1, float* __restrict__ S2,
+           int64_t n, const lnn_opt_params p) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  float lr0 = p.lr;
+  if (p.lr_decay != 0.0f) lr0 = fmul(lr0, fdiv(1.0f, fadd(1.0f, fmul(p.lr_decay, __uint2float_rn(p.iteration)))));
+  const float uif = 1.0f / 4294967296.0f;
+  for (int64_t i = tid; i < n; i += nthreads) {
+    float g = G[i];
+    if (p.gscale != 1.0f) g = fmul(g, p.gscale);
+    float lr_a = lr0, lr_b = lr0;
+    if (p.lr_dropout != 0.0f) {
+      if (fmul(__uint2float_rn(pcg_hash((uint32_t)i + p.seed_a)), uif) <= p.lr_dropout) lr_a = 0.0f;
+      if (fmul(__uint2float_rn(pcg_hash((uint32_t)i + p.seed_b)), uif) <= p.lr_dropout) lr_b = 0.0f;
+    }
+    if (KIND == LNN_OPT_SGD) {
+      // A = momentum*A - lr*G ; V += A   (nesterov: V += momentum*A - lr*G with the new A)
+      const float a = fsub(fmul(p.beta1, S1[i]), fmul(lr_a, g));
+      S1[i] = a;
+      V[i] = fadd(V[i], p.nesterov ? fsub(fmul(p.beta1, a), fmul(lr_b, g)) : a);
+    } else if (KIND == LNN_OPT_RMSPROP) {
+      // A = rho*A + (1-rho)*g*g ; V += -lr*G / (sqrt(A) + 1e-7)
+      const float a = fadd(fmul(p.beta1, S1[i]), fmul(fmul(fsub(1.0f, p.beta1), g), g));
+      S1[i] = a;
+      V[i] = fadd(V[i], fdiv(fmul(-lr_b, g), fadd(__fsqrt_rn(a), 1e-7f)));
+    } else {
+      // M = b1*M + (1-b1)*G ; U = b2*U + (1-b2)*g*g ; V += -lr*M / (sqrt(U) + 1e-7)
+      const float m = fadd(fmul(p.beta1, S1[i]), fmul(fsub(1.0f, p.beta1), g));
+      const float u = fadd(fmul(p.beta2, S2[i]), fmul(fmul(fsub(1.0f, p.beta2), g), g));
+      S1[i] = m; S2[i] = u;
+      V[i] = fadd(V[i], fdiv(fmul(-lr_b, m), fadd(__fsqrt_rn(u), 1e-7f)));
+    }
+  }
+}
+
 // Random initializers: counter-based, one hash of (element index + seed) per element, so the
 // result does not depend on the launch geometry.  PCG output functions as the reference uses
 // them (litenn/core/CLKernelHelper.py:210-233; initializer/RandomUniform.py:12-20,
@@ -632,6 +677,24 @@ int lnn_scale_bias_lrelu(int dev, uint64_t y, uint64_t x, uint64_t g, uint64_t b
         (float*)(uintptr_t)y, (const float*)(uintptr_t)x, (const float*)(uintptr_t)g,
         (const float*)(uintptr_t)b, total, hw, c, alpha, accumulate);
   }
+  LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
+}
+
+int lnn_optimizer_step(int dev, int kind, uint64_t V, uint64_t G, uint64_t S1, uint64_t S2, int64_t n,
+                       const lnn_opt_params* p) {
+  LNN_DEV(d, dev);
+  LNN_REQUIRE(V && G && n > 0 && p, "bad arguments");
+  LNN_REQUIRE(kind >= LNN_OPT_SGD && kind <= LNN_OPT_ADAM, "unknown optimizer kind %d", kind);
+  LNN_REQUIRE(S1 && (kind != LNN_OPT_ADAM || S2), "optimizer state buffer missing");
+  float* v = (float*)(uintptr_t)V;
+  const float* g = (const float*)(uintptr_t)G;
+  float* s1 = (float*)(uintptr_t)S1;
+  float* s2 = (float*)(uintptr_t)S2;
+  const unsigned grid = (unsigned)grid_for(d, n);
+  if (kind == LNN_OPT_SGD) opt_kernel<LNN_OPT_SGD><<<grid, kThreads, 0, d->stream>>>(v, g, s1, s2, n, *p);
+  else if (kind == LNN_OPT_RMSPROP) opt_kernel<LNN_OPT_RMSPROP><<<grid, kThreads, 0, d->stream>>>(v, g, s1, s2, n, *p);
+  else opt_kernel<LNN_OPT_ADAM><<<grid, kThreads, 0, d->stream>>>(v, g, s1, s2, n, *p);
   LNN_CHECK_LAUNCH(d);
   return LNN_OK;
 }

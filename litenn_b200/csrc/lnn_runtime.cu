@@ -28,17 +28,24 @@ Device* get_device(int dev) {
   return &g_devices[dev];
 }
 
-// Host-side fault injection for tests: LNN_FAIL_ALLOC_AFTER=n makes the n-th and later
-// fresh cudaMalloc calls report an allocation failure (never touches the GPU).
+// Host-side fault injection for tests (never touches the GPU): after LNN_FAIL_ALLOC_AFTER=n
+// successful fresh cudaMalloc calls, the next LNN_FAIL_ALLOC_TIMES=k calls (default: all of
+// them) report an allocation failure.
 static long g_fail_alloc_after = -2;
+static long g_fail_alloc_times = -1;
 static long g_fresh_allocs = 0;
+static long g_failed_allocs = 0;
 
 static cudaError_t raw_malloc(void** p, uint64_t bytes) {
   if (g_fail_alloc_after == -2) {
     const char* e = getenv("LNN_FAIL_ALLOC_AFTER");
     g_fail_alloc_after = e ? atol(e) : -1;
+    const char* t = getenv("LNN_FAIL_ALLOC_TIMES");
+    g_fail_alloc_times = t ? atol(t) : -1;
   }
-  if (g_fail_alloc_after >= 0 && g_fresh_allocs >= g_fail_alloc_after) {
+  if (g_fail_alloc_after >= 0 && g_fresh_allocs >= g_fail_alloc_after &&
+      (g_fail_alloc_times < 0 || g_failed_allocs < g_fail_alloc_times)) {
+    g_failed_allocs++;
     return cudaErrorMemoryAllocation;
   }
   g_fresh_allocs++;
@@ -223,12 +230,30 @@ int lnn_h2d(int dev, uint64_t dst, const void* src, uint64_t bytes) {
   return LNN_OK;
 }
 
+// The device status word travels with every host synchronisation (its 16 bytes ride on the
+// stream in front of the sync the caller pays anyway): a bounded wait that expired in a tile
+// kernel makes the kernels after it return at once, so whatever the host is about to read is
+// not a result.  Reporting clears the word, so that work can go on afterwards.
+static int sync_and_report(lnn::Device* d) {
+  LNN_CUDA(cudaMemcpyAsync(d->status_host, d->status_dev, sizeof(int) * 4, cudaMemcpyDeviceToHost, d->stream));
+  LNN_CUDA(cudaStreamSynchronize(d->stream));
+  if (d->status_host[0] != 0) {
+    const int st[4] = {d->status_host[0], d->status_host[1], d->status_host[2], d->status_host[3]};
+    LNN_CUDA(cudaMemsetAsync(d->status_dev, 0, sizeof(int) * 4, d->stream));
+    LNN_CUDA(cudaStreamSynchronize(d->stream));
+    return lnn::set_error(LNN_E_TIMEOUT,
+                          "device status %d (role %d, tile %d, step %d): a bounded wait expired in a tile kernel; "
+                          "results computed since then are invalid (the status has been cleared)",
+                          st[0], st[1], st[2], st[3]);
+  }
+  return LNN_OK;
+}
+
 int lnn_d2h(int dev, void* dst, uint64_t src, uint64_t bytes) {
   LNN_DEV(d, dev);
   LNN_REQUIRE(dst && src, "null pointer");
   LNN_CUDA(cudaMemcpyAsync(dst, (const void*)(uintptr_t)src, bytes, cudaMemcpyDeviceToHost, d->stream));
-  LNN_CUDA(cudaStreamSynchronize(d->stream));
-  return LNN_OK;
+  return sync_and_report(d);
 }
 
 int lnn_h2d_async(int dev, uint64_t dst, const void* src, uint64_t bytes) {
@@ -288,6 +313,13 @@ int lnn_d2d(int dev, uint64_t dst, uint64_t src, uint64_t bytes) {
 
 int lnn_sync(int dev) {
   LNN_DEV(d, dev);
+  return sync_and_report(d);
+}
+
+int lnn_debug_set_status(int dev, int code, int role, int tile, int step) {
+  LNN_DEV(d, dev);
+  const int st[4] = {code, role, tile, step};
+  LNN_CUDA(cudaMemcpyAsync(d->status_dev, st, sizeof(st), cudaMemcpyHostToDevice, d->stream));
   LNN_CUDA(cudaStreamSynchronize(d->stream));
   return LNN_OK;
 }

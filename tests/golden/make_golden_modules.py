@@ -10,6 +10,7 @@ of cl_on_cpu.py (no OpenCL device exists where this runs).  Contents of the pick
     losses        the loss of each of the three training steps (two before the save, one after)
     after_step3   dump_state() of the trainer after a third step taken after saving
     input         the training input
+    optimizers    {case: tensors and state after three steps} for module_cases.OPTIMIZERS
 """
 import os
 import pickle
@@ -50,7 +51,8 @@ def main():
     names = [t.get_name() for t in trainer.mod1.trainables()]
     losses.append(module_cases.train_step(nn, trainer, x))
     out = {"file_bytes": file_bytes, "names": names, "losses": [np.asarray(v) for v in losses],
-           "after_step3": trainer.dump_state(), "input": x}
+           "after_step3": trainer.dump_state(), "input": x,
+           "optimizers": {name: module_cases.run_optimizer(nn, name) for name in module_cases.OPTIMIZERS}}
     dst = os.path.join(HERE, "module_ckpt.pkl")
     with open(dst, "wb") as f:
         pickle.dump(out, f, protocol=4)

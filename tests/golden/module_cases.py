@@ -54,3 +54,37 @@ def train_step(nn, trainer, x_np):
     loss.backward()
     opt.step()
     return loss.np()
+
+
+# ---- optimizer update rules ------------------------------------------------------------------
+OPTIMIZERS = {
+    "sgd_plain": ("SGD", dict(lr=0.05)),
+    "sgd_momentum": ("SGD", dict(momentum=0.9, lr=0.05)),
+    "sgd_nesterov_decay": ("SGD", dict(momentum=0.8, nesterov=True, lr=0.05, lr_decay=0.3)),
+    "sgd_dropout": ("SGD", dict(momentum=0.5, lr=0.05, lr_dropout=0.6)),
+    "rmsprop": ("RMSprop", dict(rho=0.9, lr=0.01)),
+    "rmsprop_decay_dropout": ("RMSprop", dict(rho=0.95, lr=0.01, lr_decay=0.1, lr_dropout=0.3)),
+    "adam": ("Adam", dict(beta_1=0.9, beta_2=0.999, lr=0.01)),
+    "adam_dropout": ("Adam", dict(beta_1=0.8, beta_2=0.99, lr=0.02, lr_dropout=0.5)),
+    "sgd_clipnorm": ("SGD", dict(lr=0.05, clipnorm=1.5)),
+}
+
+
+def run_optimizer(nn, name, steps=3):
+    """Three steps of one optimizer on two seeded tensors with seeded gradients; the host random
+    stream is seeded so that the learning-rate-dropout seeds are the same on both sides."""
+    cls, kw = OPTIMIZERS[name]
+    rng = np.random.default_rng(sum(map(ord, name)))
+    ts = [nn.Tensor_from_value(rng.standard_normal(shape).astype(np.float32)) for shape in ((37,), (4, 9))]
+    opt = getattr(nn.optimizer, cls)(ts, **kw)
+    np.random.seed(1234)
+    for _ in range(steps):
+        for t in ts:
+            t.get_grad().set(rng.standard_normal(tuple(t.shape)).astype(np.float32))
+        opt.step()
+    out = {f"t{i}": t.np() for i, t in enumerate(ts)}
+    for k, v in opt.dump_state().items():
+        if isinstance(v, tuple) and v[0] == "np.ndarray":
+            out[f"state/{len(out)}"] = v[1]
+    out["iteration"] = np.asarray(opt.iteration)
+    return out
