@@ -6,14 +6,20 @@ Headline workload (the one quoted at 1/2/4/8 GPUs): inference of the small CNN c
 (conv3x3 3->32 +leaky_relu, maxpool2; 32->64; 64->128; 128->256 +leaky_relu, global average;
 Dense 256->1000), random He-init fp32 weights, input [4096,3,128,128] ~U(0,1) sharded over the
 GPUs by batch index (no collective on the data path).  One step = one pass of a rank over its
-whole shard, in micro-batches of 512 images.  `value` times the pass with inputs resident in
+whole shard, in micro-batches of 1024 images.  `value` times the pass with inputs resident in
 HBM; `e2e` times the same pass through the public API from pinned HOST buffers, host->device
 copy of the images and device->host copy of the logits inside the timed region.  Timing is
 by CUDA events on the stream the kernels run on, max over ranks.
 
+`stock_api` repeats both measurements for the same network written with nothing but the
+reference's namespace (nn.Conv2D, nn.leaky_relu, nn.max_pool2D, ...): the library defers each
+convolution until its consumer is known, so that chain runs through the same fused kernels.
+`e2e.h2d_ceiling_gbs` is a copy-only run of the same uploads (no kernels): what the host side
+can deliver to this rank while all ranks upload at once.
+
 With N = 1 the line also carries `ops`: the single-op configurations (matmul / Dense / conv
-stages in TFLOP/s, the memory-bound sweep in GB/s) and `train`: one training step (softmax-CE,
-SGD lr 1e-3, NCCL gradient all-reduce when N > 1) in images/s.
+stages in TFLOP/s, the memory-bound sweep in GB/s, forward and backward) and `train`: one
+training step (softmax-CE, SGD lr 1e-3, NCCL gradient all-reduce when N > 1) in images/s.
 
 `--impl reference` times the CPU path on the host cores: the C oracle (oracle/lnn_oracle.c,
 a restatement of the reference's kernels, OpenMP over all host threads) on a bounded sample
@@ -35,7 +41,7 @@ sys.path.insert(0, ROOT)
 
 TOTAL_BATCH = 4096
 MICRO_BATCH = 1024
-NCU_TRAFFIC_RATIO = 775.3 / 805.3     # dram bytes / (operand + output bytes), ncu capture of the CNN's conv 2 (tc_halo_kernel)
+NCU_TRAFFIC_RATIO = 775.3 / 805.3     # dram bytes / (operand + output bytes) in an ncu capture of the same kernel on 512 images
 IMG = (3, 128, 128)
 CHANS = [3, 32, 64, 128, 256]
 NCLASS = 1000
@@ -197,51 +203,72 @@ def cnn_weights(seed=0):
     return w
 
 
-class CNN:
-    """The classifier on the product namespace; conv bias + leaky_relu ride in the conv epilogue."""
+def make_cnn(nn, weights, stock=False):
+    """The classifier as an nn.Module (tensor names come from the module tree, as the optimizer
+    requires).
 
-    def __init__(self, nn, weights):
-        self.nn = nn
-        self.training = False      # inference uses the fused conv+bias+lrelu+maxpool entry
-        self.packed = os.environ.get("LNN_BENCH_PACKED", "1") != "0"
-        self.block = os.environ.get("LNN_BENCH_BLOCK", "1") != "0"
-        self.convs = []
-        for i in range(4):
-            c = nn.Conv2D(CHANS[i], CHANS[i + 1], 3, padding="same",
-                          kernel_initializer=nn.initializer.NumpyArray(weights[f"k{i}"]),
-                          bias_initializer=nn.initializer.NumpyArray(weights[f"b{i}"]))
-            self.convs.append(c)
-        self.dense = nn.Dense(256, NCLASS, weight_initializer=nn.initializer.NumpyArray(weights["dw"]),
-                              bias_initializer=nn.initializer.NumpyArray(weights["db"]))
+    stock=False: the library's explicit entries -- conv2D_infer with bias, leaky_relu and the
+    max-pool in the convolution's epilogue and the activation between two convolutions kept in
+    the tensor-core operand format (inference), conv2D_block (training).
+    stock=True: the model as a LiteNN user writes it -- nn.Conv2D modules (conv2D, then + bias),
+    nn.leaky_relu, nn.max_pool2D, nn.reduce_mean, nn.flatten, nn.Dense -- nothing that the
+    reference's namespace does not have."""
 
-    def trainables(self):
-        out = []
-        for c in self.convs:
-            out += c.trainables()
-        return out + self.dense.trainables()
+    class CNN(nn.Module):
+        def __init__(self):
+            self._training_path = False
+            self._packed = os.environ.get("LNN_BENCH_PACKED", "1") != "0"
+            self._block = os.environ.get("LNN_BENCH_BLOCK", "1") != "0"
+            self.convs = [nn.Conv2D(CHANS[i], CHANS[i + 1], 3, padding="same",
+                                    kernel_initializer=nn.initializer.NumpyArray(weights[f"k{i}"]),
+                                    bias_initializer=nn.initializer.NumpyArray(weights[f"b{i}"])) for i in range(4)]
+            self.dense = nn.Dense(256, NCLASS, weight_initializer=nn.initializer.NumpyArray(weights["dw"]),
+                                  bias_initializer=nn.initializer.NumpyArray(weights["db"]))
 
-    def forward(self, x):
-        nn = self.nn
-        for i, c in enumerate(self.convs):
-            if not self.training:
-                # inference: bias, leaky_relu and the max-pool ride in the convolution's epilogue and the
-                # activation between two convolutions stays in the tensor-core operand format
-                x = nn.conv2D_infer(x, c.kernel, 1, 1, "same", bias_t=c.bias, activation="leaky_relu", alpha=0.1,
-                                    pool=i < 3, packed_output=(i < 3 and self.packed))
-                continue
-            if i < 3 and self.block:
-                # trainable fused block: same values and gradients as conv2D -> leaky_relu -> max_pool2D
-                x = nn.conv2D_block(x, c.kernel, 1, 1, "same", bias_t=c.bias, activation="leaky_relu", alpha=0.1)
-            else:
-                x = nn.conv2D(x, c.kernel, 1, 1, "same", bias_t=c.bias, activation="leaky_relu", alpha=0.1)
-                if i < 3:
-                    x = nn.max_pool2D(x, 2, 2, "same")
-        x = nn.flatten(nn.reduce_mean(x, (2, 3)))
-        return self.dense(x)
+        def forward(self, x):
+            for i, c in enumerate(self.convs):
+                if not self._training_path:
+                    x = nn.conv2D_infer(x, c.kernel, 1, 1, "same", bias_t=c.bias, activation="leaky_relu", alpha=0.1,
+                                        pool=i < 3, packed_output=(i < 3 and self._packed))
+                    continue
+                if i < 3 and self._block:
+                    # trainable fused block: same values and gradients as conv2D -> leaky_relu -> max_pool2D
+                    x = nn.conv2D_block(x, c.kernel, 1, 1, "same", bias_t=c.bias, activation="leaky_relu", alpha=0.1)
+                else:
+                    x = nn.conv2D(x, c.kernel, 1, 1, "same", bias_t=c.bias, activation="leaky_relu", alpha=0.1)
+                    if i < 3:
+                        x = nn.max_pool2D(x, 2, 2, "same")
+            x = nn.flatten(nn.reduce_mean(x, (2, 3)))
+            return self.dense(x)
 
-    def loss(self, logits, onehot):
-        nn = self.nn
-        return nn.categorical_crossentropy(nn.softmax(logits), onehot).mean()
+        def loss(self, logits, onehot):
+            return nn.categorical_crossentropy(nn.softmax(logits), onehot).mean()
+
+    class StockCNN(nn.Module):
+        def __init__(self):
+            self.conv1 = nn.Conv2D(3, 32, 3, kernel_initializer=nn.initializer.NumpyArray(weights["k0"]),
+                                   bias_initializer=nn.initializer.NumpyArray(weights["b0"]))
+            self.conv2 = nn.Conv2D(32, 64, 3, kernel_initializer=nn.initializer.NumpyArray(weights["k1"]),
+                                   bias_initializer=nn.initializer.NumpyArray(weights["b1"]))
+            self.conv3 = nn.Conv2D(64, 128, 3, kernel_initializer=nn.initializer.NumpyArray(weights["k2"]),
+                                   bias_initializer=nn.initializer.NumpyArray(weights["b2"]))
+            self.conv4 = nn.Conv2D(128, 256, 3, kernel_initializer=nn.initializer.NumpyArray(weights["k3"]),
+                                   bias_initializer=nn.initializer.NumpyArray(weights["b3"]))
+            self.dense = nn.Dense(256, NCLASS, weight_initializer=nn.initializer.NumpyArray(weights["dw"]),
+                                  bias_initializer=nn.initializer.NumpyArray(weights["db"]))
+
+        def forward(self, x):
+            x = nn.max_pool2D(nn.leaky_relu(self.conv1(x), 0.1))
+            x = nn.max_pool2D(nn.leaky_relu(self.conv2(x), 0.1))
+            x = nn.max_pool2D(nn.leaky_relu(self.conv3(x), 0.1))
+            x = nn.leaky_relu(self.conv4(x), 0.1)
+            x = nn.flatten(nn.reduce_mean(x, (2, 3)))
+            return self.dense(x)
+
+        def loss(self, logits, onehot):
+            return nn.categorical_crossentropy(nn.softmax(logits), onehot).mean()
+
+    return StockCNN() if stock else CNN()
 
 
 def cnn_forward_oracle(o, w, x):
@@ -489,7 +516,8 @@ def run_ours(args):
     n_mb = local_batch // mb
     begin, end = parallel.shard_bounds(TOTAL_BATCH, world, rank)
     weights = cnn_weights()
-    model = CNN(nn, weights)
+    model = make_cnn(nn, weights)
+    stock_model = make_cnn(nn, weights, stock=True)
 
     # synthetic input shard in PINNED host memory + resident device copies
     img_elems = int(np.prod(IMG))
@@ -507,10 +535,11 @@ def run_ours(args):
         lib.lnn_h2d(dev.index, t._ptr(0), host_ptr.value + j * mb * img_elems * 4, mb * img_elems * 4)
         resident.append(t)
 
-    def step_resident():
+    def step_resident(m=None):
+        m = m or model
         last = None
         for t in resident:
-            last = model.forward(t)
+            last = m.forward(t)
         return last
 
     stages = [nn.Tensor((mb,) + IMG), nn.Tensor((mb,) + IMG)]
@@ -528,7 +557,7 @@ def run_ours(args):
         mb_bytes = mb * img_elems * 4
         lib.lnn_h2d_prefetch(dev.index, stages[slot]._ptr(0), host_ptr.value + j * mb_bytes, mb_bytes, done_ev[slot].value)
 
-    def step_e2e(more_steps_follow):
+    def step_e2e(more_steps_follow, m=None):
         """Host images in, logits out.  Every micro-batch of the step is uploaded from pinned host
         memory on the copy stream while the previous one computes; the step's first upload overlaps
         the tail of the previous step (a serving loop with two staging buffers), and is exposed
@@ -542,7 +571,8 @@ def run_ours(args):
                 upload(j + 1, slot ^ 1)
             elif more_steps_follow:
                 upload(0, slot ^ 1)               # first micro-batch of the next step
-            logits = model.forward(stages[slot])
+            logits = (m or model).forward(stages[slot])
+            logits._ptr(0)                            # a deferred chain is launched here
             lib.lnn_event_record(dev.index, done_ev[slot].value)
             # the logits travel to pinned host memory on the read-back stream while the next
             # micro-batch computes; the tensors stay alive until the copies have finished
@@ -557,35 +587,81 @@ def run_ours(args):
     sampler.start()
     timer = DevTimer(nn, dev)
 
+    def timed_blocks(step_fn, steps):
+        """The K-step block, repeated until 0.5 s have been timed (at most 40 blocks); every rank
+        times its own blocks with CUDA events between barriers.  Returns the per-block maxima over
+        the ranks."""
+        blocks = []
+        total = 0.0
+        while True:
+            nn.devices.wait()
+            dist.barrier()
+            timer.start()
+            step_fn(steps)
+            ms_b = timer.stop_ms()
+            nn.devices.wait()
+            dist.barrier()
+            ms_b = dist.max(ms_b)
+            blocks.append(ms_b)
+            total += ms_b
+            if total >= 500.0 or len(blocks) >= 40:
+                return blocks
+
+    def resident_block(m):
+        def run(steps):
+            for _ in range(steps):
+                out = step_resident(m)
+                out._ptr(0)                           # a deferred chain is launched here
+        return run
+
+    def e2e_block(m):
+        def run(steps):
+            for i in range(steps):
+                step_e2e(i + 1 < steps, m)
+        return run
+
     # ---- value: inputs resident in HBM --------------------------------------------------------
-    for _ in range(args.warmup):
-        step_resident()
+    resident_block(model)(args.warmup)
     nn.devices.wait()
     dist.barrier()
     launches0 = dev.launch_count()
     m0 = sampler.mark()
-    timer.start()
-    for _ in range(args.steps):
-        step_resident()
-    ms = timer.stop_ms()
-    nn.devices.wait()
-    dist.barrier()
+    blocks = timed_blocks(resident_block(model), args.steps)
     m1 = sampler.mark()
-    launches = dev.launch_count() - launches0
-    ms_max = dist.max(ms)
+    launches = (dev.launch_count() - launches0) // len(blocks)
+    ms_max = float(np.median(blocks))
     value = TOTAL_BATCH * args.steps / (ms_max / 1000.0)
 
     # ---- e2e: host buffers in, logits out -----------------------------------------------------
-    for _ in range(max(1, args.warmup // 2)):
-        step_e2e(False)
-    dist.barrier()
-    timer.start()
-    for i in range(args.steps):
-        step_e2e(i + 1 < args.steps)
-    ms_e = timer.stop_ms()
-    dist.barrier()
-    ms_e_max = dist.max(ms_e)
+    e2e_block(model)(max(1, args.warmup // 2))
+    e_blocks = timed_blocks(e2e_block(model), args.steps)
+    ms_e_max = float(np.median(e_blocks))
     e2e_value = TOTAL_BATCH * args.steps / (ms_e_max / 1000.0)
+
+    # ---- the same two measurements on the model written with the reference's namespace only -----
+    resident_block(stock_model)(args.warmup)
+    s_blocks = timed_blocks(resident_block(stock_model), args.steps)
+    e2e_block(stock_model)(max(1, args.warmup // 2))
+    se_blocks = timed_blocks(e2e_block(stock_model), args.steps)
+    stock = {"value": round(TOTAL_BATCH * args.steps / (float(np.median(s_blocks)) / 1000.0), 1),
+             "e2e": round(TOTAL_BATCH * args.steps / (float(np.median(se_blocks)) / 1000.0), 1), "unit": "images/s",
+             "what": "the same network built from nn.Conv2D / nn.leaky_relu / nn.max_pool2D / nn.reduce_mean / "
+                     "nn.flatten / nn.Dense only; value = inputs resident, e2e = host buffers in, logits out"}
+
+    # ---- copy-only ceiling of the uploads: same pinned buffers, same calls, all ranks at once ----
+    def copy_block(steps):
+        for _ in range(steps):
+            for j in range(n_mb):
+                slot = j & 1
+                lib.lnn_event_record(dev.index, done_ev[slot].value)
+                upload(j, slot)
+                lib.lnn_wait_prefetch(dev.index)
+    copy_block(1)
+    c_blocks = timed_blocks(copy_block, args.steps)
+    copy_ms = float(np.median(c_blocks)) / args.steps
+    h2d_gbs = -dist.max(-(local_batch * img_elems * 4 / copy_ms / 1e6))     # slowest rank
+    copy_ms = dist.max(copy_ms)
+    e2e_state["primed"] = False
 
     # ---- roofline of the dominant kernel: the implicit-GEMM convolution tile kernel -------------
     lib.lnn_profile_enable(dev.index, 1)
@@ -596,27 +672,41 @@ def run_ours(args):
     lib.lnn_profile_read(dev.index, 1, ctypes.byref(nl), ctypes.byref(tms))
     npre, tpre = ctypes.c_uint64(), ctypes.c_float()
     lib.lnn_profile_read(dev.index, 3, ctypes.byref(npre), ctypes.byref(tpre))
+    nfc, tfc = ctypes.c_uint64(), ctypes.c_float()
+    lib.lnn_profile_read(dev.index, 4, ctypes.byref(nfc), ctypes.byref(tfc))
     lib.lnn_profile_enable(dev.index, 0)
-    # the tile kernel runs convolutions 2-4; the 3-channel input layer runs on the FP32 pipes
+    # the tile engine runs convolutions 2-4; the 3-channel input layer has its own kernel
     conv_flop = (FWD_FLOP_PER_IMAGE - 2 * 256 * 1000 - 2 * 32 * 27 * 128 * 128) * local_batch * prof_steps
     conv_tflops = conv_flop / (tms.value / 1000.0) / 1e12 if tms.value > 0 else 0.0
-    tf32_peak = peaks["bf16_tflops_sustained"] / 2.0
-    # DRAM traffic per launch: operand + output bytes of convolutions 2-4 (hi and lo NHWC copies read
-    # once, NCHW output written once) times the traffic/algorithmic ratio of the committed ncu capture
-    # of the engine's kernels (profiles/tc_halo_kernel_cnn_conv2_ncu.md, profiles/tc_kernel_conv3a_fwd_ncu.md: 0.963 and 0.948);
-    # traffic grows with the units processed.
-    # conv 2 and 3 read packed hi+lo input and write pooled packed hi+lo output; conv 4 writes NCHW
-    conv_bytes_per_image = 4 * ((2 * 32 * 4096 + 2 * 64 * 1024) + (2 * 64 * 1024 + 2 * 128 * 256) + (2 * 128 * 256 + 256 * 256))
+    # Denominators.  fp32 operands are split in two parts and three products are issued per fp32
+    # product.  Split FP16 issues them as kind::f16 (the bf16 / fp16 rate), split TF32 as
+    # kind::tf32 (half that rate).  `frac` keeps the yardstick named for this workload, dense
+    # TF32 = half the measured bf16 rate; `issued_frac` is the share of the pipe actually in use.
+    f16_peak = peaks["bf16_tflops_sustained"]
+    tf32_peak = f16_peak / 2.0
+    products = 1 if passes == 1 else 3
+    pipe_peak = f16_peak if passes == 2 else tf32_peak
+    # DRAM traffic per launch: operand + output bytes of convolutions 2-4 (hi and lo channel-innermost
+    # copies read once, result written once) times the traffic / algorithmic ratio of an ncu capture of
+    # the same kernel on 512 images; traffic grows with the units processed.
+    esz = 2 if passes == 2 else 4
+    conv_bytes_per_image = ((2 * esz * 32 * 4096 + 4 * 64 * 1024) + (2 * esz * 64 * 1024 + 4 * 128 * 256) +
+                            (2 * esz * 128 * 256 + 4 * 256 * 256))
     traffic = NCU_TRAFFIC_RATIO * conv_bytes_per_image * local_batch * prof_steps / max(1, nl.value)
-    roofline = {"bound": "tensor", "kernel": "tcgen05 tile engine (tc_halo_kernel + tc_kernel, implicit-GEMM conv2D, kind::tf32), convolutions 2-4",
+    kind = {1: "kind::tf32, hi only", 2: "kind::f16, split FP16", 3: "kind::tf32, split TF32"}[passes]
+    roofline = {"bound": "tensor", "kernel": f"tcgen05 tile engine (tc_halo_kernel + tc_kernel, implicit-GEMM conv2D, {kind}), convolutions 2-4",
                 "achieved": round(conv_tflops, 2), "peak": round(tf32_peak, 1), "unit": "TFLOP/s",
                 "frac": round(conv_tflops / tf32_peak, 4), "traffic": int(traffic),
-                "traffic_source": "algorithmic operand+output bytes x 0.963, the DRAM/algorithmic ratio ncu measured on the CNN's conv 2 (profiles/tc_halo_kernel_cnn_conv2_ncu.md)",
-                "issued_frac": round(passes * conv_tflops / tf32_peak, 4),
+                "traffic_source": "algorithmic operand+output bytes x 0.963, the DRAM/algorithmic ratio ncu measured on the same kernel at 512 images",
+                "issued_frac": round(products * conv_tflops / pipe_peak, 4),
+                "frac_of_f16_peak": round(conv_tflops / f16_peak, 4),
                 "launches": int(nl.value), "avg_launch_ms": round(tms.value / max(1, nl.value), 4),
                 "prepass_ms_per_step": round(tpre.value / prof_steps, 3),
-                "peak_source": f"dense TF32 taken as half of the {peaks['source']} sustained bf16 cuBLAS rate; "
-                               f"achieved counts algorithmic 2*M*N*K flops, issued_frac counts the {passes} TF32 MMAs per product"}
+                "first_layer": {"kernel": "fewch_conv_kernel (3-channel input layer on the tensor cores)",
+                                "launches": int(nfc.value), "avg_launch_ms": round(tfc.value / max(1, nfc.value), 4)},
+                "peak_source": f"peak = dense TF32 taken as half of the {peaks['source']} sustained bf16 cuBLAS rate; achieved counts "
+                               f"algorithmic 2*M*N*K flops; issued_frac counts the {products} products issued per fp32 product "
+                               f"against the {peaks['source']} rate of the pipe they run on ({pipe_peak:.0f} TFLOP/s)"}
 
     # ---- training step (softmax-CE, SGD lr 1e-3, NCCL gradient all-reduce) ---------------------
     train = None
@@ -634,7 +724,7 @@ def run_ours(args):
             onehots.append(nn.Tensor_from_value(oh))
         scale = 1.0 / n_mb
 
-        model.training = True
+        model._training_path = True
 
         def train_step():
             last = None
@@ -663,6 +753,10 @@ def run_ours(args):
         train = {"value": round(TOTAL_BATCH * tsteps / (ms_t_max / 1000.0), 1), "unit": "images/s", "steps": tsteps,
                  "ms_per_step": round(ms_t_max / tsteps, 2), "last_micro_batch_loss": loss_val,
                  "what": "forward + softmax-CE + backward + SGD(lr 1e-3)" + (" + NCCL all-reduce of 645,416 gradients" if world > 1 else "")}
+        if world > 1:
+            # the replicas started equal and applied the same averaged gradient: they must still be equal
+            sums = [float(t.sum().np()[0]) for t in model.trainables()]
+            train["replicas_equal"] = all(dist.max(v) == -dist.max(-v) for v in sums)
         del onehots
 
     clocks = sampler.summary(m0, m1)
@@ -688,7 +782,12 @@ def run_ours(args):
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": workload_config(world),
                 "e2e": {"value": round(e2e_value, 1), "unit": "images/s", "h2d_bytes_per_step": local_batch * img_elems * 4,
-                        "d2h_bytes_per_step": local_batch * NCLASS * 4, "ms_per_step": round(ms_e_max / args.steps, 3)},
+                        "d2h_bytes_per_step": local_batch * NCLASS * 4, "ms_per_step": round(ms_e_max / args.steps, 3),
+                        "h2d_ceiling_gbs": round(h2d_gbs, 2),
+                        "h2d_ceiling_images_per_s": round(TOTAL_BATCH / (copy_ms / 1000.0), 1),
+                        "h2d_ceiling_what": "copy-only run of the same uploads (same pinned buffers and calls, no kernels), all "
+                                            "ranks at once: slowest rank's GB/s, and the images/s that upload rate allows"},
+                "stock_api": stock, "timed_blocks": len(blocks),
                 "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline,
                 "model_tflops": round(value * FWD_FLOP_PER_IMAGE / 1e12, 2)}
         if cpu is not None:

@@ -108,7 +108,8 @@ int lnn_event_destroy(int dev, uint64_t ev);
 /* Optional per-kernel timing: while enabled, launches of the slots below are bracketed by
  * CUDA events on the device stream; lnn_profile_read synchronises, then returns how many
  * launches a slot saw and their summed device time, and clears the slot. */
-enum { LNN_PROF_TC_GEMM = 0, LNN_PROF_TC_CONV = 1, LNN_PROF_TC_DW = 2, LNN_PROF_PREP = 3, LNN_PROF_SLOTS = 4 };
+enum { LNN_PROF_TC_GEMM = 0, LNN_PROF_TC_CONV = 1, LNN_PROF_TC_DW = 2, LNN_PROF_PREP = 3, LNN_PROF_FEWCH = 4,
+       LNN_PROF_SLOTS = 5 };
 int lnn_profile_enable(int dev, int on);
 int lnn_profile_read(int dev, int slot, uint64_t* launches, float* total_ms);
 

@@ -7,11 +7,11 @@ Classes and Modules are upper case, operators lower case, initializers under
 Every operator runs hand-written sm_100a kernels through a C-ABI shared library
 (include/litenn_b200.h); there is no CPU or PyTorch fallback.
 """
-from . import info, initializer, optimizer, ops, parallel
+from . import deferred, info, initializer, optimizer, ops, parallel
 from ._lib import LnnError
 from .autograd import backward
 from .devices import devices
-from .module import Conv2D, Dense, Module
+from .module import Conv2D, Dense, Module, ModuleBase
 from .ops import (abs, add, add_const, avg_pool2D, binary_crossentropy, categorical_crossentropy, clip,
                   conv2D, conv2D_block, conv2D_infer, conv2D_pool, pack_activation, PackedActivation, cos, dense, div, div_const, exp, flatten, leaky_relu, log, matmul, max, max_pool2D,
                   min, min_pool2D, moments, mul, mul_const, rdiv_const, reduce_max, reduce_mean, reduce_min,

@@ -38,11 +38,9 @@ def backward(loss, stop_grad=None, grad_for_non_trainables=False, keep_gradient_
             reaches[sid] = False          # cycle guard; the tape is a DAG
             r = t._is_trainable()
             if not r:
-                fns = t._get_gradfns()
-                if fns is not None:
-                    for inp in fns:
-                        if visit(inp):
-                            r = True
+                for inp in t._tape_inputs():
+                    if visit(inp):
+                        r = True
             reaches[sid] = r
             return r
 

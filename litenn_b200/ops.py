@@ -11,6 +11,7 @@ import numpy as np
 from collections.abc import Iterable
 
 from . import _lib
+from . import deferred as _deferred
 from . import initializer as _initializer
 from .devices import devices
 from .info import (InfoBroadcast, InfoConv2D, InfoReduction, InfoReshape, InfoSlice, InfoTranspose)
@@ -88,7 +89,9 @@ def cos(input_t): return cos_op(input_t)
 def exp_op(input_t, output_t=None, is_add_to_output=False): return _ew("exp", (0.0, 0.0, 0), input_t, output_t, is_add_to_output)
 def exp(input_t): return exp_op(input_t)
 def leaky_relu_op(input_t, alpha, output_t=None, is_add_to_output=False): return _ew("leaky_relu", (float(alpha), 0.0, 0), input_t, output_t, is_add_to_output)
-def leaky_relu(input_t, alpha=0.1): return leaky_relu_op(input_t, alpha)
+def leaky_relu(input_t, alpha=0.1):
+    fused = _deferred.try_act(input_t, alpha)       # joins a convolution that has not been launched yet
+    return fused if fused is not None else leaky_relu_op(input_t, alpha)
 def log_op(input_t, output_t=None, is_add_to_output=False): return _ew("log", (0.0, 0.0, 0), input_t, output_t, is_add_to_output)
 def log(input_t): return log_op(input_t)
 def mul_const_op(input_t, value, output_t=None, is_add_to_output=False): return _ew("mul_const", (float(value), 0.0, 0), input_t, output_t, is_add_to_output)
@@ -165,7 +168,13 @@ def _bin_grad(name, info, which, a_t, b_t, O_t, dO_t):
         reduce_sum_op(dst, red, output_t=target.get_grad(), is_add_to_output=True)
 
 
-def add_op(a_t, b_t, output_t=None, is_add_to_output=False): return _bin("add", a_t, b_t, output_t, is_add_to_output)
+def add_op(a_t, b_t, output_t=None, is_add_to_output=False):
+    if output_t is None:
+        # conv2D(...) + bias.reshape(1, OC, 1, 1): the bias joins the convolution's epilogue
+        fused = _deferred.try_bias(a_t, b_t) or _deferred.try_bias(b_t, a_t)
+        if fused is not None:
+            return fused
+    return _bin("add", a_t, b_t, output_t, is_add_to_output)
 def add(a_t, b_t): return add_op(a_t, b_t)
 def sub_op(a_t, b_t, output_t=None, is_add_to_output=False): return _bin("sub", a_t, b_t, output_t, is_add_to_output)
 def sub(a_t, b_t): return sub_op(a_t, b_t)
@@ -427,6 +436,9 @@ def pool2D_op(op_type, input_t, pool_size=2, stride=2, padding="same"):
     pool_size, stride = int(pool_size), int(stride)
     if pool_size < 2:
         raise ValueError(f"pool_size {pool_size} must be at least 2")
+    fused = _deferred.try_pool(op_type, input_t, pool_size, stride, padding)
+    if fused is not None:
+        return fused
     N, IC, IH, IW = input_t.shape
     ci = InfoConv2D(IH, IW, pool_size, pool_size, stride, 1, padding)
     geom = (N, IC, IH, IW, ci.OH, ci.OW, pool_size, stride, ci.PADL, ci.PADT)
@@ -548,10 +560,20 @@ def conv2D(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t=None,
         raise ValueError(f"unknown activation {activation}")
     if bias_t is not None and bias_t.shape.size != g.oc:
         raise ValueError(f"bias must have {g.oc} elements")
+    if activation == "leaky_relu" and alpha <= 0.0:
+        # the fused gradient reads leaky_relu' off the sign of the OUTPUT, which only mirrors the
+        # sign of the input for alpha > 0: other slopes run as the separate operators
+        y = leaky_relu(conv2D(input_t, kernel_t, stride, dilation, padding, bias_t=bias_t), alpha)
+        return pool2D_op("max", y, 2, 2, "same") if _pooled else y
+    act = 1 if activation == "leaky_relu" else 0
+    if not _pooled:
+        # nothing upstream needs a gradient: the launch waits until the consumer is known
+        lazy = _deferred.start(input_t, kernel_t, stride, dilation, padding, g, out_shape, bias_t, act, alpha)
+        if lazy is not None:
+            return lazy
     passes = _lib.precision()
     output_t = _out(out_shape)
     output_t._set_op_name("conv2D")
-    act = 1 if activation == "leaky_relu" else 0
     conv_out_t = output_t
     if _pooled:
         # conv2D_block: the tensor handed to the caller (and carrying the grad functions) is the

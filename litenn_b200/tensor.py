@@ -31,6 +31,7 @@ class Tensor(DevicesBuffers):
         self._op_name = None
         self._op = None
         self._parent_module_w = None
+        self._pending = None        # work not launched yet (deferred.py); None for ordinary tensors
         super().__init__(shape.size * 4, init_func=lambda buf: init.initialize_buffer(buf, shape))
 
     def __del__(self):
@@ -236,12 +237,31 @@ class Tensor(DevicesBuffers):
     def _as_ref(self, shape):
         return TensorRef(self, shape)
 
+    def _get_buffers(self):
+        """The device buffers; a deferred convolution is launched first (deferred.py)."""
+        if self._pending is not None and not self._pending.done:
+            from . import deferred
+            deferred.materialize(self)
+        return self._buffers
+
     def _is_freezed(self): return self._freezed
     def _is_reference(self): return False
     def _is_grad(self): return False
     def _is_trainable(self): return self._trainable
-    def _is_produced_by_op(self): return self._get_gradfns() is not None
-    def _get_gradfns(self): return self._gradfns
+    def _is_produced_by_op(self): return self._gradfns is not None or self._pending is not None
+
+    def _get_gradfns(self):
+        if self._gradfns is None and self._pending is not None:
+            from . import deferred
+            self._gradfns = deferred.build_gradfns(self)
+        return self._gradfns
+
+    def _tape_inputs(self):
+        """Input tensors of the op that produced this one (empty for leaves)."""
+        if self._gradfns is None and self._pending is not None:
+            from . import deferred
+            return deferred.tape_inputs(self)
+        return list(self._gradfns.keys()) if self._gradfns is not None else []
     def _get_reference_source(self): return self
     def _get_seq_id(self): return self._seq_id
 
@@ -291,6 +311,8 @@ class TensorRef(Tensor):
     def _is_trainable(self): return self._t._is_trainable()
     def _get_buffers(self): return self._t._get_buffers()
     def _get_gradfns(self): return self._t._get_gradfns()
+    def _tape_inputs(self): return self._t._tape_inputs()
+    def _is_produced_by_op(self): return self._t._is_produced_by_op()
     def _get_reference_source(self): return self._t
     def _get_seq_id(self): return self._t._get_seq_id()
     def _set_trainable(self, *a, **k): self._t._set_trainable(*a, **k)

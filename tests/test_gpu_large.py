@@ -173,10 +173,13 @@ def test_cnn_micro_batch_against_oracle(nn_gpu):
     import oracle as o
     nn = nn_gpu
     w = bench.cnn_weights()
-    model = bench.CNN(nn, w)
     x = np.random.default_rng(9).uniform(0, 1, (bench.MICRO_BATCH,) + bench.IMG).astype(np.float32)
-    logits = model.forward(nn.Tensor_from_value(x)).np()
-    idx = [0, 17, 255, 511]
+    xt = nn.Tensor_from_value(x)
+    logits = bench.make_cnn(nn, w).forward(xt).np()
+    idx = [0, 17, 255, 511, bench.MICRO_BATCH - 1]
     want = bench.cnn_forward_oracle(o, w, x[idx])
     np.testing.assert_allclose(logits[idx], want, rtol=2e-4, atol=2e-4)
+    # the same network written with the reference's namespace only: same kernels, same values
+    stock = bench.make_cnn(nn, w, stock=True).forward(xt).np()
+    assert_bit_exact(stock, logits, "stock-namespace model vs the explicit fused entries")
     nn.devices.check_status()

@@ -190,7 +190,7 @@ def test_shallow_forward_allocates_nothing(nn_gpu):
 
     dev = nn.devices.get_current()[0]
     before = dev.get_used_memory()
-    launches = dev.get_launch_count() if hasattr(dev, "get_launch_count") else None
+    launches = dev.launch_count() if hasattr(dev, "launch_count") else None
     m = Module1()
     m.set_training(True)
     assert m.is_training() and m.conv.is_training()
@@ -198,7 +198,7 @@ def test_shallow_forward_allocates_nothing(nn_gpu):
     assert tuple(out.shape) == (1, 1, 8, 8)
     assert dev.get_used_memory() == before, "memory was allocated in shallow_forward"
     if launches is not None:
-        assert dev.get_launch_count() == launches, "kernels were launched in shallow_forward"
+        assert dev.launch_count() == launches, "kernels were launched in shallow_forward"
 
 
 def test_expired_wait_is_reported_by_the_next_read(nn_gpu):

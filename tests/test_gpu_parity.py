@@ -105,14 +105,16 @@ def test_fused_conv_bias_lrelu_equals_unfused(nn_gpu):
     nn = nn_gpu
     ins, _ = load_golden("conv_config1")["conv_config1"]
     x, w, b = (nn.Tensor_from_value(ins[k]) for k in ("x", "w", "b"))
-    unfused = nn.leaky_relu(nn.conv2D(x, w) + b.reshape((1, -1, 1, 1)), 0.1).np()
+    with nn.deferred.disabled():          # one kernel per operator, as the reference runs the chain
+        unfused = nn.leaky_relu(nn.conv2D(x, w) + b.reshape((1, -1, 1, 1)), 0.1).np()
     fused = nn.conv2D(x, w, bias_t=b, activation="leaky_relu", alpha=0.1).np()
     assert_bit_exact(fused, unfused, "conv epilogue fusion")
     # non-finite pre-activations must take the reference's literal form (0 * inf = NaN)
     bs = ins["b"].copy()
     bs[:4] = [np.inf, -np.inf, np.nan, 3e38]
     b2 = nn.Tensor_from_value(bs)
-    unfused = nn.leaky_relu(nn.conv2D(x, w) + b2.reshape((1, -1, 1, 1)), 0.1).np()
+    with nn.deferred.disabled():
+        unfused = nn.leaky_relu(nn.conv2D(x, w) + b2.reshape((1, -1, 1, 1)), 0.1).np()
     fused = nn.conv2D(x, w, bias_t=b2, activation="leaky_relu", alpha=0.1).np()
     assert_bit_exact(fused, unfused, "conv epilogue fusion, non-finite bias")
 
@@ -129,7 +131,8 @@ def test_conv_pool_fusion_equals_chain(nn_gpu, xs, ws):
     w = (rng.standard_normal(ws) * 0.2).astype(np.float32)
     b = rng.uniform(-0.1, 0.1, (ws[0],)).astype(np.float32)
     xt, wt, bt = nn.Tensor_from_value(x), nn.Tensor_from_value(w), nn.Tensor_from_value(b)
-    chain = nn.max_pool2D(nn.conv2D(xt, wt, bias_t=bt, activation="leaky_relu", alpha=0.1), 2, 2, "same").np()
+    with nn.deferred.disabled():
+        chain = nn.max_pool2D(nn.conv2D(xt, wt, bias_t=bt, activation="leaky_relu", alpha=0.1), 2, 2, "same").np()
     fused = nn.conv2D_pool(xt, wt, bias_t=bt, activation="leaky_relu", alpha=0.1).np()
     assert_bit_exact(fused, chain, "conv2D_pool vs chain")
     want = o.pool2d_fwd("max", o.conv2d_fwd(x, w, 1, 1, "same", bias=b, act=1, alpha=0.1, accum64=True), 2, 2, "same")
@@ -233,12 +236,18 @@ def test_training_steps_do_not_accumulate_memory(nn_gpu):
     lib = _lib.get_lib()
     dev = nn.devices.get_current()[0]
     rng = np.random.default_rng(3)
-    c1 = nn.Conv2D(3, 8, 3)
-    c2 = nn.Conv2D(8, 16, 3)
-    dense = nn.Dense(16, 5)
+
+    class Net(nn.Module):
+        def __init__(self):
+            self.c1 = nn.Conv2D(3, 8, 3)
+            self.c2 = nn.Conv2D(8, 16, 3)
+            self.dense = nn.Dense(16, 5)
+
+    net = Net()
+    c1, c2, dense = net.c1, net.c2, net.dense
     x = nn.Tensor_from_value(rng.standard_normal((4, 3, 16, 16)).astype(np.float32))
     onehot = nn.Tensor_from_value(np.eye(5, dtype=np.float32)[rng.integers(0, 5, 4)])
-    opt = nn.optimizer.SGD(c1.trainables() + c2.trainables() + dense.trainables(), lr=1e-3)
+    opt = nn.optimizer.SGD(net.trainables(), lr=1e-3)
 
     def step():
         h = nn.conv2D_block(x, c1.kernel, bias_t=c1.bias, activation="leaky_relu", alpha=0.1)
@@ -301,7 +310,8 @@ def test_conv_infer_fused_and_packed(nn_gpu, xs, ws):
     b = rng.uniform(-0.1, 0.1, (ws[0],)).astype(np.float32)
     xt, wt, bt = nn.Tensor_from_value(x), nn.Tensor_from_value(w), nn.Tensor_from_value(b)
     kw = dict(bias_t=bt, activation="leaky_relu", alpha=0.1)
-    chain = nn.max_pool2D(nn.conv2D(xt, wt, **kw), 2, 2, "same").np()
+    with nn.deferred.disabled():
+        chain = nn.max_pool2D(nn.conv2D(xt, wt, **kw), 2, 2, "same").np()
     pooled = nn.conv2D_infer(xt, wt, pool=True, **kw).np()
     assert_bit_exact(pooled, chain, "pool fused into the epilogue")
     packed = nn.conv2D_infer(xt, wt, pool=True, packed_output=True, **kw)
@@ -342,7 +352,8 @@ def test_fused_pool_epilogue_non_finite(nn_gpu, xs, ws):
     x[1, 1, 9, 4] = np.nan
     xt, wt, bt = nn.Tensor_from_value(x), nn.Tensor_from_value(w), nn.Tensor_from_value(b)
     kw = dict(bias_t=bt, activation="leaky_relu", alpha=0.1)
-    chain = nn.max_pool2D(nn.conv2D(xt, wt, **kw), 2, 2, "same").np()
+    with nn.deferred.disabled():
+        chain = nn.max_pool2D(nn.conv2D(xt, wt, **kw), 2, 2, "same").np()
     fused = nn.conv2D_infer(xt, wt, pool=True, **kw).np()
     assert_bit_exact(fused, chain, "fused pool epilogue with non-finite values")
     nn.devices.check_status()
