@@ -305,6 +305,41 @@ def cpu_cnn_images_per_s(target_seconds, seed=1):
     return n / dt, cores, f"{n} of {TOTAL_BATCH} images, forward pass, C oracle with OpenMP on {cores} threads", dt
 
 
+def cpu_single_ops():
+    """The reference's CPU path on configurations 1 and 2 at full size (one run each): the C
+    oracle's sequential-k GEMM and direct convolution with OpenMP over all host threads."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle as o
+    o.build()
+    cores = o.set_threads(len(os.sched_getaffinity(0)))
+    rng = np.random.default_rng(0)
+    out = {}
+    x = rng.standard_normal((8, 16, 32, 32)).astype(np.float32)
+    w = (rng.standard_normal((32, 16, 3, 3)) * np.sqrt(2.0 / 144)).astype(np.float32)
+    b = rng.uniform(-0.1, 0.1, (32,)).astype(np.float32)
+    o.conv2d_fwd(x, w, 1, 1, "same", bias=b)
+    t0 = time.perf_counter()
+    for _ in range(5):
+        o.conv2d_fwd(x, w, 1, 1, "same", bias=b)
+    dt = (time.perf_counter() - t0) / 5
+    out["conv_config1_8x16x32x32_k3_fwd"] = {"ms": round(dt * 1e3, 3), "gflops": round(75497472 / dt / 1e9, 2)}
+    a = (rng.standard_normal((4096, 4096)) / 64).astype(np.float32)
+    bm = (rng.standard_normal((4096, 4096)) / 64).astype(np.float32)
+    t0 = time.perf_counter()
+    o.gemm(a, bm)
+    dt = time.perf_counter() - t0
+    out["matmul_4096_fwd"] = {"ms": round(dt * 1e3, 1), "gflops": round(2.0 * 4096 ** 3 / dt / 1e9, 2)}
+    xd = rng.standard_normal((8192, 1024)).astype(np.float32)
+    wd = (rng.standard_normal((1024, 4096)) / 32).astype(np.float32)
+    bd = rng.uniform(-0.1, 0.1, (4096,)).astype(np.float32)
+    t0 = time.perf_counter()
+    o.gemm(xd, wd, bias=bd)
+    dt = time.perf_counter() - t0
+    out["dense_8192x1024x4096_fwd"] = {"ms": round(dt * 1e3, 1), "gflops": round(2.0 * 8192 * 1024 * 4096 / dt / 1e9, 2)}
+    return {"cores": cores, "kind": "port", "what": "C oracle (the reference's kernels restated), OpenMP, one full-size run each",
+            "ops": out}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -385,6 +420,39 @@ def op_cases(nn, dev, lib, passes):
 
     cases.append(("dense_8192x1024x4096_fwd", dense_setup))
 
+    def dense_bwd(kind):
+        def setup():
+            x = T(rng.standard_normal((8192, 1024)).astype(np.float32))
+            w = T(rng.standard_normal((1024, 4096)).astype(np.float32) / 32)
+            dy = T(np.random.default_rng(1).standard_normal((8192, 4096)).astype(np.float32))
+            if kind == "dX":      # dX += dY . W^T
+                dx = nn.Tensor((8192, 1024))
+                return (lambda: gemm(dx, dy, w, 0, 8192, 1024, 4096, 0, 1, 1)), 2.0 * 8192 * 1024 * 4096, None, None
+            if kind == "dW":      # dW += X^T . dY
+                dw = nn.Tensor((1024, 4096))
+                return (lambda: gemm(dw, x, dy, 0, 1024, 4096, 8192, 1, 0, 1)), 2.0 * 8192 * 1024 * 4096, None, None
+            db = nn.Tensor((4096,))   # db += reduce_sum(dY, 0)
+            return (lambda: nn.ops.reduce_sum_op(dy, 0, output_t=db, is_add_to_output=True)), None, 8192 * 4096 * 4, None
+        return setup
+
+    for kind in ("dX", "dW", "db"):
+        cases.append((f"dense_8192x1024x4096_{kind}", dense_bwd(kind)))
+
+    def tape_bwd(forward, shape, nbytes, note, lo=-1.0, hi=1.0, extra=()):
+        """Backward of a single operator: its grad functions, called as backward() calls them
+        (gradients are accumulated, "+=", into a gradient tensor that already exists)."""
+        def setup():
+            x = T(rng.uniform(lo, hi, shape).astype(np.float32))
+            others = [T(a) for a in extra]
+            y = forward(x, *others)
+            y._ptr(0)
+            dy = T(np.random.default_rng(2).standard_normal(tuple(y.shape)).astype(np.float32))
+            fns = [f for inp, fl in y._get_gradfns().items() if inp is x for f in fl]
+            x.get_grad()._ptr(0)
+            keep = (x, y, dy, others)
+            return (lambda: [f(y, dy) for f in fns] and keep and None), None, nbytes, note
+        return setup
+
     convs = [("conv3a_256x64x56x56_k3s1", (256, 64, 56, 56), (64, 64, 3, 3), 1, 1),
              ("conv3b_256x128x56x56_k3s2", (256, 128, 56, 56), (256, 128, 3, 3), 2, 1),
              ("conv3c_256x256x28x28_k1", (256, 256, 28, 28), (1024, 256, 1, 1), 1, 0),
@@ -423,6 +491,11 @@ def op_cases(nn, dev, lib, passes):
 
     cases.append(("max_pool2D_256x128x112x112", pool("max_pool2D")))
     cases.append(("avg_pool2D_256x128x112x112", pool("avg_pool2D")))
+    pin, pout = 256 * 128 * 112 * 112 * 4, 256 * 128 * 56 * 56 * 4
+    cases.append(("max_pool2D_256x128x112x112_bwd", tape_bwd(lambda x: nn.max_pool2D(x), (256, 128, 112, 112), 3 * pin + 2 * pout,
+                                                             "dI += dO at the first maximum of each window: reads I, O, dO, dI; writes dI")))
+    cases.append(("avg_pool2D_256x128x112x112_bwd", tape_bwd(lambda x: nn.avg_pool2D(x), (256, 128, 112, 112), 2 * pin + pout,
+                                                             "dI += dO / count: reads dO, dI; writes dI")))
 
     rb = 256 * 512 * 1024 * 4
 
@@ -444,6 +517,10 @@ def op_cases(nn, dev, lib, passes):
         cases.append((f"reduce_{opname}_all", red(opname, "all")))
         cases.append((f"reduce_{opname}_axes23_view", red(opname, "view")))
 
+    cases.append(("reduce_sum_axis1_bwd", tape_bwd(lambda x: nn.reduce_sum(x, (1,)), (256, 512, 1024), 2 * rb + 256 * 1024 * 4,
+                                                   "dI += broadcast(dO): reads dO, dI; writes dI")))
+    cases.append(("reduce_max_axis1_bwd", tape_bwd(lambda x: nn.reduce_max(x, (1,)), (256, 512, 1024), 3 * rb + 2 * 256 * 1024 * 4,
+                                                   "dI += dO at the maximum: reads I, O, dO, dI; writes dI")))
     cb = 2 * 256 * 256 * 56 * 56 * 4
 
     def chain(fused):
@@ -460,6 +537,21 @@ def op_cases(nn, dev, lib, passes):
 
     cases.append(("chain_lrelu_xg_b_fused", chain(True)))
     cases.append(("chain_lrelu_xg_b_3ops", chain(False)))
+
+    def chain_bwd():
+        xc = T(rng.standard_normal((256, 256, 56, 56)).astype(np.float32))
+        gc = T(rng.uniform(0.5, 1.5, (1, 256, 1, 1)).astype(np.float32))
+        bc = T(rng.uniform(-0.5, 0.5, (1, 256, 1, 1)).astype(np.float32))
+        dy = T(np.random.default_rng(2).standard_normal((256, 256, 56, 56)).astype(np.float32))
+        xc.get_grad()._ptr(0)
+
+        def run():
+            y = nn.leaky_relu(xc * gc + bc, 0.1)
+            nn.backward({y: dy}, grad_for_non_trainables=True)
+        return run, None, 2 * cb, "forward and backward of the three-operator chain through the tape (dx, dg, db); GB/s " \
+                                  "counts x, y, dy, dx once each"
+
+    cases.append(("chain_lrelu_xg_b_3ops_fwd_bwd", chain_bwd))
     return cases
 
 
@@ -775,6 +867,8 @@ def run_ours(args):
     if rank == 0 and world == 1 and not args.no_cpu:
         v, cores, sample, _ = cpu_cnn_images_per_s(15.0)
         cpu = {"value": round(v, 3), "unit": "images/s", "cores": cores, "kind": "port", "sample": sample}
+        if not args.no_ops:
+            cpu["single_ops"] = cpu_single_ops()
 
     if rank == 0:
         line = {"metric": "cnn_inference_images_per_s", "value": round(value, 1), "unit": "images/s", "n_gpus": world,

@@ -387,6 +387,31 @@ reduce_bwd_bcast_rows4_kernel(float4* __restrict__ dI, const float* __restrict__
   }
 }
 
+// The same gradient when kept axes follow the reduced ones (inner > 1): four consecutive elements
+// of dI share every index but the innermost, so dO is read as float4 too (inner % 4 == 0).
+__global__ void __launch_bounds__(kThreads)
+reduce_bwd_bcast_inner4_kernel(float4* __restrict__ dI, const float4* __restrict__ dO, int64_t total4,
+                               RedGeom g, float mean_div) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  const int64_t inner4 = g.inner >> 2;
+  for (int64_t gid = tid; gid < total4; gid += nthreads) {
+    int64_t x = gid;
+    const int64_t inner_i = x % inner4; x /= inner4;
+    x /= g.r1;
+    const int64_t mid_i = x % g.mid; x /= g.mid;
+    x /= g.r0;
+    float4 v = __ldg(dO + (x * g.mid + mid_i) * inner4 + inner_i);
+    if (mean_div != 0.0f) {
+      v.x = __fdiv_rn(v.x, mean_div); v.y = __fdiv_rn(v.y, mean_div);
+      v.z = __fdiv_rn(v.z, mean_div); v.w = __fdiv_rn(v.w, mean_div);
+    }
+    float4 o = dI[gid];
+    o.x = __fadd_rn(o.x, v.x); o.y = __fadd_rn(o.y, v.y); o.z = __fadd_rn(o.z, v.z); o.w = __fadd_rn(o.w, v.w);
+    dI[gid] = o;
+  }
+}
+
 __global__ void __launch_bounds__(kThreads)
 reduce_bwd_bcast_kernel(float* __restrict__ dI, const float* __restrict__ dO, int64_t total,
                         RedGeom g, float mean_div) {
@@ -660,6 +685,13 @@ int lnn_reduce_bwd(int dev, int op, uint64_t dI, uint64_t I, uint64_t dO, uint64
     const float mean_div_rows = op == LNN_RED_MEAN ? (float)(r0 * r1) : 0.0f;
     reduce_bwd_bcast_rows4_kernel<<<grid_for(d, total / 4), kThreads, 0, d->stream>>>(
         (float4*)(uintptr_t)dI, (const float*)(uintptr_t)dO, total / 4, r1 / 4, mean_div_rows);
+    LNN_CHECK_LAUNCH(d);
+    return LNN_OK;
+  }
+  if ((op == LNN_RED_SUM || op == LNN_RED_MEAN) && inner % 4 == 0 && ((dI | dO) & 15) == 0) {
+    reduce_bwd_bcast_inner4_kernel<<<grid_for(d, total / 4), kThreads, 0, d->stream>>>(
+        (float4*)(uintptr_t)dI, (const float4*)(uintptr_t)dO, total / 4, g,
+        op == LNN_RED_MEAN ? (float)(r0 * r1) : 0.0f);
     LNN_CHECK_LAUNCH(d);
     return LNN_OK;
   }

@@ -1693,7 +1693,10 @@ int launch_conv_like(lnn::Device* d, const Operand& act, const Operand& w, const
   // 256 pixels) goes on N and the channels on M ("channels on M", MODE_CONVT); with very few
   // output channels the pixels go on M and the channels on N.
   int orient = knobs().orient;
-  if (orient == 0) orient = (c.OCv >= 64 && c.OCv <= 128) ? 2 : 1;
+  // (measured: with 64 or more output channels the channels-on-M epilogue -- 128-bit stores along
+  // W -- is the faster one whenever the output is unit-stride along W; the strided scatter of a
+  // stride-2 input gradient is better served by pixels on M)
+  if (orient == 0) orient = (c.OCv >= 64 && c.out_sb == 1) ? 2 : 1;
   const bool chan_m = orient == 2;
   PixTile t = plan_conv_tile(c.NL, c.AH, c.AW, c.es, chan_m ? 256 : 128);
   if (pooled) {

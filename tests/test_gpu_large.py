@@ -57,10 +57,27 @@ def test_matmul_4096_and_dense(nn_gpu):
     x = rng.standard_normal((8192, 1024)).astype(np.float32)
     w = (rng.standard_normal((1024, 4096)) / 32).astype(np.float32)
     bias = rng.uniform(-0.1, 0.1, (4096,)).astype(np.float32)
-    y = nn.dense(nn.Tensor_from_value(x), nn.Tensor_from_value(w), nn.Tensor_from_value(bias)).np()
+    xt, wt, bt2 = nn.Tensor_from_value(x), nn.Tensor_from_value(w), nn.Tensor_from_value(bias)
+    yt = nn.dense(xt, wt, bt2)
+    y = yt.np()
     rows = rng.choice(8192, 32, replace=False)
     want = x[rows].astype(np.float64) @ w.astype(np.float64) + bias
     assert_contraction_close(y[rows], want, 1024, "Dense forward (sampled rows)")
+    # Dense backward at the same size: dX = dY.W^T, dW = X^T.dY, db = sum over the batch, each
+    # accumulated into a gradient pre-filled with 1 (module/Dense.py:44-48, op/matmul.py:64-72,
+    # op/dual_wise_op.py:110-130)
+    dy = np.random.default_rng(1).standard_normal((8192, 4096)).astype(np.float32)
+    for t in (xt, wt, bt2):
+        t.get_grad().fill(1.0)
+    nn.backward({yt: dy}, grad_for_non_trainables=True)
+    dx, dw, dbias = xt.get_grad().np(), wt.get_grad().np(), bt2.get_grad().np()
+    want_dx = 1.0 + dy[rows].astype(np.float64) @ w.astype(np.float64).T
+    assert_contraction_close(dx[rows], want_dx, 4096, "Dense dX (sampled rows)")
+    wrows = rng.choice(1024, 32, replace=False)
+    want_dw = 1.0 + x.astype(np.float64).T[wrows] @ dy.astype(np.float64)
+    assert_contraction_close(dw[wrows], want_dw, 8192, "Dense dW (sampled rows)")
+    want_db = 1.0 + dy.astype(np.float64).sum(0)
+    np.testing.assert_allclose(dbias, want_db, rtol=1e-5, atol=2e-3, err_msg="Dense db")
 
 
 CONV_STAGES = [((256, 64, 56, 56), (64, 64, 3, 3), 1, 1), ((256, 128, 56, 56), (256, 128, 3, 3), 2, 1),
@@ -128,6 +145,19 @@ def test_pools_full_size(nn_gpu):
     nn.backward({y: dy}, grad_for_non_trainables=True)
     want = np.float32(1.0) + np.repeat(np.repeat(dy / np.float32(4), 2, axis=2), 2, axis=3)
     assert_bit_exact(xt.get_grad().np(), want, "avg_pool2D backward")
+    # backward of max: dO goes to the first maximum of each window in row-major order
+    # (op/pool2D.py:181-230)
+    xt.get_grad().fill(1.0)
+    ym = nn.max_pool2D(xt)
+    nn.backward({ym: dy}, grad_for_non_trainables=True)
+    m = np.maximum(np.maximum(t00, t01), np.maximum(t10, t11))
+    want = np.ones_like(x)
+    taken = np.zeros(m.shape, bool)                     # the first tap that equals the maximum takes it
+    for (r, c), tap in (((0, 0), t00), ((0, 1), t01), ((1, 0), t10), ((1, 1), t11)):
+        hit = (tap == m) & ~taken
+        want[:, :, r::2, c::2] += np.where(hit, dy, np.float32(0))
+        taken |= hit
+    assert_bit_exact(xt.get_grad().np(), want, "max_pool2D backward")
 
 
 def test_reductions_full_size(nn_gpu):
@@ -138,6 +168,21 @@ def test_reductions_full_size(nn_gpu):
     assert_bit_exact(nn.reduce_sum(xt, (1,)).np(), _tree_reduce(xa, "sum"), "reduce_sum axis 1")
     assert_bit_exact(nn.reduce_max(xt, (1,)).np(), _tree_reduce(xa, "max"), "reduce_max axis 1")
     assert_bit_exact(nn.reduce_mean(xt, (1,)).np(), _tree_reduce(xa, "sum") / np.float32(512), "reduce_mean axis 1")
+    # backward over axis 1, accumulated into a gradient pre-filled with 1 (op/reduce.py:207-216,250-276)
+    do = np.random.default_rng(8).standard_normal((256, 1024)).astype(np.float32)
+    xt.get_grad().fill(1.0)
+    ys = nn.reduce_sum(xt, (1,))
+    nn.backward({ys: do}, grad_for_non_trainables=True)
+    assert_bit_exact(xt.get_grad().np(), np.float32(1.0) + np.broadcast_to(do[:, None, :], x.shape), "reduce_sum backward")
+    xt.get_grad().fill(1.0)
+    ym = nn.reduce_max(xt, (1,))
+    nn.backward({ym: do}, grad_for_non_trainables=True)
+    want = np.ones_like(x)
+    first = np.argmax(x, axis=1)                         # ties: the lowest index takes the gradient
+    np.add.at(want, (np.arange(256)[:, None], first, np.arange(1024)[None, :]), do)
+    assert_bit_exact(xt.get_grad().np(), want, "reduce_max backward")
+    del want
+    xt.free_grad()
     del xa
     flat = x.reshape(1, -1)
     assert_bit_exact(nn.reduce_sum(xt).np(), _tree_reduce(flat, "sum"), "reduce_sum all axes")
