@@ -145,6 +145,19 @@ int lnn_binary_fwd(int dev, int op, uint64_t O, uint64_t A, uint64_t B, int rank
 int lnn_binary_bwd(int dev, int op, int which, uint64_t dX, uint64_t A, uint64_t B,
                    uint64_t O, uint64_t dO, int rank, const int64_t* o_shape,
                    const int64_t* a_shape, const int64_t* b_shape);
+/* Softmax over the rows of X[rows, cols] and its gradient, one launch each: P = exp(X) / sum(exp(X))
+ * with no max-subtraction and the row sum in the reference's halving-tree order (the values of its
+ * exp, reduce_sum, div composition); dX += gradient of that composition.  cols <= 8192.
+ * ref: op/element_wise_op.py:309-314, op/reduce.py:279-301, op/dual_wise_op.py:268-281 */
+int lnn_softmax_fwd(int dev, uint64_t P, uint64_t X, int64_t rows, int64_t cols);
+int lnn_softmax_bwd(int dev, uint64_t dX, uint64_t X, uint64_t dP, int64_t rows, int64_t cols);
+/* Categorical cross-entropy of probabilities P[rows, cols] against targets T (one row per sample, or
+ * a single row with t_row_stride = 0): L[r] = sum_j -T[r][j] * log(clip(P[r][j], 1e-7, 1 - 1e-7)),
+ * and dP += its gradient for an upstream dL[rows].  One launch each.
+ * ref: op/dual_wise_op.py:228-250, op/element_wise_op.py:133-176 (clip), :225-232 (log) */
+int lnn_cce_fwd(int dev, uint64_t L, uint64_t P, uint64_t T, int64_t rows, int64_t cols, int64_t t_row_stride);
+int lnn_cce_bwd(int dev, uint64_t dP, uint64_t P, uint64_t T, uint64_t dL, int64_t rows, int64_t cols,
+                int64_t t_row_stride);
 /* y (+)= leaky_relu(x*g + b, alpha) for x[N,C,HW], g,b[C]: the three reference kernels
  * mul, add, leaky_relu (separately rounded) in one pass.
  * ref: op/dual_wise_op.py:194-204,283-295 + op/element_wise_op.py:207-221 */
@@ -283,6 +296,23 @@ int lnn_conv2d_dx_packed(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t 
                          uint64_t W, int precision);
 int lnn_conv2d_dw_packed(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY_hi, uint64_t dY_lo,
                          uint64_t X_hi, uint64_t X_lo, int precision);
+
+/* Transposed convolution Y[n, OC, OH, OW] (+)= conv2DTranspose(X[n, IC, IH, IW], K[OC, IC, KH, KW]) and its two
+ * gradients, on the same tile engine: they are the three GEMMs of a convolution with the roles
+ * swapped.  `g` is the geometry of the convolution whose input gradient the forward pass is:
+ * g->ic = OC, g->ih / g->iw = OH / OW, g->oc = IC, g->oh / g->ow = IH / IW, stride, dilation, padl, padt.
+ * ref: op/conv2DTranspose.py:8-46,68-70, op/unfold2D.py:112-138 */
+int lnn_conv2d_transpose_fwd(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint64_t K, int accumulate,
+                             int precision);
+int lnn_conv2d_transpose_dx(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY, uint64_t K, int precision);
+int lnn_conv2d_transpose_dk(int dev, const lnn_conv_geom* g, uint64_t dK, uint64_t dY, uint64_t X, int precision);
+
+/* Depthwise convolution (one KH x KW filter per channel; g->oc == g->ic, K is [C, KH, KW]) and its
+ * gradients; HBM-bound kernels, forward and dX bit-identical to the reference's, dK by its two
+ * steps (products, then tree-ordered row sums).  ref: op/depthwise_conv2D.py:9-123 */
+int lnn_depthwise_conv2d_fwd(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint64_t K, int accumulate);
+int lnn_depthwise_conv2d_dx(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY, uint64_t K);
+int lnn_depthwise_conv2d_dk(int dev, const lnn_conv_geom* g, uint64_t dK, uint64_t dY, uint64_t X);
 
 /* ---- optimiser + data-parallel sync --------------------------------------------------- */
 

@@ -13,7 +13,7 @@ from .autograd import backward
 from .devices import devices
 from .module import Conv2D, Dense, Module, ModuleBase
 from .ops import (abs, add, add_const, avg_pool2D, binary_crossentropy, categorical_crossentropy, clip,
-                  conv2D, conv2D_block, conv2D_infer, conv2D_pool, pack_activation, PackedActivation, cos, dense, div, div_const, exp, flatten, leaky_relu, log, matmul, max, max_pool2D,
+                  conv2D, conv2DTranspose, conv2D_block, conv2D_infer, conv2D_pool, depthwise_conv2D, pack_activation, PackedActivation, cos, dense, div, div_const, exp, flatten, leaky_relu, log, matmul, max, max_pool2D,
                   min, min_pool2D, moments, mul, mul_const, rdiv_const, reduce_max, reduce_mean, reduce_min,
                   reduce_std, reduce_sum, reduce_variance, relu, reshape, rsub_const, scale_bias_leaky_relu,
                   sigmoid, sin, slice, softmax, sqrt, square, sub, sub_const, tanh, transpose)

@@ -79,6 +79,10 @@ _SIGNATURES = {
     "lnn_eltwise_bwd": (c_int, [c_int, c_int, c_uint64, c_uint64, c_uint64, c_uint64, c_int64, c_float, c_float, c_int]),
     "lnn_binary_fwd": (c_int, [c_int, c_int, c_uint64, c_uint64, c_uint64, c_int, _I64P, _I64P, _I64P, c_int]),
     "lnn_binary_bwd": (c_int, [c_int, c_int, c_int, c_uint64, c_uint64, c_uint64, c_uint64, c_uint64, c_int, _I64P, _I64P, _I64P]),
+    "lnn_softmax_fwd": (c_int, [c_int, c_uint64, c_uint64, c_int64, c_int64]),
+    "lnn_softmax_bwd": (c_int, [c_int, c_uint64, c_uint64, c_uint64, c_int64, c_int64]),
+    "lnn_cce_fwd": (c_int, [c_int, c_uint64, c_uint64, c_uint64, c_int64, c_int64, c_int64]),
+    "lnn_cce_bwd": (c_int, [c_int, c_uint64, c_uint64, c_uint64, c_uint64, c_int64, c_int64, c_int64]),
     "lnn_scale_bias_lrelu": (c_int, [c_int, c_uint64, c_uint64, c_uint64, c_uint64, c_int64, c_int64, c_int64, c_float, c_int]),
     "lnn_pool2d_fwd": (c_int, [c_int, c_int, c_uint64, c_uint64, c_int64, c_int64] + [c_int] * 8),
     "lnn_pool2d_bwd": (c_int, [c_int, c_int, c_uint64, c_uint64, c_uint64, c_uint64, c_int64, c_int64] + [c_int] * 8),
@@ -100,6 +104,12 @@ _SIGNATURES = {
     "lnn_conv2d_dw": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64, c_int]),
     "lnn_conv2d_dx_packed": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64, c_uint64, c_int]),
     "lnn_conv2d_dw_packed": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64, c_uint64, c_uint64, c_int]),
+    "lnn_conv2d_transpose_fwd": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64, c_int, c_int]),
+    "lnn_conv2d_transpose_dx": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64, c_int]),
+    "lnn_conv2d_transpose_dk": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64, c_int]),
+    "lnn_depthwise_conv2d_fwd": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64, c_int]),
+    "lnn_depthwise_conv2d_dx": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64]),
+    "lnn_depthwise_conv2d_dk": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64]),
     "lnn_sgd_step": (c_int, [c_int, c_uint64, c_uint64, c_int64, c_float, c_float]),
     "lnn_optimizer_step": (c_int, [c_int, c_int, c_uint64, c_uint64, c_uint64, c_uint64, c_int64, c_void_p]),
     "lnn_nccl_unique_id": (c_int, [c_void_p]),

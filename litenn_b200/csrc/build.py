@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
 SOURCES = ["lnn_runtime.cu", "lnn_eltwise.cu", "lnn_pool.cu", "lnn_reduce.cu", "lnn_move.cu",
-           "lnn_tc.cu", "lnn_fewch.cu", "lnn_direct.cu", "lnn_nccl.cu"]
+           "lnn_tc.cu", "lnn_fewch.cu", "lnn_direct.cu", "lnn_depthwise.cu", "lnn_nccl.cu"]
 HEADERS = ["lnn_common.cuh", "lnn_tc.cuh", "lnn_tc_dev.cuh", os.path.join("..", "..", "include", "litenn_b200.h")]
 LIB = os.path.join(PKG, "liblitenn_b200.so")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -5,6 +5,7 @@
 // in, and no fused multiply-add: each reference operator is its own rounding step, so
 // the intrinsics __fmul_rn/__fadd_rn/__fsub_rn/__fdiv_rn are used throughout.
 #include "lnn_common.cuh"
+#include <algorithm>
 
 namespace {
 
@@ -438,6 +439,104 @@ namespace {
 
 __device__ __forceinline__ uint32_t pcg_hash(uint32_t v);
 
+// ---- softmax and categorical cross-entropy over the rows of a [rows, cols] matrix -------------
+// The reference composes them from exp, reduce_sum, div (softmax, element_wise_op.py:309-314) and
+// clip, log, mul_const, mul, reduce_sum (categorical_crossentropy, dual_wise_op.py:228-250), nine
+// launches and as many gradient launches.  Here one block owns a row: same operations in the
+// same order per element (no max-subtraction, clip to [1e-7, 1 - 1e-7]) and the row sums in the
+// reference's ceil-halving tree order (reduce.py:285-291), so forward values are identical.
+constexpr int kRowThreads = 256;
+constexpr int kRowMax = 8192;        // columns a block keeps in shared memory (32 KB)
+
+// In-place ceil-halving tree over v[0..n): v[i] += v[i + ceil(n/2)], n = ceil(n/2), ... ; result in v[0].
+__device__ __forceinline__ float row_tree_sum(float* v, int n) {
+  while (n > 1) {
+    const int h = (n + 1) >> 1;
+    __syncthreads();
+    for (int i = threadIdx.x; i + h < n; i += blockDim.x) v[i] = fadd(v[i], v[i + h]);
+    n = h;
+  }
+  __syncthreads();
+  return v[0];
+}
+
+__global__ void __launch_bounds__(kRowThreads)
+softmax_fwd_kernel(float* __restrict__ P, const float* __restrict__ X, int64_t rows, int cols) {
+  __shared__ float e[kRowMax];
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const float* x = X + r * cols;
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) e[i] = expf(x[i]);
+    const float s = row_tree_sum(e, cols);
+    __syncthreads();
+    // the tree consumed e: the quotient uses a fresh exp of the same input (same value)
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) P[r * cols + i] = fdiv(expf(x[i]), s);
+    __syncthreads();
+  }
+}
+
+// dX += (dP / s - sum_j(dP_j * e_j / s^2)) * e : the gradients of div (both operands), of the
+// keepdims sum and of exp, in that association (dual_wise_op.py:268-281, reduce.py:250-260,
+// element_wise_op.py:181-188)
+__global__ void __launch_bounds__(kRowThreads)
+softmax_bwd_kernel(float* __restrict__ dX, const float* __restrict__ X, const float* __restrict__ dP,
+                   int64_t rows, int cols) {
+  __shared__ float e[kRowMax];
+  __shared__ float s_sh;
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const float* x = X + r * cols;
+    const float* dp = dP + r * cols;
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) e[i] = expf(x[i]);
+    const float s = row_tree_sum(e, cols);
+    __syncthreads();
+    if (threadIdx.x == 0) s_sh = s;
+    // ds = sum_j dP_j * (-e_j / (s * s))
+    const float ss = fmul(s, s);
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) e[i] = fmul(dp[i], fdiv(-expf(x[i]), ss));
+    const float ds = row_tree_sum(e, cols);
+    __syncthreads();
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+      const float de = fadd(fdiv(dp[i], s), ds);
+      dX[r * cols + i] = fadd(dX[r * cols + i], fmul(de, expf(x[i])));
+    }
+    __syncthreads();
+  }
+}
+
+// L[r] = sum_j (-T[r][j]) * log(clip(P[r][j], 1e-7, 1 - 1e-7)); T is [rows, cols] or one row (stride 0)
+__global__ void __launch_bounds__(kRowThreads)
+cce_fwd_kernel(float* __restrict__ L, const float* __restrict__ P, const float* __restrict__ T, int64_t rows,
+               int cols, int64_t t_row_stride) {
+  __shared__ float v[kRowMax];
+  const float lo = 1e-7f, hi = fsub(1.0f, 1e-7f);
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const float* p = P + r * cols;
+    const float* t = T + r * t_row_stride;
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+      const float c = fminf(fmaxf(p[i], lo), hi);
+      v[i] = fmul(fmul(t[i], -1.0f), logf(c));
+    }
+    const float s = row_tree_sum(v, cols);
+    if (threadIdx.x == 0) L[r] = s;
+    __syncthreads();
+  }
+}
+
+// dP += dL[r] * (-T) * (1 / c) where the clip passed the value through (element_wise_op.py:133-139)
+__global__ void __launch_bounds__(kThreads)
+cce_bwd_kernel(float* __restrict__ dP, const float* __restrict__ P, const float* __restrict__ T,
+               const float* __restrict__ dL, int64_t total, int64_t cols, int64_t t_row_stride) {
+  const float lo = 1e-7f, hi = fsub(1.0f, 1e-7f);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / cols, j = i - r * cols;
+    const float p = P[i];
+    const float c = fminf(fmaxf(p, lo), hi);
+    // reduce_sum' broadcasts dL; mul' gives dL * (-T); log' gives * (1 / c); clip' passes inside [lo, hi]
+    const float dlog = fmul(dL[r], fmul(T[r * t_row_stride + j], -1.0f));
+    const float dc = fmul(dlog, fdiv(1.0f, c));
+    dP[i] = fadd(dP[i], fmul(dc, (p >= lo && p <= hi) ? 1.0f : 0.0f));
+  }
+}
+
 // One optimizer update per element, the reference's two or three kernels per tensor in one pass
 // with the same operations in the same order (litenn/core/optimizer/SGD.py:42-83,
 // RMSprop.py:37-69, Adam.py:43-84) and its learning-rate prologue (Optimizer.py:186-203):
@@ -677,6 +776,45 @@ int lnn_scale_bias_lrelu(int dev, uint64_t y, uint64_t x, uint64_t g, uint64_t b
         (float*)(uintptr_t)y, (const float*)(uintptr_t)x, (const float*)(uintptr_t)g,
         (const float*)(uintptr_t)b, total, hw, c, alpha, accumulate);
   }
+  LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
+}
+
+int lnn_softmax_fwd(int dev, uint64_t P, uint64_t X, int64_t rows, int64_t cols) {
+  LNN_DEV(d, dev);
+  LNN_REQUIRE(P && X && rows > 0 && cols > 0, "bad arguments");
+  LNN_REQUIRE(cols <= kRowMax, "rows longer than %d elements are not supported by the fused softmax", kRowMax);
+  softmax_fwd_kernel<<<(unsigned)std::min<int64_t>(rows, (int64_t)d->sm_count * 8), kRowThreads, 0, d->stream>>>(
+      (float*)(uintptr_t)P, (const float*)(uintptr_t)X, rows, (int)cols);
+  LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
+}
+
+int lnn_softmax_bwd(int dev, uint64_t dX, uint64_t X, uint64_t dP, int64_t rows, int64_t cols) {
+  LNN_DEV(d, dev);
+  LNN_REQUIRE(dX && X && dP && rows > 0 && cols > 0 && cols <= kRowMax, "bad arguments");
+  softmax_bwd_kernel<<<(unsigned)std::min<int64_t>(rows, (int64_t)d->sm_count * 8), kRowThreads, 0, d->stream>>>(
+      (float*)(uintptr_t)dX, (const float*)(uintptr_t)X, (const float*)(uintptr_t)dP, rows, (int)cols);
+  LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
+}
+
+int lnn_cce_fwd(int dev, uint64_t L, uint64_t P, uint64_t T, int64_t rows, int64_t cols, int64_t t_row_stride) {
+  LNN_DEV(d, dev);
+  LNN_REQUIRE(L && P && T && rows > 0 && cols > 0 && cols <= kRowMax, "bad arguments");
+  cce_fwd_kernel<<<(unsigned)std::min<int64_t>(rows, (int64_t)d->sm_count * 8), kRowThreads, 0, d->stream>>>(
+      (float*)(uintptr_t)L, (const float*)(uintptr_t)P, (const float*)(uintptr_t)T, rows, (int)cols, t_row_stride);
+  LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
+}
+
+int lnn_cce_bwd(int dev, uint64_t dP, uint64_t P, uint64_t T, uint64_t dL, int64_t rows, int64_t cols,
+                int64_t t_row_stride) {
+  LNN_DEV(d, dev);
+  LNN_REQUIRE(dP && P && T && dL && rows > 0 && cols > 0, "bad arguments");
+  cce_bwd_kernel<<<grid_for(d, rows * cols), kThreads, 0, d->stream>>>(
+      (float*)(uintptr_t)dP, (const float*)(uintptr_t)P, (const float*)(uintptr_t)T, (const float*)(uintptr_t)dL,
+      rows * cols, cols, t_row_stride);
   LNN_CHECK_LAUNCH(d);
   return LNN_OK;
 }

@@ -1128,7 +1128,7 @@ weight_split_kernel(typename Splitter<F16>::T* __restrict__ hi, typename Splitte
 // dW[oc][ic][tap] += sum over splits of P[split][oc][(tap, ic block, eb)], splits added in order
 __global__ void __launch_bounds__(kThreads)
 dw_finalize_kernel(float* __restrict__ dW, const float* __restrict__ P, int oc, int ic, int taps,
-                   int splits, int64_t stride_split, int icb, int64_t ld, int eb) {
+                   int splits, int64_t stride_split, int icb, int64_t ld, int eb, int swapped) {
   const int64_t total = (int64_t)oc * ic * taps;
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
@@ -1140,7 +1140,8 @@ dw_finalize_kernel(float* __restrict__ dW, const float* __restrict__ P, int oc, 
     const float* pp = P + (int64_t)o * ld + ((int64_t)t * icb + c / eb) * eb + c % eb;
     float s = 0.0f;
     for (int k = 0; k < splits; ++k) s = __fadd_rn(s, pp[(int64_t)k * stride_split]);
-    dW[i] = __fadd_rn(dW[i], s);
+    const int64_t dst = swapped ? ((int64_t)c * oc + o) * taps + t : i;     // [ic][oc][tap] or [oc][ic][tap]
+    dW[dst] = __fadd_rn(dW[dst], s);
   }
 }
 
@@ -1850,6 +1851,7 @@ struct FwdOpts {
   int pool = 0;          // Y = max_pool2D(act(conv + bias), 2, 2, 'same')
   int in_packed = 0;     // X / x_lo are channel-innermost hi / lo copies [n][ih][iw][chan_pad(ic)]
   int out_packed = 0;    // Y / y_lo receive such copies of the result instead of the NCHW tensor
+  int w_swapped = 0;     // W is stored [ic][oc][kh][kw] (the kernel of a transposed convolution)
 };
 
 // fp32 channel-innermost tensor (its largest magnitude already in the trailer of `hi`) -> fp16 copies
@@ -1895,7 +1897,7 @@ int conv_fwd_impl(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint6
     return LNN_OK;
   };
 
-  if (!o.in_packed && f16 && !accumulate && knobs().fewch && lnn::conv_fewch_applicable(g)) {
+  if (!o.in_packed && !o.w_swapped && f16 && !accumulate && knobs().fewch && lnn::conv_fewch_applicable(g)) {
     // few input channels, 3x3, unit stride: the tensor-core kernel that builds its own operand
     lnn::Scratch xmax(d), full(d), pooled(d);
     const float* xp = (const float*)(uintptr_t)X;
@@ -1942,7 +1944,7 @@ int conv_fwd_impl(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint6
                            g->oc, oh_p, ow_p, ocp, precision);
     return LNN_OK;
   }
-  if (!o.in_packed && lnn::conv_direct_applicable(g) && knobs().direct && (!o.out_packed || o.pool)) {
+  if (!o.in_packed && !o.w_swapped && lnn::conv_direct_applicable(g) && knobs().direct && (!o.out_packed || o.pool)) {
     if (o.out_packed && f16) {
       float* dst; uint32_t* amax;
       rc = raw_target(&dst, &amax);
@@ -1966,7 +1968,11 @@ int conv_fwd_impl(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint6
   else
     rc = nhwc_split(d, xh, xl, &ox, (const float*)(uintptr_t)X, g->n, g->ic, g->ih, g->iw, cp, precision);
   if (rc) return rc;
-  rc = weights_split(d, wh, wl, &ow, (const float*)(uintptr_t)W, g->oc, g->ic, taps, cp, 0, precision);
+  // rows = output channels, k = input channels; a swapped kernel [ic][oc] is read transposed
+  if (o.w_swapped)
+    rc = weights_split(d, wh, wl, &ow, (const float*)(uintptr_t)W, g->ic, g->oc, taps, cp, 1, precision);
+  else
+    rc = weights_split(d, wh, wl, &ow, (const float*)(uintptr_t)W, g->oc, g->ic, taps, cp, 0, precision);
   if (rc) return rc;
   int dy[kMaxTaps], dx[kMaxTaps], wi[kMaxTaps];
   for (int kh = 0; kh < g->kh; ++kh)
@@ -2085,8 +2091,10 @@ int lnn_nhwc_split(int dev, uint64_t hi, uint64_t lo, uint64_t X, int n, int c, 
 namespace {
 
 // dX += ...; dY is NCHW (dy_lo == 0, dy_packed == 0) or the packed hi / lo copies
+// w_swapped: W is stored [ic][oc][kh][kw].  accumulate = 0: dX is overwritten (every input pixel
+// belongs to exactly one residue class; classes no tap reaches are zero-filled).
 int conv_dx_impl(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY, uint64_t dY_lo, int dy_packed,
-                 uint64_t W, int precision) {
+                 uint64_t W, int precision, int w_swapped = 0, int accumulate = 1) {
   LNN_DEV(d, dev);
   int rc = check_geom(g);
   if (rc) return rc;
@@ -2103,9 +2111,28 @@ int conv_dx_impl(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY, uint
   else
     rc = nhwc_split(d, yh, yl, &oy, (const float*)(uintptr_t)dY, g->n, g->oc, g->oh, g->ow, ocp, precision);
   if (rc) return rc;
-  rc = weights_split(d, wh, wl, &ow, (const float*)(uintptr_t)W, g->oc, g->ic, taps, ocp, 1, precision);
+  // rows = input channels, k = output channels
+  if (w_swapped)
+    rc = weights_split(d, wh, wl, &ow, (const float*)(uintptr_t)W, g->ic, g->oc, taps, ocp, 0, precision);
+  else
+    rc = weights_split(d, wh, wl, &ow, (const float*)(uintptr_t)W, g->oc, g->ic, taps, ocp, 1, precision);
   if (rc) return rc;
   const int64_t plane = (int64_t)g->ih * g->iw;
+  if (!accumulate) {
+    // a class without taps (kernel extent smaller than the stride) is never written by a launch
+    bool all_reached = true;
+    for (int ph = 0; ph < s && all_reached; ++ph)
+      for (int pw = 0; pw < s; ++pw) {
+        bool any_h = false, any_w = false;
+        for (int kh = 0; kh < g->kh; ++kh) any_h |= (((ph + g->padt - kh * g->dilation) % s) + s) % s == 0;
+        for (int kw = 0; kw < g->kw; ++kw) any_w |= (((pw + g->padl - kw * g->dilation) % s) + s) % s == 0;
+        if (!(any_h && any_w)) { all_reached = false; break; }
+      }
+    if (!all_reached) {
+      LNN_CUDA(cudaMemsetAsync((void*)(uintptr_t)dX, 0, (size_t)g->n * g->ic * plane * 4, d->stream));
+      accumulate = 1;
+    }
+  }
   // One launch per residue class (ih % s, iw % s): within a class every tap that reaches an
   // input pixel does so from output row oh = a + dy with a = (ih - ph) / s.
   for (int ph = 0; ph < s; ++ph)
@@ -2132,7 +2159,7 @@ int conv_dx_impl(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY, uint
       c.AH = AH; c.AW = AW; c.es = 1; c.ntaps = nt; c.dy = dy; c.dx = dx; c.widx = wi;
       c.OCv = g->ic; c.out = (float*)(uintptr_t)dX; c.out_base = (int64_t)ph * g->iw + pw;
       c.out_sn = (int64_t)g->ic * plane; c.out_sa = (int64_t)s * g->iw; c.out_sb = s; c.out_sc = plane;
-      c.accumulate = 1; c.precision = precision;
+      c.accumulate = accumulate; c.precision = precision;
       rc = launch_conv_like(d, oy, ow, c);
       if (rc) return rc;
     }
@@ -2140,15 +2167,16 @@ int conv_dx_impl(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY, uint
 }
 
 // dW += ...; dY and X are each NCHW or the packed hi / lo copies
+// out_swapped: dW is stored [ic][oc][kh][kw]
 int conv_dw_impl(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY, uint64_t dY_lo, int dy_packed,
-                 uint64_t X, uint64_t X_lo, int x_packed, int precision) {
+                 uint64_t X, uint64_t X_lo, int x_packed, int precision, int out_swapped = 0) {
   LNN_DEV(d, dev);
   int rc = check_geom(g);
   if (rc) return rc;
   rc = check_passes(precision);
   if (rc) return rc;
   LNN_REQUIRE(dW && dY && X, "null buffer");
-  if (!dy_packed && !x_packed && lnn::conv_direct_dw_applicable(g) && knobs().direct)
+  if (!dy_packed && !x_packed && !out_swapped && lnn::conv_direct_dw_applicable(g) && knobs().direct)
     return lnn::conv_direct_dw(d, g, (float*)(uintptr_t)dW, (const float*)(uintptr_t)dY,
                                (const float*)(uintptr_t)X);
   const int esz = esz_of(precision);
@@ -2272,7 +2300,7 @@ int conv_dw_impl(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY, uint
   if (rc) return rc;
   dw_finalize_kernel<<<grid_for(d, (int64_t)g->oc * g->ic * taps), kThreads, 0, d->stream>>>(
       (float*)(uintptr_t)dW, part.as<float>(), g->oc, g->ic, taps, (int)splits, stride_split,
-      icb, part_ld, eb);
+      icb, part_ld, eb, out_swapped);
   LNN_CHECK_LAUNCH(d);
   return LNN_OK;
 }
@@ -2299,6 +2327,29 @@ int lnn_conv2d_dx_packed(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t 
 int lnn_conv2d_dw_packed(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY_hi, uint64_t dY_lo,
                          uint64_t X_hi, uint64_t X_lo, int tf32_passes) {
   return conv_dw_impl(dev, g, dW, dY_hi, dY_lo, 1, X_hi, X_lo, 1, tf32_passes);
+}
+
+// ---- transposed convolution ---------------------------------------------------------------
+// Y[n, OC, OH, OW] = sum over (ic, kh, kw) of X[n, ic, ih, iw] * K[OC, ic, kh, kw] scattered to
+// oh = ih*stride + kh*dilation - padt (conv2DTranspose.py:33-35, unfold2D.py:112-138): exactly the
+// input gradient of the convolution that maps [n, OC, OH, OW] to [n, ic, ih, iw], with K stored
+// [conv ic][conv oc] -- so the three GEMMs of the transposed convolution are the convolution's three
+// with the roles swapped, and `g` is the geometry of THAT convolution: g->ic = OC, g->ih/iw = OH/OW,
+// g->oc = the transposed convolution's input channels, g->oh/ow = its input size.
+int lnn_conv2d_transpose_fwd(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint64_t K, int accumulate,
+                             int precision) {
+  return conv_dx_impl(dev, g, Y, X, 0, 0, K, precision, 1, accumulate);
+}
+// dX += conv2D(dY, K^T): the forward pass of the underlying convolution (conv2DTranspose.py:37-41)
+int lnn_conv2d_transpose_dx(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY, uint64_t K, int precision) {
+  FwdOpts o;
+  o.w_swapped = 1;
+  return conv_fwd_impl(dev, g, dX, dY, K, 0, 0, 0.0f, 1, precision, o);
+}
+// dK[OC][ic] += the underlying convolution's kernel gradient with dY in the role of its input and
+// X in the role of its output gradient, written transposed (conv2DTranspose.py:43-46)
+int lnn_conv2d_transpose_dk(int dev, const lnn_conv_geom* g, uint64_t dK, uint64_t dY, uint64_t X, int precision) {
+  return conv_dw_impl(dev, g, dK, X, 0, 0, dY, 0, 0, precision, 1);
 }
 
 }  // extern "C"

@@ -35,15 +35,20 @@ import os
 _enabled = [os.environ.get("LNN_EAGER", "0") != "1"]      # LNN_EAGER=1: every operator launches at once
 
 
+composed_softmax = [False]      # True: softmax / categorical_crossentropy run as the reference's compositions
+
+
 @contextlib.contextmanager
 def disabled():
-    """Inside this context conv2D launches eagerly (the un-fused chain, one kernel per operator)."""
-    old = _enabled[0]
-    _enabled[0] = False
+    """Inside this context every operator is the reference's own composition, one kernel per
+    operator: conv2D launches eagerly, softmax and categorical_crossentropy are built from exp,
+    reduce_sum, div, clip, log, mul."""
+    old = _enabled[0], composed_softmax[0]
+    _enabled[0], composed_softmax[0] = False, True
     try:
         yield
     finally:
-        _enabled[0] = old
+        _enabled[0], composed_softmax[0] = old
 
 
 class Pending:

@@ -116,8 +116,28 @@ def tanh_op(input_t, output_t=None, is_add_to_output=False): return _ew("tanh", 
 def tanh(input_t): return tanh_op(input_t)
 
 
+_FUSED_ROW_MAX = 8192      # columns the fused row kernels keep in shared memory
+
+
 def softmax(input_t, axis=-1):
-    """exp(x) / sum(exp(x)) with no max-subtraction (element_wise_op.py:309-314)."""
+    """exp(x) / sum(exp(x)) with no max-subtraction (element_wise_op.py:309-314).  Over the last
+    axis of a matrix it is one kernel (and one for the gradient) with the values of the
+    reference's exp / reduce_sum / div composition; other cases run that composition."""
+    rank = input_t.shape.rank
+    if rank == 2 and axis in (-1, 1) and input_t.shape[1] <= _FUSED_ROW_MAX and not _deferred.composed_softmax[0]:
+        rows, cols = input_t.shape
+        output_t = _out(input_t.shape)
+        output_t._set_op_name("softmax")
+
+        def grad(O_t, dO_t):
+            g = input_t.get_grad()
+            for i, dev in _each_device():
+                _lib_().lnn_softmax_bwd(dev, g._ptr(i), input_t._ptr(i), dO_t._ptr(i), rows, cols)
+
+        output_t._assign_gradfn(input_t, grad)
+        for i, dev in _each_device():
+            _lib_().lnn_softmax_fwd(dev, output_t._ptr(i), input_t._ptr(i), rows, cols)
+        return output_t
     e = exp(input_t)
     return e / e.sum(axis, keepdims=True)
 
@@ -196,6 +216,24 @@ def categorical_crossentropy(input_t, target_t):
         raise ValueError("input_t.shape.rank != 2")
     if target_t.shape.rank not in (1, 2):
         raise ValueError("target_t.shape.rank != 1 or 2")
+    rows, cols = input_t.shape
+    t_ok = tuple(target_t.shape.shape) in ((cols,), (rows, cols))
+    if t_ok and cols <= _FUSED_ROW_MAX and not _deferred.composed_softmax[0] and not _deferred.reaches_trainable(target_t):
+        # one kernel (and one for the gradient of the probabilities) with the values of the
+        # composition below; a target that needs a gradient itself takes the composition
+        t_stride = cols if target_t.shape.rank == 2 else 0
+        output_t = _out((rows,))
+        output_t._set_op_name("categorical_crossentropy")
+
+        def grad(O_t, dO_t):
+            g = input_t.get_grad()
+            for i, dev in _each_device():
+                _lib_().lnn_cce_bwd(dev, g._ptr(i), input_t._ptr(i), target_t._ptr(i), dO_t._ptr(i), rows, cols, t_stride)
+
+        output_t._assign_gradfn(input_t, grad)
+        for i, dev in _each_device():
+            _lib_().lnn_cce_fwd(dev, output_t._ptr(i), input_t._ptr(i), target_t._ptr(i), rows, cols, t_stride)
+        return output_t
     input_t = clip(input_t, 1e-7, 1 - 1e-7)
     return reduce_sum(-target_t * log(input_t), axes=-1)
 
@@ -684,6 +722,77 @@ def conv2D_block(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t
         y = conv2D(input_t, kernel_t, stride, dilation, padding, bias_t, activation, alpha)
         return pool2D_op("max", y, 2, 2, "same")
     return conv2D(input_t, kernel_t, stride, dilation, padding, bias_t, activation, alpha, _pooled=True)
+
+
+def conv2DTranspose(input_t, kernel_t, stride=2, dilation=1, padding="same"):
+    """Transposed convolution, input (N,IC,H,W), kernel (OC,IC,KH,KW), padding 'same' | 'valid'
+    (conv2DTranspose.py:8-46).  Forward, dI and dK are the three GEMMs of a convolution with the
+    roles swapped, issued on the tile engine without materialising an unfolded buffer."""
+    if padding not in ("valid", "same"):
+        raise ValueError("Wrong padding value, only valid or same supported for conv2DTranspose.")
+    if input_t.shape.rank != 4 or kernel_t.shape.rank != 4:
+        raise ValueError("conv2DTranspose expects (N,IC,H,W) input and (OC,IC,KH,KW) kernel")
+    stride, dilation = int(stride), int(dilation)
+    N, IC, IH, IW = input_t.shape
+    KO, KI, KH, KW = kernel_t.shape
+    if KI != IC:
+        raise ValueError(f"Kernel input channels {KI} does not match input channels {IC}.")
+    ci = InfoConv2D(IH, IW, KH, KW, stride, dilation, padding)
+    OH, OW = ci.OH_T, ci.OW_T
+    # geometry of the convolution [N,KO,OH,OW] -> [N,IC,IH,IW] whose input gradient this is
+    g = _lib.ConvGeom(N, KO, OH, OW, IC, KH, KW, IH, IW, stride, dilation, ci.PADL, ci.PADT)
+    passes = _lib.precision()
+    output_t = _out((N, KO, OH, OW))
+    output_t._set_op_name("conv2DTranspose")
+
+    def grad_x(O_t, dO_t):
+        gx = input_t.get_grad()
+        for i, dev in _each_device():
+            _lib_().lnn_conv2d_transpose_dx(dev, ctypes.byref(g), gx._ptr(i), dO_t._ptr(i), kernel_t._ptr(i), passes)
+
+    def grad_k(O_t, dO_t):
+        gk = kernel_t.get_grad()
+        for i, dev in _each_device():
+            _lib_().lnn_conv2d_transpose_dk(dev, ctypes.byref(g), gk._ptr(i), dO_t._ptr(i), input_t._ptr(i), passes)
+
+    output_t._assign_gradfn(input_t, grad_x)
+    output_t._assign_gradfn(kernel_t, grad_k)
+    for i, dev in _each_device():
+        _lib_().lnn_conv2d_transpose_fwd(dev, ctypes.byref(g), output_t._ptr(i), input_t._ptr(i), kernel_t._ptr(i), 0, passes)
+    return output_t
+
+
+def depthwise_conv2D(input_t, kernel_t, stride=1, dilation=1, padding="same"):
+    """Depthwise convolution, input (N,IC,H,W), kernel (IC,KH,KW) (depthwise_conv2D.py:9-123)."""
+    if kernel_t.shape.rank != 3:
+        raise ValueError("Kernel shape rank must be == 3")
+    if input_t.shape.rank != 4:
+        raise ValueError("depthwise_conv2D expects an (N,IC,H,W) input")
+    stride, dilation = int(stride), int(dilation)
+    N, IC, IH, IW = input_t.shape
+    KI, KH, KW = kernel_t.shape
+    if KI != IC:
+        raise ValueError(f"Kernel input channels {KI} does not match tensor input channels {IC}.")
+    ci = InfoConv2D(IH, IW, KH, KW, stride, dilation, padding)
+    g = _lib.ConvGeom(N, IC, IH, IW, IC, KH, KW, ci.OH, ci.OW, stride, dilation, ci.PADL, ci.PADT)
+    output_t = _out((N, IC, ci.OH, ci.OW))
+    output_t._set_op_name("depthwise_conv2D")
+
+    def grad_x(O_t, dO_t):
+        gx = input_t.get_grad()
+        for i, dev in _each_device():
+            _lib_().lnn_depthwise_conv2d_dx(dev, ctypes.byref(g), gx._ptr(i), dO_t._ptr(i), kernel_t._ptr(i))
+
+    def grad_k(O_t, dO_t):
+        gk = kernel_t.get_grad()
+        for i, dev in _each_device():
+            _lib_().lnn_depthwise_conv2d_dk(dev, ctypes.byref(g), gk._ptr(i), dO_t._ptr(i), input_t._ptr(i))
+
+    output_t._assign_gradfn(input_t, grad_x)
+    output_t._assign_gradfn(kernel_t, grad_k)
+    for i, dev in _each_device():
+        _lib_().lnn_depthwise_conv2d_fwd(dev, ctypes.byref(g), output_t._ptr(i), input_t._ptr(i), kernel_t._ptr(i), 0)
+    return output_t
 
 
 class PackedActivation:

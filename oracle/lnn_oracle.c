@@ -439,6 +439,130 @@ void lnn_o_conv2d_dw(const conv_geom* g, float* dW, const float* dY, const float
   }
 }
 
+/* ---- conv2DTranspose: op/conv2DTranspose.py:33-46, op/unfold2D.py:112-138 ----------------
+ * g describes the transposed convolution itself: input X[n][ic][ih][iw], kernel K[oc][ic][kh][kw],
+ * output Y[n][oc][oh][ow] with oh = ih*stride + kh*dilation - padt.  The "transposed unfold" of
+ * the reference gathers, for output pixel (oh, ow) and tap (kh, kw), input pixel
+ * ((oh + padt - kh*d) / s, ...) when that division is exact and inside the image, else 0. */
+static float convt_gather(const conv_geom* g, const float* X, i64 n, int ic, int oh, int ow, int kh, int kw) {
+  int ny = oh + g->padt - kh * g->dilation, nx = ow + g->padl - kw * g->dilation;
+  if (ny < 0 || nx < 0 || ny % g->stride != 0 || nx % g->stride != 0) return 0.0f;
+  int ih = ny / g->stride, iw = nx / g->stride;
+  if (ih >= g->ih || iw >= g->iw) return 0.0f;
+  return X[((n * g->ic + ic) * g->ih + ih) * g->iw + iw];
+}
+/* forward: GEMM of kernel[OC][IC*KH*KW] with im2colT(X); contraction index (ic, kh, kw) ascending */
+void lnn_o_convt_fwd(const conv_geom* g, float* Y, const float* X, const float* K, int accum64) {
+  i64 total = (i64)g->n * g->oc * g->oh * g->ow;
+#pragma omp parallel for
+  for (i64 gid = 0; gid < total; ++gid) {
+    int ow = (int)(gid % g->ow); i64 t = gid / g->ow; int oh = (int)(t % g->oh); t /= g->oh;
+    int oc = (int)(t % g->oc); i64 n = t / g->oc;
+    float s = 0.0f; double s64 = 0.0;
+    for (int ic = 0; ic < g->ic; ++ic)
+      for (int kh = 0; kh < g->kh; ++kh)
+        for (int kw = 0; kw < g->kw; ++kw) {
+          float k = K[(((i64)oc * g->ic + ic) * g->kh + kh) * g->kw + kw];
+          float x = convt_gather(g, X, n, ic, oh, ow, kh, kw);
+          if (accum64) s64 += (double)k * (double)x; else s += k * x;
+        }
+    Y[gid] = accum64 ? (float)s64 : s;
+  }
+}
+/* input gradient: dX += GEMM(im2row(dY)[N*IH*IW][OC*KH*KW], K'[OC*KH*KW][IC]); index (oc, kh, kw) ascending */
+void lnn_o_convt_dx(const conv_geom* g, float* dX, const float* dY, const float* K, int accum64) {
+  i64 total = (i64)g->n * g->ic * g->ih * g->iw;
+#pragma omp parallel for
+  for (i64 gid = 0; gid < total; ++gid) {
+    int iw = (int)(gid % g->iw); i64 t = gid / g->iw; int ih = (int)(t % g->ih); t /= g->ih;
+    int ic = (int)(t % g->ic); i64 n = t / g->ic;
+    float s = 0.0f; double s64 = 0.0;
+    for (int oc = 0; oc < g->oc; ++oc)
+      for (int kh = 0; kh < g->kh; ++kh)
+        for (int kw = 0; kw < g->kw; ++kw) {
+          int oh = ih * g->stride + kh * g->dilation - g->padt, ow = iw * g->stride + kw * g->dilation - g->padl;
+          float d = 0.0f;
+          if (oh >= 0 && ow >= 0 && oh < g->oh && ow < g->ow) d = dY[((n * g->oc + oc) * g->oh + oh) * g->ow + ow];
+          float k = K[(((i64)oc * g->ic + ic) * g->kh + kh) * g->kw + kw];
+          if (accum64) s64 += (double)d * (double)k; else s += d * k;
+        }
+    dX[gid] += accum64 ? (float)s64 : s;
+  }
+}
+/* kernel gradient: dK += GEMM(dY^T[OC][N*OH*OW], im2rowT(X)[N*OH*OW][IC*KH*KW]); index (n, oh, ow) ascending */
+void lnn_o_convt_dk(const conv_geom* g, float* dK, const float* dY, const float* X, int accum64) {
+  i64 total = (i64)g->oc * g->ic * g->kh * g->kw;
+#pragma omp parallel for
+  for (i64 gid = 0; gid < total; ++gid) {
+    int kw = (int)(gid % g->kw); i64 t = gid / g->kw; int kh = (int)(t % g->kh); t /= g->kh;
+    int ic = (int)(t % g->ic); int oc = (int)(t / g->ic);
+    float s = 0.0f; double s64 = 0.0;
+    for (i64 n = 0; n < g->n; ++n)
+      for (int oh = 0; oh < g->oh; ++oh)
+        for (int ow = 0; ow < g->ow; ++ow) {
+          float d = dY[((n * g->oc + oc) * g->oh + oh) * g->ow + ow];
+          float x = convt_gather(g, X, n, ic, oh, ow, kh, kw);
+          if (accum64) s64 += (double)d * (double)x; else s += d * x;
+        }
+    dK[gid] += accum64 ? (float)s64 : s;
+  }
+}
+
+/* ---- depthwise_conv2D: op/depthwise_conv2D.py:78-123 (g->oc == g->ic, K[c][kh][kw]) ------- */
+void lnn_o_depthwise_fwd(const conv_geom* g, float* O, const float* I, const float* K) {
+  i64 total = (i64)g->n * g->ic * g->oh * g->ow;
+#pragma omp parallel for
+  for (i64 gid = 0; gid < total; ++gid) {
+    int ow = (int)(gid % g->ow); i64 t = gid / g->ow; int oh = (int)(t % g->oh); t /= g->oh;
+    int c = (int)(t % g->ic);
+    float v = 0.0f;
+    for (int kh = 0; kh < g->kh; ++kh) {
+      int ih = -g->padt + kh * g->dilation + oh * g->stride;
+      if (ih >= 0 && ih < g->ih)
+        for (int kw = 0; kw < g->kw; ++kw) {
+          int iw = -g->padl + kw * g->dilation + ow * g->stride;
+          if (iw >= 0 && iw < g->iw) v += I[(t * g->ih + ih) * g->iw + iw] * K[((i64)c * g->kh + kh) * g->kw + kw];
+        }
+    }
+    O[gid] = v;
+  }
+}
+void lnn_o_depthwise_dx(const conv_geom* g, float* dI, const float* K, const float* dO) {
+  i64 total = (i64)g->n * g->ic * g->ih * g->iw;
+#pragma omp parallel for
+  for (i64 gid = 0; gid < total; ++gid) {
+    int iw = (int)(gid % g->iw); i64 t = gid / g->iw; int ih = (int)(t % g->ih); t /= g->ih;
+    int c = (int)(t % g->ic);
+    float v = 0.0f;
+    for (int kh = 0; kh < g->kh; ++kh) {
+      int oh = (g->padt + ih - kh * g->dilation) / g->stride;
+      if (oh >= 0 && oh < g->oh)
+        for (int kw = 0; kw < g->kw; ++kw) {
+          int ow = (g->padl + iw - kw * g->dilation) / g->stride;
+          if (ow >= 0 && ow < g->ow && iw == (-g->padl + kw * g->dilation + ow * g->stride) &&
+              ih == (-g->padt + kh * g->dilation + oh * g->stride))
+            v += dO[(t * g->oh + oh) * g->ow + ow] * K[((i64)c * g->kh + kh) * g->kw + kw];
+        }
+    }
+    dI[gid] += v;
+  }
+}
+/* products of the kernel gradient: P[(c, kh, kw)][(n, oh, ow)] = im2col(I) * dO; the caller sums the
+ * rows with lnn_o_reduce (the reference's reduce_sum over the last axis, += into dK) */
+void lnn_o_depthwise_dk_products(const conv_geom* g, float* P, const float* I, const float* dO) {
+  i64 cols = (i64)g->n * g->oh * g->ow, total = (i64)g->ic * g->kh * g->kw * cols;
+#pragma omp parallel for
+  for (i64 gid = 0; gid < total; ++gid) {
+    i64 col = gid % cols, row = gid / cols;
+    int kw = (int)(row % g->kw); row /= g->kw; int kh = (int)(row % g->kh); int c = (int)(row / g->kh);
+    int ow = (int)(col % g->ow); i64 t = col / g->ow; int oh = (int)(t % g->oh); i64 n = t / g->oh;
+    int ih = -g->padt + kh * g->dilation + oh * g->stride, iw = -g->padl + kw * g->dilation + ow * g->stride;
+    float x = 0.0f;
+    if (ih >= 0 && ih < g->ih && iw >= 0 && iw < g->iw) x = I[((n * g->ic + c) * g->ih + ih) * g->iw + iw];
+    P[gid] = x * dO[((n * g->ic + c) * g->oh + oh) * g->ow + ow];
+  }
+}
+
 /* ---- SGD, momentum 0: optimizer/SGD.py:42-74 (A = 0*A - lr*G ; V += A) ---------------- */
 void lnn_o_sgd(float* V, const float* G, i64 n, float lr, float gscale) {
 #pragma omp parallel for

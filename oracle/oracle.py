@@ -245,6 +245,74 @@ def conv2d_dw(dW, dY, X, stride=1, dilation=1, padding="same", accum64=False):
     return dW
 
 
+def convt_geom(x_shape, k_shape, stride=2, dilation=1, padding="same"):
+    """Geometry of conv2DTranspose: output size as info/InfoConv2D.py:41-77 (OH_T, OW_T)."""
+    N, IC, IH, IW = x_shape
+    OC, _, KH, KW = k_shape
+    ekh, ekw = (KH - 1) * dilation + 1, (KW - 1) * dilation + 1
+    if padding == "same":
+        pl, pt = (ekw - 1) // 2, (ekh - 1) // 2
+        oh, ow = IH * stride, IW * stride
+    elif padding == "valid":
+        pl = pt = 0
+        oh, ow = IH * stride + max(ekh - stride, 0), IW * stride + max(ekw - stride, 0)
+    else:
+        raise ValueError("only valid or same")
+    return ConvGeom(N, IC, IH, IW, OC, KH, KW, oh, ow, stride, dilation, pl, pt)
+
+
+def conv2d_transpose_fwd(X, K, stride=2, dilation=1, padding="same", accum64=False):
+    X, K = _f(X), _f(K)
+    g = convt_geom(X.shape, K.shape, stride, dilation, padding)
+    Y = np.empty((g.n, g.oc, g.oh, g.ow), np.float32)
+    lib().lnn_o_convt_fwd(ctypes.byref(g), _p(Y), _p(X), _p(K), INT(accum64))
+    return Y
+
+
+def conv2d_transpose_dx(dX, dY, K, stride=2, dilation=1, padding="same", accum64=False):
+    dX, dY, K = _f(dX).copy(), _f(dY), _f(K)
+    g = convt_geom(dX.shape, K.shape, stride, dilation, padding)
+    lib().lnn_o_convt_dx(ctypes.byref(g), _p(dX), _p(dY), _p(K), INT(accum64))
+    return dX
+
+
+def conv2d_transpose_dk(dK, dY, X, stride=2, dilation=1, padding="same", accum64=False):
+    dK, dY, X = _f(dK).copy(), _f(dY), _f(X)
+    g = convt_geom(X.shape, dK.shape, stride, dilation, padding)
+    lib().lnn_o_convt_dk(ctypes.byref(g), _p(dK), _p(dY), _p(X), INT(accum64))
+    return dK
+
+
+def _dw_geom(x_shape, k_shape, stride, dilation, padding):
+    C, KH, KW = k_shape
+    return conv_geom(x_shape, (C, C, KH, KW), stride, dilation, padding)
+
+
+def depthwise_fwd(X, K, stride=1, dilation=1, padding="same"):
+    X, K = _f(X), _f(K)
+    g = _dw_geom(X.shape, K.shape, stride, dilation, padding)
+    Y = np.empty((g.n, g.ic, g.oh, g.ow), np.float32)
+    lib().lnn_o_depthwise_fwd(ctypes.byref(g), _p(Y), _p(X), _p(K))
+    return Y
+
+
+def depthwise_dx(dX, dY, K, stride=1, dilation=1, padding="same"):
+    dX, dY, K = _f(dX).copy(), _f(dY), _f(K)
+    g = _dw_geom(dX.shape, K.shape, stride, dilation, padding)
+    lib().lnn_o_depthwise_dx(ctypes.byref(g), _p(dX), _p(K), _p(dY))
+    return dX
+
+
+def depthwise_dk(dK, dY, X, stride=1, dilation=1, padding="same"):
+    """Products, then the tree-ordered row sums added to dK (depthwise_conv2D.py:45-50)."""
+    dK, dY, X = _f(dK).copy(), _f(dY), _f(X)
+    g = _dw_geom(X.shape, dK.shape, stride, dilation, padding)
+    rows, cols = dK.size, g.n * g.oh * g.ow
+    P = np.empty((rows, cols), np.float32)
+    lib().lnn_o_depthwise_dk_products(ctypes.byref(g), _p(P), _p(X), _p(dY))
+    return reduce5("sum", P, rows, 1, 1, cols, 1, out=dK.reshape(-1)).reshape(dK.shape)
+
+
 def sgd(V, G, lr, gscale=1.0):
     V, G = _f(V).copy(), _f(G)
     lib().lnn_o_sgd(_p(V), _p(G), I64(V.size), F32(lr), F32(gscale))

@@ -78,6 +78,29 @@ CONV_CASES = [  # (x_shape, w_shape, stride, dilation, padding, integer_valued)
     ((3, 3, 16, 16), (8, 3, 3, 3), 1, 1, (1, 0, 2, 1), False),
 ]
 
+# conv2DTranspose (op/conv2DTranspose.py:8-46): kernel (out_ch, in_ch, KH, KW), padding 'same' / 'valid'
+CONVT_CASES = [  # (x_shape, k_shape, stride, dilation, padding, integer_valued)
+    ((2, 3, 5, 6), (4, 3, 3, 3), 2, 1, "same", True),
+    ((1, 4, 7, 5), (6, 4, 3, 3), 1, 1, "same", True),
+    ((2, 2, 4, 4), (3, 2, 2, 2), 3, 1, "valid", True),      # kernel smaller than the stride: untouched pixels
+    ((1, 3, 6, 6), (5, 3, 3, 3), 2, 2, "valid", True),
+    ((2, 8, 6, 6), (16, 8, 1, 1), 2, 1, "same", True),
+    ((2, 16, 9, 9), (24, 16, 3, 3), 2, 1, "same", False),
+    ((1, 40, 8, 8), (12, 40, 4, 4), 2, 1, "same", False),
+    ((2, 12, 10, 7), (20, 12, 3, 3), 1, 1, "valid", False),
+]
+
+# depthwise_conv2D (op/depthwise_conv2D.py:9-123): kernel (in_ch, KH, KW)
+DEPTHWISE_CASES = [  # (x_shape, k_shape, stride, dilation, padding, integer_valued)
+    ((2, 3, 8, 8), (3, 3, 3), 1, 1, "same", True),
+    ((1, 4, 9, 7), (4, 3, 3), 2, 1, "same", True),
+    ((2, 2, 10, 10), (2, 5, 5), 1, 2, "valid", True),
+    ((1, 5, 11, 13), (5, 3, 3), 3, 1, 2, True),
+    ((2, 16, 14, 14), (16, 3, 3), 1, 1, "same", False),
+    ((3, 6, 16, 12), (6, 7, 7), 2, 1, (1, 0, 2, 1), False),
+    ((2, 32, 20, 20), (32, 1, 1), 1, 1, "valid", False),
+]
+
 
 # random initializers (initializer/RandomUniform.py, RandomNormal.py, He.py, Glorot.py): the seed
 # of the device-side hash is np.random.randint(2**31) drawn at initialisation time, so a case
@@ -125,6 +148,10 @@ def all_cases():
         cases.append((f"matmul_{i}", "matmul", {"a_shape": sa, "b_shape": sb, "integer": integer}))
     for i, (sx, sw, s, d, p, integer) in enumerate(CONV_CASES):
         cases.append((f"conv_{i}", "conv", {"x_shape": sx, "w_shape": sw, "stride": s, "dilation": d, "padding": p, "integer": integer}))
+    for i, (sx, sw, s, d, p, integer) in enumerate(CONVT_CASES):
+        cases.append((f"convt_{i}", "conv_transpose", {"x_shape": sx, "w_shape": sw, "stride": s, "dilation": d, "padding": p, "integer": integer}))
+    for i, (sx, sw, s, d, p, integer) in enumerate(DEPTHWISE_CASES):
+        cases.append((f"depthwise_{i}", "depthwise", {"x_shape": sx, "w_shape": sw, "stride": s, "dilation": d, "padding": p, "integer": integer}))
     for i, p in enumerate(INIT_CASES):
         cases.append((f"init_{p['kind']}_{i}", "init", p))
     cases.append(("conv_config1", "conv_config1", {}))
@@ -171,13 +198,13 @@ def make_inputs(name, family, p):
             a = r.standard_normal(p["a_shape"]).astype(f32)
             b = r.standard_normal(p["b_shape"]).astype(f32)
         return {"a": a, "b": b, "seed_dy": np.array([r.integers(1 << 30)], np.int64)}
-    if family == "conv":
+    if family in ("conv", "conv_transpose", "depthwise"):
         if p["integer"]:
             x = r.integers(0, 16, p["x_shape"]).astype(f32)
             w = r.integers(0, 16, p["w_shape"]).astype(f32)
         else:
             x = r.standard_normal(p["x_shape"]).astype(f32)
-            fan = p["w_shape"][1] * p["w_shape"][2] * p["w_shape"][3]
+            fan = int(np.prod(p["w_shape"][1:]))
             w = (r.standard_normal(p["w_shape"]) * np.sqrt(2.0 / fan)).astype(f32)
         return {"x": x, "w": w, "seed_dy": np.array([r.integers(1 << 30)], np.int64), "integer": np.array([int(p["integer"])])}
     if family == "conv_config1":
@@ -283,6 +310,15 @@ def run_case(nn, family, p, inp):
         _prefill(x, 1.0)
         _prefill(w, 1.0)
         y = nn.conv2D(x, w, stride=p["stride"], dilation=p["dilation"], padding=p["padding"])
+        out["y"] = y.np()
+        nn.backward({y: _dy_like(inp["seed_dy"], y.shape, p["integer"])}, grad_for_non_trainables=True)
+        out["dx"], out["dw"] = x.get_grad().np(), w.get_grad().np()
+    elif family in ("conv_transpose", "depthwise"):
+        x, w = T(inp["x"]), T(inp["w"])
+        _prefill(x, 1.0)
+        _prefill(w, 1.0)
+        fn = nn.conv2DTranspose if family == "conv_transpose" else nn.depthwise_conv2D
+        y = fn(x, w, stride=p["stride"], dilation=p["dilation"], padding=p["padding"])
         out["y"] = y.np()
         nn.backward({y: _dy_like(inp["seed_dy"], y.shape, p["integer"])}, grad_for_non_trainables=True)
         out["dx"], out["dw"] = x.get_grad().np(), w.get_grad().np()

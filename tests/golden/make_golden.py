@@ -3,7 +3,9 @@ reference (iperov/litenn) on the cases of cases.py.  The reference's Python op l
 own generated kernel text are used as they are; only the OpenCL binding is replaced by the
 host-C executor of cl_on_cpu.py because no OpenCL device exists where this runs.
 
-    python tests/golden/make_golden.py [/path/to/litenn/checkout]
+    python tests/golden/make_golden.py /path/to/litenn/checkout [family ...]
+
+Without family names every fixture is regenerated; with them only the named ones.
 
 The fixtures hold inputs and outputs, so the tests never need the reference.
 """
@@ -15,7 +17,10 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, HERE)
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: make_golden.py /path/to/litenn/checkout [family ...]")
+REF = sys.argv[1]
+ONLY = set(sys.argv[2:])
 sys.path.insert(0, REF)
 
 import cl_on_cpu  # noqa: E402
@@ -31,6 +36,8 @@ def main():
     by_family = {}
     t0 = time.time()
     for name, family, params in cases.all_cases():
+        if ONLY and family not in ONLY:
+            continue
         inp = cases.make_inputs(name, family, params)
         out = cases.run_case(nn, family, params, inp)
         store = by_family.setdefault(family, {})

@@ -87,6 +87,32 @@ def test_conv(nn_gpu, name, family, p):
             assert_contraction_close(got[k], outs[k], ks[k], f"{name} {k}")
 
 
+@pytest.mark.parametrize("name,family,p", _cases("conv_transpose"))
+def test_conv_transpose(nn_gpu, name, family, p):
+    """conv2DTranspose forward, dI and dK on the tile engine against the unmodified reference
+    (gradients accumulated into tensors pre-filled with 1); integer cases bit for bit."""
+    ins, outs = load_golden(family)[name]
+    got = cases.run_case(nn_gpu, family, p, ins)
+    (N, IC, IH, IW), (OC, _, KH, KW) = p["x_shape"], p["w_shape"]
+    OH, OW = outs["y"].shape[2:]
+    ks = {"y": IC * KH * KW, "dx": OC * KH * KW, "dw": N * OH * OW}
+    for k in outs:
+        if p["integer"]:
+            assert_bit_exact(got[k], outs[k], f"{name} {k}")
+        else:
+            assert_contraction_close(got[k], outs[k], ks[k], f"{name} {k}")
+    nn_gpu.devices.check_status()
+
+
+@pytest.mark.parametrize("name,family,p", _cases("depthwise"))
+def test_depthwise(nn_gpu, name, family, p):
+    """depthwise_conv2D: forward, dI and dK bit for bit (same products, same order of additions)."""
+    ins, outs = load_golden(family)[name]
+    got = cases.run_case(nn_gpu, family, p, ins)
+    for k in outs:
+        assert_bit_exact(got[k], outs[k], f"{name} {k}")
+
+
 def test_conv_config1(nn_gpu):
     """The single-conv configuration: x[8,16,32,32], w[32,16,3,3] He-normal, bias, 'same'."""
     import oracle as o
@@ -417,10 +443,54 @@ def test_conv_random_geometries(nn_gpu, n, ic, h, w, oc, k, stride, dil):
 
 
 def test_softmax_ce(nn_gpu):
+    """Fused softmax / categorical cross-entropy (one kernel each way) and the reference's
+    composition of nine operators, both against what the unmodified reference produced."""
     ins, outs = load_golden("softmax_ce")["softmax_ce"]
     got = cases.run_case(nn_gpu, "softmax_ce", {}, ins)
     for k in outs:
-        np.testing.assert_allclose(got[k], outs[k], rtol=1e-5, atol=1e-6, err_msg=k)
+        np.testing.assert_allclose(got[k], outs[k], rtol=1e-5, atol=1e-6, err_msg=f"fused {k}")
+    with nn_gpu.deferred.disabled():
+        comp = cases.run_case(nn_gpu, "softmax_ce", {}, ins)
+    for k in outs:
+        np.testing.assert_allclose(comp[k], outs[k], rtol=1e-5, atol=1e-6, err_msg=f"composition {k}")
+    # forward values of the fused kernels are those of the composition, bit for bit
+    assert_bit_exact(got["prob"], comp["prob"], "softmax")
+    assert_bit_exact(got["loss"], comp["loss"], "cross-entropy")
+    np.testing.assert_allclose(got["dlogits"], comp["dlogits"], rtol=2e-6, atol=1e-8)
+
+
+def test_softmax_ce_classifier_size(nn_gpu):
+    """[1024, 1000] logits (the classifier's micro-batch), one-hot targets and a shared target
+    row: fused kernels against the composition."""
+    nn = nn_gpu
+    rng = np.random.default_rng(41)
+    lg = (rng.standard_normal((1024, 1000)) * 3).astype(np.float32)
+    onehot = np.zeros((1024, 1000), np.float32)
+    onehot[np.arange(1024), rng.integers(0, 1000, 1024)] = 1
+    shared = rng.dirichlet(np.ones(1000)).astype(np.float32)
+    launches = {}
+    for tg in (onehot, shared):
+        res = {}
+        for mode in ("fused", "composed"):
+            lt, tt = nn.Tensor_from_value(lg), nn.Tensor_from_value(tg)
+            dev = nn.devices.get_current()[0]
+            n0 = dev.launch_count()
+            if mode == "composed":
+                with nn.deferred.disabled():
+                    p = nn.softmax(lt)
+                    loss = nn.categorical_crossentropy(p, tt).mean()
+                    loss.backward(grad_for_non_trainables=True)
+            else:
+                p = nn.softmax(lt)
+                loss = nn.categorical_crossentropy(p, tt).mean()
+                loss.backward(grad_for_non_trainables=True)
+            launches[mode] = dev.launch_count() - n0
+            res[mode] = (p.np(), loss.np(), lt.get_grad().np())
+        assert_bit_exact(res["fused"][0], res["composed"][0], "softmax")
+        assert_bit_exact(res["fused"][1], res["composed"][1], "mean cross-entropy")
+        np.testing.assert_allclose(res["fused"][2], res["composed"][2], rtol=1e-5, atol=1e-9)
+    assert launches["fused"] * 2 <= launches["composed"], launches
+    nn.devices.check_status()
 
 
 def test_cnn_training_step(nn_gpu):

@@ -135,6 +135,30 @@ def test_conv(name, p):
     assert_bit_exact(dw, outs["dw"], name + " dw")
 
 
+@pytest.mark.parametrize("name,p", _cases("conv_transpose"))
+def test_conv_transpose(name, p):
+    ins, outs = load_golden("conv_transpose")[name]
+    x, k = ins["x"], ins["w"]
+    args = (p["stride"], p["dilation"], p["padding"])
+    y = o.conv2d_transpose_fwd(x, k, *args)
+    dy = cases._dy_like(ins["seed_dy"], y.shape, p["integer"])
+    assert_bit_exact(y, outs["y"], name + " y")
+    assert_bit_exact(o.conv2d_transpose_dx(np.ones_like(x), dy, k, *args), outs["dx"], name + " dx")
+    assert_bit_exact(o.conv2d_transpose_dk(np.ones_like(k), dy, x, *args), outs["dw"], name + " dk")
+
+
+@pytest.mark.parametrize("name,p", _cases("depthwise"))
+def test_depthwise(name, p):
+    ins, outs = load_golden("depthwise")[name]
+    x, k = ins["x"], ins["w"]
+    args = (p["stride"], p["dilation"], p["padding"])
+    y = o.depthwise_fwd(x, k, *args)
+    dy = cases._dy_like(ins["seed_dy"], y.shape, p["integer"])
+    assert_bit_exact(y, outs["y"], name + " y")
+    assert_bit_exact(o.depthwise_dx(np.ones_like(x), dy, k, *args), outs["dx"], name + " dx")
+    assert_bit_exact(o.depthwise_dk(np.ones_like(k), dy, x, *args), outs["dw"], name + " dk")
+
+
 def _init_oracle(p, hash_seed):
     kind, a = p["kind"], p["args"]
     if kind == "uniform":
