@@ -3,7 +3,8 @@
 // window order; avg divides the ordered sum by the number of in-bounds taps; max/min of
 // an empty window is 0; the max/min gradient goes to the FIRST tap (row-major) equal to
 // the pooled value.  HBM-bound: the 2x2/stride-2 even-width case reads two float4 rows
-// per two outputs and writes float2; everything else uses the generic scalar kernel.
+// per two outputs and writes float2; everything else uses the generic kernels, which clip each
+// window to the image once instead of testing every tap.
 #include "lnn_common.cuh"
 #include <math_constants.h>
 
@@ -15,34 +16,41 @@ struct PoolGeom {
   int ih, iw, oh, ow, pool, stride, padl, padt;
 };
 
+// The part of window (oh, ow) that lies inside the image: rows [h0, h1), columns [w0, w1).
+struct Window { int h0, h1, w0, w1; };
+__device__ __forceinline__ Window window_of(const PoolGeom& g, int oh, int ow) {
+  Window w;
+  const int top = oh * g.stride - g.padt, left = ow * g.stride - g.padl;
+  w.h0 = max(top, 0); w.h1 = min(top + g.pool, g.ih);
+  w.w0 = max(left, 0); w.w1 = min(left + g.pool, g.iw);
+  return w;
+}
+
+// Generic forward: one thread per output.  The window is clipped to the image once, then its
+// elements are combined in row-major order, which is the order in which the reference visits
+// the taps it does not skip (pool2D.py:111-146): sum / (number of in-image taps), or max / min
+// with 0 for a window that lies entirely outside.
 template <int MODE>
 __global__ void __launch_bounds__(kThreads)
 pool_fwd_kernel(float* __restrict__ O, const float* __restrict__ I, int64_t total, PoolGeom g) {
-  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t gid = tid; gid < total; gid += nthreads) {
+  for (int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; gid < total; gid += (int64_t)gridDim.x * blockDim.x) {
     const int ow = (int)(gid % g.ow);
-    const int64_t t = gid / g.ow;
-    const int oh = (int)(t % g.oh);
-    const int64_t plane = t / g.oh;               // n*C + c
-    const float* ip = I + plane * g.ih * g.iw;
-    float v = MODE == LNN_POOL_AVG ? 0.0f : (MODE == LNN_POOL_MAX ? -CUDART_INF_F : CUDART_INF_F);
-    int cnt = 0;
-    for (int ph = 0; ph < g.pool; ++ph)
-      for (int pw = 0; pw < g.pool; ++pw) {
-        const int ih = -g.padt + ph + oh * g.stride;
-        const int iw = -g.padl + pw + ow * g.stride;
-        if (iw >= 0 && ih >= 0 && iw < g.iw && ih < g.ih) {
-          const float x = ip[(int64_t)ih * g.iw + iw];
-          if (MODE == LNN_POOL_AVG) { v = __fadd_rn(v, x); ++cnt; }
-          else if (MODE == LNN_POOL_MAX) v = fmaxf(v, x);
-          else v = fminf(v, x);
-        }
+    const int64_t rest = gid / g.ow;
+    const int oh = (int)(rest % g.oh);
+    const float* plane = I + (rest / g.oh) * g.ih * g.iw;
+    const Window w = window_of(g, oh, ow);
+    float acc = MODE == LNN_POOL_AVG ? 0.0f : (MODE == LNN_POOL_MAX ? -CUDART_INF_F : CUDART_INF_F);
+    for (int h = w.h0; h < w.h1; ++h) {
+      const float* row = plane + (int64_t)h * g.iw;
+      for (int x = w.w0; x < w.w1; ++x) {
+        const float v = row[x];
+        acc = MODE == LNN_POOL_AVG ? __fadd_rn(acc, v) : (MODE == LNN_POOL_MAX ? fmaxf(acc, v) : fminf(acc, v));
       }
-    if (MODE == LNN_POOL_AVG) { if (cnt != 0) v = __fdiv_rn(v, (float)cnt); }
-    else if (MODE == LNN_POOL_MAX) { if (v == -CUDART_INF_F) v = 0.0f; }
-    else { if (v == CUDART_INF_F) v = 0.0f; }
-    O[gid] = v;
+    }
+    const int count = max(w.h1 - w.h0, 0) * max(w.w1 - w.w0, 0);
+    if (MODE == LNN_POOL_AVG) { if (count > 0) acc = __fdiv_rn(acc, (float)count); }
+    else if (acc == (MODE == LNN_POOL_MAX ? -CUDART_INF_F : CUDART_INF_F)) acc = 0.0f;
+    O[gid] = acc;
   }
 }
 
@@ -143,52 +151,49 @@ pool2x2_bwd_kernel(float* __restrict__ dI, const float* __restrict__ I, const fl
   }
 }
 
-// Backward, one thread per INPUT element, exactly the reference's gather formulation.
+// Generic backward: one thread per INPUT element (so "+=" needs no atomics).  The windows that
+// contain element (ih, iw) form a rectangle of outputs, oh in [oh_lo, oh_hi], ow likewise; their
+// contributions are added from the highest (oh, ow) down, the order in which the reference meets
+// them while it walks its taps upwards (pool2D.py:147-230), so overlapping windows accumulate
+// identically.  avg: dO / (in-image size of the window).  max / min: dO if this element is the
+// first one of the window, in row-major order, that equals the pooled value.
 template <int MODE>
 __global__ void __launch_bounds__(kThreads)
 pool_bwd_kernel(float* __restrict__ dI, const float* __restrict__ I, const float* __restrict__ dO,
                 const float* __restrict__ O, int64_t total, PoolGeom g) {
-  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t gid = tid; gid < total; gid += nthreads) {
+  for (int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; gid < total; gid += (int64_t)gridDim.x * blockDim.x) {
     const int iw = (int)(gid % g.iw);
-    const int64_t t = gid / g.iw;
-    const int ih = (int)(t % g.ih);
-    const int64_t plane = t / g.ih;
-    const float* ip = I ? I + plane * g.ih * g.iw : nullptr;
-    const float* op = O ? O + plane * g.oh * g.ow : nullptr;
-    const float* dop = dO + plane * g.oh * g.ow;
-    float v = 0.0f;
-    for (int ph = 0; ph < g.pool; ++ph)
-      for (int pw = 0; pw < g.pool; ++pw) {
-        const int oh = (g.padt + ih - ph) / g.stride;   // C division truncates toward zero
-        const int ow = (g.padl + iw - pw) / g.stride;
-        if (ow >= 0 && oh >= 0 && ow < g.ow && oh < g.oh &&
-            iw == (-g.padl + pw + ow * g.stride) && ih == (-g.padt + ph + oh * g.stride)) {
-          if (MODE == LNN_POOL_AVG) {
-            int dcount = 0;
-            for (int dph = 0; dph < g.pool; ++dph)
-              for (int dpw = 0; dpw < g.pool; ++dpw) {
-                const int dih = -g.padt + dph + oh * g.stride;
-                const int diw = -g.padl + dpw + ow * g.stride;
-                dcount += (diw >= 0 && dih >= 0 && diw < g.iw && dih < g.ih);
-              }
-            v = __fadd_rn(v, __fdiv_rn(dop[(int64_t)oh * g.ow + ow], (float)dcount));
-          } else {
-            const float ov = op[(int64_t)oh * g.ow + ow];
-            for (int k = 0; k < g.pool * g.pool; ++k) {
-              const int dih = -g.padt + (k / g.pool) + oh * g.stride;
-              const int diw = -g.padl + (k % g.pool) + ow * g.stride;
-              if (diw >= 0 && dih >= 0 && diw < g.iw && dih < g.ih &&
-                  ip[(int64_t)dih * g.iw + diw] == ov) {
-                if (dih == ih && diw == iw) v = __fadd_rn(v, dop[(int64_t)oh * g.ow + ow]);
-                break;
-              }
-            }
+    const int64_t rest = gid / g.iw;
+    const int ih = (int)(rest % g.ih);
+    const int64_t pl = rest / g.ih;
+    const float* iplane = I ? I + pl * g.ih * g.iw : nullptr;
+    const float* oplane = O ? O + pl * g.oh * g.ow : nullptr;
+    const float* gplane = dO + pl * g.oh * g.ow;
+    // windows covering the element: oh*stride - padt <= ih < oh*stride - padt + pool
+    const int ah = ih + g.padt, aw = iw + g.padl;
+    const int oh_hi = min(ah / g.stride, g.oh - 1), ow_hi = min(aw / g.stride, g.ow - 1);
+    const int oh_lo = max((ah - g.pool + g.stride) / g.stride, 0), ow_lo = max((aw - g.pool + g.stride) / g.stride, 0);
+    float sum = 0.0f;
+    for (int oh = oh_hi; oh >= oh_lo; --oh)
+      for (int ow = ow_hi; ow >= ow_lo; --ow) {
+        const Window w = window_of(g, oh, ow);
+        const float go = gplane[(int64_t)oh * g.ow + ow];
+        if (MODE == LNN_POOL_AVG) {
+          sum = __fadd_rn(sum, __fdiv_rn(go, (float)((w.h1 - w.h0) * (w.w1 - w.w0))));
+        } else {
+          const float pooled = oplane[(int64_t)oh * g.ow + ow];
+          if (iplane[(int64_t)ih * g.iw + iw] != pooled) continue;
+          // is an earlier element of the window equal to the pooled value too?
+          bool first = true;
+          for (int h = w.h0; h <= ih && first; ++h) {
+            const int stop = h == ih ? iw : w.w1;
+            for (int x = w.w0; x < stop; ++x)
+              if (iplane[(int64_t)h * g.iw + x] == pooled) { first = false; break; }
           }
+          if (first) sum = __fadd_rn(sum, go);
         }
       }
-    dI[gid] = __fadd_rn(dI[gid], v);
+    dI[gid] = __fadd_rn(dI[gid], sum);
   }
 }
 
