@@ -57,7 +57,9 @@ struct FcParams {
   int nsub, pws;                          // MMA tiles per super-tile, slots per patch row (8*nsub + 2)
   int tiles_w, tiles_h;
   int act; float alpha;
-  int ep_mode;                            // 0 NCHW, 1 pooled NCHW, 3 pooled channel-innermost fp32 + largest magnitude
+  int ep_mode;                            // 0 NCHW, 1 pooled NCHW, 3 pooled channel-innermost fp32 + largest magnitude,
+                                          // 4 pooled channel-innermost split fp16 (scale from the bound in amax_out[-1])
+  float* out_lo;
   int ocp;                                // channel pitch of the ep_mode 3 output
   const uint32_t* amax_x; uint32_t* amax_out;
   int* status;
@@ -310,6 +312,7 @@ fewch_conv_kernel(const __grid_constant__ FcParams p) {
     const int jfirst = (warp - 5) >> 2;                         // the two warps of a quarter take alternate tiles
     const int prow = 4 * quarter + (lane >> 3), pcol = lane & 7;
     const FastPow2 sc(exp_of_amax(__ldg(p.amax_x)) + e_w);
+    const FastPow2 so(p.ep_mode == 4 ? -exp_of_amax(__ldg(p.amax_out - 1)) : 0);
     const int ohp = p.oh >> 1, owp = p.ow >> 1;
     const int sub4 = (lane & 1) | ((lane >> 2) & 2);            // position inside the 2x2 window
     const bool sel_b0 = (sub4 & 1) != 0, sel_b1 = (sub4 & 2) != 0;
@@ -462,6 +465,17 @@ fewch_conv_kernel(const __grid_constant__ FcParams p) {
 #pragma unroll
                 for (int k = 0; k < 8; ++k)
                   if (cb + k < p.oc) dst[k * cstride] = q[k];
+              } else if (ep_mode == 4 && cb < p.ocp) {
+                // the next convolution's operand, written here: eight channels = 16 bytes of hi and of lo
+                const int64_t off = (((int64_t)img * ohp + ph_) * owp + pw_) * p.ocp + cb;
+                __align__(16) __half h[8];
+                __align__(16) __half l[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) split_half(so(q[k]), h[k], l[k]);
+                *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.out) + off) = *reinterpret_cast<const uint4*>(h);
+                *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.out_lo) + off) = *reinterpret_cast<const uint4*>(l);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) amax_acc = max(amax_acc, __float_as_uint(q[k]) & 0x7fffffffu);
               } else if (cb < p.ocp) {
                 float* dst = p.out + (((int64_t)img * ohp + ph_) * owp + pw_) * p.ocp + cb;
                 if (!FC_DBG(p, 8)) {
@@ -491,7 +505,7 @@ fewch_conv_kernel(const __grid_constant__ FcParams p) {
       printf("epilogue warp %d: %d tiles, wait %lld work %lld clocks per tile; per tile: ld-wait %lld, through pooling %lld\n", warp, it,
              dbg_wait / max(it, 1), dbg_work / max(it, 1), dbg_ph0 / max(it, 1), dbg_ph1 / max(it, 1));
 #endif
-    if (ep_mode == 3 || (FC_DBG(p, 8) && p.amax_out)) warp_amax_commit(amax_acc, p.amax_out);
+    if (ep_mode >= 3 || (FC_DBG(p, 8) && p.amax_out)) warp_amax_commit(amax_acc, p.amax_out);
   }
 
   // ---- tear-down -----------------------------------------------------------------------------
@@ -514,14 +528,15 @@ bool conv_fewch_applicable(const lnn_conv_geom* g) {
 }
 
 // ep_mode 0: Y = NCHW result; 1: pooled NCHW; 3: pooled channel-innermost fp32 with channel pitch
-// ocp, its largest magnitude accumulated into *amax_out (which the caller zeroed).  amax_x holds
-// the fp32 bit pattern of the input's largest magnitude.
+// ocp, its largest magnitude accumulated into *amax_out (which the caller zeroed); 4: pooled
+// channel-innermost split fp16 (Y = hi, Y_lo = lo) scaled by the bound in amax_out[-1].  amax_x
+// holds the fp32 bit pattern of the input's largest magnitude.
 int conv_fewch_fwd(Device* d, const lnn_conv_geom* g, float* Y, const float* X, const float* W,
                    const float* bias, int act, float alpha, int ep_mode, int ocp, const uint32_t* amax_x,
-                   uint32_t* amax_out) {
+                   uint32_t* amax_out, float* Y_lo) {
   FcParams p;
   memset(&p, 0, sizeof(p));
-  p.X = X; p.W = W; p.bias = bias; p.out = Y;
+  p.X = X; p.W = W; p.bias = bias; p.out = Y; p.out_lo = Y_lo;
   p.n = g->n; p.ic = g->ic; p.ih = g->ih; p.iw = g->iw; p.oc = g->oc; p.oh = g->oh; p.ow = g->ow;
   p.padl = g->padl; p.padt = g->padt;
   p.ocn = (g->oc + 31) & ~31;

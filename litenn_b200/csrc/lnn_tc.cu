@@ -72,12 +72,29 @@ __device__ __forceinline__ void pooled_store(const TcParams& p, const Pow2Scale&
         if (p.out_lo) p.out_lo[base + (int64_t)j * p.out_sb] = lo;
       }
     }
-  } else {
+  } else if (p.ep_mode == 3) {
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
       if (j < npool) {
         const float v = real ? m[j] : 0.0f;                  // pad channels are written as zeros
         p.out[base + (int64_t)j * p.out_sb] = v;
+        amax = max(amax, __float_as_uint(v) & 0x7fffffffu);
+      }
+    }
+  } else {
+    // fp16 split written directly: the scale comes from an upper bound of the result that was
+    // known before the launch (word 0 of the output's trailer)
+    const Pow2Scale so(-exp_of_amax(__ldg(p.amax_out - 1)));
+    __half* const oh = reinterpret_cast<__half*>(p.out);
+    __half* const ol = reinterpret_cast<__half*>(p.out_lo);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      if (j < npool) {
+        const float v = real ? m[j] : 0.0f;
+        __half h, l;
+        split_half(so(v), h, l);
+        oh[base + (int64_t)j * p.out_sb] = h;
+        ol[base + (int64_t)j * p.out_sb] = l;
         amax = max(amax, __float_as_uint(v) & 0x7fffffffu);
       }
     }
@@ -550,7 +567,7 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
       if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
     }
     __syncwarp();
-    if (p.ep_mode == 3) warp_amax_commit(amax_acc, p.amax_out);
+    if (p.ep_mode >= 3) warp_amax_commit(amax_acc, p.amax_out);
   }
 
   // ---- tear-down ------------------------------------------------------------------------
@@ -850,7 +867,7 @@ tc_halo_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
       if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
     }
     __syncwarp();
-    if (p.ep_mode == 3) warp_amax_commit(amax_acc, p.amax_out);
+    if (p.ep_mode >= 3) warp_amax_commit(amax_acc, p.amax_out);
   }
 
   tc_fence_before();
@@ -888,6 +905,53 @@ absmax_kernel(const float* __restrict__ src, int64_t n, uint32_t* __restrict__ o
     for (int64_t i = tid; i < n; i += nthreads) m = max(m, __float_as_uint(src[i]) & 0x7fffffffu);
   }
   warp_amax_commit(m, out);
+}
+
+// Upper bound of |act(conv2D(x, W) + bias)|: amax(x) * max over oc of sum |W[oc]| + max |bias|, times
+// max(1, |alpha|) for leaky_relu, with a 2^-6 margin for the roundings on the way.  A result that is
+// packed with the scale of this bound cannot overflow fp16, so the epilogue can write the split
+// fp16 operand of the next layer itself instead of an fp32 tensor that a second pass would have to
+// measure and split.  The bound exceeds the true maximum by a few bits, which only moves the
+// 18-binade window of full relative precision; the absolute error floor of the format (2^-40 of
+// the scale) stays far below an fp32 rounding of the tensor's large elements.
+// out[0] = bound (bit pattern), out[1] = 0 (the epilogue accumulates the true maximum there).
+__global__ void __launch_bounds__(256)
+conv_bound_kernel(uint32_t* __restrict__ out, const float* __restrict__ W, int oc, int per_oc,
+                  const float* __restrict__ bias, const uint32_t* __restrict__ amax_x, int act, float alpha) {
+  __shared__ float red[256];
+  float best = 0.0f;
+  for (int o = threadIdx.x; o < oc; o += blockDim.x) {
+    const float* w = W + (int64_t)o * per_oc;
+    float s = 0.0f;
+    for (int k = 0; k < per_oc; ++k) s += fabsf(w[k]);
+    best = fmaxf(best, s);
+  }
+  float bm = 0.0f;
+  if (bias)
+    for (int o = threadIdx.x; o < oc; o += blockDim.x) bm = fmaxf(bm, fabsf(bias[o]));
+  red[threadIdx.x] = best;
+  __syncthreads();
+  for (int h = 128; h > 0; h >>= 1) {
+    if (threadIdx.x < h) red[threadIdx.x] = fmaxf(red[threadIdx.x], red[threadIdx.x + h]);
+    __syncthreads();
+  }
+  const float wnorm = red[0];
+  __syncthreads();
+  red[threadIdx.x] = bm;
+  __syncthreads();
+  for (int h = 128; h > 0; h >>= 1) {
+    if (threadIdx.x < h) red[threadIdx.x] = fmaxf(red[threadIdx.x], red[threadIdx.x + h]);
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    const uint32_t ax_bits = amax_x[1] != 0u ? amax_x[1] : amax_x[0];
+    float b = __uint_as_float(ax_bits) * wnorm + red[0];
+    if (act) b *= fmaxf(1.0f, fabsf(alpha));
+    b *= 1.015625f;
+    // a non-finite bound (non-finite input, weights or bias) means "no scaling", like a measured one
+    out[0] = __float_as_uint(b);
+    out[1] = 0u;
+  }
 }
 
 // What a split pass needs per thread: the tf32 split needs nothing, the fp16 split the two
@@ -1304,7 +1368,9 @@ int check_passes(int precision) {
 
 // Largest magnitude of `count` floats into *amax (zeroed first, on the stream).
 int launch_absmax(lnn::Device* d, uint32_t* amax, const float* src, int64_t count) {
-  LNN_CUDA(cudaMemsetAsync(amax, 0, sizeof(uint32_t), d->stream));
+  // word 0: the magnitude that defines the scale; word 1: the measured largest magnitude when
+  // word 0 is only an upper bound (0 = "the same as word 0")
+  LNN_CUDA(cudaMemsetAsync(amax, 0, 2 * sizeof(uint32_t), d->stream));
   absmax_kernel<<<grid_for(d, count / 4 + 1), kThreads, 0, d->stream>>>(src, count, amax);
   LNN_CHECK_LAUNCH(d);
   return LNN_OK;
@@ -1885,15 +1951,16 @@ int conv_fwd_impl(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint6
   const uint64_t out_elems = (uint64_t)g->n * oh_p * ow_p * ocp;   // of a packed result
   float* const y_lo = want_lo ? (float*)(uintptr_t)o.y_lo : nullptr;
 
-  // fp16 packed output: the kernels write the fp32 channel-innermost result and its largest
-  // magnitude, then one element-wise pass splits it (the scale must be known before the split)
-  lnn::Scratch raw(d);
-  auto raw_target = [&](float** dst, uint32_t** amax) -> int {
-    int r = raw.get(out_elems * 4);
-    if (r) return r;
-    *dst = raw.as<float>();
-    *amax = trailer_of((void*)(uintptr_t)Y, out_elems);
-    LNN_CUDA(cudaMemsetAsync(*amax, 0, sizeof(uint32_t), d->stream));
+  // fp16 packed output written by the epilogue itself: its scale comes from an upper bound of the
+  // result (conv_bound_kernel) placed in word 0 of the output's trailer before the launch; the
+  // epilogue accumulates the true largest magnitude in word 1 for the next layer's bound
+  auto bound_target = [&](const uint32_t* amax_x, uint32_t** amax_true) -> int {
+    uint32_t* tr = trailer_of((void*)(uintptr_t)Y, out_elems);
+    lnn::ProfScope prof(d, LNN_PROF_PREP);
+    conv_bound_kernel<<<1, 256, 0, d->stream>>>(tr, (const float*)(uintptr_t)W, g->oc, g->ic * g->kh * g->kw, biasp,
+                                                amax_x, act, alpha);
+    LNN_CHECK_LAUNCH(d);
+    *amax_true = tr + 1;
     return LNN_OK;
   };
 
@@ -1911,12 +1978,11 @@ int conv_fwd_impl(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint6
     }
     const bool can_pool = o.pool && !((g->oh | g->ow) & 1);     // the fused pool pairs rows and columns
     if (can_pool && o.out_packed) {
-      float* dst; uint32_t* amax;
-      rc = raw_target(&dst, &amax);
+      uint32_t* amax_true;
+      rc = bound_target(xmax.as<uint32_t>(), &amax_true);
       if (rc) return rc;
-      rc = lnn::conv_fewch_fwd(d, g, dst, xp, wp, biasp, act, alpha, 3, ocp, xmax.as<uint32_t>(), amax);
-      if (rc) return rc;
-      return half_split_packed(d, (void*)(uintptr_t)Y, y_lo, dst, out_elems);
+      return lnn::conv_fewch_fwd(d, g, (float*)(uintptr_t)Y, xp, wp, biasp, act, alpha, 4, ocp, xmax.as<uint32_t>(),
+                                 amax_true, y_lo);
     }
     if (can_pool || (!o.pool && !o.out_packed))
       return lnn::conv_fewch_fwd(d, g, (float*)(uintptr_t)Y, xp, wp, biasp, act, alpha, can_pool ? 1 : 0, ocp,
@@ -1946,9 +2012,13 @@ int conv_fwd_impl(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint6
   }
   if (!o.in_packed && !o.w_swapped && lnn::conv_direct_applicable(g) && knobs().direct && (!o.out_packed || o.pool)) {
     if (o.out_packed && f16) {
-      float* dst; uint32_t* amax;
-      rc = raw_target(&dst, &amax);
+      // this kernel writes fp32 and the largest magnitude; one element-wise pass splits it
+      lnn::Scratch raw(d);
+      rc = raw.get(out_elems * 4);
       if (rc) return rc;
+      float* dst = raw.as<float>();
+      uint32_t* amax = trailer_of((void*)(uintptr_t)Y, out_elems);
+      LNN_CUDA(cudaMemsetAsync(amax, 0, 2 * sizeof(uint32_t), d->stream));
       rc = lnn::conv_direct_fwd(d, g, dst, (const float*)(uintptr_t)X, (const float*)(uintptr_t)W, biasp, act,
                                 alpha, 0, o.pool, 2, (float*)amax, ocp);
       if (rc) return rc;
@@ -1998,8 +2068,8 @@ int conv_fwd_impl(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint6
     if (o.out_packed) {
       cf.out = (float*)(uintptr_t)Y;
       if (f16) {
-        ex.ep_mode = 3;
-        rc = raw_target(&cf.out, &ex.amax_out);
+        ex.ep_mode = 4; ex.out_lo = y_lo;
+        rc = bound_target(ox.amax, &ex.amax_out);
         if (rc) return rc;
       } else {
         ex.ep_mode = 2; ex.out_lo = y_lo;
@@ -2012,10 +2082,7 @@ int conv_fwd_impl(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint6
     int fused = 0;
     rc = launch_conv_like(d, ox, ow, cf, &ex, &fused);
     if (rc) return rc;
-    if (fused) {
-      if (o.out_packed && f16) return half_split_packed(d, (void*)(uintptr_t)Y, y_lo, cf.out, out_elems);
-      return LNN_OK;
-    }
+    if (fused) return LNN_OK;
   }
   // un-fused: convolution into its NCHW result (scratch when more steps follow)
   lnn::Scratch conv_out(d), pool_out(d);

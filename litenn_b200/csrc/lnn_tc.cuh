@@ -93,8 +93,9 @@ struct TcParams {
   // fused 2x2/stride-2 max pool (channels-on-M kernels): ep_mode 1 writes the pooled NCHW
   // tensor, ep_mode 2 writes it channel-innermost and pre-split in tf32 (out = hi, out_lo = lo,
   // channel pitch ocp) as the next convolution's operand, ep_mode 3 writes it channel-innermost
-  // in fp32 and records its largest magnitude (the fp16 split needs that before it can run);
-  // the out_s* strides then address pooled pixels
+  // in fp32 and records its largest magnitude, ep_mode 4 writes the fp16 split (out = hi, out_lo = lo)
+  // scaled by an upper bound that sits in the word before *amax_out, and records the true
+  // largest magnitude in *amax_out; the out_s* strides then address pooled pixels
   int ep_mode;
   float* out_lo;
   int ocp;

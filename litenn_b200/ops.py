@@ -799,7 +799,8 @@ class PackedActivation:
     """An activation kept in the tensor-core convolution's operand format between the layers of
     an inference chain: channel-innermost copies hi and lo, each (N, H, W, C rounded up to 8).
     Split FP16 (the default precision): fp16 values of x / s with s a power of two derived from
-    the tensor's largest magnitude, whose bit pattern sits in a trailer behind hi.  Split TF32:
+    the tensor's largest magnitude or an upper bound of it, whose bit pattern sits in a trailer
+    behind hi.  Split TF32:
     hi = tf32(x), lo = tf32(x - hi) as fp32.  Only conv2D_infer / conv2D_pool and the gradient
     entries consume it; the reference has no counterpart (its conv2D builds an im2col buffer per
     call, conv2D.py:39-41).  hi / lo are flat fp32-typed tensors used as raw storage."""
@@ -834,6 +835,15 @@ class PackedActivation:
             return 0
         off = (self._elems() * 2 + 15) & ~15
         return scale_exponent_of(int(self.hi.np().view(np.uint8)[off:off + 4].view(np.uint32)[0]))
+
+    def largest_magnitude(self):
+        """The largest |x| of the activation as measured by the kernel that wrote it (split FP16
+        only).  A convolution that writes this format takes its scale from an upper bound of its
+        result (trailer word 0) and records the measured maximum in trailer word 1; the split
+        pre-pass measures first and leaves word 1 zero."""
+        off = (self._elems() * 2 + 15) & ~15
+        w = self.hi.np().view(np.uint8)[off:off + 8].view(np.uint32)
+        return float(w[1:2].view(np.float32)[0] if w[1] else w[0:1].view(np.float32)[0])
 
     def np(self):
         """(hi + lo) * 2**e as an NCHW array: the fp32 activation up to its last two mantissa bits."""
