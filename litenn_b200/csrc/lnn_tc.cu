@@ -915,39 +915,33 @@ absmax_kernel(const float* __restrict__ src, int64_t n, uint32_t* __restrict__ o
 // 18-binade window of full relative precision; the absolute error floor of the format (2^-40 of
 // the scale) stays far below an fp32 rounding of the tensor's large elements.
 // out[0] = bound (bit pattern), out[1] = 0 (the epilogue accumulates the true maximum there).
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 conv_bound_kernel(uint32_t* __restrict__ out, const float* __restrict__ W, int oc, int per_oc,
                   const float* __restrict__ bias, const uint32_t* __restrict__ amax_x, int act, float alpha) {
-  __shared__ float red[256];
-  float best = 0.0f;
-  for (int o = threadIdx.x; o < oc; o += blockDim.x) {
+  __shared__ float red_w[32], red_b[32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  float best = 0.0f, bm = 0.0f;
+  for (int o = warp; o < oc; o += nwarps) {          // one warp per output channel, coalesced
     const float* w = W + (int64_t)o * per_oc;
     float s = 0.0f;
-    for (int k = 0; k < per_oc; ++k) s += fabsf(w[k]);
+    for (int k = lane; k < per_oc; k += 32) s += fabsf(__ldg(w + k));
+#pragma unroll
+    for (int sh = 16; sh > 0; sh >>= 1) s += __shfl_xor_sync(0xffffffffu, s, sh);
     best = fmaxf(best, s);
   }
-  float bm = 0.0f;
   if (bias)
-    for (int o = threadIdx.x; o < oc; o += blockDim.x) bm = fmaxf(bm, fabsf(bias[o]));
-  red[threadIdx.x] = best;
+    for (int o = threadIdx.x; o < oc; o += blockDim.x) bm = fmaxf(bm, fabsf(__ldg(bias + o)));
+#pragma unroll
+  for (int sh = 16; sh > 0; sh >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, sh));
+  if (lane == 0) { red_w[warp] = best; red_b[warp] = bm; }
   __syncthreads();
-  for (int h = 128; h > 0; h >>= 1) {
-    if (threadIdx.x < h) red[threadIdx.x] = fmaxf(red[threadIdx.x], red[threadIdx.x + h]);
-    __syncthreads();
-  }
-  const float wnorm = red[0];
-  __syncthreads();
-  red[threadIdx.x] = bm;
-  __syncthreads();
-  for (int h = 128; h > 0; h >>= 1) {
-    if (threadIdx.x < h) red[threadIdx.x] = fmaxf(red[threadIdx.x], red[threadIdx.x + h]);
-    __syncthreads();
-  }
   if (threadIdx.x == 0) {
+    float wnorm = 0.0f, bmax = 0.0f;
+    for (int i = 0; i < nwarps; ++i) { wnorm = fmaxf(wnorm, red_w[i]); bmax = fmaxf(bmax, red_b[i]); }
     const uint32_t ax_bits = amax_x[1] != 0u ? amax_x[1] : amax_x[0];
-    float b = __uint_as_float(ax_bits) * wnorm + red[0];
+    float b = __uint_as_float(ax_bits) * wnorm + bmax;
     if (act) b *= fmaxf(1.0f, fabsf(alpha));
-    b *= 1.015625f;
+    b *= 1.015625f;       // covers the rounding of the sums above and of the accumulation itself
     // a non-finite bound (non-finite input, weights or bias) means "no scaling", like a measured one
     out[0] = __float_as_uint(b);
     out[1] = 0u;
@@ -1763,7 +1757,8 @@ int launch_conv_like(lnn::Device* d, const Operand& act, const Operand& w, const
   // (measured: with 64 or more output channels the channels-on-M epilogue -- 128-bit stores along
   // W -- is the faster one whenever the output is unit-stride along W; the strided scatter of a
   // stride-2 input gradient is better served by pixels on M)
-  if (orient == 0) orient = (c.OCv >= 64 && c.out_sb == 1) ? 2 : 1;
+  // (a fused pool / packed output exists only in the channels-on-M epilogue)
+  if (orient == 0) orient = (pooled || (c.OCv >= 64 && c.out_sb == 1)) ? 2 : 1;
   const bool chan_m = orient == 2;
   PixTile t = plan_conv_tile(c.NL, c.AH, c.AW, c.es, chan_m ? 256 : 128);
   if (pooled) {
@@ -1957,7 +1952,7 @@ int conv_fwd_impl(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint6
   auto bound_target = [&](const uint32_t* amax_x, uint32_t** amax_true) -> int {
     uint32_t* tr = trailer_of((void*)(uintptr_t)Y, out_elems);
     lnn::ProfScope prof(d, LNN_PROF_PREP);
-    conv_bound_kernel<<<1, 256, 0, d->stream>>>(tr, (const float*)(uintptr_t)W, g->oc, g->ic * g->kh * g->kw, biasp,
+    conv_bound_kernel<<<1, 1024, 0, d->stream>>>(tr, (const float*)(uintptr_t)W, g->oc, g->ic * g->kh * g->kw, biasp,
                                                 amax_x, act, alpha);
     LNN_CHECK_LAUNCH(d);
     *amax_true = tr + 1;
