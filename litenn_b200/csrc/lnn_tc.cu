@@ -34,19 +34,37 @@ __device__ __forceinline__ void pooled_store(const TcParams& p, const Pow2Scale&
   if (p.ep_mode == 1 && !real) return;
   if (p.ep_mode >= 2 && oc >= p.ocp) return;
   float m[16];
+  // Scaling by a power of two, adding the bias and leaky_relu with alpha >= 0 never reverse the
+  // order of two values, so the window's maximum is taken on the raw accumulators and only the
+  // winner goes through them: a quarter of the arithmetic, the same value.  (An accumulator that
+  // overflowed to +inf wins here and may become the NaN -> 0 of the pooling kernel where the
+  // literal order would have skipped it.)  alpha < 0 takes the literal order.
+  if (!(p.act && p.alpha < 0.0f)) {
 #pragma unroll
-  for (int j = 0; j < 16; ++j) {
-    float t00 = __uint_as_float(v0[2 * j]), t01 = __uint_as_float(v0[2 * j + 1]);
-    float t10 = __uint_as_float(v1[2 * j]), t11 = __uint_as_float(v1[2 * j + 1]);
-    if (p.esz == 2) { t00 = sc(t00); t01 = sc(t01); t10 = sc(t10); t11 = sc(t11); }
-    if (p.bias) {
-      t00 = __fadd_rn(t00, bias_v); t01 = __fadd_rn(t01, bias_v);
-      t10 = __fadd_rn(t10, bias_v); t11 = __fadd_rn(t11, bias_v);
+    for (int j = 0; j < 16; ++j) {
+      float t = fmaxf(fmaxf(__uint_as_float(v0[2 * j]), __uint_as_float(v0[2 * j + 1])),
+                      fmaxf(__uint_as_float(v1[2 * j]), __uint_as_float(v1[2 * j + 1])));
+      if (p.esz == 2) t = sc(t);
+      if (p.bias) t = __fadd_rn(t, bias_v);
+      t = apply_act(t, p.act, p.alpha);
+      const float mm = fmaxf(-CUDART_INF_F, t);
+      m[j] = (mm == -CUDART_INF_F) ? 0.0f : mm;
     }
-    t00 = apply_act(t00, p.act, p.alpha); t01 = apply_act(t01, p.act, p.alpha);
-    t10 = apply_act(t10, p.act, p.alpha); t11 = apply_act(t11, p.act, p.alpha);
-    const float mm = fmaxf(fmaxf(fmaxf(fmaxf(-CUDART_INF_F, t00), t01), t10), t11);
-    m[j] = (mm == -CUDART_INF_F) ? 0.0f : mm;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      float t00 = __uint_as_float(v0[2 * j]), t01 = __uint_as_float(v0[2 * j + 1]);
+      float t10 = __uint_as_float(v1[2 * j]), t11 = __uint_as_float(v1[2 * j + 1]);
+      if (p.esz == 2) { t00 = sc(t00); t01 = sc(t01); t10 = sc(t10); t11 = sc(t11); }
+      if (p.bias) {
+        t00 = __fadd_rn(t00, bias_v); t01 = __fadd_rn(t01, bias_v);
+        t10 = __fadd_rn(t10, bias_v); t11 = __fadd_rn(t11, bias_v);
+      }
+      t00 = apply_act(t00, p.act, p.alpha); t01 = apply_act(t01, p.act, p.alpha);
+      t10 = apply_act(t10, p.act, p.alpha); t11 = apply_act(t11, p.act, p.alpha);
+      const float mm = fmaxf(fmaxf(fmaxf(fmaxf(-CUDART_INF_F, t00), t01), t10), t11);
+      m[j] = (mm == -CUDART_INF_F) ? 0.0f : mm;
+    }
   }
   const int npool = min(wvalid, p.AW - b0) >> 1;          // pooled pixels of this chunk that exist
   const int64_t base = n * p.out_sn + (int64_t)(a >> 1) * p.out_sa + (int64_t)(b0 >> 1) * p.out_sb +
@@ -181,7 +199,7 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&tmem_full_bar[a]), 1);
-      mbar_init(smem_u32(&tmem_empty_bar[a]), 4);     // one arrival per epilogue warp
+      mbar_init(smem_u32(&tmem_empty_bar[a]), kEpilogueWarps);     // one arrival per epilogue warp
     }
     fence_barrier_init();
   }
@@ -337,8 +355,10 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
       }
     }
   } else {
-    // ---- epilogue warps: TMEM lane quarter = warp % 4 --------------------------------------
+    // ---- epilogue warps: TMEM lane quarter = warp % 4; the two warps of a quarter take the
+    // even and the odd 32-column chunks of the accumulator --------------------------------------
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;
     // fp16 split: the accumulator holds the product of the scaled operands
     const bool scaled = p.esz == 2;
@@ -364,9 +384,11 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
           // fused max pool: tw is a multiple of 32 and th even, so a 32-column chunk is a piece
           // of one image row and the chunk tw columns later is the row below it
           const int chunks_per_row = p.tw >> 5;
+          int turn = 0;
           for (int tn_i = 0; tn_i < p.tn; ++tn_i) {
             for (int th_i = 0; th_i < p.th; th_i += 2) {
               for (int ch = 0; ch < chunks_per_row; ++ch) {
+                if (((turn++) & 1) != half) continue;
                 const int c_top = (tn_i * p.th + th_i) * p.tw + ch * 32;
                 uint32_t v0[32], v1[32];
                 tmem_ld32(d_tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c_top, v0);
@@ -385,9 +407,11 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
           continue;
         }
         float* const obase = p.out + p.out_base + (int64_t)oc * p.out_sc;
-        // running (image, row, column) of the first pixel of the current group of four
-        int tn_i = 0, th_i = 0, tw_i = 0;
-        for (int c0 = 0; c0 < p.bn; c0 += 32) {
+        for (int c0 = half * 32; c0 < p.bn; c0 += 64) {
+          // (image, row, column) of the first pixel of the current group of four
+          int tn_i = c0 / (p.th * p.tw);
+          int th_i = (c0 - tn_i * p.th * p.tw) / p.tw;
+          int tw_i = c0 - (tn_i * p.th + th_i) * p.tw;
           uint32_t v[32];
           tmem_ld32(d_tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
           tmem_ld_wait();
@@ -496,7 +520,7 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
       }
       float* outp = p.out + row_off;
       const bool vec_ok = (MODE != MODE_CONV) && ((((uintptr_t)outp) & 15) == 0);
-      for (int c0 = 0; c0 < p.bn; c0 += 32) {
+      for (int c0 = half * 32; c0 < p.bn; c0 += 64) {
         uint32_t v[32];
         if (t.num_kb > 0) {
           tmem_ld32(d_tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
@@ -599,7 +623,7 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
 // Channels sit on M (kernel tile = operand A, one unit per tap), pixels on N.
 //   warp 0 : kernel-unit producer      warp 1 : MMA issuer, TMEM owner
 //   warp 6 : patch producer            warps 2-5 : epilogue
-constexpr int kThreadsHalo = 224;
+constexpr int kThreadsHalo = 32 * (kEpilogueWarps + 3);   // two producers, the MMA warp, the epilogue warps
 
 __global__ void __launch_bounds__(kThreadsHalo, 1)
 tc_halo_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUtensorMap tmAl,
@@ -645,7 +669,7 @@ tc_halo_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&tmem_full_bar[a]), 1);
-      mbar_init(smem_u32(&tmem_empty_bar[a]), 4);
+      mbar_init(smem_u32(&tmem_empty_bar[a]), kEpilogueWarps);
     }
     fence_barrier_init();
   }
@@ -660,7 +684,7 @@ tc_halo_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
   const uint32_t afull0 = smem_u32(&a_full_bar[0]), aempty0 = smem_u32(&a_empty_bar[0]);
   const uint32_t bfull0 = smem_u32(&b_full_bar[0]), bempty0 = smem_u32(&b_empty_bar[0]);
 
-  if (warp == 6) {
+  if (warp == 2 + kEpilogueWarps) {
     // ---- patch producer -----------------------------------------------------------------
     if (lane == 0) {
       const uint32_t tx = (uint32_t)nbuf * (uint32_t)(p.h_pw * p.h_ph) * row_bytes;
@@ -756,6 +780,7 @@ tc_halo_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
   } else {
     // ---- epilogue: lane = output channel, columns = flattened patch positions ---------------
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;                 // the two warps of a quarter alternate over the chunks
     const int r = quarter * 32 + lane;
     const int ncols = p.th * p.h_pw;                  // columns that can hold a real pixel
     const bool scaled = p.esz == 2;
@@ -776,8 +801,10 @@ tc_halo_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
       const float bias_v = (row_ok && p.bias) ? __ldg(p.bias + oc) : 0.0f;
       if (p.ep_mode != 0) {
         // fused max pool: th even, tw a multiple of 32; the row below column c is column c + h_pw
+        int turn = 0;
         for (int h_i = 0; h_i < p.th; h_i += 2) {
           for (int w0 = 0; w0 < p.tw; w0 += 32) {
+            if (((turn++) & 1) != half) continue;
             const int c_top = h_i * p.h_pw + w0;
             uint32_t v0[32], v1[32];
             tmem_ld32(d_tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c_top, v0);
@@ -795,8 +822,8 @@ tc_halo_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
         continue;
       }
       float* const obase = p.out + p.out_base + (int64_t)oc * p.out_sc + (int64_t)t.pn0 * p.out_sn;
-      int h_i = 0, w_i = 0;                           // position of the current group of four
-      for (int c0 = 0; c0 < ncols; c0 += 32) {
+      for (int c0 = half * 32; c0 < ncols; c0 += 64) {
+        int h_i = c0 / p.h_pw, w_i = c0 - h_i * p.h_pw;      // position of the current group of four
         uint32_t v[32];
         tmem_ld32(d_tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
         tmem_ld_wait();
@@ -1680,7 +1707,11 @@ int launch_conv_halo(lnn::Device* d, const Operand& act, const Operand& w, const
   // TMA writes, about 90 bytes per clock), so the resident patch only pays where the per-tap
   // kernel is at its worst: one tap per ring stage (a single channel block) or so few output
   // channels that it would put them on N; and only when few accumulator columns are wasted.
+  // With the fused pool the tile must be whole rows of 32 pixels and the two halo columns of each
+  // row cost accumulator columns (192 real pixels of 256 at best): measured slower than the
+  // per-tap kernel on its full 256-pixel tiles (1.05 against 0.73 ms for 1024 x 32->64 @ 64x64).
   if (!hp.ok) return LNN_OK;
+  if (pooled && knobs().halo != 2) return LNN_OK;
   if (knobs().halo != 2 && !(hp.px_per_clk >= 1.15 && (c.OCv < 64 || c.kp == cb))) return LNN_OK;
 
   TcParams p;

@@ -1,6 +1,6 @@
 // tcgen05 / TMEM / TMA tile engine shared by matmul and the three convolution passes.
 //
-// One persistent CTA per SM (192 threads) walks the 128 x BN output tiles round-robin:
+// One persistent CTA per SM (320 threads) walks the 128 x BN output tiles round-robin:
 //   warp 0    : TMA producer  -- cp.async.bulk.tensor loads into a ring of smem stages,
 //                                running ahead across tile boundaries
 //   warp 1    : MMA issuer    -- one elected thread issues tcgen05.mma (kind::f16 or kind::tf32)
@@ -36,7 +36,8 @@
 
 namespace lnn_tc {
 
-constexpr int kThreadsTc = 192;
+constexpr int kEpilogueWarps = 8;                 // two per TMEM lane quarter
+constexpr int kThreadsTc = 32 * (kEpilogueWarps + 2);   // producer warp, MMA warp, epilogue warps
 constexpr int kMaxTaps = 64;
 constexpr long long kWaitBudget = 1500000000ll;   // ~0.8 s of SM clocks
 constexpr int kAbortDelay = 400000;               // cycles granted to in-flight TMA copies
