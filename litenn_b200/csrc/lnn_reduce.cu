@@ -324,6 +324,47 @@ reduce_warp4_kernel(float* __restrict__ O, const float* __restrict__ I, RedGeom 
   }
 }
 
+// The same for short rows (128 ... 1024 columns, S = s known at compile time): a warp works on four
+// rows at a time so that the loads of all four are in flight before the first shuffle (one row
+// per iteration left the kernel latency-bound at 2.7 TB/s on rows of 256 columns).
+template <int OP, int S>
+__global__ void __launch_bounds__(kThreads)
+reduce_warp4_short_kernel(float* __restrict__ O, const float* __restrict__ I, RedGeom g, Levels L, int acc,
+                          float mean_div) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int64_t ns = L.n[S];
+  for (int64_t row0 = warp0 * 4; row0 < g.rows; row0 += nwarps * 4) {
+    float4 v[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int64_t row = row0 + q < g.rows ? row0 + q : g.rows - 1;      // the tail repeats the last row
+      v[q] = subtree_pow2_v4<OP, S, 0>(I + row_base(g, row), 4 * lane, ns, g);
+    }
+#pragma unroll
+    for (int h = 16; h >= 1; h >>= 1) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float4 o;
+        o.x = __shfl_down_sync(0xffffffffu, v[q].x, h); o.y = __shfl_down_sync(0xffffffffu, v[q].y, h);
+        o.z = __shfl_down_sync(0xffffffffu, v[q].z, h); o.w = __shfl_down_sync(0xffffffffu, v[q].w, h);
+        if (lane < h) v[q] = comb4<OP>(v[q], o);
+      }
+    }
+    if (lane == 0) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (row0 + q < g.rows) {
+          float r = comb<OP>(comb<OP>(v[q].x, v[q].z), comb<OP>(v[q].y, v[q].w));
+          if (mean_div != 0.0f) r = __fdiv_rn(r, mean_div);
+          O[row0 + q] = acc ? __fadd_rn(O[row0 + q], r) : r;
+        }
+      }
+    }
+  }
+}
+
 // 128-bit variant of reduce_parts_kernel.  rows_vec != 0: a thread owns four adjacent kept
 // rows (inner % 4 == 0) of one c0; else four adjacent columns c0..c0+3 of one row (inner == 1,
 // mid == 1).  Either way its four results are adjacent in O / P.
@@ -538,7 +579,17 @@ int reduce_impl(lnn::Device* d, PartialSpace& space, float* O, const float* I, i
         int64_t blocks = lnn_ceil_div(g.rows, kThreads / 32);
         const int64_t cap = (int64_t)d->sm_count * 16;
         if (blocks > cap) blocks = cap;
-        reduce_warp4_kernel<OP><<<(unsigned)blocks, kThreads, 0, d->stream>>>(O, I, g, L, s, acc, mean_div);
+        if (s <= 3 && g.rows >= 4096) {
+          blocks = std::min<int64_t>(lnn_ceil_div(g.rows, 4 * (kThreads / 32)), cap);
+          switch (s) {
+            case 0: reduce_warp4_short_kernel<OP, 0><<<(unsigned)blocks, kThreads, 0, d->stream>>>(O, I, g, L, acc, mean_div); break;
+            case 1: reduce_warp4_short_kernel<OP, 1><<<(unsigned)blocks, kThreads, 0, d->stream>>>(O, I, g, L, acc, mean_div); break;
+            case 2: reduce_warp4_short_kernel<OP, 2><<<(unsigned)blocks, kThreads, 0, d->stream>>>(O, I, g, L, acc, mean_div); break;
+            default: reduce_warp4_short_kernel<OP, 3><<<(unsigned)blocks, kThreads, 0, d->stream>>>(O, I, g, L, acc, mean_div); break;
+          }
+        } else {
+          reduce_warp4_kernel<OP><<<(unsigned)blocks, kThreads, 0, d->stream>>>(O, I, g, L, s, acc, mean_div);
+        }
         LNN_CHECK_LAUNCH(d);
         return LNN_OK;
       }
