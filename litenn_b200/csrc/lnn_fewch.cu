@@ -69,30 +69,6 @@ struct FcParams {
   int debug;                              // experiments: 1 no MMAs, 2 no patch fill, 4 no epilogue math / stores
 };
 
-// Bounded wait that polls with mbarrier.test_wait: the super-tiles of this kernel are short
-// (a few thousand clocks), so the wake-up latency of a suspended try_wait would show in every
-// hand-over between the roles.
-__device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                               int* status, int role, int step) {
-  if (mbar_test_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  for (int spin = 0;; ++spin) {
-    if (mbar_test_wait(bar, parity)) return true;
-    if ((spin & 63) == 63) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitBudget) {
-        *abort_flag = 1;
-        if (atomicCAS(status, 0, LNN_E_TIMEOUT) == 0) {
-          status[1] = role;
-          status[2] = (int)blockIdx.x;
-          status[3] = step;
-        }
-        return false;
-      }
-    }
-  }
-}
-
 __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
@@ -235,7 +211,7 @@ fewch_conv_kernel(const __grid_constant__ FcParams p) {
       const int th_i = (tile / p.tiles_w) % p.tiles_h;
       const int img = tile / (p.tiles_w * p.tiles_h);
       const int row0 = th_i * kRows - p.padt, col0 = tw_i * 8 * p.nsub - p.padl;
-      ok = mbar_wait_poll(smem_u32(&patch_empty[s]), ph ^ 1u, abort_flag, p.status, 0, tile);
+      ok = mbar_wait(smem_u32(&patch_empty[s]), ph ^ 1u, abort_flag, p.status, 0, tile);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       uint8_t* const dst_hi = gen_base + 2 * p.w_bytes + (size_t)s * 2 * p.patch_bytes;
@@ -281,8 +257,8 @@ fewch_conv_kernel(const __grid_constant__ FcParams p) {
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++it) {
         const int set = it & 1;
         const uint32_t set_ph = (uint32_t)(it >> 1) & 1u;
-        if (!mbar_wait_poll(smem_u32(&tmem_empty[set]), set_ph ^ 1u, abort_flag, p.status, 3, it)) { ok = false; break; }
-        if (!mbar_wait_poll(smem_u32(&patch_full[s]), ph, abort_flag, p.status, 1, it)) { ok = false; break; }
+        if (!mbar_wait(smem_u32(&tmem_empty[set]), set_ph ^ 1u, abort_flag, p.status, 3, it)) { ok = false; break; }
+        if (!mbar_wait(smem_u32(&patch_full[s]), ph, abort_flag, p.status, 1, it)) { ok = false; break; }
         tc_fence_after();
         const uint32_t pa = patch0 + s * 2u * (uint32_t)p.patch_bytes;
         for (int j = 0; j < (FC_DBG(p, 1) ? 0 : p.nsub); ++j) {
@@ -330,7 +306,7 @@ fewch_conv_kernel(const __grid_constant__ FcParams p) {
 #ifdef LNN_TC_EXPERIMENTS
       const long long tw0 = clock64();
 #endif
-      bool have = mbar_wait_poll(smem_u32(&tmem_full[set]), set_ph, abort_flag, p.status, 2, it);
+      bool have = mbar_wait(smem_u32(&tmem_full[set]), set_ph, abort_flag, p.status, 2, it);
       have = __all_sync(0xffffffffu, have);
       if (!have) break;
       tc_fence_after();
