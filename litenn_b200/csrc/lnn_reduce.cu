@@ -365,6 +365,41 @@ reduce_warp4_short_kernel(float* __restrict__ O, const float* __restrict__ I, Re
   }
 }
 
+// Number of blocks of a single-row reduction that have stored their partials; the block that
+// finds itself last finishes the row and resets the counter for the next launch.
+static __device__ unsigned int g_blocks_done;
+
+// The halving tree over x[i] = P[first + stride * i], i < m (m a power of two): stage after stage
+// element i is combined with element i + m/2.  Leaves are visited in bit-reversed order so that
+// a binary-counter stack meets them in exactly that pairing; eight loads are in flight at a time.
+// P was written by other blocks of the same launch: the loads go to L2.
+template <int OP>
+__device__ float strided_halving_tree(const float* P, int64_t first, int64_t stride, int m) {
+  float stack[24];
+  const int bits = 31 - __clz(m);
+  float w = 0.0f;
+  for (int k0 = 0; k0 < m; k0 += 8) {
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int k = k0 + u;
+      const int i = bits ? (int)(__brev((unsigned)k) >> (32 - bits)) : 0;
+      v[u] = k < m ? __ldcg(P + first + stride * i) : 0.0f;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int k = k0 + u;
+      if (k < m) {
+        w = v[u];
+        int level = 0;
+        for (int kk = k; kk & 1; kk >>= 1, ++level) w = comb<OP>(stack[level], w);
+        stack[level] = w;
+      }
+    }
+  }
+  return w;
+}
+
 // 128-bit variant of reduce_parts_kernel.  rows_vec != 0: a thread owns four adjacent kept
 // rows (inner % 4 == 0) of one c0; else four adjacent columns c0..c0+3 of one row (inner == 1,
 // mid == 1).  Either way its four results are adjacent in O / P.
@@ -373,7 +408,9 @@ template <int OP>
 // occupancy (measured: 0.67 -> 0.76 of the copy bandwidth on the axis-1 case; 6 blocks: 0.59)
 __global__ void __launch_bounds__(kThreads, 4)
 reduce_parts4_kernel(float* __restrict__ O, float* __restrict__ P, const float* __restrict__ I,
-                     RedGeom g, Levels L, int s, int rows_vec, int acc, float mean_div) {
+                     RedGeom g, Levels L, int s, int rows_vec, int acc, float mean_div, int finish_row = 0) {
+  __shared__ float tail_vals[kThreads];
+  __shared__ int is_last;
   const int64_t parts = L.n[s];
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
@@ -407,6 +444,36 @@ reduce_parts4_kernel(float* __restrict__ O, float* __restrict__ P, const float* 
       const int64_t c0 = (gid - row * parts4) << 2;
       const float4 v = subtree_v4<OP>(I + row_base(g, row), c0, s, L, g);
       *reinterpret_cast<float4*>(P + row * parts + c0) = v;     // partials of a row are contiguous
+    }
+    if (finish_row) {
+      // One kept row, power-of-two column count, few partials: the last block to arrive runs the
+      // rest of the same tree over them instead of two more dependent launches.
+      __threadfence();
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        const unsigned int prev = atomicAdd(&g_blocks_done, 1u);
+        is_last = prev == gridDim.x - 1;
+      }
+      __syncthreads();
+      if (!is_last) return;
+      __threadfence();
+      const int width = parts < kThreads ? (int)parts : kThreads;      // a power of two
+      if ((int)threadIdx.x < width)
+        tail_vals[threadIdx.x] = strided_halving_tree<OP>(P, threadIdx.x, width, (int)(parts / width));
+      __syncthreads();
+      for (int h = width >> 1; h >= 1; h >>= 1) {
+        float nv = 0.0f;
+        if ((int)threadIdx.x < h) nv = comb<OP>(tail_vals[threadIdx.x], tail_vals[threadIdx.x + h]);
+        __syncthreads();
+        if ((int)threadIdx.x < h) tail_vals[threadIdx.x] = nv;
+        __syncthreads();
+      }
+      if (threadIdx.x == 0) {
+        float r = tail_vals[0];
+        if (mean_div != 0.0f) r = __fdiv_rn(r, mean_div);
+        O[0] = acc ? __fadd_rn(O[0], r) : r;
+        g_blocks_done = 0u;
+      }
     }
   }
 }
@@ -565,7 +632,8 @@ int reduce_impl(lnn::Device* d, PartialSpace& space, float* O, const float* I, i
   const int64_t cols = r0 * r1;
   const int64_t kTargetThreads = 1 << 19;
   if (inner == 1) {
-    const bool split = (g.rows * kThreads < kTargetThreads / 2) && cols > 65536;
+    const bool split = ((g.rows * kThreads < kTargetThreads / 2) && cols > 65536) ||
+                       (g.rows == 1 && L.pow2 && cols >= 8192);
     // 128-bit paths need contiguous, 16-byte aligned columns
     const bool cols_vec = L.pow2 && ((((uintptr_t)I) & 15) == 0) &&
                           (r0 == 1 || (r1 % 4 == 0 && g.stride_r0 % 4 == 0)) && g.stride_mid % 4 == 0 &&
@@ -620,6 +688,10 @@ int reduce_impl(lnn::Device* d, PartialSpace& space, float* O, const float* I, i
     int s = 6;
     while (s < L.S && g.rows * L.n[s] > target_vals) ++s;
     if (L.pow2 && s > kMaxPow2Levels) s = kMaxPow2Levels;   // stay on the unrolled subtree (more partials)
+    // A single row of a few hundred thousand columns (the partials of an all-axes reduction): 16
+    // leaves per thread and at most 2^14 partials, which the last block of the same launch finishes.
+    const bool finish_here = g.rows == 1 && L.pow2 && cols_vec && cols <= (1ll << 18) && cols >= (1ll << 12);
+    if (finish_here) s = 4;
     const int64_t parts = L.n[s];
     float* part = nullptr;
     rc = space.get(g.rows * parts, &part);
@@ -628,6 +700,12 @@ int reduce_impl(lnn::Device* d, PartialSpace& space, float* O, const float* I, i
     // the kept axes: the second pass is then a plain row reduction over `parts` columns, the tail
     // of the same tree
     if (cols_vec && s <= kMaxPow2Levels && parts % 4 == 0 && ((((uintptr_t)part) & 15) == 0)) {
+      if (finish_here) {
+        reduce_parts4_kernel<OP><<<grid_for(d, parts / 4), kThreads, 0, d->stream>>>(
+            O, part, I, g, L, s, 0, acc, mean_div, 1);
+        LNN_CHECK_LAUNCH(d);
+        return LNN_OK;
+      }
       reduce_parts4_kernel<OP><<<grid_for(d, g.rows * parts / 4), kThreads, 0, d->stream>>>(
           nullptr, part, I, g, L, s, 0, 0, 0.0f);
     } else {
