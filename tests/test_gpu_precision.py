@@ -128,3 +128,37 @@ def test_split_fp16_wide_dynamic_range(nn_gpu, monkeypatch):
     got = nn.matmul(nn.Tensor_from_value(a), nn.Tensor_from_value(b0)).np()
     assert not np.isfinite(got[0]).any() and np.isfinite(got[1:]).all()
     nn.devices.check_status()
+
+
+@pytest.mark.parametrize("spread", [1e-2, 1e-5])
+def test_packed_chain_with_a_loose_scale_bound(nn_gpu, monkeypatch, spread):
+    """A convolution that hands its result on in the packed format scales it by an upper bound
+    of the result, not by the measured maximum.  Weights that cancel (a zero-sum high-pass
+    filter on a nearly constant image) make that bound loose by the factor 1 / spread: the second
+    convolution of the chain must still come out with the accuracy of the chain that passes fp32
+    tensors, because the format has 17 bits of headroom below its largest element."""
+    monkeypatch.setenv("LNN_PRECISION", "2")
+    nn = nn_gpu
+    rng = np.random.default_rng(11)
+    n, c, h, w = 2, 32, 32, 32
+    x = (1.0 + spread * rng.standard_normal((n, c, h, w))).astype(np.float32)
+    w1 = rng.standard_normal((64, c, 3, 3)).astype(np.float32)
+    w1 -= w1.mean(axis=(1, 2, 3), keepdims=True)                # every output channel sums to zero
+    w1 = w1.astype(np.float32)
+    w2 = (rng.standard_normal((64, 64, 3, 3)) * 0.1).astype(np.float32)
+    xt, w1t, w2t = nn.Tensor_from_value(x), nn.Tensor_from_value(w1), nn.Tensor_from_value(w2)
+    # interior pixels only see the noise: the border (zero padding) sees the constant and is cropped
+    y1 = o.conv2d_fwd(x, w1, 1, 1, "same", accum64=True)
+    p1 = y1.reshape(n, 64, h // 2, 2, w // 2, 2).max(axis=(3, 5))
+    want = o.conv2d_fwd(p1, w2, 1, 1, "same", accum64=True).astype(np.float64)
+    packed = nn.conv2D_infer(xt, w1t, pool=True, packed_output=True)
+    loose = packed.scale_exponent() - nn.ops.scale_exponent_of(
+        int(np.float32(packed.largest_magnitude()).view(np.uint32)))
+    assert loose >= 0
+    got = nn.conv2D_infer(packed, w2t).np()
+    with nn.deferred.disabled():
+        chain = nn.conv2D(nn.max_pool2D(nn.conv2D(xt, w1t), 2, 2, "same"), w2t).np()
+    scale = float(np.abs(want).max())
+    e_packed, e_chain = _err(got, want), _err(chain, want)
+    assert e_packed <= 2 * e_chain + 1e-6 * scale, (e_packed, e_chain, scale, loose)
+    nn.devices.check_status()
