@@ -177,6 +177,14 @@ int lnn_pool2d_fwd(int dev, int mode, uint64_t O, uint64_t I, int64_t n, int64_t
  * LNN_E_UNSUPPORTED otherwise.  ref: op/pool2D.py:147-230 + op/element_wise_op.py:207-221 */
 int lnn_pool2x2_lrelu_bwd(int dev, uint64_t dZ, uint64_t Y, uint64_t P, uint64_t dP, int64_t n,
                           int64_t c, int ih, int iw, float alpha, int act);
+/* The same gradient without the full-resolution activation: IDX [n,c,ih/2,iw/2] bytes is the map
+ * of winning window positions (0..3 row-major, 4 = none) that lnn_conv2d_fwd_packed writes beside
+ * a pooled NCHW result.  T (optional, pooled size) receives the winner's gradient: its sum over
+ * (n, h, w) is the bias gradient of the block, so no pass over a full-resolution tensor is needed
+ * for it.  dZ bit-identical to lnn_pool2x2_lrelu_bwd.  Same shape / alignment rules.
+ * ref: op/pool2D.py:147-230 + op/element_wise_op.py:207-221 */
+int lnn_pool2x2_idx_lrelu_bwd(int dev, uint64_t dZ, uint64_t T, uint64_t IDX, uint64_t P, uint64_t dP,
+                              int64_t n, int64_t c, int ih, int iw, float alpha, int act);
 /* dI += ... ; ref: op/pool2D.py:147-230 (I and O are only read for max/min) */
 int lnn_pool2d_bwd(int dev, int mode, uint64_t dI, uint64_t I, uint64_t dO, uint64_t O,
                    int64_t n, int64_t c, int ih, int iw, int oh, int ow,
@@ -275,8 +283,13 @@ int lnn_nhwc_split(int dev, uint64_t hi, uint64_t lo, uint64_t X, int n, int c, 
  * stay in that format, so that a chain of convolutions never writes or re-reads the NCHW
  * activations between layers.  in_packed: X / X_lo are the packed copies of the input
  * [n][ih][iw][pad8(ic)].  out_packed: Y / Y_lo receive the packed copies of the (pooled) result
- * [n][oh'][ow'][pad8(oc)]; otherwise Y is the NCHW result and Y_lo is ignored.  The values are
- * those of the un-fused entries (the packed result equals lnn_nhwc_split of their output).
+ * [n][oh'][ow'][pad8(oc)]; otherwise Y is the NCHW result.  With pool = 1 and out_packed = 0 a
+ * non-zero Y_lo receives one byte per pooled element [n][oc][oh'][ow']: the window position
+ * (0..3 in row-major order, 4 = none) of the first element equal to the pooled value, which is
+ * all that lnn_pool2x2_idx_lrelu_bwd needs of the full-resolution activation (a training step
+ * then never writes it); in every other combination Y_lo is ignored when out_packed = 0.  The
+ * values are those of the un-fused entries (the packed result equals lnn_nhwc_split of their
+ * output for precisions 1 and 3; for precision 2 its scale comes from a bound of the result).
  * ref: op/conv2D.py:9-44, module/Conv2D.py:58-62, op/element_wise_op.py:207-221,
  * op/pool2D.py:47-146 */
 int lnn_conv2d_fwd_packed(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t Y_lo, uint64_t X,

@@ -251,6 +251,44 @@ pool2x2_lrelu_bwd_kernel(float* __restrict__ dZ, const float* __restrict__ Y, co
   }
 }
 
+// The same gradient from the map of winning window positions a fused forward epilogue wrote
+// (0..3 in row-major order, 4 = no position matched) instead of the full-resolution activation:
+// the winner holds the pooled value itself, so leaky_relu' is taken from the sign of P, and every
+// other position is +0 whatever its activation was.  T (optional, pooled size) receives the
+// winner's value: its sum over (n, h, w) is the bias gradient.
+__global__ void __launch_bounds__(kThreads)
+pool2x2_idx_lrelu_bwd_kernel(float* __restrict__ dZ, float2* __restrict__ T, const uchar2* __restrict__ IDX,
+                             const float2* __restrict__ dP, const float2* __restrict__ P, int64_t total2, int ih,
+                             int iw, int oh, int ow2, float alpha, int act) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t gid = tid; gid < total2; gid += nthreads) {
+    const int x2 = (int)(gid % ow2);
+    const int64_t t = gid / ow2;
+    const int y = (int)(t % oh);
+    const int64_t plane = t / oh;
+    const int64_t off0 = (plane * ih + 2 * y) * (int64_t)iw + 4 * x2;
+    const uchar2 w = IDX[gid];
+    const float2 g = dP[gid];
+    const float2 o = P[gid];
+    float u[2] = {__fadd_rn(0.0f, __fadd_rn(0.0f, g.x)), __fadd_rn(0.0f, __fadd_rn(0.0f, g.y))};
+    if (act) {
+      const float f0 = __fadd_rn(o.x >= 0.0f ? 1.0f : 0.0f, __fmul_rn(alpha, o.x < 0.0f ? 1.0f : 0.0f));
+      const float f1 = __fadd_rn(o.y >= 0.0f ? 1.0f : 0.0f, __fmul_rn(alpha, o.y < 0.0f ? 1.0f : 0.0f));
+      u[0] = __fadd_rn(0.0f, __fmul_rn(u[0], f0));
+      u[1] = __fadd_rn(0.0f, __fmul_rn(u[1], f1));
+    }
+    if (w.x > 3) u[0] = 0.0f;
+    if (w.y > 3) u[1] = 0.0f;
+    float ra[4] = {0.f, 0.f, 0.f, 0.f}, rb[4] = {0.f, 0.f, 0.f, 0.f};
+    if (w.x == 0) ra[0] = u[0]; else if (w.x == 1) ra[1] = u[0]; else if (w.x == 2) rb[0] = u[0]; else if (w.x == 3) rb[1] = u[0];
+    if (w.y == 0) ra[2] = u[1]; else if (w.y == 1) ra[3] = u[1]; else if (w.y == 2) rb[2] = u[1]; else if (w.y == 3) rb[3] = u[1];
+    __stcs(reinterpret_cast<float4*>(dZ + off0), make_float4(ra[0], ra[1], ra[2], ra[3]));
+    __stcs(reinterpret_cast<float4*>(dZ + off0 + iw), make_float4(rb[0], rb[1], rb[2], rb[3]));
+    if (T) T[gid] = make_float2(u[0], u[1]);
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -331,6 +369,24 @@ int lnn_pool2d_bwd(int dev, int mode, uint64_t dI, uint64_t I, uint64_t dO, uint
   return LNN_OK;
 }
 
+
+int lnn_pool2x2_idx_lrelu_bwd(int dev, uint64_t dZ, uint64_t T, uint64_t IDX, uint64_t P, uint64_t dP, int64_t n,
+                              int64_t c, int ih, int iw, float alpha, int act) {
+  LNN_DEV(d, dev);
+  LNN_REQUIRE(dZ && IDX && P && dP, "null buffer");
+  LNN_REQUIRE(n > 0 && c > 0 && ih > 0 && iw > 0, "bad extents");
+  LNN_REQUIRE(act == 0 || act == 1, "unknown activation %d", act);
+  if ((ih & 1) || (iw & 3) || (dZ & 15) || ((P | dP | T) & 7) || (IDX & 1))
+    return lnn::set_error(LNN_E_UNSUPPORTED,
+                          "fused pooling gradient needs an even height, a width that is a multiple of 4 and aligned buffers");
+  const int oh = ih / 2, ow = iw / 2;
+  const int64_t total2 = n * c * oh * (ow / 2);
+  pool2x2_idx_lrelu_bwd_kernel<<<grid_for(d, total2), kThreads, 0, d->stream>>>(
+      (float*)(uintptr_t)dZ, (float2*)(uintptr_t)T, (const uchar2*)(uintptr_t)IDX, (const float2*)(uintptr_t)dP,
+      (const float2*)(uintptr_t)P, total2, ih, iw, oh, ow / 2, alpha, act);
+  LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
+}
 
 int lnn_pool2x2_lrelu_bwd(int dev, uint64_t dZ, uint64_t Y, uint64_t P, uint64_t dP, int64_t n, int64_t c,
                           int ih, int iw, float alpha, int act) {

@@ -39,7 +39,8 @@ __device__ __forceinline__ void pooled_store(const TcParams& p, const Pow2Scale&
   // winner goes through them: a quarter of the arithmetic, the same value.  (An accumulator that
   // overflowed to +inf wins here and may become the NaN -> 0 of the pooling kernel where the
   // literal order would have skipped it.)  alpha < 0 takes the literal order.
-  if (!(p.act && p.alpha < 0.0f)) {
+  uint8_t widx[16];
+  if (!(p.act && p.alpha < 0.0f) && p.idx_out == nullptr) {
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
       float t = fmaxf(fmaxf(__uint_as_float(v0[2 * j]), __uint_as_float(v0[2 * j + 1])),
@@ -64,6 +65,9 @@ __device__ __forceinline__ void pooled_store(const TcParams& p, const Pow2Scale&
       t10 = apply_act(t10, p.act, p.alpha); t11 = apply_act(t11, p.act, p.alpha);
       const float mm = fmaxf(fmaxf(fmaxf(fmaxf(-CUDART_INF_F, t00), t01), t10), t11);
       m[j] = (mm == -CUDART_INF_F) ? 0.0f : mm;
+      // where the pooling gradient goes: the first position equal to the stored value
+      // (pool2D.py:147-230); none when the window held nothing comparable
+      widx[j] = t00 == m[j] ? 0 : t01 == m[j] ? 1 : t10 == m[j] ? 2 : t11 == m[j] ? 3 : 4;
     }
   }
   const int npool = min(wvalid, p.AW - b0) >> 1;          // pooled pixels of this chunk that exist
@@ -79,6 +83,21 @@ __device__ __forceinline__ void pooled_store(const TcParams& p, const Pow2Scale&
 #pragma unroll
       for (int j = 0; j < 16; ++j)
         if (j < npool) dst[j] = m[j];
+    }
+    if (p.idx_out) {
+      uint8_t* di = p.idx_out + base;
+      if (npool == 16 && ((((uintptr_t)di) & 15) == 0)) {
+        uint32_t w4[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          w4[q] = (uint32_t)widx[4 * q] | ((uint32_t)widx[4 * q + 1] << 8) | ((uint32_t)widx[4 * q + 2] << 16) |
+                  ((uint32_t)widx[4 * q + 3] << 24);
+        *reinterpret_cast<uint4*>(di) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (j < npool) di[j] = widx[j];
+      }
     }
   } else if (p.ep_mode == 2) {
 #pragma unroll
@@ -975,6 +994,31 @@ conv_bound_kernel(uint32_t* __restrict__ out, const float* __restrict__ W, int o
   }
 }
 
+// Window position (0..3 in row-major order, 4 = none) of the first element equal to the pooled
+// value, for max_pool2D(2, 2, 'same') of Y [planes][ih][iw] into P [planes][oh][ow]: where the
+// pooling gradient goes (pool2D.py:147-230).  Used when the pool did not run in an epilogue.
+__global__ void __launch_bounds__(kThreads)
+pool2x2_argmax_kernel(uint8_t* __restrict__ idx, const float* __restrict__ Y, const float* __restrict__ P,
+                      int64_t total, int ih, int iw, int oh, int ow) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t gid = tid; gid < total; gid += nthreads) {
+    const int x = (int)(gid % ow);
+    const int64_t t = gid / ow;
+    const int y = (int)(t % oh);
+    const int64_t plane = t / oh;
+    const float o = P[gid];
+    const float* src = Y + (plane * ih + 2 * y) * (int64_t)iw + 2 * x;
+    const bool right = 2 * x + 1 < iw, below = 2 * y + 1 < ih;
+    int w = 4;
+    if (src[0] == o) w = 0;
+    else if (right && src[1] == o) w = 1;
+    else if (below && src[iw] == o) w = 2;
+    else if (right && below && src[iw + 1] == o) w = 3;
+    idx[gid] = (uint8_t)w;
+  }
+}
+
 // What a split pass needs per thread: the tf32 split needs nothing, the fp16 split the two
 // factors of 2^-e with e the scale exponent of the tensor.
 template <bool F16> struct Splitter;
@@ -1609,7 +1653,7 @@ int check_geom(const lnn_conv_geom* g) {
 // must fit shared memory; among the tilings that do, take the one with most real pixels per
 // MMA clock under the measured cost of one tcgen05.mma in this kernel, about max(150, 0.7 * N) clocks.
 // Optional fused pooling / packed output of the channels-on-M kernels (TcParams::ep_mode).
-struct EpiExtra { int ep_mode; float* out_lo; int ocp; uint32_t* amax_out; };
+struct EpiExtra { int ep_mode; float* out_lo; int ocp; uint32_t* amax_out; uint8_t* idx_out = nullptr; };
 
 struct HaloPlan { bool ok; int tw, th, pw, ph, bn, sa, bbuf, acb; double px_per_clk; };
 
@@ -1726,7 +1770,9 @@ int launch_conv_halo(lnn::Device* d, const Operand& act, const Operand& w, const
   p.ncb = c.kp / cb; p.cb = cb;
   p.tw = hp.tw; p.th = hp.th; p.tn = 1;
   p.tiles_b = (c.AW + hp.tw - 1) / hp.tw; p.tiles_a = (c.AH + hp.th - 1) / hp.th; p.tiles_n = c.NL;
-  if (pooled) { p.ep_mode = ex->ep_mode; p.out_lo = ex->out_lo; p.ocp = ex->ocp; p.amax_out = ex->amax_out; }
+  if (pooled) {
+    p.ep_mode = ex->ep_mode; p.out_lo = ex->out_lo; p.ocp = ex->ocp; p.amax_out = ex->amax_out; p.idx_out = ex->idx_out;
+  }
   p.h_pw = hp.pw; p.h_ph = hp.ph; p.h_x0 = x0; p.h_y0 = y0; p.h_arows = a_rows; p.h_acb = hp.acb;
   p.h_sa = hp.sa; p.h_sb = 2; p.h_bbuf = hp.bbuf;
   p.debug = knobs().debug;
@@ -1824,6 +1870,7 @@ int launch_conv_like(lnn::Device* d, const Operand& act, const Operand& w, const
   p.rows_valid = pix;
   if (pooled) {
     p.ep_mode = ex->ep_mode; p.out_lo = ex->out_lo; p.ocp = ex->ocp; p.amax_out = ex->amax_out;
+    p.idx_out = ex->idx_out;
     if (fused) *fused = 1;
   }
   CUtensorMap act_h, act_l, w_h, w_l;
@@ -1976,6 +2023,15 @@ int conv_fwd_impl(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint6
   const int ocp = chan_pad(g->oc);
   const uint64_t out_elems = (uint64_t)g->n * oh_p * ow_p * ocp;   // of a packed result
   float* const y_lo = want_lo ? (float*)(uintptr_t)o.y_lo : nullptr;
+  // a pooled NCHW result may come with the map of winning window positions (one byte per element)
+  uint8_t* const idx = (o.pool && !o.out_packed) ? (uint8_t*)(uintptr_t)o.y_lo : nullptr;
+  auto argmax_of = [&](const float* full) -> int {
+    const int64_t total = (int64_t)g->n * g->oc * oh_p * ow_p;
+    pool2x2_argmax_kernel<<<grid_for(d, total), kThreads, 0, d->stream>>>(idx, full, (const float*)(uintptr_t)Y, total,
+                                                                        g->oh, g->ow, oh_p, ow_p);
+    LNN_CHECK_LAUNCH(d);
+    return LNN_OK;
+  };
 
   // fp16 packed output written by the epilogue itself: its scale comes from an upper bound of the
   // result (conv_bound_kernel) placed in word 0 of the output's trailer before the launch; the
@@ -2010,7 +2066,7 @@ int conv_fwd_impl(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint6
       return lnn::conv_fewch_fwd(d, g, (float*)(uintptr_t)Y, xp, wp, biasp, act, alpha, 4, ocp, xmax.as<uint32_t>(),
                                  amax_true, y_lo);
     }
-    if (can_pool || (!o.pool && !o.out_packed))
+    if ((can_pool && !idx) || (!o.pool && !o.out_packed))
       return lnn::conv_fewch_fwd(d, g, (float*)(uintptr_t)Y, xp, wp, biasp, act, alpha, can_pool ? 1 : 0, ocp,
                                  xmax.as<uint32_t>(), nullptr);
     // what the epilogue cannot fuse (odd sizes, packed output without pooling) runs as separate kernels
@@ -2029,6 +2085,7 @@ int conv_fwd_impl(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint6
       rc = lnn_pool2d_fwd(dev, LNN_POOL_MAX, (uint64_t)(uintptr_t)pdst, (uint64_t)(uintptr_t)cur, g->n, g->oc, g->oh,
                           g->ow, oh_p, ow_p, 2, 2, 0, 0);
       if (rc) return rc;
+      if (idx) { rc = argmax_of(cur); if (rc) return rc; }
       cur = pdst;
     }
     if (o.out_packed)
@@ -2036,7 +2093,8 @@ int conv_fwd_impl(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint6
                            g->oc, oh_p, ow_p, ocp, precision);
     return LNN_OK;
   }
-  if (!o.in_packed && !o.w_swapped && lnn::conv_direct_applicable(g) && knobs().direct && (!o.out_packed || o.pool)) {
+  if (!o.in_packed && !o.w_swapped && !idx && lnn::conv_direct_applicable(g) && knobs().direct &&
+      (!o.out_packed || o.pool)) {
     if (o.out_packed && f16) {
       // this kernel writes fp32 and the largest magnitude; one element-wise pass splits it
       lnn::Scratch raw(d);
@@ -2104,6 +2162,7 @@ int conv_fwd_impl(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint6
     } else {
       cf.out = (float*)(uintptr_t)Y;
       cf.out_sn = (int64_t)g->oc * pplane; cf.out_sa = ow_p; cf.out_sb = 1; cf.out_sc = pplane;
+      ex.idx_out = idx;
     }
     int fused = 0;
     rc = launch_conv_like(d, ox, ow, cf, &ex, &fused);
@@ -2133,6 +2192,7 @@ int conv_fwd_impl(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint6
     rc = lnn_pool2d_fwd(dev, LNN_POOL_MAX, (uint64_t)(uintptr_t)pdst, (uint64_t)(uintptr_t)cur, g->n, g->oc,
                         g->oh, g->ow, oh_p, ow_p, 2, 2, 0, 0);
     if (rc) return rc;
+    if (idx) { rc = argmax_of(cur); if (rc) return rc; }
     cur = pdst;
   }
   if (o.out_packed)

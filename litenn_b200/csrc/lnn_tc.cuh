@@ -99,6 +99,7 @@ struct TcParams {
   // largest magnitude in *amax_out; the out_s* strides then address pooled pixels
   int ep_mode;
   float* out_lo;
+  uint8_t* idx_out;   // ep_mode 1 only, optional: window position (0..3 row-major, 4 = none) of each pooled value
   int ocp;
   int tap_dy[kMaxTaps], tap_dx[kMaxTaps], tap_w[kMaxTaps];
   // halo-resident pixel patch (tc_halo_kernel): the patch of one channel block, with its halo,

@@ -612,29 +612,31 @@ def conv2D(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t=None,
     passes = _lib.precision()
     output_t = _out(out_shape)
     output_t._set_op_name("conv2D")
-    conv_out_t = output_t
+    idx_t = None
     if _pooled:
-        # conv2D_block: the tensor handed to the caller (and carrying the grad functions) is the
-        # max-pooled one; the full-resolution activation is kept for the backward pass only
+        # conv2D_block: the pool runs in the convolution's epilogue and the full-resolution
+        # activation is never written; the backward pass gets the map of winning window positions
+        # instead (one byte per pooled element, kept in a flat tensor used as raw storage)
         output_t = _out((g.n, g.oc, g.oh // 2, g.ow // 2))
         output_t._set_op_name("conv2D_block")
+        idx_t = _out(((output_t.shape.size + 3) // 4,))
+    full_shape = out_shape
 
     # The grad functions below are stored inside output_t, so they must not capture output_t itself
     # (a reference cycle would keep the whole chain of activations alive until the cycle collector
-    # runs): they receive it as O_t.  Only the pooled variant needs a second tensor, the
-    # full-resolution activation, which does not refer back to the pooled one.
-    full_res_t = conv_out_t if _pooled else None
+    # runs): they receive it as O_t.
 
     def pre_act_grad(O_t, dO_t):
         # gradient w.r.t. the convolution output (before the fused activation)
         if _pooled:
             cached = getattr(O_t, "_pre_act_grad", None)
             if cached is None or cached[0] is not dO_t:
-                d = _out(full_res_t.shape)              # every element is written
+                d = _out(full_shape)                    # every element is written
+                t = _out(O_t.shape)                     # the winners' gradients: what the bias gradient sums
                 for i, dev in _each_device():
-                    _lib_().lnn_pool2x2_lrelu_bwd(dev, d._ptr(i), full_res_t._ptr(i), O_t._ptr(i), dO_t._ptr(i),
-                                                  g.n, g.oc, g.oh, g.ow, float(alpha), act)
-                cached = (dO_t, d)
+                    _lib_().lnn_pool2x2_idx_lrelu_bwd(dev, d._ptr(i), t._ptr(i), idx_t._ptr(i), O_t._ptr(i),
+                                                      dO_t._ptr(i), g.n, g.oc, g.oh, g.ow, float(alpha), act)
+                cached = (dO_t, d, t)
                 O_t._pre_act_grad = cached
             return cached[1]
         if not act:
@@ -690,30 +692,38 @@ def conv2D(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t=None,
 
     def grad_b(O_t, dO_t):
         d = pre_act_grad(O_t, dO_t)
+        if _pooled:
+            # every other element of d is zero: sum the winners (pooled size) instead
+            d = O_t._pre_act_grad[2]
         reduce_sum_op(d, (0, 2, 3), output_t=bias_t.get_grad(), is_add_to_output=True)
 
     output_t._assign_gradfn(input_t, grad_x)
     output_t._assign_gradfn(kernel_t, grad_w)
     if bias_t is not None:
         output_t._assign_gradfn(bias_t, grad_b)
+    bias_ptr = (lambda i: bias_t._ptr(i)) if bias_t is not None else (lambda i: 0)
     for i, dev in _each_device():
-        if keep_packed:
-            _lib_().lnn_conv2d_fwd_packed(dev, ctypes.byref(g), conv_out_t._ptr(i), 0, packed_x.hi._ptr(i), _lo(packed_x, i),
-                                          kernel_t._ptr(i), bias_t._ptr(i) if bias_t is not None else 0, act,
-                                          float(alpha), 0, 1, 0, passes)
-        else:
-            _lib_().lnn_conv2d_fwd(dev, ctypes.byref(g), conv_out_t._ptr(i), input_t._ptr(i), kernel_t._ptr(i),
-                                   bias_t._ptr(i) if bias_t is not None else 0, act, float(alpha), 0, passes)
         if _pooled:
-            _lib_().lnn_pool2d_fwd(dev, _lib.POOL["max"], output_t._ptr(i), conv_out_t._ptr(i), g.n, g.oc, g.oh, g.ow,
-                                   g.oh // 2, g.ow // 2, 2, 2, 0, 0)
+            x, x_lo = (packed_x.hi._ptr(i), _lo(packed_x, i)) if keep_packed else (input_t._ptr(i), 0)
+            _lib_().lnn_conv2d_fwd_packed(dev, ctypes.byref(g), output_t._ptr(i), idx_t._ptr(i), x, x_lo,
+                                          kernel_t._ptr(i), bias_ptr(i), act, float(alpha), 1,
+                                          1 if keep_packed else 0, 0, passes)
+        elif keep_packed:
+            _lib_().lnn_conv2d_fwd_packed(dev, ctypes.byref(g), output_t._ptr(i), 0, packed_x.hi._ptr(i), _lo(packed_x, i),
+                                          kernel_t._ptr(i), bias_ptr(i), act, float(alpha), 0, 1, 0, passes)
+        else:
+            _lib_().lnn_conv2d_fwd(dev, ctypes.byref(g), output_t._ptr(i), input_t._ptr(i), kernel_t._ptr(i),
+                                   bias_ptr(i), act, float(alpha), 0, passes)
     return output_t
 
 
 def conv2D_block(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t=None, activation=None, alpha=0.1):
     """max_pool2D(activation(conv2D(x, k) + bias), 2, 2, 'same') as ONE trainable op: same values
-    and gradients as the chain nn.conv2D -> nn.leaky_relu -> nn.max_pool2D, but the backward pass
-    computes the gradient of the convolution output from the pooled gradient in a single kernel
+    and gradients as the chain nn.conv2D -> nn.leaky_relu -> nn.max_pool2D (the bias gradient sums
+    the same non-zero terms in another order).  The pool runs in the convolution's epilogue,
+    which also records the winning position of every window, so the full-resolution activation is
+    never written; the backward pass computes the gradient of the convolution output from the
+    pooled gradient and that map in a single kernel
     instead of two zero fills and two read-modify-write passes over full-resolution tensors
     (pool2D.py:147-230, element_wise_op.py:207-221).  Shapes the fused gradient kernel does not
     cover (odd height, width not a multiple of 4) run as the chain."""
