@@ -72,7 +72,7 @@ int conv_direct_fwd(Device* d, const lnn_conv_geom* g, float* Y, const float* X,
 bool conv_fewch_applicable(const lnn_conv_geom* g);
 int conv_fewch_fwd(Device* d, const lnn_conv_geom* g, float* Y, const float* X, const float* W,
                    const float* bias, int act, float alpha, int ep_mode, int ocp, const uint32_t* amax_x,
-                   uint32_t* amax_out, float* Y_lo = nullptr);
+                   uint32_t* amax_out, float* Y_lo = nullptr, uint8_t* idx = nullptr);
 // kernel gradient of the same layers (IC <= 4, 3x3): dW += ...
 bool conv_direct_dw_applicable(const lnn_conv_geom* g);
 int conv_direct_dw(Device* d, const lnn_conv_geom* g, float* dW, const float* dY, const float* X);

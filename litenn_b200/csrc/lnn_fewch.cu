@@ -60,6 +60,7 @@ struct FcParams {
   int ep_mode;                            // 0 NCHW, 1 pooled NCHW, 3 pooled channel-innermost fp32 + largest magnitude,
                                           // 4 pooled channel-innermost split fp16 (scale from the bound in amax_out[-1])
   float* out_lo;
+  uint8_t* idx_out;                       // ep_mode 1, optional: winning window position of every pooled value
   int ocp;                                // channel pitch of the ep_mode 3 output
   const uint32_t* amax_x; uint32_t* amax_out;
   int* status;
@@ -119,7 +120,9 @@ __device__ __forceinline__ void store_slot(uint8_t* dst_hi, uint8_t* dst_lo, con
   *reinterpret_cast<uint4*>(dst_lo) = *reinterpret_cast<const uint4*>(l);
 }
 
-template <int IC>
+// WANT_IDX: the instance that also writes the map of winning pool positions (training); kept apart
+// so that its extra registers do not touch the inference instances.
+template <int IC, bool WANT_IDX>
 __global__ void __launch_bounds__(kFcThreads, 1)
 fewch_conv_kernel(const __grid_constant__ FcParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -382,7 +385,9 @@ fewch_conv_kernel(const __grid_constant__ FcParams p) {
             // (op/pool2D.py:111-146), at a quarter of the arithmetic.  (An accumulator that
             // overflowed to infinity would win here and turn into the reference's NaN -> 0, where
             // the reference would have skipped it; alpha < 0 takes the literal order below.)
-            const bool pool_first = !(p.act && p.alpha < 0.0f);
+            // (the map of winning positions compares finished values: literal order as well)
+            constexpr bool want_idx = WANT_IDX;
+            const bool pool_first = !(p.act && p.alpha < 0.0f) && !want_idx;
             float y[32];
 #pragma unroll
             for (int k = 0; k < 32; ++k) y[k] = __uint_as_float(v[k]);
@@ -393,6 +398,11 @@ fewch_conv_kernel(const __grid_constant__ FcParams p) {
                 if (p.bias) t = __fadd_rn(t, bias_s[c0 + k]);
                 y[k] = p.act ? lrelu_as_reference(t, p.alpha) : t;
               }
+            }
+            float yo[32];
+            if (want_idx) {
+#pragma unroll
+              for (int k = 0; k < 32; ++k) yo[k] = y[k];
             }
             {
               float o[32];
@@ -408,6 +418,24 @@ fewch_conv_kernel(const __grid_constant__ FcParams p) {
 #ifdef LNN_TC_EXPERIMENTS
             dbg_ph1 += clock64() - tp0;
 #endif
+            // Where the pooling gradient of each window goes: the first position, in row-major
+            // order, whose value equals the stored one (op/pool2D.py:147-230); 4 = none.  Every lane
+            // marks the channels in which it holds that value, the four lanes exchange the marks.
+            uint32_t eq0 = 0u, eq1 = 0u, eq2 = 0u, eq3 = 0u;
+            if (want_idx) {
+              uint32_t eq = 0u;
+#pragma unroll
+              for (int k = 0; k < 32; ++k) {
+                const float m = fmaxf(-CUDART_INF_F, y[k]);
+                const float st = (m == -CUDART_INF_F) ? 0.0f : m;
+                eq |= (yo[k] == st ? 1u : 0u) << k;
+              }
+              const int wbase = lane & ~9;
+              eq0 = __shfl_sync(0xffffffffu, eq, wbase);
+              eq1 = __shfl_sync(0xffffffffu, eq, wbase | 1);
+              eq2 = __shfl_sync(0xffffffffu, eq, wbase | 8);
+              eq3 = __shfl_sync(0xffffffffu, eq, wbase | 9);
+            }
             // each lane of the window finishes and stores a quarter of the 32 channels
             float q[8];
             const int cb = c0 + 8 * sub4;
@@ -441,6 +469,15 @@ fewch_conv_kernel(const __grid_constant__ FcParams p) {
 #pragma unroll
                 for (int k = 0; k < 8; ++k)
                   if (cb + k < p.oc) dst[k * cstride] = q[k];
+                if (want_idx) {
+                  uint8_t* di = p.idx_out + (((int64_t)img * p.oc + cb) * ohp + ph_) * owp + pw_;
+#pragma unroll
+                  for (int k = 0; k < 8; ++k) {
+                    const int c = 8 * sub4 + k;
+                    const int w = ((eq0 >> c) & 1u) ? 0 : ((eq1 >> c) & 1u) ? 1 : ((eq2 >> c) & 1u) ? 2 : ((eq3 >> c) & 1u) ? 3 : 4;
+                    if (cb + k < p.oc) di[k * cstride] = (uint8_t)w;
+                  }
+                }
               } else if (ep_mode == 4 && cb < p.ocp) {
                 // the next convolution's operand, written here: eight channels = 16 bytes of hi and of lo
                 const int64_t off = (((int64_t)img * ohp + ph_) * owp + pw_) * p.ocp + cb;
@@ -506,13 +543,14 @@ bool conv_fewch_applicable(const lnn_conv_geom* g) {
 // ep_mode 0: Y = NCHW result; 1: pooled NCHW; 3: pooled channel-innermost fp32 with channel pitch
 // ocp, its largest magnitude accumulated into *amax_out (which the caller zeroed); 4: pooled
 // channel-innermost split fp16 (Y = hi, Y_lo = lo) scaled by the bound in amax_out[-1].  amax_x
-// holds the fp32 bit pattern of the input's largest magnitude.
+// holds the fp32 bit pattern of the input's largest magnitude.  idx (ep_mode 1, optional): one byte
+// per pooled element, the window position that holds the pooled value.
 int conv_fewch_fwd(Device* d, const lnn_conv_geom* g, float* Y, const float* X, const float* W,
                    const float* bias, int act, float alpha, int ep_mode, int ocp, const uint32_t* amax_x,
-                   uint32_t* amax_out, float* Y_lo) {
+                   uint32_t* amax_out, float* Y_lo, uint8_t* idx) {
   FcParams p;
   memset(&p, 0, sizeof(p));
-  p.X = X; p.W = W; p.bias = bias; p.out = Y; p.out_lo = Y_lo;
+  p.X = X; p.W = W; p.bias = bias; p.out = Y; p.out_lo = Y_lo; p.idx_out = ep_mode == 1 ? idx : nullptr;
   p.n = g->n; p.ic = g->ic; p.ih = g->ih; p.iw = g->iw; p.oc = g->oc; p.oh = g->oh; p.ow = g->ow;
   p.padl = g->padl; p.padt = g->padt;
   p.ocn = (g->oc + 31) & ~31;
@@ -535,20 +573,34 @@ int conv_fewch_fwd(Device* d, const lnn_conv_geom* g, float* Y, const float* X, 
   const int smem = 2 * p.w_bytes + 4 * p.patch_bytes + 1024;
   LNN_REQUIRE(smem <= 227 * 1024 - 4096, "operands of %d bytes do not fit shared memory", smem);
   if (!(d->smem_attr_done & (1u << 9))) {
-    LNN_CUDA(cudaFuncSetAttribute(fewch_conv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 4096));
-    LNN_CUDA(cudaFuncSetAttribute(fewch_conv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 4096));
-    LNN_CUDA(cudaFuncSetAttribute(fewch_conv_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 4096));
-    LNN_CUDA(cudaFuncSetAttribute(fewch_conv_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 4096));
+    const int lim = 227 * 1024 - 4096;
+    LNN_CUDA(cudaFuncSetAttribute(fewch_conv_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+    LNN_CUDA(cudaFuncSetAttribute(fewch_conv_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+    LNN_CUDA(cudaFuncSetAttribute(fewch_conv_kernel<3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+    LNN_CUDA(cudaFuncSetAttribute(fewch_conv_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+    LNN_CUDA(cudaFuncSetAttribute(fewch_conv_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+    LNN_CUDA(cudaFuncSetAttribute(fewch_conv_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+    LNN_CUDA(cudaFuncSetAttribute(fewch_conv_kernel<3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+    LNN_CUDA(cudaFuncSetAttribute(fewch_conv_kernel<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
     d->smem_attr_done |= 1u << 9;
   }
   const unsigned ctas = (unsigned)std::min<int64_t>(tiles, d->sm_count);
   {
     ProfScope prof(d, (int)LNN_PROF_FEWCH);
-    switch (g->ic) {
-      case 1: fewch_conv_kernel<1><<<ctas, kFcThreads, smem, d->stream>>>(p); break;
-      case 2: fewch_conv_kernel<2><<<ctas, kFcThreads, smem, d->stream>>>(p); break;
-      case 3: fewch_conv_kernel<3><<<ctas, kFcThreads, smem, d->stream>>>(p); break;
-      default: fewch_conv_kernel<4><<<ctas, kFcThreads, smem, d->stream>>>(p); break;
+    if (p.idx_out) {
+      switch (g->ic) {
+        case 1: fewch_conv_kernel<1, true><<<ctas, kFcThreads, smem, d->stream>>>(p); break;
+        case 2: fewch_conv_kernel<2, true><<<ctas, kFcThreads, smem, d->stream>>>(p); break;
+        case 3: fewch_conv_kernel<3, true><<<ctas, kFcThreads, smem, d->stream>>>(p); break;
+        default: fewch_conv_kernel<4, true><<<ctas, kFcThreads, smem, d->stream>>>(p); break;
+      }
+    } else {
+      switch (g->ic) {
+        case 1: fewch_conv_kernel<1, false><<<ctas, kFcThreads, smem, d->stream>>>(p); break;
+        case 2: fewch_conv_kernel<2, false><<<ctas, kFcThreads, smem, d->stream>>>(p); break;
+        case 3: fewch_conv_kernel<3, false><<<ctas, kFcThreads, smem, d->stream>>>(p); break;
+        default: fewch_conv_kernel<4, false><<<ctas, kFcThreads, smem, d->stream>>>(p); break;
+      }
     }
   }
   LNN_CHECK_LAUNCH(d);

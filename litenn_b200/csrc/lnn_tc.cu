@@ -2066,9 +2066,9 @@ int conv_fwd_impl(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint6
       return lnn::conv_fewch_fwd(d, g, (float*)(uintptr_t)Y, xp, wp, biasp, act, alpha, 4, ocp, xmax.as<uint32_t>(),
                                  amax_true, y_lo);
     }
-    if ((can_pool && !idx) || (!o.pool && !o.out_packed))
+    if (can_pool || (!o.pool && !o.out_packed))
       return lnn::conv_fewch_fwd(d, g, (float*)(uintptr_t)Y, xp, wp, biasp, act, alpha, can_pool ? 1 : 0, ocp,
-                                 xmax.as<uint32_t>(), nullptr);
+                                 xmax.as<uint32_t>(), nullptr, nullptr, idx);
     // what the epilogue cannot fuse (odd sizes, packed output without pooling) runs as separate kernels
     rc = full.get((uint64_t)g->n * g->oc * g->oh * g->ow * 4);
     if (rc) return rc;
