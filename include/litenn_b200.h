@@ -185,6 +185,15 @@ int lnn_pool2x2_lrelu_bwd(int dev, uint64_t dZ, uint64_t Y, uint64_t P, uint64_t
  * ref: op/pool2D.py:147-230 + op/element_wise_op.py:207-221 */
 int lnn_pool2x2_idx_lrelu_bwd(int dev, uint64_t dZ, uint64_t T, uint64_t IDX, uint64_t P, uint64_t dP,
                               int64_t n, int64_t c, int ih, int iw, float alpha, int act);
+/* The same gradient written straight into the packed split-FP16 operand format (HI / LO as sized
+ * by lnn_packed_bytes(n, c, ih, iw, 2)) that lnn_conv2d_dx_packed / _dw_packed read: no
+ * full-resolution fp32 gradient, no largest-magnitude pass and no split pass over it.  T (pooled
+ * size, required) receives the winners' gradients.  The copies equal lnn_nhwc_split of the dZ that
+ * lnn_pool2x2_idx_lrelu_bwd writes, bit for bit.  Precision 2 only.
+ * ref: op/pool2D.py:147-230 + op/element_wise_op.py:207-221 */
+int lnn_pool2x2_idx_lrelu_bwd_packed(int dev, uint64_t HI, uint64_t LO, uint64_t T, uint64_t IDX,
+                                     uint64_t P, uint64_t dP, int64_t n, int64_t c, int ih, int iw,
+                                     float alpha, int act);
 /* dI += ... ; ref: op/pool2D.py:147-230 (I and O are only read for max/min) */
 int lnn_pool2d_bwd(int dev, int mode, uint64_t dI, uint64_t I, uint64_t dO, uint64_t O,
                    int64_t n, int64_t c, int ih, int iw, int oh, int ow,

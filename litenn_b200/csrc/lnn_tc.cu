@@ -1151,6 +1151,88 @@ half_split_kernel(__half* __restrict__ hi, __half* __restrict__ lo, const float*
   }
 }
 
+// Gradient of max_pool2D(2, 2) + leaky_relu written straight into the packed fp16 operand format.
+// Pass 1 (pooled size): T = the gradient that reaches the winner of each window,
+// 0 + (0 + dP) then 0 + that * leaky_relu'(P) -- the roundings of the un-fused kernels
+// (pool2D.py:147-230, element_wise_op.py:207-221) -- or 0 where no position matched, and its
+// largest magnitude, which is the largest magnitude of the whole full-resolution gradient.
+__global__ void __launch_bounds__(kThreads)
+pool_winner_grad_kernel(float* __restrict__ T, uint32_t* __restrict__ amax, const uint8_t* __restrict__ IDX,
+                        const float* __restrict__ dP, const float* __restrict__ P, int64_t total, float alpha,
+                        int act) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  uint32_t best = 0u;
+  for (int64_t i = tid; i < total; i += nthreads) {
+    float u = __fadd_rn(0.0f, __fadd_rn(0.0f, dP[i]));
+    if (act) {
+      const float o = P[i];
+      const float f = __fadd_rn(o >= 0.0f ? 1.0f : 0.0f, __fmul_rn(alpha, o < 0.0f ? 1.0f : 0.0f));
+      u = __fadd_rn(0.0f, __fmul_rn(u, f));
+    }
+    if (IDX[i] > 3) u = 0.0f;
+    T[i] = u;
+    best = max(best, __float_as_uint(u) & 0x7fffffffu);
+  }
+  warp_amax_commit(best, amax);
+}
+
+// Pass 2: one thread = two adjacent windows x eight channels; consecutive threads take consecutive
+// channel groups of the same pixels, so the 16-byte stores of a warp are contiguous.  hi / lo are
+// [n][2*oh][2*ow][cp]; T and IDX are NCHW planes of [oh][ow].  Every element is written (zeros
+// outside the winners and in the pad channels).
+__global__ void __launch_bounds__(kThreads)
+unpool_packed_kernel(__half* __restrict__ hi, __half* __restrict__ lo, const float* __restrict__ T,
+                     const uint8_t* __restrict__ IDX, const uint32_t* __restrict__ amax, int64_t n, int c, int cp,
+                     int oh, int ow) {
+  const Splitter<true> split(amax);
+  const int cgs = cp >> 3, ow2 = ow >> 1;
+  const int64_t total = n * oh * (int64_t)ow2 * cgs;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  const int64_t plane = (int64_t)oh * ow;
+  for (int64_t gid = tid; gid < total; gid += nthreads) {
+    const int cg = (int)(gid % cgs);
+    int64_t r = gid / cgs;
+    const int x2 = (int)(r % ow2); r /= ow2;
+    const int y = (int)(r % oh);
+    const int64_t img = r / oh;
+    __align__(16) __half h[2][4][8];      // [row of the window][column 0..3 of the two windows][channel]
+    __align__(16) __half l[2][4][8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int ch = cg * 8 + k;
+      float2 t = make_float2(0.0f, 0.0f);
+      uchar2 w = make_uchar2(4, 4);
+      if (ch < c) {
+        const int64_t off = (img * c + ch) * plane + (int64_t)y * ow + 2 * x2;
+        t = *reinterpret_cast<const float2*>(T + off);
+        w = *reinterpret_cast<const uchar2*>(IDX + off);
+      }
+      __half th0, tl0, th1, tl1;
+      split(t.x, th0, tl0);
+      split(t.y, th1, tl1);
+      const __half z = Splitter<true>::zero();
+#pragma unroll
+      for (int pos = 0; pos < 4; ++pos) {
+        const bool a = w.x == pos, b = w.y == pos;
+        h[pos >> 1][pos & 1][k] = a ? th0 : z;       l[pos >> 1][pos & 1][k] = a ? tl0 : z;
+        h[pos >> 1][2 + (pos & 1)][k] = b ? th1 : z; l[pos >> 1][2 + (pos & 1)][k] = b ? tl1 : z;
+      }
+    }
+    const int64_t iw = 2 * (int64_t)ow;
+#pragma unroll
+    for (int row = 0; row < 2; ++row) {
+#pragma unroll
+      for (int col = 0; col < 4; ++col) {
+        const int64_t px = (img * 2 * oh + 2 * y + row) * iw + 4 * x2 + col;
+        store_vec<__half, 8>(hi + px * cp + cg * 8, h[row][col], true);
+        store_vec<__half, 8>(lo + px * cp + cg * 8, l[row][col], true);
+      }
+    }
+  }
+}
+
 // NCHW -> NHWC with channel padding to cp, split into hi/lo.  One block transposes a
 // [32 channels] x [32 pixels] tile of one image through shared memory.
 template <bool F16>
@@ -2237,6 +2319,31 @@ int lnn_nhwc_split(int dev, uint64_t hi, uint64_t lo, uint64_t X, int n, int c, 
   return nhwc_split_to(d, hp, tf32_passes == 1 ? nullptr : (void*)(uintptr_t)lo,
                        tf32_passes == 2 ? trailer_of(hp, (uint64_t)n * h * w * cp) : nullptr,
                        (const float*)(uintptr_t)X, n, c, h, w, cp, tf32_passes);
+}
+
+int lnn_pool2x2_idx_lrelu_bwd_packed(int dev, uint64_t HI, uint64_t LO, uint64_t T, uint64_t IDX, uint64_t P,
+                                     uint64_t dP, int64_t n, int64_t c, int ih, int iw, float alpha, int act) {
+  LNN_DEV(d, dev);
+  LNN_REQUIRE(HI && LO && T && IDX && P && dP, "null buffer");
+  LNN_REQUIRE(n > 0 && c > 0 && ih > 0 && iw > 0, "bad extents");
+  LNN_REQUIRE(act == 0 || act == 1, "unknown activation %d", act);
+  if ((ih & 1) || (iw & 3) || ((HI | LO) & 15) || (T & 7) || (IDX & 1))
+    return lnn::set_error(LNN_E_UNSUPPORTED,
+                          "fused pooling gradient needs an even height, a width that is a multiple of 4 and aligned buffers");
+  const int oh = ih / 2, ow = iw / 2, cp = chan_pad((int)c);
+  const int64_t pooled = n * c * oh * ow;
+  uint32_t* amax = trailer_of((void*)(uintptr_t)HI, (uint64_t)n * ih * iw * cp);
+  lnn::ProfScope prof(d, LNN_PROF_PREP);
+  LNN_CUDA(cudaMemsetAsync(amax, 0, 2 * sizeof(uint32_t), d->stream));
+  pool_winner_grad_kernel<<<grid_for(d, pooled), kThreads, 0, d->stream>>>(
+      (float*)(uintptr_t)T, amax, (const uint8_t*)(uintptr_t)IDX, (const float*)(uintptr_t)dP,
+      (const float*)(uintptr_t)P, pooled, alpha, act);
+  LNN_CHECK_LAUNCH(d);
+  unpool_packed_kernel<<<grid_for(d, n * oh * (ow / 2) * (cp / 8)), kThreads, 0, d->stream>>>(
+      (__half*)(uintptr_t)HI, (__half*)(uintptr_t)LO, (const float*)(uintptr_t)T, (const uint8_t*)(uintptr_t)IDX, amax,
+      n, (int)c, cp, oh, ow);
+  LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
 }
 
 }  // extern "C"

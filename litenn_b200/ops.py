@@ -656,7 +656,22 @@ def conv2D(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t=None,
     keep_packed = g.ic > 4
     packed_x = pack_activation(input_t) if keep_packed else None
 
+    # a pooled block whose gradients all read the packed format never needs dZ as an NCHW tensor
+    direct_packed = _pooled and keep_packed and passes == 2
+
     def packed_dy(O_t, dO_t):
+        if direct_packed:
+            cached = getattr(O_t, "_packed_dy", None)
+            if cached is None or cached[0] is not dO_t:
+                pd = _packed_like(g.n, g.oc, g.oh, g.ow)
+                t = _out(O_t.shape)                 # the winners' gradients: what the bias gradient sums
+                for i, dev in _each_device():
+                    _lib_().lnn_pool2x2_idx_lrelu_bwd_packed(dev, pd.hi._ptr(i), pd.lo._ptr(i), t._ptr(i), idx_t._ptr(i),
+                                                             O_t._ptr(i), dO_t._ptr(i), g.n, g.oc, g.oh, g.ow,
+                                                             float(alpha), act)
+                cached = (dO_t, pd, t)
+                O_t._packed_dy = cached
+            return cached[1]
         d = pre_act_grad(O_t, dO_t)
         cached = getattr(O_t, "_packed_dy", None)
         if cached is None or cached[0] is not d:
@@ -691,10 +706,14 @@ def conv2D(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t=None,
             _lib_().lnn_conv2d_dw(dev, ctypes.byref(g), gw._ptr(i), d._ptr(i), input_t._ptr(i), passes)
 
     def grad_b(O_t, dO_t):
-        d = pre_act_grad(O_t, dO_t)
-        if _pooled:
-            # every other element of d is zero: sum the winners (pooled size) instead
-            d = O_t._pre_act_grad[2]
+        if direct_packed:
+            packed_dy(O_t, dO_t)
+            d = O_t._packed_dy[2]
+        else:
+            d = pre_act_grad(O_t, dO_t)
+            if _pooled:
+                # every other element of d is zero: sum the winners (pooled size) instead
+                d = O_t._pre_act_grad[2]
         reduce_sum_op(d, (0, 2, 3), output_t=bias_t.get_grad(), is_add_to_output=True)
 
     output_t._assign_gradfn(input_t, grad_x)
