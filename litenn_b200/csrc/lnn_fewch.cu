@@ -48,6 +48,7 @@ namespace {
 constexpr int kFcThreads = 416;
 constexpr int kFcEpiWarps = 8;
 constexpr int kFcProducers = 128;
+constexpr int kFcEpilogueWarps = 8;         // warps 5..12
 constexpr int kRows = 16;                 // image rows of a tile (row groups of M = 128)
 
 struct FcParams {
@@ -294,6 +295,13 @@ fewch_conv_kernel(const __grid_constant__ FcParams p) {
     const FastPow2 so(p.ep_mode == 4 ? -exp_of_amax(__ldg(p.amax_out - 1)) : 0);
     const int ohp = p.oh >> 1, owp = p.ow >> 1;
     const int sub4 = (lane & 1) | ((lane >> 2) & 2);            // position inside the 2x2 window
+    // Transposing stage of the fused pool: 32 pixels x 32 channels of fp32 per warp, a row = one
+    // pixel = eight 16-byte chunks stored at chunk (j + rot(pixel)) mod 8.  rot makes both access
+    // patterns conflict-free: the writes (a quarter-warp = eight consecutive pixels, one chunk
+    // index) and the reads (a quarter-warp = four pixels two apart, two chunk indices two apart).
+    uint8_t* const xpose = gen_base + 2 * p.w_bytes + 4 * (size_t)p.patch_bytes + (size_t)(warp - 5) * 4096;
+    auto rot = [](int px) { return ((px >> 1) & 1) + 4 * ((px >> 2) & 1) + 2 * (px & 1); };
+    const int wbase_px = lane & ~9;
     const bool sel_b0 = (sub4 & 1) != 0, sel_b1 = (sub4 & 2) != 0;
     uint32_t amax_acc = 0u;
 #ifdef LNN_TC_EXPERIMENTS
@@ -399,12 +407,42 @@ fewch_conv_kernel(const __grid_constant__ FcParams p) {
                 y[k] = p.act ? lrelu_as_reference(t, p.alpha) : t;
               }
             }
+            float q[8];
+            const int cb = c0 + 8 * sub4;
+            if (!want_idx) {
+              // the four pixels of a window come together through shared memory: each lane leaves
+              // with its quarter of the channels for all four, and the maximum is taken in-thread
+              // (the shuffle form below costs 64 shuffles and 24 selects per 32 accumulators)
+              const int my_rot = rot(lane);
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                *reinterpret_cast<float4*>(xpose + lane * 128 + (((j + my_rot) & 7) << 4)) =
+                    make_float4(y[4 * j], y[4 * j + 1], y[4 * j + 2], y[4 * j + 3]);
+              __syncwarp();
+              float4 w4[4][2];
+#pragma unroll
+              for (int pix = 0; pix < 4; ++pix) {
+                const int px = wbase_px | (pix & 1) | ((pix >> 1) << 3);
+                const int r = rot(px);
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+                  w4[pix][i] = *reinterpret_cast<const float4*>(xpose + px * 128 + (((2 * sub4 + i + r) & 7) << 4));
+              }
+              __syncwarp();
+#pragma unroll
+              for (int i = 0; i < 2; ++i) {
+                q[4 * i + 0] = fmaxf(fmaxf(w4[0][i].x, w4[1][i].x), fmaxf(w4[2][i].x, w4[3][i].x));
+                q[4 * i + 1] = fmaxf(fmaxf(w4[0][i].y, w4[1][i].y), fmaxf(w4[2][i].y, w4[3][i].y));
+                q[4 * i + 2] = fmaxf(fmaxf(w4[0][i].z, w4[1][i].z), fmaxf(w4[2][i].z, w4[3][i].z));
+                q[4 * i + 3] = fmaxf(fmaxf(w4[0][i].w, w4[1][i].w), fmaxf(w4[2][i].w, w4[3][i].w));
+              }
+            }
             float yo[32];
             if (want_idx) {
 #pragma unroll
               for (int k = 0; k < 32; ++k) yo[k] = y[k];
             }
-            {
+            if (want_idx) {
               float o[32];
 #pragma unroll
               for (int k = 0; k < 32; ++k) o[k] = __shfl_xor_sync(0xffffffffu, y[k], 1);
@@ -437,12 +475,12 @@ fewch_conv_kernel(const __grid_constant__ FcParams p) {
               eq3 = __shfl_sync(0xffffffffu, eq, wbase | 9);
             }
             // each lane of the window finishes and stores a quarter of the 32 channels
-            float q[8];
-            const int cb = c0 + 8 * sub4;
+            if (want_idx) {
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              const float lo2 = sel_b0 ? y[8 + k] : y[k], hi2 = sel_b0 ? y[24 + k] : y[16 + k];
-              q[k] = sel_b1 ? hi2 : lo2;
+              for (int k = 0; k < 8; ++k) {
+                const float lo2 = sel_b0 ? y[8 + k] : y[k], hi2 = sel_b0 ? y[24 + k] : y[16 + k];
+                q[k] = sel_b1 ? hi2 : lo2;
+              }
             }
             if (pool_first) {
 #pragma unroll
@@ -570,7 +608,8 @@ int conv_fewch_fwd(Device* d, const lnn_conv_geom* g, float* Y, const float* X, 
 #endif
   const int64_t tiles = (int64_t)p.n * p.tiles_h * p.tiles_w;
   LNN_REQUIRE(tiles < (1ll << 31), "too many tiles");
-  const int smem = 2 * p.w_bytes + 4 * p.patch_bytes + 1024;
+  // operands, then 4 KB per epilogue warp for the transposing stage of the fused pool
+  const int smem = 2 * p.w_bytes + 4 * p.patch_bytes + 1024 + kFcEpilogueWarps * 4096;
   LNN_REQUIRE(smem <= 227 * 1024 - 4096, "operands of %d bytes do not fit shared memory", smem);
   if (!(d->smem_attr_done & (1u << 9))) {
     const int lim = 227 * 1024 - 4096;
