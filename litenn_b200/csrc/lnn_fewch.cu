@@ -302,7 +302,6 @@ fewch_conv_kernel(const __grid_constant__ FcParams p) {
     uint8_t* const xpose = gen_base + 2 * p.w_bytes + 4 * (size_t)p.patch_bytes + (size_t)(warp - 5) * 4096;
     auto rot = [](int px) { return ((px >> 1) & 1) + 4 * ((px >> 2) & 1) + 2 * (px & 1); };
     const int wbase_px = lane & ~9;
-    const bool sel_b0 = (sub4 & 1) != 0, sel_b1 = (sub4 & 2) != 0;
     uint32_t amax_acc = 0u;
 #ifdef LNN_TC_EXPERIMENTS
     long long dbg_wait = 0, dbg_work = 0, dbg_ph0 = 0, dbg_ph1 = 0;
@@ -386,8 +385,8 @@ fewch_conv_kernel(const __grid_constant__ FcParams p) {
               }
             }
           } else {
-            // 2x2 max pool across the four lanes of a window (bits 0 and 3 of the lane number).
-            // Scaling by a power of two, adding the bias and leaky_relu with alpha >= 0 never
+            // 2x2 max pool: the four pixels of a window sit in four lanes (bits 0 and 3 of the lane
+            // number).  Scaling by a power of two, adding the bias and leaky_relu with alpha >= 0 never
             // reverse the order of two values, so the maximum is taken on the raw accumulators and
             // only the winner goes through them: the same value as pooling the finished pixels
             // (op/pool2D.py:111-146), at a quarter of the arithmetic.  (An accumulator that
@@ -408,80 +407,46 @@ fewch_conv_kernel(const __grid_constant__ FcParams p) {
               }
             }
             float q[8];
+            uint8_t widx[8];
             const int cb = c0 + 8 * sub4;
-            if (!want_idx) {
+            {
               // the four pixels of a window come together through shared memory: each lane leaves
               // with its quarter of the channels for all four, and the maximum is taken in-thread
-              // (the shuffle form below costs 64 shuffles and 24 selects per 32 accumulators)
+              // (pooling by shuffles cost 64 shuffles and 24 selects per 32 accumulators)
               const int my_rot = rot(lane);
 #pragma unroll
               for (int j = 0; j < 8; ++j)
                 *reinterpret_cast<float4*>(xpose + lane * 128 + (((j + my_rot) & 7) << 4)) =
                     make_float4(y[4 * j], y[4 * j + 1], y[4 * j + 2], y[4 * j + 3]);
               __syncwarp();
-              float4 w4[4][2];
+              float w4[4][8];
 #pragma unroll
               for (int pix = 0; pix < 4; ++pix) {
                 const int px = wbase_px | (pix & 1) | ((pix >> 1) << 3);
                 const int r = rot(px);
 #pragma unroll
-                for (int i = 0; i < 2; ++i)
-                  w4[pix][i] = *reinterpret_cast<const float4*>(xpose + px * 128 + (((2 * sub4 + i + r) & 7) << 4));
+                for (int i = 0; i < 2; ++i) {
+                  const float4 t = *reinterpret_cast<const float4*>(xpose + px * 128 + (((2 * sub4 + i + r) & 7) << 4));
+                  w4[pix][4 * i] = t.x; w4[pix][4 * i + 1] = t.y; w4[pix][4 * i + 2] = t.z; w4[pix][4 * i + 3] = t.w;
+                }
               }
               __syncwarp();
 #pragma unroll
-              for (int i = 0; i < 2; ++i) {
-                q[4 * i + 0] = fmaxf(fmaxf(w4[0][i].x, w4[1][i].x), fmaxf(w4[2][i].x, w4[3][i].x));
-                q[4 * i + 1] = fmaxf(fmaxf(w4[0][i].y, w4[1][i].y), fmaxf(w4[2][i].y, w4[3][i].y));
-                q[4 * i + 2] = fmaxf(fmaxf(w4[0][i].z, w4[1][i].z), fmaxf(w4[2][i].z, w4[3][i].z));
-                q[4 * i + 3] = fmaxf(fmaxf(w4[0][i].w, w4[1][i].w), fmaxf(w4[2][i].w, w4[3][i].w));
+              for (int k = 0; k < 8; ++k) q[k] = fmaxf(fmaxf(w4[0][k], w4[1][k]), fmaxf(w4[2][k], w4[3][k]));
+              if (want_idx) {
+                // Where the pooling gradient of each window goes: the first position, in row-major
+                // order, whose (finished) value equals the stored one (op/pool2D.py:147-230); 4 = none.
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                  const float m = fmaxf(-CUDART_INF_F, q[k]);
+                  const float st = (m == -CUDART_INF_F) ? 0.0f : m;
+                  widx[k] = w4[0][k] == st ? 0 : w4[1][k] == st ? 1 : w4[2][k] == st ? 2 : w4[3][k] == st ? 3 : 4;
+                }
               }
-            }
-            float yo[32];
-            if (want_idx) {
-#pragma unroll
-              for (int k = 0; k < 32; ++k) yo[k] = y[k];
-            }
-            if (want_idx) {
-              float o[32];
-#pragma unroll
-              for (int k = 0; k < 32; ++k) o[k] = __shfl_xor_sync(0xffffffffu, y[k], 1);
-#pragma unroll
-              for (int k = 0; k < 32; ++k) y[k] = fmaxf(y[k], o[k]);
-#pragma unroll
-              for (int k = 0; k < 32; ++k) o[k] = __shfl_xor_sync(0xffffffffu, y[k], 8);
-#pragma unroll
-              for (int k = 0; k < 32; ++k) y[k] = fmaxf(y[k], o[k]);
             }
 #ifdef LNN_TC_EXPERIMENTS
             dbg_ph1 += clock64() - tp0;
 #endif
-            // Where the pooling gradient of each window goes: the first position, in row-major
-            // order, whose value equals the stored one (op/pool2D.py:147-230); 4 = none.  Every lane
-            // marks the channels in which it holds that value, the four lanes exchange the marks.
-            uint32_t eq0 = 0u, eq1 = 0u, eq2 = 0u, eq3 = 0u;
-            if (want_idx) {
-              uint32_t eq = 0u;
-#pragma unroll
-              for (int k = 0; k < 32; ++k) {
-                const float m = fmaxf(-CUDART_INF_F, y[k]);
-                const float st = (m == -CUDART_INF_F) ? 0.0f : m;
-                eq |= (yo[k] == st ? 1u : 0u) << k;
-              }
-              const int wbase = lane & ~9;
-              eq0 = __shfl_sync(0xffffffffu, eq, wbase);
-              eq1 = __shfl_sync(0xffffffffu, eq, wbase | 1);
-              eq2 = __shfl_sync(0xffffffffu, eq, wbase | 8);
-              eq3 = __shfl_sync(0xffffffffu, eq, wbase | 9);
-            }
-            // each lane of the window finishes and stores a quarter of the 32 channels
-            if (want_idx) {
-#pragma unroll
-              for (int k = 0; k < 8; ++k) {
-                const float lo2 = sel_b0 ? y[8 + k] : y[k], hi2 = sel_b0 ? y[24 + k] : y[16 + k];
-                q[k] = sel_b1 ? hi2 : lo2;
-              }
-            }
             if (pool_first) {
 #pragma unroll
               for (int k = 0; k < 8; ++k) q[k] = sc(q[k]);
@@ -511,9 +476,7 @@ fewch_conv_kernel(const __grid_constant__ FcParams p) {
                   uint8_t* di = p.idx_out + (((int64_t)img * p.oc + cb) * ohp + ph_) * owp + pw_;
 #pragma unroll
                   for (int k = 0; k < 8; ++k) {
-                    const int c = 8 * sub4 + k;
-                    const int w = ((eq0 >> c) & 1u) ? 0 : ((eq1 >> c) & 1u) ? 1 : ((eq2 >> c) & 1u) ? 2 : ((eq3 >> c) & 1u) ? 3 : 4;
-                    if (cb + k < p.oc) di[k * cstride] = (uint8_t)w;
+                    if (cb + k < p.oc) di[k * cstride] = widx[k];
                   }
                 }
               } else if (ep_mode == 4 && cb < p.ocp) {
