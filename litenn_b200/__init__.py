@@ -11,7 +11,7 @@ from . import deferred, info, initializer, optimizer, ops, parallel
 from ._lib import LnnError
 from .autograd import backward
 from .devices import devices
-from .module import Conv2D, Dense, Module, ModuleBase
+from .module import Conv2D, Conv2DTranspose, Dense, DepthwiseConv2D, Module, ModuleBase
 from .ops import (abs, add, add_const, avg_pool2D, binary_crossentropy, categorical_crossentropy, clip,
                   conv2D, conv2DTranspose, conv2D_block, conv2D_infer, conv2D_pool, depthwise_conv2D, pack_activation, PackedActivation, cos, dense, div, div_const, exp, flatten, leaky_relu, log, matmul, max, max_pool2D,
                   min, min_pool2D, moments, mul, mul_const, rdiv_const, reduce_max, reduce_mean, reduce_min,

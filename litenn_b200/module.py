@@ -278,6 +278,77 @@ class Conv2D(Module):
     __repr__ = __str__
 
 
+def _prepare_fans(initializer, fan_in, fan_out):
+    """Give an initializer the fans of the layer unless the caller fixed them."""
+    if initializer is None:
+        initializer = _init.GlorotUniform()
+    if getattr(initializer, "fan_in", 0) is None:
+        initializer.fan_in = fan_in
+    if getattr(initializer, "fan_out", 0) is None:
+        initializer.fan_out = fan_out
+    return initializer
+
+
+class _BiasedConvModule(Module):
+    """Shared part of the convolution modules below: a kernel, an optional per-channel bias added
+    as a (1, C, 1, 1) broadcast, saveables 'kernel' and 'bias'."""
+
+    def _make_bias(self, channels, use_bias, bias_initializer):
+        self.use_bias = use_bias
+        self.bias = Tensor((channels,), init=bias_initializer or _init.Scalar(0.0)) if use_bias else None
+
+    def _add_bias(self, x):
+        return x + self.bias.reshape((1, -1, 1, 1)) if self.use_bias else x
+
+
+class Conv2DTranspose(_BiasedConvModule):
+    """Conv2DTranspose(in_ch, out_ch, kernel_size, stride=2, dilation=1, padding='same',
+    use_bias=True, kernel_initializer=None, bias_initializer=None); forward =
+    nn.conv2DTranspose + bias; kernel (out_ch, in_ch, k, k) (module/Conv2DTranspose.py:22-58)."""
+
+    def __init__(self, in_ch, out_ch, kernel_size, stride=2, dilation=1, padding="same", use_bias=True,
+                 kernel_initializer=None, bias_initializer=None):
+        self.in_ch, self.out_ch, self.kernel_size = in_ch, out_ch, kernel_size
+        self.stride, self.padding, self.dilation = stride, padding, dilation
+        taps = kernel_size * kernel_size
+        self.kernel = Tensor((out_ch, in_ch, kernel_size, kernel_size),
+                             init=_prepare_fans(kernel_initializer, in_ch * taps, out_ch * taps))
+        self._make_bias(out_ch, use_bias, bias_initializer)
+        super().__init__(saveables=["kernel", "bias"])
+
+    def forward(self, x, **kwargs):
+        return self._add_bias(ops.conv2DTranspose(x, self.kernel, self.stride, self.dilation, padding=self.padding))
+
+    def __str__(self):
+        return f"{self.__class__.__name__} : in_ch:{self.in_ch} out_ch:{self.out_ch} "
+
+    __repr__ = __str__
+
+
+class DepthwiseConv2D(_BiasedConvModule):
+    """DepthwiseConv2D(in_ch, kernel_size, stride=1, dilation=1, padding='same', use_bias=True,
+    depthwise_initializer=None, pointwise_initializer=None, bias_initializer=None); forward =
+    nn.depthwise_conv2D + bias; kernel (in_ch, k, k) (module/DepthwiseConv2D.py:24-56; the
+    reference accepts and ignores pointwise_initializer as well)."""
+
+    def __init__(self, in_ch, kernel_size, stride=1, dilation=1, padding="same", use_bias=True,
+                 depthwise_initializer=None, pointwise_initializer=None, bias_initializer=None):
+        self.in_ch, self.kernel_size = in_ch, kernel_size
+        self.stride, self.padding, self.dilation = stride, padding, dilation
+        self.kernel = Tensor((in_ch, kernel_size, kernel_size),
+                             init=_prepare_fans(depthwise_initializer, in_ch * kernel_size * kernel_size, 0))
+        self._make_bias(in_ch, use_bias, bias_initializer)
+        super().__init__(saveables=["kernel", "bias"])
+
+    def forward(self, x, **kwargs):
+        return self._add_bias(ops.depthwise_conv2D(x, self.kernel, self.stride, self.dilation, padding=self.padding))
+
+    def __str__(self):
+        return f"{self.__class__.__name__} : in_ch:{self.in_ch} "
+
+    __repr__ = __str__
+
+
 class Dense(Module):
     """Dense(in_ch, out_ch, use_bias=True, weight_initializer=None, bias_initializer=None);
     forward = nn.matmul(x, weight) + bias (module/Dense.py:20-48)."""

@@ -277,3 +277,45 @@ def test_allocation_failure_paths(mode):
         env["LNN_FAIL_ALLOC_TIMES"] = "1"
     r = subprocess.run([sys.executable, "-c", _ALLOC_CHILD, mode], env=env, capture_output=True, text=True, timeout=300)
     assert ("EVICT-OK" if mode == "evict" else "NOMEM-OK") in r.stdout, f"{r.stdout[-400:]}\n{r.stderr[-1500:]}"
+
+
+def test_transposed_and_depthwise_conv_modules(nn_gpu):
+    """nn.Conv2DTranspose / nn.DepthwiseConv2D: the reference's constructor arguments, kernel shapes
+    and saveables (module/Conv2DTranspose.py:22-58, module/DepthwiseConv2D.py:24-56); forward is
+    the operator plus a broadcast bias, and both parameters receive gradients."""
+    nn = nn_gpu
+    rng = np.random.default_rng(51)
+
+    class Net(nn.Module):
+        def __init__(self):
+            self.up = nn.Conv2DTranspose(4, 8, 3)
+            self.dw = nn.DepthwiseConv2D(8, 3, use_bias=True)
+            self.plain = nn.DepthwiseConv2D(8, 3, use_bias=False)
+
+        def forward(self, x):
+            return self.plain(self.dw(self.up(x)))
+
+    net = Net()
+    assert tuple(net.up.kernel.shape) == (8, 4, 3, 3) and tuple(net.up.bias.shape) == (8,)
+    assert tuple(net.dw.kernel.shape) == (8, 3, 3) and net.plain.bias is None
+    names = sorted(t.get_name() for t in net.trainables())
+    assert names == ["Net.dw.bias", "Net.dw.kernel", "Net.plain.kernel", "Net.up.bias", "Net.up.kernel"], names
+    net.up.bias.set(rng.uniform(-1, 1, (8,)).astype(np.float32))
+    net.dw.bias.set(rng.uniform(-1, 1, (8,)).astype(np.float32))
+    x = nn.Tensor_from_value(rng.standard_normal((2, 4, 8, 8)).astype(np.float32))
+    up = net.up(x)
+    assert tuple(up.shape) == (2, 8, 16, 16)
+    want_up = nn.conv2DTranspose(x, net.up.kernel, 2, 1, "same").np() + net.up.bias.np().reshape(1, -1, 1, 1)
+    np.testing.assert_array_equal(up.np(), want_up.astype(np.float32))
+    y = net.dw(up)
+    want_dw = nn.depthwise_conv2D(up, net.dw.kernel, 1, 1, "same").np() + net.dw.bias.np().reshape(1, -1, 1, 1)
+    np.testing.assert_array_equal(y.np(), want_dw.astype(np.float32))
+    opt = nn.optimizer.SGD(net.trainables(), lr=1e-2)
+    before = {t.get_name(): t.np().copy() for t in net.trainables()}
+    net(x).mean().backward()
+    opt.step()
+    for t in net.trainables():
+        assert not np.array_equal(t.np(), before[t.get_name()]), f"{t.get_name()} was not updated"
+    state = net.dump_state()
+    assert any(k.endswith("up.kernel") for k in state) and any(k.endswith("dw.bias") for k in state)
+    nn.devices.check_status()
