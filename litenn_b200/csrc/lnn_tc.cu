@@ -2175,8 +2175,22 @@ int conv_fwd_impl(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint6
                            g->oc, oh_p, ow_p, ocp, precision);
     return LNN_OK;
   }
-  if (!o.in_packed && !o.w_swapped && !idx && lnn::conv_direct_applicable(g) && knobs().direct &&
+  if (!o.in_packed && !o.w_swapped && lnn::conv_direct_applicable(g) && knobs().direct &&
       (!o.out_packed || o.pool)) {
+    if (idx) {
+      // pooled result with the map of winning positions: this kernel's own values (the chain
+      // conv2D -> max_pool2D takes it too), pooled and mapped by separate kernels
+      lnn::Scratch full(d);
+      rc = full.get((uint64_t)g->n * g->oc * g->oh * g->ow * 4);
+      if (rc) return rc;
+      rc = lnn::conv_direct_fwd(d, g, full.as<float>(), (const float*)(uintptr_t)X, (const float*)(uintptr_t)W,
+                                biasp, act, alpha, 0, 0, 0, nullptr, ocp);
+      if (rc) return rc;
+      rc = lnn_pool2d_fwd(dev, LNN_POOL_MAX, Y, (uint64_t)(uintptr_t)full.as<float>(), g->n, g->oc, g->oh, g->ow,
+                          oh_p, ow_p, 2, 2, 0, 0);
+      if (rc) return rc;
+      return argmax_of(full.as<float>());
+    }
     if (o.out_packed && f16) {
       // this kernel writes fp32 and the largest magnitude; one element-wise pass splits it
       lnn::Scratch raw(d);
