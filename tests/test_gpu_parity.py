@@ -543,3 +543,14 @@ def test_output_t_and_accumulate(nn_gpu):
 def test_device_status_clean(nn_gpu):
     """No bounded device-side wait may have expired during the parity run."""
     nn_gpu.devices.check_status()
+
+
+@pytest.mark.parametrize("precision", ["3"])
+def test_fused_paths_in_split_tf32(nn_gpu, monkeypatch, precision):
+    """The fused epilogues, the packed operand format and the pooled block have separate code for
+    the tf32 split (no scale, fp32 hi / lo, FP32-pipe first layer): the same bit-exact claims hold."""
+    monkeypatch.setenv("LNN_PRECISION", precision)
+    for xs, ws in [((2, 3, 32, 32), (16, 3, 3, 3)), ((3, 32, 64, 64), (64, 32, 3, 3)), ((2, 16, 12, 12), (24, 16, 3, 3))]:
+        test_conv_block_equals_chain(nn_gpu, xs, ws)
+    for xs, ws in [((2, 3, 32, 32), (32, 3, 3, 3)), ((2, 64, 32, 32), (128, 64, 3, 3))]:
+        test_conv_infer_fused_and_packed(nn_gpu, xs, ws)
