@@ -58,11 +58,11 @@ struct FcParams {
   int nsub, pws;                          // MMA tiles per super-tile, slots per patch row (8*nsub + 2)
   int tiles_w, tiles_h;
   int act; float alpha;
-  int ep_mode;                            // 0 NCHW, 1 pooled NCHW, 3 pooled channel-innermost fp32 + largest magnitude,
+  int ep_mode;                            // 0 NCHW, 1 pooled NCHW,
                                           // 4 pooled channel-innermost split fp16 (scale from the bound in amax_out[-1])
   float* out_lo;
   uint8_t* idx_out;                       // ep_mode 1, optional: winning window position of every pooled value
-  int ocp;                                // channel pitch of the ep_mode 3 output
+  int ocp;                                // channel pitch of the ep_mode 4 output
   const uint32_t* amax_x; uint32_t* amax_out;
   int* status;
   uint32_t idesc;
@@ -490,14 +490,6 @@ fewch_conv_kernel(const __grid_constant__ FcParams p) {
                 *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.out_lo) + off) = *reinterpret_cast<const uint4*>(l);
 #pragma unroll
                 for (int k = 0; k < 8; ++k) amax_acc = max(amax_acc, __float_as_uint(q[k]) & 0x7fffffffu);
-              } else if (cb < p.ocp) {
-                float* dst = p.out + (((int64_t)img * ohp + ph_) * owp + pw_) * p.ocp + cb;
-                if (!FC_DBG(p, 8)) {
-                  *reinterpret_cast<float4*>(dst) = make_float4(q[0], q[1], q[2], q[3]);
-                  *reinterpret_cast<float4*>(dst + 4) = make_float4(q[4], q[5], q[6], q[7]);
-                }
-#pragma unroll
-                for (int k = 0; k < 8; ++k) amax_acc = max(amax_acc, __float_as_uint(q[k]) & 0x7fffffffu);
               }
             }
           }
@@ -519,7 +511,7 @@ fewch_conv_kernel(const __grid_constant__ FcParams p) {
       printf("epilogue warp %d: %d tiles, wait %lld work %lld clocks per tile; per tile: ld-wait %lld, through pooling %lld\n", warp, it,
              dbg_wait / max(it, 1), dbg_work / max(it, 1), dbg_ph0 / max(it, 1), dbg_ph1 / max(it, 1));
 #endif
-    if (ep_mode >= 3 || (FC_DBG(p, 8) && p.amax_out)) warp_amax_commit(amax_acc, p.amax_out);
+    if (ep_mode == 4 || (FC_DBG(p, 8) && p.amax_out)) warp_amax_commit(amax_acc, p.amax_out);
   }
 
   // ---- tear-down -----------------------------------------------------------------------------
@@ -541,9 +533,9 @@ bool conv_fewch_applicable(const lnn_conv_geom* g) {
   return true;
 }
 
-// ep_mode 0: Y = NCHW result; 1: pooled NCHW; 3: pooled channel-innermost fp32 with channel pitch
-// ocp, its largest magnitude accumulated into *amax_out (which the caller zeroed); 4: pooled
-// channel-innermost split fp16 (Y = hi, Y_lo = lo) scaled by the bound in amax_out[-1].  amax_x
+// ep_mode 0: Y = NCHW result; 1: pooled NCHW; 4: pooled channel-innermost split fp16 with channel
+// pitch ocp (Y = hi, Y_lo = lo) scaled by the bound in amax_out[-1], the largest magnitude
+// accumulated into *amax_out (which the caller zeroed).  amax_x
 // holds the fp32 bit pattern of the input's largest magnitude.  idx (ep_mode 1, optional): one byte
 // per pooled element, the window position that holds the pooled value.
 int conv_fewch_fwd(Device* d, const lnn_conv_geom* g, float* Y, const float* X, const float* W,

@@ -25,7 +25,7 @@ namespace {
 // `wvalid` of the 32 columns real).  The maximum is taken in the pooling kernel's order
 // (t00, t01, t10, t11 on top of -inf; litenn/core/op/pool2D.py:111-146) after bias and
 // activation, so the value equals the unfused chain bit for bit.
-// ep_mode 3 collects the largest magnitude written by this thread in `amax`; the caller
+// ep_mode 4 collects the largest magnitude written by this thread in `amax`; the caller
 // commits it once per warp when the kernel ends.
 __device__ __forceinline__ void pooled_store(const TcParams& p, const Pow2Scale& sc, const uint32_t* v0,
                                              const uint32_t* v1, float bias_v, int oc, int64_t n, int a,
@@ -107,15 +107,6 @@ __device__ __forceinline__ void pooled_store(const TcParams& p, const Pow2Scale&
         if (real) split1(m[j], hi, lo);                      // pad channels are written as zeros
         p.out[base + (int64_t)j * p.out_sb] = hi;
         if (p.out_lo) p.out_lo[base + (int64_t)j * p.out_sb] = lo;
-      }
-    }
-  } else if (p.ep_mode == 3) {
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      if (j < npool) {
-        const float v = real ? m[j] : 0.0f;                  // pad channels are written as zeros
-        p.out[base + (int64_t)j * p.out_sb] = v;
-        amax = max(amax, __float_as_uint(v) & 0x7fffffffu);
       }
     }
   } else {
@@ -610,7 +601,7 @@ tc_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__ CUte
       if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
     }
     __syncwarp();
-    if (p.ep_mode >= 3) warp_amax_commit(amax_acc, p.amax_out);
+    if (p.ep_mode == 4) warp_amax_commit(amax_acc, p.amax_out);
   }
 
   // ---- tear-down ------------------------------------------------------------------------
@@ -913,7 +904,7 @@ tc_halo_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_constant__
       if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
     }
     __syncwarp();
-    if (p.ep_mode >= 3) warp_amax_commit(amax_acc, p.amax_out);
+    if (p.ep_mode == 4) warp_amax_commit(amax_acc, p.amax_out);
   }
 
   tc_fence_before();
@@ -2240,7 +2231,7 @@ int conv_fwd_impl(int dev, const lnn_conv_geom* g, uint64_t Y, uint64_t X, uint6
   c.OCv = g->oc; c.bias = biasp; c.act = act; c.alpha = alpha; c.precision = precision;
   if (o.pool && g->stride == 1) {
     // try the fused epilogue: pooled NCHW (ep_mode 1) or pooled, channel-innermost (2: tf32 hi/lo
-    // written directly, 3: fp32 + largest magnitude for the fp16 split)
+    // written directly, 4: fp16 hi/lo written directly with the scale of a bound of the result)
     const int64_t pplane = (int64_t)oh_p * ow_p;
     EpiExtra ex{1, nullptr, ocp, nullptr};
     ConvLaunch cf = c;

@@ -90,11 +90,10 @@ struct TcParams {
   // accumulator is scaled by the product of the powers of two derived from them
   const uint32_t* amax_a;
   const uint32_t* amax_b;
-  uint32_t* amax_out;            // ep_mode 3: largest magnitude of what this launch wrote
+  uint32_t* amax_out;            // ep_mode 4: largest magnitude of what this launch wrote
   // fused 2x2/stride-2 max pool (channels-on-M kernels): ep_mode 1 writes the pooled NCHW
   // tensor, ep_mode 2 writes it channel-innermost and pre-split in tf32 (out = hi, out_lo = lo,
-  // channel pitch ocp) as the next convolution's operand, ep_mode 3 writes it channel-innermost
-  // in fp32 and records its largest magnitude, ep_mode 4 writes the fp16 split (out = hi, out_lo = lo)
+  // channel pitch ocp) as the next convolution's operand, ep_mode 4 writes the fp16 split (out = hi, out_lo = lo)
   // scaled by an upper bound that sits in the word before *amax_out, and records the true
   // largest magnitude in *amax_out; the out_s* strides then address pooled pixels
   int ep_mode;
