@@ -194,6 +194,11 @@ int lnn_pool2x2_idx_lrelu_bwd(int dev, uint64_t dZ, uint64_t T, uint64_t IDX, ui
 int lnn_pool2x2_idx_lrelu_bwd_packed(int dev, uint64_t HI, uint64_t LO, uint64_t T, uint64_t IDX,
                                      uint64_t P, uint64_t dP, int64_t n, int64_t c, int ih, int iw,
                                      float alpha, int act);
+/* T [n,c,oh,ow] = the gradient that reaches the winner of each pooling window (the non-zero
+ * elements of the dZ above, in pooled layout), from the pooled values P, their gradient dP and the
+ * map IDX.  ref: op/pool2D.py:147-230 + op/element_wise_op.py:207-221 */
+int lnn_pool2x2_winner_grad(int dev, uint64_t T, uint64_t IDX, uint64_t P, uint64_t dP, int64_t n,
+                            int64_t c, int oh, int ow, float alpha, int act);
 /* dI += ... ; ref: op/pool2D.py:147-230 (I and O are only read for max/min) */
 int lnn_pool2d_bwd(int dev, int mode, uint64_t dI, uint64_t I, uint64_t dO, uint64_t O,
                    int64_t n, int64_t c, int ih, int iw, int oh, int ow,
@@ -310,6 +315,13 @@ int lnn_conv2d_dx(int dev, const lnn_conv_geom* g, uint64_t dX, uint64_t dY, uin
 /* dW += gradient of the kernel.  ref: op/conv2D.py:52-54 */
 int lnn_conv2d_dw(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t dY, uint64_t X,
                   int precision);
+/* dW += the kernel gradient of a pooled block (conv -> [bias, leaky_relu] -> max_pool2D(2,2)) computed
+ * from the winners of its pooling windows: T and IDX as written by lnn_pool2x2_winner_grad and
+ * lnn_conv2d_fwd_packed (pooled size), X the NCHW input.  The same sums as lnn_conv2d_dw over the
+ * full-resolution gradient, whose other elements are zero, in another (fixed) order.  At most 4 input
+ * channels, 3x3, unit stride, 'same' padding, even height, width % 64 == 0; LNN_E_UNSUPPORTED
+ * otherwise.  ref: op/conv2D.py:46-54 (dK) after op/pool2D.py:147-230 */
+int lnn_conv2d_dw_winners(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t T, uint64_t IDX, uint64_t X);
 /* The same two gradients from operands that are already in the packed format of lnn_nhwc_split
  * (dY [n][oh][ow][pad8(oc)], X [n][ih][iw][pad8(ic)], hi and lo each), so that a training step
  * repacks dY once for both gradients and reuses the copy of X its forward pass made.

@@ -88,6 +88,8 @@ _SIGNATURES = {
     "lnn_pool2d_bwd": (c_int, [c_int, c_int, c_uint64, c_uint64, c_uint64, c_uint64, c_int64, c_int64] + [c_int] * 8),
     "lnn_pool2x2_lrelu_bwd": (c_int, [c_int, c_uint64, c_uint64, c_uint64, c_uint64, c_int64, c_int64, c_int, c_int, c_float, c_int]),
     "lnn_pool2x2_idx_lrelu_bwd": (c_int, [c_int, c_uint64, c_uint64, c_uint64, c_uint64, c_uint64, c_int64, c_int64, c_int, c_int, c_float, c_int]),
+    "lnn_pool2x2_winner_grad": (c_int, [c_int, c_uint64, c_uint64, c_uint64, c_uint64, c_int64, c_int64, c_int, c_int, c_float, c_int]),
+    "lnn_conv2d_dw_winners": (c_int, [c_int, POINTER(ConvGeom), c_uint64, c_uint64, c_uint64, c_uint64]),
     "lnn_pool2x2_idx_lrelu_bwd_packed": (c_int, [c_int, c_uint64, c_uint64, c_uint64, c_uint64, c_uint64, c_uint64, c_int64, c_int64, c_int, c_int, c_float, c_int]),
     "lnn_reduce": (c_int, [c_int, c_int, c_uint64, c_uint64] + [c_int64] * 5 + [c_int]),
     "lnn_reduce_noalloc": (c_int, [c_int, c_int, c_uint64, c_uint64] + [c_int64] * 5 + [c_int]),

@@ -76,6 +76,9 @@ int conv_fewch_fwd(Device* d, const lnn_conv_geom* g, float* Y, const float* X, 
 // kernel gradient of the same layers (IC <= 4, 3x3): dW += ...
 bool conv_direct_dw_applicable(const lnn_conv_geom* g);
 int conv_direct_dw(Device* d, const lnn_conv_geom* g, float* dW, const float* dY, const float* X);
+// the same gradient of a pooled block from the winners of its pooling windows (T, IDX: pooled size)
+bool conv_dw_winners_applicable(const lnn_conv_geom* g);
+int conv_dw_winners(Device* d, const lnn_conv_geom* g, float* dW, const float* T, const uint8_t* IDX, const float* X);
 
 }  // namespace lnn
 

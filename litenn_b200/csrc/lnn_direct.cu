@@ -401,6 +401,114 @@ dw_direct_finalize_kernel(float* __restrict__ dW, const float* __restrict__ part
   dW[i] = __fadd_rn(dW[i], v);
 }
 
+// Kernel gradient of a pooled block (conv -> leaky_relu -> max_pool2D(2,2)) with few input
+// channels, 3x3, unit stride, from the WINNERS: the gradient of the convolution output is zero
+// except at one position per pooling window, so instead of walking every pixel of a
+// full-resolution dZ (three quarters zeros) a lane (= output channel) walks the windows: T holds
+// the winner's gradient, IDX its position (0..3 row-major, 4 = none).  Per window 27 broadcast-free
+// shared-memory loads (four distinct addresses per warp, in distinct banks: the X row pitch is
+// 4 mod 32) and 27 FMAs, a quarter of the full-resolution kernel's.  One tile = 4 window rows x 32
+// window columns (8 x 64 pixels); accumulation order is fixed (deterministic), block partials are
+// added in slot order by dw_direct_finalize_kernel.
+constexpr int kWinRows = 4, kWinCols = 32, kWinTile = kWinRows * kWinCols;   // windows per tile
+constexpr int kWinTPitch = kWinTile + 4;          // floats per channel row of the T tile (pitch / 4 odd)
+constexpr int kWinIPitch = kWinTile + 4;          // bytes per channel row of the IDX tile (33 words)
+constexpr int kWinXRows = 2 * kWinRows + 2, kWinXPitch = 2 * kWinCols + 4;   // 10 x 68 (66 used)
+
+template <int IC>
+__global__ void __launch_bounds__(kThreads)
+conv_dw_winners_kernel(float* __restrict__ partial, const float* __restrict__ T, const uint8_t* __restrict__ IDX,
+                       const float* __restrict__ X, lnn_conv_geom g, int tiles_w, int tiles_h, int oc_chunks,
+                       int slots) {
+  constexpr int NT = IC * 9;
+  extern __shared__ __align__(16) uint8_t smw[];
+  constexpr int kTBytes = kDwOc * kWinTPitch * 4, kIBytes = kDwOc * kWinIPitch;
+  constexpr int kXFloats = IC * kWinXRows * kWinXPitch;
+  constexpr int kStage = kTBytes + kIBytes + kXFloats * 4;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int chunk = blockIdx.x % oc_chunks, slot = blockIdx.x / oc_chunks;
+  const int oc0 = chunk * kDwOc;
+  const int ohp = g.oh >> 1, owp = g.ow >> 1;
+  const int64_t in_plane = (int64_t)g.ih * g.iw, pool_plane = (int64_t)ohp * owp;
+  float acc[NT];
+#pragma unroll
+  for (int i = 0; i < NT; ++i) acc[i] = 0.0f;
+
+  const int64_t items = (int64_t)g.n * tiles_h * tiles_w;
+  auto issue = [&](int64_t item, int b) {
+    const int twi = (int)(item % tiles_w);
+    const int64_t t2 = item / tiles_w;
+    const int thi = (int)(t2 % tiles_h);
+    const int64_t n = t2 / tiles_h;
+    const int py0 = thi * kWinRows, px0 = twi * kWinCols;
+    uint8_t* st = smw + (size_t)b * kStage;
+    // T: 32 channels x 4 window rows x 32 floats = 1024 pieces of 16 bytes; IDX: as many of 4 bytes
+    for (int i = threadIdx.x; i < kDwOc * kWinRows * 8; i += kThreads) {
+      const int piece = i & 7, rw = (i >> 3) % kWinRows, o = i / (8 * kWinRows);
+      const bool ok = oc0 + o < g.oc && py0 + rw < ohp;
+      const int64_t off = ((n * g.oc + oc0 + o) * ohp + py0 + rw) * (int64_t)owp + px0 + 4 * piece;
+      cp_async_16(smem_addr(st + (o * kWinTPitch + rw * kWinCols + 4 * piece) * 4), ok ? T + off : T, ok ? 16 : 0);
+      cp_async_4(smem_addr(st + kTBytes + o * kWinIPitch + rw * kWinCols + 4 * piece), ok ? IDX + off : IDX, ok ? 4 : 0);
+    }
+    const int ih0 = 2 * py0 - 1, iw0 = 2 * px0 - 1;
+    float* xs = reinterpret_cast<float*>(st + kTBytes + kIBytes);
+    const float* xn = X + n * g.ic * in_plane;
+    for (int i = threadIdx.x; i < IC * kWinXRows * (2 * kWinCols + 2); i += kThreads) {
+      const int cc = i % (2 * kWinCols + 2), t3 = i / (2 * kWinCols + 2);
+      const int rr = t3 % kWinXRows, ic = t3 / kWinXRows;
+      const int ih = ih0 + rr, iw = iw0 + cc;
+      const bool ok = ih >= 0 && ih < g.ih && iw >= 0 && iw < g.iw;
+      cp_async_4(smem_addr(xs + (ic * kWinXRows + rr) * kWinXPitch + cc),
+                 ok ? xn + ic * in_plane + (int64_t)ih * g.iw + iw : X, ok ? 4 : 0);
+    }
+    cp_async_commit();
+  };
+
+  int b = 0;
+  if (slot < items) issue(slot, 0);
+  for (int64_t item = slot; item < items; item += slots, b ^= 1) {
+    const int64_t next = item + slots;
+    if (next < items) { issue(next, b ^ 1); cp_async_wait<1>(); }
+    else cp_async_wait<0>();
+    __syncthreads();
+    const uint8_t* st = smw + (size_t)b * kStage;
+    const float* ts = reinterpret_cast<const float*>(st) + lane * kWinTPitch;
+    const uint8_t* is = st + kTBytes + lane * kWinIPitch;
+    const float* xs = reinterpret_cast<const float*>(st + kTBytes + kIBytes);
+    for (int grp = warp; grp < kWinTile / 4; grp += kThreads / 32) {
+      const float4 t4 = *reinterpret_cast<const float4*>(ts + 4 * grp);
+      const uint32_t w4 = *reinterpret_cast<const uint32_t*>(is + 4 * grp);
+      const float tv[4] = {t4.x, t4.y, t4.z, t4.w};
+      const int rw = (4 * grp) / kWinCols, pw0 = (4 * grp) % kWinCols;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int wi = (int)((w4 >> (8 * e)) & 0xffu);
+        const float t = wi > 3 ? 0.0f : tv[e];
+        const int wy = (wi >> 1) & 1, wx = wi & 1;
+        const float* xb = xs + (2 * rw + wy) * kWinXPitch + 2 * (pw0 + e) + wx;
+#pragma unroll
+        for (int ic = 0; ic < IC; ++ic)
+#pragma unroll
+          for (int kh = 0; kh < 3; ++kh)
+#pragma unroll
+            for (int kw = 0; kw < 3; ++kw)
+              acc[(ic * 3 + kh) * 3 + kw] = fmaf(t, xb[(ic * kWinXRows + kh) * kWinXPitch + kw], acc[(ic * 3 + kh) * 3 + kw]);
+      }
+    }
+    __syncthreads();
+  }
+  float* red = reinterpret_cast<float*>(smw);      // [warps][NT][32]
+#pragma unroll
+  for (int i = 0; i < NT; ++i) red[(warp * NT + i) * 32 + lane] = acc[i];
+  __syncthreads();
+  for (int i = threadIdx.x; i < NT * 32; i += kThreads) {
+    float v = red[i];
+    for (int w = 1; w < kThreads / 32; ++w) v = __fadd_rn(v, red[w * NT * 32 + i]);
+    const int t = i >> 5, o = i & 31;
+    partial[((int64_t)slot * oc_chunks * kDwOc + oc0 + o) * NT + t] = v;
+  }
+}
+
 struct DwPlan { int tw, th, pp, xr, xwp, tiles_w, tiles_h; size_t smem; };
 
 DwPlan plan_dw(const lnn_conv_geom* g) {
@@ -460,6 +568,46 @@ int conv_direct_dw(Device* d, const lnn_conv_geom* g, float* dW, const float* dY
   LNN_CHECK_LAUNCH(d);
   dw_direct_finalize_kernel<<<(g->oc * T + kThreads - 1) / kThreads, kThreads, 0, d->stream>>>(
       dW, part.as<float>(), g->oc, T, oc_chunks * kDwOc, slots);
+  LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
+}
+
+// the pooled block's kernel gradient from winners: 3x3, unit stride and dilation, 'same' padding,
+// whole tiles of pooled columns
+bool conv_dw_winners_applicable(const lnn_conv_geom* g) {
+  return g->ic <= 4 && g->kh == 3 && g->kw == 3 && g->stride == 1 && g->dilation == 1 && g->padl == 1 &&
+         g->padt == 1 && g->oh == g->ih && g->ow == g->iw && (g->oh & 1) == 0 && g->ow % (2 * kWinCols) == 0;
+}
+
+int conv_dw_winners(Device* d, const lnn_conv_geom* g, float* dW, const float* T, const uint8_t* IDX, const float* X) {
+  const int oc_chunks = (g->oc + kDwOc - 1) / kDwOc;
+  const int tiles_w = (g->ow / 2) / kWinCols, tiles_h = (g->oh / 2 + kWinRows - 1) / kWinRows;
+  const int64_t items = (int64_t)g->n * tiles_h * tiles_w;
+  const int slots = (int)std::min<int64_t>(items, std::max(1, d->sm_count * 2 / oc_chunks));
+  const int NT = g->ic * 9;
+  Scratch part(d);
+  int rc = part.get((uint64_t)slots * oc_chunks * kDwOc * NT * sizeof(float));
+  if (rc) return rc;
+  const size_t stage = (size_t)kDwOc * kWinTPitch * 4 + (size_t)kDwOc * kWinIPitch +
+                       (size_t)g->ic * kWinXRows * kWinXPitch * 4;
+  const size_t smem = std::max(2 * stage, (size_t)(kThreads / 32) * NT * 32 * sizeof(float));
+  const unsigned grid = (unsigned)(slots * oc_chunks);
+#define LNN_WIN_CASE(IC_)                                                                           \
+  do {                                                                                              \
+    auto kern = conv_dw_winners_kernel<IC_>;                                                        \
+    LNN_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));   \
+    kern<<<grid, kThreads, smem, d->stream>>>(part.as<float>(), T, IDX, X, *g, tiles_w, tiles_h, oc_chunks, slots); \
+  } while (0)
+  switch (g->ic) {
+    case 1: LNN_WIN_CASE(1); break;
+    case 2: LNN_WIN_CASE(2); break;
+    case 3: LNN_WIN_CASE(3); break;
+    default: LNN_WIN_CASE(4); break;
+  }
+#undef LNN_WIN_CASE
+  LNN_CHECK_LAUNCH(d);
+  dw_direct_finalize_kernel<<<(g->oc * NT + kThreads - 1) / kThreads, kThreads, 0, d->stream>>>(
+      dW, part.as<float>(), g->oc, NT, oc_chunks * kDwOc, slots);
   LNN_CHECK_LAUNCH(d);
   return LNN_OK;
 }

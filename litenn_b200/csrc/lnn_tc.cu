@@ -1165,7 +1165,7 @@ pool_winner_grad_kernel(float* __restrict__ T, uint32_t* __restrict__ amax, cons
     T[i] = u;
     best = max(best, __float_as_uint(u) & 0x7fffffffu);
   }
-  warp_amax_commit(best, amax);
+  if (amax) warp_amax_commit(best, amax);
 }
 
 // Pass 2: one thread = two adjacent windows x eight channels; consecutive threads take consecutive
@@ -2324,6 +2324,33 @@ int lnn_nhwc_split(int dev, uint64_t hi, uint64_t lo, uint64_t X, int n, int c, 
   return nhwc_split_to(d, hp, tf32_passes == 1 ? nullptr : (void*)(uintptr_t)lo,
                        tf32_passes == 2 ? trailer_of(hp, (uint64_t)n * h * w * cp) : nullptr,
                        (const float*)(uintptr_t)X, n, c, h, w, cp, tf32_passes);
+}
+
+int lnn_pool2x2_winner_grad(int dev, uint64_t T, uint64_t IDX, uint64_t P, uint64_t dP, int64_t n, int64_t c,
+                            int oh, int ow, float alpha, int act) {
+  LNN_DEV(d, dev);
+  LNN_REQUIRE(T && IDX && P && dP, "null buffer");
+  LNN_REQUIRE(n > 0 && c > 0 && oh > 0 && ow > 0, "bad extents");
+  LNN_REQUIRE(act == 0 || act == 1, "unknown activation %d", act);
+  const int64_t pooled = n * c * oh * ow;
+  pool_winner_grad_kernel<<<grid_for(d, pooled), kThreads, 0, d->stream>>>(
+      (float*)(uintptr_t)T, nullptr, (const uint8_t*)(uintptr_t)IDX, (const float*)(uintptr_t)dP,
+      (const float*)(uintptr_t)P, pooled, alpha, act);
+  LNN_CHECK_LAUNCH(d);
+  return LNN_OK;
+}
+
+int lnn_conv2d_dw_winners(int dev, const lnn_conv_geom* g, uint64_t dW, uint64_t T, uint64_t IDX, uint64_t X) {
+  LNN_DEV(d, dev);
+  int rc = check_geom(g);
+  if (rc) return rc;
+  LNN_REQUIRE(dW && T && IDX && X, "null buffer");
+  if (!lnn::conv_dw_winners_applicable(g) || ((T | X) & 15) || (IDX & 3))
+    return lnn::set_error(LNN_E_UNSUPPORTED,
+                          "the winners form of the kernel gradient needs at most 4 input channels, a 3x3 kernel, unit "
+                          "stride, 'same' padding, an even height and a width that is a multiple of 64");
+  return lnn::conv_dw_winners(d, g, (float*)(uintptr_t)dW, (const float*)(uintptr_t)T,
+                              (const uint8_t*)(uintptr_t)IDX, (const float*)(uintptr_t)X);
 }
 
 int lnn_pool2x2_idx_lrelu_bwd_packed(int dev, uint64_t HI, uint64_t LO, uint64_t T, uint64_t IDX, uint64_t P,

@@ -658,6 +658,21 @@ def conv2D(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t=None,
 
     # a pooled block whose gradients all read the packed format never needs dZ as an NCHW tensor
     direct_packed = _pooled and keep_packed and passes == 2
+    # a pooled first layer (few input channels): the kernel gradient walks the winners of the
+    # pooling windows, so dZ is only built if somebody asks for the input gradient
+    winners_dw = (_pooled and not keep_packed and g.kh == 3 and g.kw == 3 and stride == 1 and dilation == 1 and
+                  g.padl == 1 and g.padt == 1 and g.ow % 64 == 0)
+
+    def winner_grads(O_t, dO_t):
+        cached = getattr(O_t, "_winner_grads", None)
+        if cached is None or cached[0] is not dO_t:
+            t = _out(O_t.shape)
+            for i, dev in _each_device():
+                _lib_().lnn_pool2x2_winner_grad(dev, t._ptr(i), idx_t._ptr(i), O_t._ptr(i), dO_t._ptr(i), g.n, g.oc,
+                                                g.oh // 2, g.ow // 2, float(alpha), act)
+            cached = (dO_t, t)
+            O_t._winner_grads = cached
+        return cached[1]
 
     def packed_dy(O_t, dO_t):
         if direct_packed:
@@ -695,6 +710,11 @@ def conv2D(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t=None,
 
     def grad_w(O_t, dO_t):
         gw = kernel_t.get_grad()
+        if winners_dw:
+            t = winner_grads(O_t, dO_t)
+            for i, dev in _each_device():
+                _lib_().lnn_conv2d_dw_winners(dev, ctypes.byref(g), gw._ptr(i), t._ptr(i), idx_t._ptr(i), input_t._ptr(i))
+            return
         if keep_packed:
             pd = packed_dy(O_t, dO_t)
             for i, dev in _each_device():
@@ -706,7 +726,9 @@ def conv2D(input_t, kernel_t, stride=1, dilation=1, padding="same", bias_t=None,
             _lib_().lnn_conv2d_dw(dev, ctypes.byref(g), gw._ptr(i), d._ptr(i), input_t._ptr(i), passes)
 
     def grad_b(O_t, dO_t):
-        if direct_packed:
+        if winners_dw:
+            d = winner_grads(O_t, dO_t)
+        elif direct_packed:
             packed_dy(O_t, dO_t)
             d = O_t._packed_dy[2]
         else:

@@ -229,7 +229,8 @@ def test_conv_direct_dw(nn_gpu, monkeypatch, xs, ws, stride, dil):
 @pytest.mark.parametrize("xs,ws", [((2, 3, 32, 32), (16, 3, 3, 3)), ((2, 32, 16, 24), (40, 32, 3, 3)),
                                    ((2, 8, 10, 10), (8, 8, 3, 3)), ((3, 32, 64, 64), (64, 32, 3, 3)),
                                    ((2, 64, 32, 32), (128, 64, 3, 3)), ((2, 16, 12, 12), (24, 16, 3, 3)),
-                                   ((2, 8, 8, 12), (8, 8, 5, 5))])
+                                   ((2, 8, 8, 12), (8, 8, 5, 5)), ((2, 3, 32, 64), (32, 3, 3, 3)),
+                                   ((3, 4, 14, 128), (40, 4, 3, 3)), ((2, 1, 64, 64), (8, 1, 3, 3))])
 def test_conv_block_equals_chain(nn_gpu, xs, ws):
     """conv2D_block (one trainable op: pool in the convolution's epilogue with the map of winning
     positions, fused pooling + leaky_relu gradient) against the chain conv2D(+bias, leaky_relu) ->
@@ -252,8 +253,15 @@ def test_conv_block_equals_chain(nn_gpu, xs, ws):
             y = nn.conv2D_block(xt, wt, bias_t=bt, activation="leaky_relu", alpha=0.1)
         nn.backward({y: dp}, grad_for_non_trainables=True)
         res[kind] = (y.np(), xt.get_grad().np(), wt.get_grad().np(), bt.get_grad().np())
+    # a pooled first layer (at most 4 input channels, width a multiple of 64) sums the kernel
+    # gradient over the winners of the pooling windows: the chain's non-zero terms, another order
+    winners = xs[1] <= 4 and ws[2] == 3 and xs[3] % 64 == 0
     for name, a, c in zip(("y", "dx", "dw"), res["block"], res["chain"]):
-        assert_bit_exact(a, c, f"conv2D_block {name}")
+        if name == "dw" and winners:
+            assert_contraction_close(a, c, xs[0] * xs[2] * xs[3], "conv2D_block dw (winners)")
+            assert float(np.abs(a - c).max()) <= 2e-5 * float(np.abs(c).max()) + 1e-6
+        else:
+            assert_bit_exact(a, c, f"conv2D_block {name}")
     np.testing.assert_allclose(res["block"][3], res["chain"][3], rtol=1e-5, atol=1e-5, err_msg="conv2D_block db")
     nn.devices.check_status()
 
