@@ -1147,6 +1147,17 @@ half_split_kernel(__half* __restrict__ hi, __half* __restrict__ lo, const float*
 // 0 + (0 + dP) then 0 + that * leaky_relu'(P) -- the roundings of the un-fused kernels
 // (pool2D.py:147-230, element_wise_op.py:207-221) -- or 0 where no position matched, and its
 // largest magnitude, which is the largest magnitude of the whole full-resolution gradient.
+__device__ __forceinline__ float winner_grad_of(float g, float o, uint8_t w, float alpha, int act) {
+  float u = __fadd_rn(0.0f, __fadd_rn(0.0f, g));
+  if (act) {
+    const float f = __fadd_rn(o >= 0.0f ? 1.0f : 0.0f, __fmul_rn(alpha, o < 0.0f ? 1.0f : 0.0f));
+    u = __fadd_rn(0.0f, __fmul_rn(u, f));
+  }
+  return w > 3 ? 0.0f : u;
+}
+
+// VEC: four elements per thread with 128-bit loads (total % 4 == 0, 16-byte aligned buffers)
+template <bool VEC>
 __global__ void __launch_bounds__(kThreads)
 pool_winner_grad_kernel(float* __restrict__ T, uint32_t* __restrict__ amax, const uint8_t* __restrict__ IDX,
                         const float* __restrict__ dP, const float* __restrict__ P, int64_t total, float alpha,
@@ -1154,16 +1165,24 @@ pool_winner_grad_kernel(float* __restrict__ T, uint32_t* __restrict__ amax, cons
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
   uint32_t best = 0u;
-  for (int64_t i = tid; i < total; i += nthreads) {
-    float u = __fadd_rn(0.0f, __fadd_rn(0.0f, dP[i]));
-    if (act) {
-      const float o = P[i];
-      const float f = __fadd_rn(o >= 0.0f ? 1.0f : 0.0f, __fmul_rn(alpha, o < 0.0f ? 1.0f : 0.0f));
-      u = __fadd_rn(0.0f, __fmul_rn(u, f));
+  if (VEC) {
+    for (int64_t i = tid; i < (total >> 2); i += nthreads) {
+      const float4 g = __ldcs(reinterpret_cast<const float4*>(dP) + i);
+      const float4 o = __ldg(reinterpret_cast<const float4*>(P) + i);
+      const uchar4 w = __ldg(reinterpret_cast<const uchar4*>(IDX) + i);
+      float4 u;
+      u.x = winner_grad_of(g.x, o.x, w.x, alpha, act); u.y = winner_grad_of(g.y, o.y, w.y, alpha, act);
+      u.z = winner_grad_of(g.z, o.z, w.z, alpha, act); u.w = winner_grad_of(g.w, o.w, w.w, alpha, act);
+      reinterpret_cast<float4*>(T)[i] = u;
+      best = max(max(best, __float_as_uint(u.x) & 0x7fffffffu), __float_as_uint(u.y) & 0x7fffffffu);
+      best = max(max(best, __float_as_uint(u.z) & 0x7fffffffu), __float_as_uint(u.w) & 0x7fffffffu);
     }
-    if (IDX[i] > 3) u = 0.0f;
-    T[i] = u;
-    best = max(best, __float_as_uint(u) & 0x7fffffffu);
+  } else {
+    for (int64_t i = tid; i < total; i += nthreads) {
+      const float u = winner_grad_of(dP[i], P[i], IDX[i], alpha, act);
+      T[i] = u;
+      best = max(best, __float_as_uint(u) & 0x7fffffffu);
+    }
   }
   if (amax) warp_amax_commit(best, amax);
 }
@@ -2066,6 +2085,16 @@ struct FwdOpts {
   int w_swapped = 0;     // W is stored [ic][oc][kh][kw] (the kernel of a transposed convolution)
 };
 
+void launch_winner_grad(lnn::Device* d, float* T, uint32_t* amax, const uint8_t* IDX, const float* dP, const float* P,
+                        int64_t total, float alpha, int act) {
+  const bool vec = (total & 3) == 0 && ((((uintptr_t)T | (uintptr_t)dP | (uintptr_t)P) & 15) == 0) &&
+                   (((uintptr_t)IDX & 3) == 0);
+  if (vec)
+    pool_winner_grad_kernel<true><<<grid_for(d, total / 4), kThreads, 0, d->stream>>>(T, amax, IDX, dP, P, total, alpha, act);
+  else
+    pool_winner_grad_kernel<false><<<grid_for(d, total), kThreads, 0, d->stream>>>(T, amax, IDX, dP, P, total, alpha, act);
+}
+
 // fp32 channel-innermost tensor (its largest magnitude already in the trailer of `hi`) -> fp16 copies
 int half_split_packed(lnn::Device* d, void* hi, void* lo, const float* src, uint64_t elems) {
   lnn::ProfScope prof(d, LNN_PROF_PREP);
@@ -2333,9 +2362,8 @@ int lnn_pool2x2_winner_grad(int dev, uint64_t T, uint64_t IDX, uint64_t P, uint6
   LNN_REQUIRE(n > 0 && c > 0 && oh > 0 && ow > 0, "bad extents");
   LNN_REQUIRE(act == 0 || act == 1, "unknown activation %d", act);
   const int64_t pooled = n * c * oh * ow;
-  pool_winner_grad_kernel<<<grid_for(d, pooled), kThreads, 0, d->stream>>>(
-      (float*)(uintptr_t)T, nullptr, (const uint8_t*)(uintptr_t)IDX, (const float*)(uintptr_t)dP,
-      (const float*)(uintptr_t)P, pooled, alpha, act);
+  launch_winner_grad(d, (float*)(uintptr_t)T, nullptr, (const uint8_t*)(uintptr_t)IDX, (const float*)(uintptr_t)dP,
+                     (const float*)(uintptr_t)P, pooled, alpha, act);
   LNN_CHECK_LAUNCH(d);
   return LNN_OK;
 }
@@ -2367,9 +2395,8 @@ int lnn_pool2x2_idx_lrelu_bwd_packed(int dev, uint64_t HI, uint64_t LO, uint64_t
   uint32_t* amax = trailer_of((void*)(uintptr_t)HI, (uint64_t)n * ih * iw * cp);
   lnn::ProfScope prof(d, LNN_PROF_PREP);
   LNN_CUDA(cudaMemsetAsync(amax, 0, 2 * sizeof(uint32_t), d->stream));
-  pool_winner_grad_kernel<<<grid_for(d, pooled), kThreads, 0, d->stream>>>(
-      (float*)(uintptr_t)T, amax, (const uint8_t*)(uintptr_t)IDX, (const float*)(uintptr_t)dP,
-      (const float*)(uintptr_t)P, pooled, alpha, act);
+  launch_winner_grad(d, (float*)(uintptr_t)T, amax, (const uint8_t*)(uintptr_t)IDX, (const float*)(uintptr_t)dP,
+                     (const float*)(uintptr_t)P, pooled, alpha, act);
   LNN_CHECK_LAUNCH(d);
   unpool_packed_kernel<<<grid_for(d, n * oh * (ow / 2) * (cp / 8)), kThreads, 0, d->stream>>>(
       (__half*)(uintptr_t)HI, (__half*)(uintptr_t)LO, (const float*)(uintptr_t)T, (const uint8_t*)(uintptr_t)IDX, amax,
