@@ -1848,7 +1848,11 @@ int launch_conv_halo(lnn::Device* d, const Operand& act, const Operand& w, const
   // per-tap kernel on its full 256-pixel tiles (1.05 against 0.73 ms for 1024 x 32->64 @ 64x64).
   if (!hp.ok) return LNN_OK;
   if (pooled && knobs().halo != 2) return LNN_OK;
-  if (knobs().halo != 2 && !(hp.px_per_clk >= 1.15 && (c.OCv < 64 || c.kp == cb))) return LNN_OK;
+  // (with 2-byte elements the per-tap kernel in the channels-on-M orientation overtakes the
+  // resident patch from 32 output channels up: 0.70 against 0.76 ms on the input gradient of a
+  // 32 <- 64 channel layer at 64x64, 512 images)
+  const int few_oc = esz == 2 ? 32 : 64;
+  if (knobs().halo != 2 && !(hp.px_per_clk >= 1.15 && (c.OCv < few_oc || c.kp == cb))) return LNN_OK;
 
   TcParams p;
   memset(&p, 0, sizeof(p));
@@ -1927,7 +1931,11 @@ int launch_conv_like(lnn::Device* d, const Operand& act, const Operand& w, const
   // W -- is the faster one whenever the output is unit-stride along W; the strided scatter of a
   // stride-2 input gradient is better served by pixels on M)
   // (a fused pool / packed output exists only in the channels-on-M epilogue)
-  if (orient == 0) orient = (pooled || (c.OCv >= 64 && c.out_sb == 1)) ? 2 : 1;
+  // (with 2-byte elements that holds from 32 output channels up, provided there are enough pixels
+  // to give every SM a 256-pixel tile; a small problem gets more tiles with 128 pixels on M)
+  const bool many_pixels = (int64_t)c.NL * c.AH * c.AW >= (int64_t)d->sm_count * 256;
+  const int oc_for_chan_m = (esz == 2 && many_pixels) ? 32 : 64;
+  if (orient == 0) orient = (pooled || (c.OCv >= oc_for_chan_m && c.out_sb == 1)) ? 2 : 1;
   const bool chan_m = orient == 2;
   PixTile t = plan_conv_tile(c.NL, c.AH, c.AW, c.es, chan_m ? 256 : 128);
   if (pooled) {
